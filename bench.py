@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the FP32 BLAS hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--path ffma|3xtf32]
+
+One JSON line on stdout (rank 0).  A "step" is one SGEMM of the workload:
+  N = 1  : row-major SGEMM M=N=K=6144, alpha=1, beta=0.5 (BASELINE config 2's largest point, the
+           size the metric "SGEMM TFLOPS @6144^3 fp32" is quoted on); inputs resident in HBM.
+  N > 1  : SGEMM M=N=K=32768, alpha=1, beta=0 (BASELINE config 5), A and C split by row blocks over
+           the ranks, B broadcast once per GEMM from rank 0 with NCCL in K-panels overlapped with
+           the compute -- strong scaling; the broadcast is inside the timed step.
+`value` is whole-job TFLOP/s (2*M*N*K per step) on the device clock (CUDA events, max over ranks).
+`e2e` is the same metric through the host-buffer API with the host<->device copies timed.
+The extra objects carry the other parts of the metric (3xTF32 path, ABFT overhead, SAXPY/SDOT
+GB/s), each with its own roofline.  `--impl reference` times the reference's own CPU GEMM
+(utils/utils.cu:93-103, compiled from the reference tree into oracle/_ref) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "SGEMM TFLOPS @6144^3 fp32"
+N1 = 6144
+NMULTI = 32768
+CPU_SAMPLE_N = 1152          # reference CPU GEMM sample: 1152^3 = (3/16 * 6144)^3, about 1/152 of the flop
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the committed
+# ncu captures (profiles/), scaled to a full launch; None until a capture exists for that kernel.
+NCU_TRAFFIC = {"sgemm_ffma_6144": None, "sgemm_3xtf32_6144": None, "saxpy_2p28": None, "sdot_2p28": None}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.stop_flag, self.thread = index, [], False, None
+
+    def _run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([v.strip() for v in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop_flag = True
+        self.thread.join(timeout=10)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        for s in self.samples:
+            try:
+                mhz.append(int(float(s[0])))
+                mx = max(mx, int(float(s[1])))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def timed(fn, steps, warmup, dist_barrier=None):
+    """ms per step: `warmup` untimed calls, then exactly `steps` calls between CUDA events on the current stream."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_barrier:
+        dist_barrier()
+    beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    beg.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if dist_barrier:
+        dist_barrier()
+    return beg.elapsed_time(end) / steps
+
+
+def cpu_reference_gemm_tflops(n, reps):
+    """The reference's own cpu_gemm (oracle/_ref) when built, else the oracle port; 1 thread (it is serial)."""
+    import numpy as np
+    import oracle
+    a = oracle.fill_uniform(n * n, 1).reshape(n, n)
+    b = oracle.fill_uniform(n * n, 2).reshape(n, n)
+    c = oracle.fill_uniform(n * n, 3).reshape(n, n)
+    use_ref = oracle.ref_lib() is not None
+    fn = (lambda: oracle.ref_cpu_gemm(1.0, 0.5, a, b, c)) if use_ref else (lambda: oracle.cpu_gemm(1.0, 0.5, a, b, c))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return 2.0 * n ** 3 / (sum(times) / len(times)) / 1e12, ("reference" if use_ref else "port"), times
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU GEMM on the host cores, same metric and unit."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import numpy as np  # noqa: F401
+    n = CPU_SAMPLE_N
+    tf_w, kind, _ = cpu_reference_gemm_tflops(n, max(0, args.warmup)) if args.warmup > 0 else (0, None, None)
+    tf, kind, times = cpu_reference_gemm_tflops(n, args.steps)
+    import oracle
+    # the same arithmetic with the row loop split over every host core (bit-identical results)
+    a = oracle.fill_uniform(n * n, 1).reshape(n, n)
+    b = oracle.fill_uniform(n * n, 2).reshape(n, n)
+    c = oracle.fill_uniform(n * n, 3).reshape(n, n)
+    t0 = time.perf_counter()
+    oracle.sgemm_f32(1.0, a, b, 0.5, c)
+    t_all = time.perf_counter() - t0
+    sample = f"row-major SGEMM {n}^3 per step (alpha=1, beta=0.5, uniform[-1,1]); 6144^3 is {(N1 / n) ** 3:.0f}x the flop"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"sgemm_rowmajor_{n}^3_cpu_sample_of_{N1}^3", "alpha": 1.0, "beta": 0.5,
+                   "code": "utils/utils.cu:93-103 cpu_gemm compiled from the reference tree (oracle/_ref)" if kind == "reference"
+                   else "oracle port of cpu_gemm"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": 1, "kind": kind, "sample": sample,
+                         "all_cores_port": {"value": 2.0 * n ** 3 / t_all / 1e12, "cores": os.cpu_count()}},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def bench_vectors(b2, torch, peaks, steps, warmup):
+    """SAXPY / SDOT at n = 2^28 (1 GiB per vector, larger than L2): GB/s against the measured HBM copy peak."""
+    out = {}
+    n = 1 << 28
+    x = b2.fill_uniform(torch.empty(n, device="cuda"), 4)
+    y = b2.fill_uniform(torch.empty(n, device="cuda"), 5)
+    res = torch.zeros(1, device="cuda")
+    ms = timed(lambda: b2.saxpy(n, 2.0, x, y), steps, warmup)
+    gbs = 12.0 * n / (ms * 1e-3) / 1e9
+    out["saxpy"] = {"n": n, "ms": ms, "value": gbs, "unit": "GB/s",
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["saxpy_2p28"],
+                                 "algorithmic_bytes": 12 * n, "peak_source": peaks["source"], "frac_of_8TBs_spec": gbs / 8000.0}}
+    ms = timed(lambda: b2.sdot(n, x, y, res), steps, warmup)
+    gbs = 8.0 * n / (ms * 1e-3) / 1e9
+    out["sdot"] = {"n": n, "ms": ms, "value": gbs, "unit": "GB/s",
+                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["sdot_2p28"],
+                                "algorithmic_bytes": 8 * n, "peak_source": peaks["source"], "frac_of_8TBs_spec": gbs / 8000.0}}
+    return out
+
+
+def run_single(args):
+    import torch
+    import hpcdeepneuralnetworks_b200 as b2
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    n = args.size or N1
+    flop = 2.0 * n ** 3
+    path = 1 if args.path == "3xtf32" else 0
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    Cm = b2.fill_uniform(torch.empty((n, n), device="cuda"), 3)
+    sm_count = b2.device_info()["sm_count"]
+
+    # FP32 SIMT peak, measured live with a register-only FMA stream (the roofline of the FFMA path)
+    ffma_peak = b2.ffma_peak_tflops()
+
+    def step(p=path):
+        b2.sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=p)
+
+    with ClockSampler(0) as clk:
+        ms = timed(step, args.steps, args.warmup)
+    b2.check_status()
+    clocks = clk.summary()
+    tflops = flop / (ms * 1e-3) / 1e12
+
+    def roof(p, tf):
+        if p == 0:
+            return {"bound": "fp32_simt", "achieved": tf, "peak": ffma_peak, "unit": "TFLOP/s", "frac": tf / ffma_peak,
+                    "traffic": NCU_TRAFFIC["sgemm_ffma_6144"], "peak_source": "register-only FFMA probe, same run",
+                    "peak_spec": sm_count * 128 * 2 * 1.965e9 / 1e12, "algorithmic_flop": flop}
+        tf32_peak = peaks["bf16_tflops"] / 2.0       # dense TF32 runs at half the bf16 rate
+        return {"bound": "tensor", "achieved": 3.0 * tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": 3.0 * tf / tf32_peak,
+                "traffic": NCU_TRAFFIC["sgemm_3xtf32_6144"], "peak_source": f"{peaks['source']} bf16 GEMM / 2",
+                "useful_tflops": tf, "algorithmic_flop": 3.0 * flop}
+
+    extras = {}
+    if not args.quick:
+        other = 1 - path
+        ms_o = timed(lambda: step(other), max(3, args.steps // 2), 3)
+        b2.check_status()
+        tf_o = flop / (ms_o * 1e-3) / 1e12
+        extras["sgemm_3xtf32" if other == 1 else "sgemm_ffma"] = {"ms": ms_o, "value": tf_o, "unit": "TFLOP/s",
+                                                                  "roofline": roof(other, tf_o)}
+        try:
+            ms_ft = timed(lambda: b2.ft_sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=0), max(3, args.steps // 2), 3)
+            ms_plain = ms if path == 0 else ms_o
+            extras["abft_ffma"] = {"ms": ms_ft, "value": flop / (ms_ft * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                   "overhead_pct": 100.0 * (ms_ft / ms_plain - 1.0)}
+        except Exception as e:  # reported, not hidden
+            extras["abft_ffma"] = {"error": str(e)}
+        extras.update(bench_vectors(b2, torch, peaks, max(5, args.steps), 3))
+
+    # end to end through the host-buffer API: pinned host A, B, C -> device -> SGEMM -> host C
+    hs = b2.HostSgemm(n, n, n, path=path)
+    hs.hA.copy_(A)
+    hs.hB.copy_(B)
+    hs.hC.copy_(Cm)
+    e2e_steps = max(2, min(args.steps, 5))
+    ms_e2e = timed(lambda: hs.run(1.0, 0.5), e2e_steps, 1)
+    e2e = {"value": flop / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": hs.h2d_bytes(),
+           "d2h_bytes_per_step": hs.d2h_bytes(), "ms_per_step": ms_e2e, "steps": e2e_steps}
+
+    cpu = None
+    if not args.no_cpu:
+        reps = 1
+        tf_cpu, kind, _ = cpu_reference_gemm_tflops(CPU_SAMPLE_N, reps)
+        cpu = {"value": tf_cpu, "unit": "TFLOP/s", "cores": 1, "kind": kind,
+               "sample": f"one row-major SGEMM {CPU_SAMPLE_N}^3 (alpha=1, beta=0.5), 1/{(N1 / CPU_SAMPLE_N) ** 3:.0f} of the flop of {N1}^3"}
+
+    line = {
+        "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"sgemm_rowmajor_{n}^3", "path": args.path, "alpha": 1.0, "beta": 0.5,
+                   "inputs": "seeded uniform[-1,1) generated on the device", "l2": "A, B, C are 3 x %d MB, larger than the 126 MB L2" % (4 * n * n // 2 ** 20),
+                   "parallelism": "1 GPU"},
+        "roofline": roof(path, tflops), "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * (1 if path == 0 else 3),
+        "clocks": clocks, "extra": extras,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_multi(args):
+    import torch
+    import torch.distributed as dist
+    import hpcdeepneuralnetworks_b200 as b2
+    from hpcdeepneuralnetworks_b200 import dist as b2dist
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    n = args.size or NMULTI
+    path = 1 if args.path == "3xtf32" else 0
+    start, rows = b2dist.row_block(n, rank, world)
+    A = torch.empty((rows, n), device="cuda")
+    # every rank fills its own row block of A from its own seeded stream; B comes from rank 0 only
+    b2.fill_uniform(A, 1000 + rank)
+    B = torch.empty((n, n), device="cuda")
+    if rank == 0:
+        b2.fill_uniform(B, 2)
+    Cm = torch.zeros((rows, n), device="cuda")
+    comm = torch.cuda.Stream()
+
+    def step():
+        b2dist.sharded_sgemm(n, n, n, 1.0, A, B, 0.0, Cm, src=0, panel=args.panel, path=path, comm_stream=comm)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    with ClockSampler(local) as clk:
+        ms_local = timed(step, args.steps, args.warmup, dist_barrier=barrier)
+    b2.check_status()
+    t = torch.tensor([ms_local], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    flop = 2.0 * n ** 3
+    tflops = flop / (ms * 1e-3) / 1e12
+
+    # sharded SDOT: 2^30 elements in total, one scalar all-reduce
+    nloc = (1 << 30) // world
+    x = b2.fill_uniform(torch.empty(nloc, device="cuda"), 4 + 10 * rank)
+    y = b2.fill_uniform(torch.empty(nloc, device="cuda"), 5 + 10 * rank)
+    ms_dot_local = timed(lambda: b2dist.sharded_sdot(nloc, x, y), max(5, args.steps), 3, dist_barrier=barrier)
+    t = torch.tensor([ms_dot_local], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_dot = float(t.item())
+
+    if rank == 0:
+        ffma_peak = b2.ffma_peak_tflops()
+        peaks = load_peaks()
+        per_gpu = tflops / world
+        line = {
+            "metric": METRIC.replace("6144", str(n)), "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"sgemm_rowmajor_{n}^3_rowblock_sharded", "path": args.path, "alpha": 1.0, "beta": 0.0,
+                       "parallelism": f"A,C row blocks over {world} GPUs; B broadcast from rank 0 per GEMM in K-panels of {args.panel} (NCCL)",
+                       "l2": "operands are GBs per GPU, far larger than L2"},
+            "roofline": {"bound": "fp32_simt" if path == 0 else "tensor", "achieved": per_gpu if path == 0 else 3 * per_gpu,
+                         "peak": ffma_peak if path == 0 else peaks["bf16_tflops"] / 2, "unit": "TFLOP/s",
+                         "frac": (per_gpu / ffma_peak) if path == 0 else (3 * per_gpu / (peaks["bf16_tflops"] / 2)),
+                         "traffic": None, "note": "per-GPU average, broadcast included in the time"},
+            "cpu_baseline": None,
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "operands of 32768^3 are generated on the device; no host copy is part of this workload"},
+            "gpu_launches": args.steps * len(b2dist.k_panels(n, args.panel)) * (1 if path == 0 else 3),
+            "clocks": clk.summary(),
+            "extra": {"sdot_sharded": {"n_total": nloc * world, "ms": ms_dot, "value": 8.0 * nloc * world / (ms_dot * 1e-3) / 1e9,
+                                       "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_dot * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="ffma", choices=["ffma", "3xtf32"])
+    ap.add_argument("--size", type=int, default=0, help="override the matrix size (profiling of small cases)")
+    ap.add_argument("--panel", type=int, default=4096, help="K-panel of the B broadcast (multi-GPU)")
+    ap.add_argument("--quick", action="store_true", help="headline kernel only (no extras); used for profiling")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.quick else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+    from hpcdeepneuralnetworks_b200 import _lib
+    _lib.load()   # raises if the CUDA library is missing: there is no fallback
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return run_multi(args)
+    return run_single(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,277 @@
+"""Host-side mirror of the reference's kernel interface, calling the CUDA library through
+its C ABI.  Names, argument order and meaning follow the reference:
+
+* ``sgemm(M, N, K, alpha, A, B, beta, C)``  -- the north-star row-major launcher
+  (kernel/sgemm/sgemm.cu:135-141 generalised), ``sgemm_series(kernel_id, N, A, B, C, alpha, beta)``
+  -- the kernels ``sgemm_1..sgemm_14`` (kernel/sgemm/include/kernel_*.cuh).
+* ``ft_sgemm(...)`` -- ABFT SGEMM (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:21).
+* ``saxpy(n, alpha, x, y)`` / ``sdot(n, x, y, out)`` (kernel/saxpy/saxpy.cu:38, kernel/sdot/sdot.cu:9).
+
+Tensors are torch CUDA float32 tensors used only as device memory; all arithmetic happens in
+libb2blas.so.  Errors surface as ``B2Error`` (the reference printf+exit()s).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import B2Error, Fault, FtReport, check
+
+PATH_FFMA = 0
+PATH_3XTF32 = 1
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise TypeError("expected a CUDA tensor")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Handle:
+    """Owner of per-device scratch (``b2_handle``).  The large workspace (3xTF32 planes) is a
+    torch allocation handed to the library, so the library itself never calls cudaMalloc for it."""
+
+    def __init__(self):
+        self._L = _lib.load()
+        self._h = C.c_void_p()
+        check(self._L.b2_create(C.byref(self._h)))
+        self._ws = None
+
+    def close(self):
+        if self._h:
+            torch.cuda.synchronize()
+            self._L.b2_destroy(self._h)
+            self._h = C.c_void_p()
+            self._ws = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def reserve(self, nbytes: int):
+        if nbytes <= 0:
+            return
+        if self._ws is None or self._ws.numel() < nbytes + 1024:
+            torch.cuda.synchronize()
+            self._ws = None
+            self._ws = torch.empty(nbytes + 2048, dtype=torch.uint8, device="cuda")
+            base = (self._ws.data_ptr() + 1023) & ~1023
+            check(self._L.b2_set_workspace(self._h, C.c_void_p(base), self._ws.numel() - (base - self._ws.data_ptr())))
+
+    @property
+    def raw(self):
+        return self._h
+
+
+_default = {}
+
+
+def default_handle() -> Handle:
+    dev = torch.cuda.current_device()
+    if dev not in _default:
+        _default[dev] = Handle()
+    return _default[dev]
+
+
+def check_status(handle: Handle | None = None) -> None:
+    """Synchronise and raise if a kernel's bounded wait ran out."""
+    h = handle or default_handle()
+    st = _lib.load().b2_check_status(h.raw, _stream())
+    if st != 0:
+        check(st if st < 0 else -3)
+
+
+def sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, lda=None, ldb=None, ldc=None, handle=None):
+    """Row-major C = alpha*A*B + beta*C on device tensors (in place on ``Cm``)."""
+    L = _lib.load()
+    h = handle or default_handle()
+    if path == PATH_3XTF32:
+        h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))
+    check(L.b2_sgemm(h.raw, path, M, N, K, alpha, _ptr(A), lda or K, _ptr(B), ldb or N, beta, _ptr(Cm), ldc or N,
+                     _stream()))
+    return Cm
+
+
+def sgemm_series(kernel_id, N, A, B, Cm, alpha, beta, threads_x=32):
+    """``sgemm_<kernel_id>(N, A, B, C, alpha, beta)`` of the reference series."""
+    check(_lib.load().b2_sgemm_series(kernel_id, threads_x, N, _ptr(A), _ptr(B), _ptr(Cm), alpha, beta, _stream()))
+    return Cm
+
+
+def sgemm_colmajor_nt(M, N, K, A, B, Cm, alpha, beta):
+    """kernel/ft_sgemm layout: column-major A (MxK), B stored NxK, C (MxN); C = alpha*A*B^T + beta*C.
+    Runs on the default stream like the reference driver (kernel/ft_sgemm/sgemm.cu:114-157)."""
+    torch.cuda.current_stream().synchronize()
+    check(_lib.load().ref_sgemm_colmajor_nt(M, N, K, _ptr(A), _ptr(B), _ptr(Cm), alpha, beta))
+    torch.cuda.synchronize()
+    return Cm
+
+
+def make_plan(plan) -> torch.Tensor | None:
+    """(n,6) int array of (tile_m, tile_n, row, col, k_step, bit) -> device tensor of b2_fault."""
+    if plan is None:
+        return None
+    arr = np.ascontiguousarray(np.asarray(plan, dtype=np.int32).reshape(-1, 6))
+    return torch.from_numpy(arr).cuda()
+
+
+def ft_sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, plan=None, tau=0.0, report=None, lda=None, ldb=None,
+             ldc=None, handle=None):
+    """ABFT SGEMM.  ``plan``: device int32 tensor (n,6) from ``make_plan`` or None.  ``report``: device
+    int32 tensor of 8 words that the call adds to (see ``FtReport``) or None.  Returns ``Cm``."""
+    L = _lib.load()
+    h = handle or default_handle()
+    if path == PATH_3XTF32:
+        h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))
+    nf = 0 if plan is None else int(plan.shape[0])
+    check(L.b2_ft_sgemm(h.raw, path, M, N, K, alpha, _ptr(A), lda or K, _ptr(B), ldb or N, beta, _ptr(Cm), ldc or N,
+                        _ptr(plan), nf, tau, _ptr(report), _stream()))
+    return Cm
+
+
+def new_report() -> torch.Tensor:
+    return torch.zeros(8, dtype=torch.int32, device="cuda")
+
+
+def read_report(report: torch.Tensor) -> dict:
+    v = report.cpu().tolist()
+    return {"tiles": v[0], "injected": v[1], "detected": v[2], "corrected": v[3], "uncorrectable": v[4]}
+
+
+def saxpy(n, alpha, x, y, handle=None):
+    """y <- alpha*x + y."""
+    h = handle or default_handle()
+    check(_lib.load().b2_saxpy(h.raw, n, alpha, _ptr(x), _ptr(y), _stream()))
+    return y
+
+
+def sdot(n, x, y, out=None, handle=None):
+    """out[0] <- x . y (overwrites).  Returns the 1-element device tensor."""
+    h = handle or default_handle()
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    check(_lib.load().b2_sdot(h.raw, n, _ptr(x), _ptr(y), _ptr(out), _stream()))
+    return out
+
+
+def sdot_partial(n, x, y, out, partial64, handle=None):
+    h = handle or default_handle()
+    check(_lib.load().b2_sdot_partial(h.raw, n, _ptr(x), _ptr(y), _ptr(out), _ptr(partial64), _stream()))
+    return out
+
+
+# ---- host-buffer forms: what a caller holding host arrays (the reference drivers' situation
+# before their cudaMemcpy calls, kernel/sgemm/sgemm.cu:50-58) would use -------------------------
+class HostSgemm:
+    """Pinned staging + device buffers for repeated row-major SGEMM calls on host arrays."""
+
+    def __init__(self, M, N, K, path=PATH_FFMA):
+        self.M, self.N, self.K, self.path = M, N, K, path
+        self.hA = torch.empty((M, K), dtype=torch.float32).pin_memory()
+        self.hB = torch.empty((K, N), dtype=torch.float32).pin_memory()
+        self.hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
+        self.dA = torch.empty((M, K), dtype=torch.float32, device="cuda")
+        self.dB = torch.empty((K, N), dtype=torch.float32, device="cuda")
+        self.dC = torch.empty((M, N), dtype=torch.float32, device="cuda")
+
+    def h2d_bytes(self):
+        return 4 * (self.M * self.K + self.K * self.N + self.M * self.N)
+
+    def d2h_bytes(self):
+        return 4 * self.M * self.N
+
+    def run(self, alpha, beta, ft=False):
+        """hC <- alpha*hA*hB + beta*hC through the device; returns hC (pinned) after sync."""
+        self.dA.copy_(self.hA, non_blocking=True)
+        self.dB.copy_(self.hB, non_blocking=True)
+        self.dC.copy_(self.hC, non_blocking=True)
+        if ft:
+            ft_sgemm(self.M, self.N, self.K, alpha, self.dA, self.dB, beta, self.dC, path=self.path)
+        else:
+            sgemm(self.M, self.N, self.K, alpha, self.dA, self.dB, beta, self.dC, path=self.path)
+        self.hC.copy_(self.dC, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.hC
+
+
+# ---- harness ---------------------------------------------------------------------------------
+def fill_uniform(t: torch.Tensor, seed: int):
+    check(_lib.load().b2_fill_uniform(_ptr(t), t.numel(), seed, _stream()))
+    return t
+
+
+def fill_const(t: torch.Tensor, value: float):
+    check(_lib.load().b2_fill_const(_ptr(t), t.numel(), value, _stream()))
+    return t
+
+
+def verify_matrix(ref: torch.Tensor, got: torch.Tensor, abs_tol: float = 1e-2):
+    """verify_matrix of utils/utils.cu:75-91 on the device: (passed, max_abs_diff)."""
+    rows, cols = ref.shape
+    mx = C.c_float(0.0)
+    r = check(_lib.load().b2_verify_matrix(_ptr(ref), _ptr(got), rows, cols, ref.stride(0), abs_tol, C.byref(mx), _stream()))
+    return r == 0, mx.value
+
+
+class EventTimer:
+    """CUDA-event timer on the current stream (replaces the host-clock saxpy_timer, utils/utils.cuh:56-77)."""
+
+    def __init__(self):
+        self._L = _lib.load()
+        self._t = C.c_void_p()
+        check(self._L.b2_timer_create(C.byref(self._t)))
+
+    def start(self):
+        check(self._L.b2_timer_start(self._t, _stream()))
+
+    def stop(self):
+        check(self._L.b2_timer_stop(self._t, _stream()))
+
+    def elapsed_ms(self) -> float:
+        ms = C.c_float(0.0)
+        check(self._L.b2_timer_elapsed_ms(self._t, C.byref(ms)))
+        return ms.value
+
+    def __del__(self):
+        try:
+            self._L.b2_timer_destroy(self._t)
+        except Exception:
+            pass
+
+
+def ffma_peak_tflops(launches: int = 3, ffma_per_thread: int = 1 << 20) -> float:
+    """Measured FP32 SIMT peak of the current device (register-only FMA stream), TFLOP/s."""
+    L = _lib.load()
+    flops = C.c_double(0.0)
+    check(L.b2_ffma_peak_probe(1, ffma_per_thread, C.byref(flops), _stream()))  # warm-up
+    torch.cuda.synchronize()
+    t = EventTimer()
+    t.start()
+    check(L.b2_ffma_peak_probe(launches, ffma_per_thread, C.byref(flops), _stream()))
+    t.stop()
+    return flops.value / (t.elapsed_ms() * 1e-3) / 1e12
+
+
+def device_info() -> dict:
+    sm, khz, mem = C.c_int(), C.c_int(), C.c_size_t()
+    check(_lib.load().b2_device_info(C.byref(sm), C.byref(khz), C.byref(mem)))
+    return {"sm_count": sm.value, "sm_clock_khz": khz.value, "global_mem_bytes": mem.value}
+
+
+def set_ffma_variant(v: int):
+    check(_lib.load().b2_set_ffma_variant(v))
+
+
+def set_tf32_b_layout(mn_major: bool):
+    check(_lib.load().b2_set_tf32_b_layout(1 if mn_major else 0))

@@ -1,0 +1,355 @@
+// 3xTF32 split-precision SGEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// The reference has no tensor-core path (every kernel of kernel/sgemm is FP32 FFMA); this
+// path computes the same row-major C = alpha*A*B + beta*C with FP32-level accuracy:
+//     x = hi + lo,  hi = tf32(x), lo = tf32(x - hi)          (round to nearest)
+//     A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi               (lo*lo dropped, ~2^-22)
+// Three tcgen05.mma.kind::tf32 per K-step accumulate into one FP32 accumulator tile in TMEM,
+// small terms first.
+//
+// Two kernels:
+//   split_planes_kernel   one pass over A and B writing the hi/lo planes (low 13 mantissa
+//                         bits already zero, so the tensor core's own treatment of them is
+//                         irrelevant) into the workspace.  B is written either as is
+//                         (K x N, "MN-major" operand) or transposed (N x K, "K-major").
+//   sgemm_3xtf32_kernel   one 128 x 256 output tile per CTA, K-slabs of 32; warp 0 = TMA
+//                         producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
+//                         epilogue (tcgen05.ld -> alpha/beta -> global).  2-stage ring of
+//                         96 KB (A_hi, A_lo: 128x32; B_hi, B_lo: 256x32), all tiles under the
+//                         128-byte swizzle.
+// Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace b2 {
+
+constexpr int TBM = 128, TBN = 256, TBK = 32, TSTAGES = 2;
+constexpr int kTA = TBM * TBK * 4;                 // 16 KB per A plane tile
+constexpr int kTB = TBN * TBK * 4;                 // 32 KB per B plane tile
+constexpr int kTStage = 2 * kTA + 2 * kTB;         // 96 KB
+constexpr int kTf32Smem = 1024 + TSTAGES * kTStage + 256;
+constexpr int kTmemCols = 256;
+
+__device__ __forceinline__ float tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r & 0xFFFFE000u);
+}
+
+// hi/lo planes of a rows x cols row-major matrix (pitch ld) into dense planes of pitch ldp.
+__global__ void split_planes_kernel(const float *__restrict__ X, int rows, int cols, int ld, float *__restrict__ hi,
+                                    float *__restrict__ lo, int ldp) {
+  const int64_t total = (int64_t)rows * ldp;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / ldp;
+    const int c = (int)(i - r * ldp);
+    float h = 0.f, l = 0.f;
+    if (c < cols) {
+      const float x = X[r * ld + c];
+      h = tf32_rna(x);
+      l = tf32_rna(x - h);
+    }
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// Transposing variant: X is rows x cols (pitch ld); planes are cols x rows (pitch ldp >= rows).
+__global__ void split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld, float *__restrict__ hi,
+                                      float *__restrict__ lo, int ldp) {
+  __shared__ float t[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    t[j][threadIdx.x] = (r < rows && c < cols) ? X[(int64_t)r * ld + c] : 0.f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, r = r0 + threadIdx.x;  // output row = c, output column = r
+    if (c < cols && r < ldp) {
+      const float x = (r < rows) ? t[threadIdx.x][j] : 0.f;
+      const float h = tf32_rna(x);
+      hi[(int64_t)c * ldp + r] = h;
+      lo[(int64_t)c * ldp + r] = tf32_rna(x - h);
+    }
+  }
+}
+
+struct Tf32Args {
+  float *C;
+  int M, N, K, ldc;
+  float alpha, beta;
+  int vec_c;
+  int *status;
+};
+
+template <bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                    const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + TSTAGES * kTStage);
+  uint64_t *empty = full + TSTAGES;
+  uint64_t *acc_ready = empty + TSTAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_n = (p.N + TBN - 1) / TBN;
+  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  const int m0 = tile_m * TBM, n0 = tile_n * TBN;
+  const int nkb = (p.K + TBK - 1) / TBK;
+
+  if (tid == 0) {
+    for (int s = 0; s < TSTAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmAh);
+    tma_prefetch_desc(&tmAl);
+    tma_prefetch_desc(&tmBh);
+    tma_prefetch_desc(&tmBl);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer -----------------------------------------------------------------
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % TSTAGES;
+        if (!mbar_wait(&empty[s], ((uint32_t)(kb / TSTAGES) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        unsigned char *st = smem + s * kTStage;
+        mbar_expect_tx(&full[s], kTStage);
+        tma_load_2d(st, &tmAh, &full[s], kb * TBK, m0);
+        tma_load_2d(st + kTA, &tmAl, &full[s], kb * TBK, m0);
+        if (B_MN) {
+          // planes are K x N: eight 32(n) x 32(k) boxes per plane, each 4 KB under the 128B swizzle
+#pragma unroll
+          for (int j = 0; j < TBN / 32; ++j) {
+            tma_load_2d(st + 2 * kTA + j * 4096, &tmBh, &full[s], n0 + j * 32, kb * TBK);
+            tma_load_2d(st + 2 * kTA + kTB + j * 4096, &tmBl, &full[s], n0 + j * 32, kb * TBK);
+          }
+        } else {
+          tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * TBK, n0);
+          tma_load_2d(st + 2 * kTA + kTB, &tmBl, &full[s], kb * TBK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(TBM, TBN, 0, B_MN ? 1 : 0);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % TSTAGES;
+        if (!mbar_wait(&full[s], (uint32_t)(kb / TSTAGES) & 1u)) {
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + s * kTStage);
+#pragma unroll
+        for (int k4 = 0; k4 < TBK / 8; ++k4) {
+          // K-major, 128B swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart; a K-step of
+          // 8 floats is 32 bytes further along the row.
+          const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
+          const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
+          uint64_t b_hi, b_lo;
+          if (B_MN) {
+            // MN-major, 128B swizzle: 32 n contiguous (128 bytes), next 32 n at LBO = 4096,
+            // 8-k groups at SBO = 1024; one K-step of 8 is one group.
+            b_hi = umma_smem_desc(st + 2 * kTA + k4 * 1024, 4096, 1024, 2);
+            b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 1024, 4096, 1024, 2);
+          } else {
+            b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
+            b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
+          }
+          umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
+          umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
+        }
+        umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(acc_ready);
+    }
+  } else {
+    // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 -------------------------------
+    const int q = warp & 3;
+    bool ok = true;
+    if (nkb > 0) {
+      // poll in slices so that an abort raised by the other roles is seen
+      bool done = false;
+      for (int it = 0; it < (1 << 14) && !done; ++it) {
+        done = mbar_wait(acc_ready, 0, 1u << 10);
+        if (!done && *abort_flag) break;
+      }
+      ok = done;
+    }
+    if (!ok) *abort_flag = 1;
+    tc_fence_after();
+    const int row = m0 + q * 32 + lane;
+    const bool read_c = (p.beta != 0.f);
+    float *crow = p.C + (size_t)row * p.ldc;
+#pragma unroll 1
+    for (int c = 0; c < TBN / 32; ++c) {
+      uint32_t v[32];
+      if (ok && nkb > 0) {
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      if (!ok || row >= p.M) continue;
+      const int col0 = n0 + c * 32;
+      if (p.vec_c && col0 + 31 < p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 o;
+          if (read_c) {
+            const float4 cc = *reinterpret_cast<const float4 *>(crow + col0 + j);
+            o.x = __fmaf_rn(p.alpha, __uint_as_float(v[j + 0]), __fmul_rn(p.beta, cc.x));
+            o.y = __fmaf_rn(p.alpha, __uint_as_float(v[j + 1]), __fmul_rn(p.beta, cc.y));
+            o.z = __fmaf_rn(p.alpha, __uint_as_float(v[j + 2]), __fmul_rn(p.beta, cc.z));
+            o.w = __fmaf_rn(p.alpha, __uint_as_float(v[j + 3]), __fmul_rn(p.beta, cc.w));
+          } else {
+            o.x = __fmul_rn(p.alpha, __uint_as_float(v[j + 0]));
+            o.y = __fmul_rn(p.alpha, __uint_as_float(v[j + 1]));
+            o.z = __fmul_rn(p.alpha, __uint_as_float(v[j + 2]));
+            o.w = __fmul_rn(p.alpha, __uint_as_float(v[j + 3]));
+          }
+          *reinterpret_cast<float4 *>(crow + col0 + j) = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < p.N) {
+            const float a = __uint_as_float(v[j]);
+            crow[col0 + j] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col0 + j])) : __fmul_rn(p.alpha, a);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+}
+
+static int g_tf32_b_mn = -1;  // -1: from B2_TF32_B_MN (default 0: K-major planes of B)
+
+size_t tf32_workspace_bytes(int M, int N, int K) {
+  const size_t kp = ((size_t)K + 3) & ~(size_t)3, np = ((size_t)N + 3) & ~(size_t)3;
+  const size_t a = (size_t)M * kp, b1 = (size_t)N * kp, b2 = (size_t)K * np;
+  const size_t b = b1 > b2 ? b1 : b2;
+  return (2 * a + 2 * b) * sizeof(float) + 4 * 1024;
+}
+
+template <bool B_MN>
+static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTf32Smem));
+    configured = true;
+  }
+  sgemm_3xtf32_kernel<B_MN><<<grid, 192, kTf32Smem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
+                        const float *B, int ldb, float beta, float *C, int ldc, cudaStream_t s);
+
+int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
+                          float beta, float *C, int ldc, cudaStream_t s) {
+  if (M == 0 || N == 0) return B2_OK;
+  if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, s);
+  if (g_tf32_b_mn < 0) {
+    const char *e = getenv("B2_TF32_B_MN");
+    g_tf32_b_mn = (e && atoi(e) != 0) ? 1 : 0;
+  }
+  const bool b_mn = g_tf32_b_mn != 0;
+  int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
+  if (st != B2_OK) return st;
+  const int kp = (K + 3) & ~3, np = (N + 3) & ~3;
+  char *w = (char *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023);
+  const size_t a_elems = (size_t)M * kp, b_elems = b_mn ? (size_t)K * np : (size_t)N * kp;
+  auto align1k = [](size_t bytes) { return (bytes + 1023) & ~(size_t)1023; };
+  float *Ah = (float *)w;
+  float *Al = (float *)(w + align1k(a_elems * 4));
+  float *Bh = (float *)(w + 2 * align1k(a_elems * 4));
+  float *Bl = (float *)(w + 2 * align1k(a_elems * 4) + align1k(b_elems * 4));
+
+  const int blocks = ctx->sm_count * 8;
+  split_planes_kernel<<<blocks, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp);
+  if (b_mn) {
+    split_planes_kernel<<<blocks, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, np);
+  } else {
+    dim3 g((N + 31) / 32, (kp + 31) / 32), blk(32, 8);
+    split_planes_t_kernel<<<g, blk, 0, s>>>(B, K, N, ldb, Bh, Bl, kp);
+  }
+  B2_CUDA(cudaGetLastError());
+
+  CUtensorMap maps[4];
+  st = make_tmap_2d(&maps[0], Ah, (uint64_t)K, (uint64_t)M, (uint64_t)kp, TBK, TBM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != B2_OK) return st;
+  st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, TBK, TBM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != B2_OK) return st;
+  if (b_mn) {
+    st = make_tmap_2d(&maps[2], Bh, (uint64_t)N, (uint64_t)K, (uint64_t)np, 32, TBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != B2_OK) return st;
+    st = make_tmap_2d(&maps[3], Bl, (uint64_t)N, (uint64_t)K, (uint64_t)np, 32, TBK, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != B2_OK) return st;
+    st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (st != B2_OK) return st;
+
+  Tf32Args args;
+  args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
+  args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
+  args.status = (int *)((char *)ctx->fixed + kFixedStatus);
+  const int grid = ((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN);
+  return b_mn ? launch_tf32<true>(maps, args, grid, s) : launch_tf32<false>(maps, args, grid, s);
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K) {
+  if (path != B2_PATH_3XTF32 || M <= 0 || N <= 0 || K <= 0) return 0;
+  return tf32_workspace_bytes(M, N, K);
+}
+
+// 0: B planes written transposed (N x K) and fed K-major; 1: B planes as is (K x N), fed MN-major.
+int b2_set_tf32_b_layout(int mn_major) {
+  b2::g_tf32_b_mn = mn_major ? 1 : 0;
+  return B2_OK;
+}
+
+}  // extern "C"

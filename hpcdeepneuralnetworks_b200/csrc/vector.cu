@@ -1,0 +1,340 @@
+// SAXPY / SDOT streaming kernels and the device side of the harness (seeded fill, constant
+// fill, matrix compare, FFMA-peak probe).
+//
+// SAXPY replaces _saxpy / saxpy3 / saxpy of the reference (kernel/saxpy/saxpy.cu:15-48):
+// one kernel, 128-bit grid-stride body with 4 independent 16-byte loads per operand in
+// flight per thread, scalar head/tail for any n and any (mutually compatible) alignment.
+// SDOT replaces _sdot / sdot + reduction (kernel/sdot/sdot.cu:9-67): grid-stride 128-bit
+// loads into independent FP32 accumulators, warp-shuffle + one shared-memory stage per
+// block, block partials in double, and a last-block finish in a fixed order, so that the
+// result is deterministic (the reference's atomicAdd of block sums is not).
+#include <string.h>
+
+#include "common.cuh"
+
+namespace b2 {
+
+constexpr int kVecThreads = 256;
+constexpr int kVecUnroll = 4;
+
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+
+// y[i] = fma(alpha, x[i], y[i]).  The body covers [head, head + 4*n4); x + head and y + head
+// are 16-byte aligned when XALIGNED, otherwise only y + head is and x is read as scalars.
+template <bool XALIGNED>
+__global__ void __launch_bounds__(kVecThreads) saxpy_kernel(int64_t n, int64_t head, int64_t n4, float alpha,
+                                                            const float *__restrict__ x, float *__restrict__ y) {
+  const int64_t tid = (int64_t)blockIdx.x * kVecThreads + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * kVecThreads;
+  // scalar head and tail (at most 3 + 3 elements), handled by the first threads
+  if (tid < head) y[tid] = __fmaf_rn(alpha, x[tid], y[tid]);
+  const int64_t tail0 = head + 4 * n4;
+  if (tid < n - tail0) y[tail0 + tid] = __fmaf_rn(alpha, x[tail0 + tid], y[tail0 + tid]);
+
+  float4 *y4 = reinterpret_cast<float4 *>(y + head);
+  const float *xs = x + head;
+  const float4 *x4 = reinterpret_cast<const float4 *>(xs);
+  // Each block owns UNROLL consecutive 256-wide float4 rows per trip: fully coalesced.
+  int64_t base = (int64_t)blockIdx.x * (kVecThreads * kVecUnroll) + threadIdx.x;
+  const int64_t step = nthreads * kVecUnroll;
+  for (; base + (kVecUnroll - 1) * kVecThreads < n4; base += step) {
+    float4 xv[kVecUnroll], yv[kVecUnroll];
+#pragma unroll
+    for (int u = 0; u < kVecUnroll; ++u) {
+      const int64_t i = base + u * kVecThreads;
+      if (XALIGNED) {
+        xv[u] = ld_stream(x4 + i);
+      } else {
+        xv[u] = make_float4(__ldcs(xs + 4 * i), __ldcs(xs + 4 * i + 1), __ldcs(xs + 4 * i + 2), __ldcs(xs + 4 * i + 3));
+      }
+      yv[u] = ld_stream(y4 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kVecUnroll; ++u) {
+      yv[u].x = __fmaf_rn(alpha, xv[u].x, yv[u].x);
+      yv[u].y = __fmaf_rn(alpha, xv[u].y, yv[u].y);
+      yv[u].z = __fmaf_rn(alpha, xv[u].z, yv[u].z);
+      yv[u].w = __fmaf_rn(alpha, xv[u].w, yv[u].w);
+      __stcs(y4 + base + u * kVecThreads, yv[u]);
+    }
+  }
+  // ragged last trip
+  for (int u = 0; u < kVecUnroll; ++u) {
+    const int64_t i = base + u * kVecThreads;
+    if (i < n4) {
+      float4 xv, yv = ld_stream(y4 + i);
+      if (XALIGNED) xv = ld_stream(x4 + i);
+      else xv = make_float4(xs[4 * i], xs[4 * i + 1], xs[4 * i + 2], xs[4 * i + 3]);
+      yv.x = __fmaf_rn(alpha, xv.x, yv.x);
+      yv.y = __fmaf_rn(alpha, xv.y, yv.y);
+      yv.z = __fmaf_rn(alpha, xv.z, yv.z);
+      yv.w = __fmaf_rn(alpha, xv.w, yv.w);
+      __stcs(y4 + i, yv);
+    }
+  }
+}
+
+// Deterministic block / grid reduction shared by the SDOT entry points.  `partials` holds one
+// double per block; the last block to finish (ticket counter) adds them in index order per
+// lane and then by a fixed shuffle tree, writes the result and re-arms the ticket.
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void sdot_finish(double thread_sum, double *partials, unsigned int *ticket,
+                                            float *result, double *result64) {
+  __shared__ double warp_part[kVecThreads / 32];
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  double w = warp_sum(thread_sum);
+  if (lane == 0) warp_part[warp] = w;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double b = 0.0;
+#pragma unroll
+    for (int i = 0; i < kVecThreads / 32; ++i) b += warp_part[i];
+    partials[blockIdx.x] = b;
+    __threadfence();
+    unsigned int t = atomicAdd(ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    double s = 0.0;
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += kVecThreads) s += __ldcg(partials + i);
+    s = warp_sum(s);
+    if (lane == 0) warp_part[warp] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double tot = 0.0;
+#pragma unroll
+      for (int i = 0; i < kVecThreads / 32; ++i) tot += warp_part[i];
+      *result = (float)tot;
+      if (result64) *result64 = tot;
+      *ticket = 0u;  // re-arm for the next launch on this scratch
+    }
+  }
+}
+
+template <bool ALIGNED>
+__device__ __forceinline__ double sdot_thread_sum(int64_t n, const float *__restrict__ x, const float *__restrict__ y) {
+  const int64_t tid = (int64_t)blockIdx.x * kVecThreads + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * kVecThreads;
+  float acc[kVecUnroll] = {0.f, 0.f, 0.f, 0.f};
+  float tailacc = 0.f;
+  if (ALIGNED) {
+    const int64_t n4 = n >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x), *y4 = reinterpret_cast<const float4 *>(y);
+    int64_t base = (int64_t)blockIdx.x * (kVecThreads * kVecUnroll) + threadIdx.x;
+    const int64_t step = nthreads * kVecUnroll;
+    for (; base + (kVecUnroll - 1) * kVecThreads < n4; base += step) {
+      float4 xv[kVecUnroll], yv[kVecUnroll];
+#pragma unroll
+      for (int u = 0; u < kVecUnroll; ++u) {
+        xv[u] = ld_stream(x4 + base + u * kVecThreads);
+        yv[u] = ld_stream(y4 + base + u * kVecThreads);
+      }
+#pragma unroll
+      for (int u = 0; u < kVecUnroll; ++u) {
+        acc[u] = __fmaf_rn(xv[u].x, yv[u].x, acc[u]);
+        acc[u] = __fmaf_rn(xv[u].y, yv[u].y, acc[u]);
+        acc[u] = __fmaf_rn(xv[u].z, yv[u].z, acc[u]);
+        acc[u] = __fmaf_rn(xv[u].w, yv[u].w, acc[u]);
+      }
+    }
+    for (int u = 0; u < kVecUnroll; ++u) {
+      const int64_t i = base + u * kVecThreads;
+      if (i < n4) {
+        float4 xv = ld_stream(x4 + i), yv = ld_stream(y4 + i);
+        acc[u] = __fmaf_rn(xv.x, yv.x, acc[u]);
+        acc[u] = __fmaf_rn(xv.y, yv.y, acc[u]);
+        acc[u] = __fmaf_rn(xv.z, yv.z, acc[u]);
+        acc[u] = __fmaf_rn(xv.w, yv.w, acc[u]);
+      }
+    }
+    const int64_t t0 = n4 << 2;
+    if (tid < n - t0) tailacc = x[t0 + tid] * y[t0 + tid];
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) tailacc = __fmaf_rn(x[i], y[i], tailacc);
+  }
+  return ((double)acc[0] + (double)acc[1]) + ((double)acc[2] + (double)acc[3]) + (double)tailacc;
+}
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(kVecThreads) sdot_kernel(int64_t n, const float *__restrict__ x,
+                                                           const float *__restrict__ y, double *partials,
+                                                           unsigned int *ticket, float *result, double *result64) {
+  sdot_finish(sdot_thread_sum<ALIGNED>(n, x, y), partials, ticket, result, result64);
+}
+
+__global__ void fill_uniform_kernel(float *dst, int64_t n, uint64_t mixed_seed) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) dst[i] = uniform_at(mixed_seed, (uint64_t)i);
+}
+
+__global__ void fill_const_kernel(float *dst, int64_t n, float v) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) dst[i] = v;
+}
+
+// out[0] = number of entries with |ref-got| > tol (or NaN), out[1] = bits of max |ref-got|.
+__global__ void verify_kernel(const float *ref, const float *got, int64_t rows, int64_t cols, int64_t ld, float tol,
+                              unsigned int *out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x, total = rows * cols;
+  unsigned int fails = 0;
+  float worst = 0.f;
+  for (; i < total; i += step) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float d = fabsf(ref[r * ld + c] - got[r * ld + c]);
+    if (!(d <= tol)) ++fails;
+    if (!(d <= worst)) worst = (d == d) ? d : __int_as_float(0x7f800000);
+  }
+  if (fails) atomicAdd(out, fails);
+  atomicMax(out + 1, __float_as_uint(worst));
+}
+
+// Register-only FFMA stream: 16 independent chains per thread, 8 warps per scheduler.
+__global__ void __launch_bounds__(256) ffma_probe_kernel(int64_t iters, float a, float b, float *sink) {
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = (float)(threadIdx.x + i);
+  for (int64_t it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] = __fmaf_rn(acc[i], a, b);
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += acc[i];
+  if (s == 123.456f) *sink = s;  // keeps the chains alive; practically never true
+}
+
+static int vec_grid(Context *ctx, int64_t work_items, int per_block) {
+  int64_t need = (work_items + per_block - 1) / per_block;
+  int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 blocks of 256 threads fill an SM
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+int b2_saxpy(b2_handle h, int64_t n, float alpha, const float *x, float *y, void *stream) {
+  B2_REQUIRE(n >= 0, B2_ERR_INVALID_ARG, "b2_saxpy: n = %lld is negative", (long long)n);
+  if (n == 0) return B2_OK;
+  B2_REQUIRE(x != nullptr && y != nullptr, B2_ERR_INVALID_ARG, "b2_saxpy: null vector");
+  B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_saxpy: vectors must be 4-byte aligned");
+  Context *ctx = h ? (Context *)h : default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_saxpy: no context (%s)", b2_last_error());
+  int64_t head = ((16 - ((uintptr_t)y & 15)) & 15) >> 2;
+  if (head > n) head = n;
+  const int64_t n4 = (n - head) >> 2;
+  const bool xal = (((uintptr_t)(x + head)) & 15) == 0;
+  const int grid = vec_grid(ctx, n4 > 0 ? n4 : 1, kVecThreads * kVecUnroll);
+  if (xal) saxpy_kernel<true><<<grid, kVecThreads, 0, (cudaStream_t)stream>>>(n, head, n4, alpha, x, y);
+  else saxpy_kernel<false><<<grid, kVecThreads, 0, (cudaStream_t)stream>>>(n, head, n4, alpha, x, y);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, double *partial_dev,
+                    void *stream) {
+  B2_REQUIRE(n >= 0, B2_ERR_INVALID_ARG, "b2_sdot: n = %lld is negative", (long long)n);
+  B2_REQUIRE(result_dev != nullptr, B2_ERR_INVALID_ARG, "b2_sdot: result pointer is NULL");
+  B2_REQUIRE(n == 0 || (x != nullptr && y != nullptr), B2_ERR_INVALID_ARG, "b2_sdot: null vector");
+  B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_sdot: vectors must be 4-byte aligned");
+  Context *ctx = h ? (Context *)h : default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_sdot: no context (%s)", b2_last_error());
+  char *fixed = (char *)ctx->fixed;
+  double *partials = (double *)(fixed + kFixedSdotPartials);
+  unsigned int *ticket = (unsigned int *)(fixed + kFixedSdotTicket);
+  const bool al = (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+  int grid = vec_grid(ctx, (n >> 2) > 0 ? (n >> 2) : 1, kVecThreads * kVecUnroll);
+  if (grid > (int)kSdotMaxBlocks) grid = (int)kSdotMaxBlocks;
+  if (al) sdot_kernel<true><<<grid, kVecThreads, 0, (cudaStream_t)stream>>>(n, x, y, partials, ticket, result_dev, partial_dev);
+  else sdot_kernel<false><<<grid, kVecThreads, 0, (cudaStream_t)stream>>>(n, x, y, partials, ticket, result_dev, partial_dev);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, void *stream) {
+  return b2_sdot_partial(h, n, x, y, result_dev, nullptr, stream);
+}
+
+int saxpy(int n, float alpha, const float *x, float *y) { return b2_saxpy(nullptr, n, alpha, x, y, nullptr); }
+int sdot(int n, const float *x, const float *y, float *result_dev) { return b2_sdot(nullptr, n, x, y, result_dev, nullptr); }
+
+int b2_fill_uniform(float *dev, int64_t n, uint64_t seed, void *stream) {
+  B2_REQUIRE(n >= 0 && (n == 0 || dev != nullptr), B2_ERR_INVALID_ARG, "b2_fill_uniform: bad arguments");
+  if (n == 0) return B2_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  fill_uniform_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(dev, n, mix64(seed));
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int b2_fill_uniform_host(float *host, int64_t n, uint64_t seed) {
+  B2_REQUIRE(n >= 0 && (n == 0 || host != nullptr), B2_ERR_INVALID_ARG, "b2_fill_uniform_host: bad arguments");
+  const uint64_t ms = mix64(seed);
+  for (int64_t i = 0; i < n; ++i) host[i] = uniform_at(ms, (uint64_t)i);
+  return B2_OK;
+}
+
+int b2_fill_const(float *dev, int64_t n, float value, void *stream) {
+  B2_REQUIRE(n >= 0 && (n == 0 || dev != nullptr), B2_ERR_INVALID_ARG, "b2_fill_const: bad arguments");
+  if (n == 0) return B2_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  fill_const_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(dev, n, value);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int b2_verify_matrix(const float *ref_dev, const float *got_dev, int64_t rows, int64_t cols, int64_t ld, float abs_tol,
+                     float *max_abs_host, void *stream) {
+  Context *ctx = default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_verify_matrix: no context");
+  B2_REQUIRE(rows >= 0 && cols >= 0 && ld >= cols, B2_ERR_INVALID_ARG, "b2_verify_matrix: bad shape");
+  B2_REQUIRE(rows * cols == 0 || (ref_dev && got_dev), B2_ERR_INVALID_ARG, "b2_verify_matrix: null matrix");
+  unsigned int *out = (unsigned int *)((char *)ctx->fixed + kFixedVerify);
+  cudaStream_t s = (cudaStream_t)stream;
+  B2_CUDA(cudaMemsetAsync(out, 0, 8, s));
+  if (rows * cols > 0) {
+    int64_t blocks = (rows * cols + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    verify_kernel<<<(int)blocks, 256, 0, s>>>(ref_dev, got_dev, rows, cols, ld, abs_tol, out);
+    B2_CUDA(cudaGetLastError());
+  }
+  unsigned int hostv[2];
+  B2_CUDA(cudaMemcpyAsync(hostv, out, 8, cudaMemcpyDeviceToHost, s));
+  B2_CUDA(cudaStreamSynchronize(s));
+  if (max_abs_host) memcpy(max_abs_host, &hostv[1], 4);
+  return hostv[0] ? 1 : 0;
+}
+
+int b2_ffma_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
+  Context *ctx = default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ffma_peak_probe: no context");
+  B2_REQUIRE(launches > 0 && ffma_per_thread > 0, B2_ERR_INVALID_ARG, "b2_ffma_peak_probe: bad arguments");
+  const int64_t iters = (ffma_per_thread + 127) / 128;
+  const int grid = ctx->sm_count * 8;
+  float *sink = (float *)((char *)ctx->fixed + kFixedVerify + 64);
+  for (int l = 0; l < launches; ++l) ffma_probe_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.999f, 0.001f, sink);
+  B2_CUDA(cudaGetLastError());
+  if (flops_out) *flops_out = 2.0 * (double)launches * (double)grid * 256.0 * (double)iters * 128.0;
+  return B2_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+/*
+ * b2blas.h -- C ABI of the B200 (sm_100a) FP32 BLAS-kernel library.
+ *
+ * The reference project (shixun404/HPCDeepNeuralNetworks) has no library API: its
+ * "interface" is the __global__ signature of each kernel plus the launch geometry that
+ * each driver main() hard-codes.  Every entry point below replaces one such
+ * kernel-plus-launch pair; the comment above it cites the reference file:line it stands
+ * in for.  All pointers named *_dev / A / B / C / x / y are caller-owned DEVICE pointers.
+ * Every function returns a b2_status (0 = ok, negative = error) and never exits the
+ * process; b2_last_error() gives a thread-local human-readable message.
+ *
+ * `stream` arguments are cudaStream_t values passed as void* so that this header needs
+ * no CUDA header; NULL is the default stream.  Work is enqueued, not synchronised,
+ * unless stated otherwise.
+ */
+#ifndef B2BLAS_H
+#define B2BLAS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  B2_OK = 0,
+  B2_ERR_INVALID_ARG = -1,   /* null pointer, negative size, bad leading dimension */
+  B2_ERR_UNSUPPORTED = -2,   /* shape the selected kernel cannot run (e.g. N not a tile multiple) */
+  B2_ERR_CUDA = -3,          /* a CUDA runtime/driver call failed; see b2_last_error() */
+  B2_ERR_TIMEOUT = -4,       /* a bounded device-side wait ran out (status word set by the kernel) */
+  B2_ERR_UNCORRECTABLE = -5, /* ABFT found a fault it could not locate or correct */
+  B2_ERR_WORKSPACE = -6      /* scratch workspace missing or too small */
+} b2_status;
+
+/* SGEMM math paths (north-star: two paths behind one launcher). */
+enum { B2_PATH_FFMA = 0, B2_PATH_3XTF32 = 1 };
+
+typedef struct b2_context *b2_handle;
+
+/* ---- library / handle ------------------------------------------------------------- */
+
+const char *b2_status_string(int status);
+const char *b2_last_error(void);
+/* Version as major*10000 + minor*100 + patch. */
+int b2_version(void);
+
+/* A handle owns per-device scratch (SDOT block partials, 3xTF32 split planes, ABFT
+ * report words).  b2_create allocates a small fixed scratch with cudaMalloc on the
+ * current device; larger scratch is either grown on demand (cudaMalloc, synchronising)
+ * or supplied by the caller with b2_set_workspace (no allocation inside the library). */
+int b2_create(b2_handle *out);
+int b2_destroy(b2_handle h);
+int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
+/* Bytes of workspace b2_sgemm(path=3xTF32) needs for an MxNxK problem. */
+size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K);
+
+/* ---- SGEMM: row-major C = alpha*A*B + beta*C --------------------------------------- */
+
+/* North-star launcher `sgemm(M,N,K,alpha,A,B,beta,C)`: row-major NN, lda=K, ldb=N, ldc=N,
+ * FFMA path, default stream, process-wide default handle.  Stands in for
+ * kernel/sgemm/sgemm.cu:135-141 (sgemm_14<<<grid,256,64KB>>>) generalised to M,N,K. */
+int sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C);
+
+/* Full form.  path = B2_PATH_FFMA | B2_PATH_3XTF32.  Any M,N,K >= 0, any lda>=K, ldb>=N,
+ * ldc>=N.  beta == 0 means C is not read (BLAS convention; the reference kernels read it,
+ * kernel/sgemm/include/kernel_14.cuh:5-9).  Replaces the `if (kernel_number == k)` launch
+ * ladder of kernel/sgemm/sgemm.cu:70-144. */
+int b2_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda,
+             const float *B, int ldb, float beta, float *C, int ldc, void *stream);
+
+/* The reference's optimisation series sgemm_1..sgemm_14 as sm_100a kernels, square N only,
+ * N a multiple of the rung's block tile (else B2_ERR_UNSUPPORTED), argument order exactly
+ * as the reference kernels: (N, A, B, C, alpha, beta)
+ * (kernel/sgemm/include/kernel_1.cuh:2 ... kernel_14.cuh:12; launches kernel/sgemm/sgemm.cu:70-141).
+ * `threads_x` is the reference driver's 4th argv (tile edge t of rungs 1-5; ignored >= 6). */
+int b2_sgemm_series(int kernel_id, int threads_x, int N, const float *A, const float *B, float *C,
+                    float alpha, float beta, void *stream);
+/* Reference-shaped shim, kernel/sgemm semantics: best kernel, default stream
+ * (kernel/sgemm/include/kernel_14.cuh:12). */
+int ref_sgemm_rowmajor(int N, float *A, float *B, float *C, float alpha, float beta);
+/* Reference-shaped shim, kernel/ft_sgemm semantics: column-major A (MxK, lda=M),
+ * B stored NxK (ldb=N), C MxN (ldc=M); C = alpha*A*B^T + beta*C
+ * (kernel/ft_sgemm/include_code_gen/sgemm_huge.cuh:11, oracle call kernel/ft_sgemm/sgemm.cu:111). */
+int ref_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, float alpha, float beta);
+
+/* ---- ABFT (fault-tolerant) SGEMM --------------------------------------------------- */
+
+/* One simulated soft error: after K-slab `k_step` of output tile (`tile_m`,`tile_n`)
+ * (128x128 tiles), bit `bit` of the FP32 accumulator of tile-local element
+ * (`row`,`col`) is flipped in registers.  A simulated fault never faults the GPU. */
+typedef struct {
+  int32_t tile_m, tile_n;
+  int32_t row, col;     /* 0..127 inside the tile */
+  int32_t k_step;       /* K-slab index (slab = 32 of K); clamped to the last slab */
+  int32_t bit;          /* 0..31 */
+} b2_fault;
+
+typedef struct {
+  int32_t tiles;          /* output tiles verified */
+  int32_t injected;       /* faults applied from the plan */
+  int32_t detected;       /* tiles whose row AND column checksum both flagged */
+  int32_t corrected;      /* accumulators rebuilt from the row checksum */
+  int32_t uncorrectable;  /* flagged but not locatable as a single element */
+  int32_t reserved[3];
+} b2_ft_report;
+
+/* North-star launcher `ft_sgemm`: as sgemm() with checksum encode in the mainloop and
+ * verify/locate/correct in the epilogue, no injection.  Stands in for
+ * kernel/ft_sgemm/sgemm.cu:144-151 (ft_sgemm_huge launch) and
+ * kernel/ft_sgemm/include/ft_sgemm_huge.cuh:21. */
+int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C);
+
+/* Full form.  `plan_dev`/`n_faults`: optional device array of faults to inject (NULL/0 =
+ * clean run).  `tau` <= 0 selects the default threshold 2e-6*K (inputs of unit scale);
+ * the reference uses a fixed 0.1 (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:30).
+ * `report_dev`: optional device b2_ft_report that this call ADDS to (caller zeroes it). */
+int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda,
+                const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
+                int n_faults, float tau, b2_ft_report *report_dev, void *stream);
+
+/* ---- SAXPY / SDOT ----------------------------------------------------------------- */
+
+/* y <- alpha*x + y, one fused multiply-add per element (bit-exact with fmaf on the host).
+ * Replaces saxpy<<<ceil(n/4/tpb),tpb>>> / saxpy3 / _saxpy (kernel/saxpy/saxpy.cu:15-48,
+ * launches :109-126). */
+int saxpy(int n, float alpha, const float *x, float *y);
+int b2_saxpy(b2_handle h, int64_t n, float alpha, const float *x, float *y, void *stream);
+
+/* *result_dev <- sum_i x[i]*y[i].  OVERWRITES the result (the reference's _sdot
+ * atomically adds into it, kernel/sdot/sdot.cu:32-33) and is deterministic run to run.
+ * Replaces _sdot / sdot+reduction (kernel/sdot/sdot.cu:9-67, launches :156,:172-195). */
+int sdot(int n, const float *x, const float *y, float *result_dev);
+int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, void *stream);
+/* As b2_sdot, but also leaves the double-precision partial sum in *partial_dev (used by
+ * the multi-GPU finish, which all-reduces the double). */
+int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev,
+                    double *partial_dev, void *stream);
+
+/* ---- harness (rebuild of utils/utils.cu around CUDA events) ----------------------- */
+
+/* Element i of the stream `seed` is a counter-based hash of (seed, i) mapped to a
+ * multiple of 2^-23 in [-1,1); identical bits on host and device.  Replaces
+ * generate_random_vector/matrix (utils/utils.cu:28-44), whose rand() grid cannot be
+ * reproduced on the device. */
+int b2_fill_uniform(float *dev, int64_t n, uint64_t seed, void *stream);
+int b2_fill_uniform_host(float *host, int64_t n, uint64_t seed);
+/* fill_vector (utils/utils.cu:15-19) on the device. */
+int b2_fill_const(float *dev, int64_t n, float value, void *stream);
+
+/* verify_matrix (utils/utils.cu:75-91): first element with |ref-got| > abs_tol fails.
+ * Device-side compare; returns 0 if all pass, 1 if any fail, <0 on error, and writes the
+ * max |ref-got| to *max_abs_host when non-NULL.  Synchronises the stream. */
+int b2_verify_matrix(const float *ref_dev, const float *got_dev, int64_t rows, int64_t cols,
+                     int64_t ld, float abs_tol, float *max_abs_host, void *stream);
+
+/* CUDA-event timer replacing saxpy_timer (utils/utils.cuh:56-77, host chrono). */
+typedef struct b2_timer_s *b2_timer;
+int b2_timer_create(b2_timer *out);
+int b2_timer_destroy(b2_timer t);
+int b2_timer_start(b2_timer t, void *stream);
+int b2_timer_stop(b2_timer t, void *stream);
+/* Synchronises on the stop event; milliseconds between start and stop. */
+int b2_timer_elapsed_ms(b2_timer t, float *ms_out);
+
+/* Register-only FFMA throughput microbenchmark: enqueues `launches` launches of a kernel
+ * that performs `ffma_per_thread` dependent-chain-free FMAs per thread on every SM and
+ * returns the total flop count (2 per FMA) in *flops_out.  Used to measure the FP32 SIMT
+ * peak that SGEMM's roofline fraction is quoted against. */
+int b2_ffma_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream);
+
+/* getDetails (utils/utils.cu:21-26): SM count and clock of the current device. */
+int b2_device_info(int *sm_count, int *sm_clock_khz, size_t *global_mem_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2BLAS_H */

@@ -1,0 +1,28 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (runs on the B200 box only)")
+
+
+@pytest.fixture(scope="session")
+def built_lib():
+    """Builds libb2blas.so if needed (nvcc cross-compiles without a GPU) and returns its path."""
+    from hpcdeepneuralnetworks_b200 import build
+    return build.build()
+
+
+@pytest.fixture(scope="session")
+def cuda(built_lib):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.cuda.set_device(0)
+    return torch.device("cuda:0")

@@ -1,0 +1,66 @@
+"""CPU tests of the C-ABI boundary: the library builds, loads, exports every symbol that
+include/b2blas.h declares, and validates arguments before touching the device."""
+import ctypes as C
+
+import pytest
+
+from hpcdeepneuralnetworks_b200 import _lib
+
+
+@pytest.fixture(scope="module")
+def L(built_lib):
+    return _lib.load()
+
+
+def test_exports_every_declared_symbol(L):
+    names = _lib.declared_symbols()
+    assert len(names) >= 28
+    for required in ("sgemm", "ft_sgemm", "saxpy", "sdot", "b2_sgemm", "b2_ft_sgemm", "b2_saxpy", "b2_sdot",
+                     "b2_sgemm_series", "ref_sgemm_rowmajor", "ref_sgemm_colmajor_nt"):
+        assert required in names
+    missing = [n for n in names if not hasattr(L, n)]
+    assert missing == []
+
+
+def test_status_strings(L):
+    assert L.b2_status_string(0) == b"ok"
+    for code in range(-6, 0):
+        assert L.b2_status_string(code) not in (b"ok", b"unknown status")
+    assert L.b2_status_string(-99) == b"unknown status"
+    assert L.b2_version() >= 100
+
+
+def test_argument_validation_needs_no_device(L):
+    null = C.c_void_p(None)
+    fake = C.c_void_p(0x1000)
+    assert L.b2_sgemm(null, 0, -1, 4, 4, 1.0, fake, 4, fake, 4, 0.0, fake, 4, null) == -1
+    assert b"negative" in L.b2_last_error()
+    assert L.b2_sgemm(null, 7, 4, 4, 4, 1.0, fake, 4, fake, 4, 0.0, fake, 4, null) == -1
+    assert L.b2_sgemm(null, 0, 4, 4, 4, 1.0, fake, 2, fake, 4, 0.0, fake, 4, null) == -1       # lda < K
+    assert L.b2_sgemm(null, 0, 4, 4, 4, 1.0, fake, 4, fake, 4, 0.0, fake, 3, null) == -1       # ldc < N
+    assert L.b2_sgemm(null, 0, 4, 4, 4, 1.0, null, 4, fake, 4, 0.0, fake, 4, null) == -1       # A NULL
+    assert L.b2_sgemm(null, 0, 0, 4, 4, 1.0, null, 4, null, 4, 0.0, null, 4, null) == 0        # empty: no-op
+    assert L.b2_saxpy(null, -5, 2.0, fake, fake, null) == -1
+    assert L.b2_saxpy(null, 0, 2.0, null, null, null) == 0
+    assert L.b2_saxpy(null, 4, 2.0, C.c_void_p(0x1001), fake, null) == -1                      # misaligned
+    assert L.b2_sdot(null, 4, fake, fake, null, null) == -1                                    # result NULL
+    assert L.b2_sgemm_series(0, 32, 256, fake, fake, fake, 1.0, 0.0, null) == -1
+    assert L.b2_sgemm_series(15, 32, 256, fake, fake, fake, 1.0, 0.0, null) == -1
+    assert L.b2_sgemm_series(9, 32, 200, fake, fake, fake, 1.0, 0.0, null) == -2               # 200 % 128 != 0
+    assert b"multiple of 128" in L.b2_last_error()
+    assert L.b2_set_ffma_variant(9) == -1
+    assert L.b2_timer_start(null, null) == -1
+
+
+def test_host_fill_matches_oracle(L):
+    import numpy as np
+    import oracle
+    buf = np.empty(1000, np.float32)
+    assert L.b2_fill_uniform_host(buf.ctypes.data_as(C.c_void_p), 1000, 42) == 0
+    assert np.array_equal(buf, oracle.fill_uniform(1000, 42))
+
+
+def test_workspace_query(L):
+    assert L.b2_sgemm_workspace_bytes(0, 1024, 1024, 1024) == 0
+    need = L.b2_sgemm_workspace_bytes(1, 1024, 1024, 1024)
+    assert need >= 4 * 1024 * 1024 * 4

@@ -1,0 +1,241 @@
+"""GPU parity of the SGEMM kernels against the CPU oracle, through the C ABI.
+
+FFMA path and every rung of the series: bit-exact against the fused oracle (one fmaf per k in
+ascending k) and within the north-star tolerance max|C-C_ref|/(|A|.|B|) <= 1e-5 of the double
+reference.  3xTF32 path: <= 2e-5."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL_FFMA = 1e-5     # north-star tolerance of the FP32 path
+TOL_3XTF32 = 2e-5   # and of the split-precision path
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def mats(M, N, K, beta=0.5):
+    a = oracle.fill_uniform(M * K, 1).reshape(M, K)
+    b = oracle.fill_uniform(K * N, 2).reshape(K, N)
+    c = np.zeros((M, N), np.float32) if beta == 0.0 else oracle.fill_uniform(M * N, 3).reshape(M, N)
+    return a, b, c
+
+
+def run_gpu(path, a, b, c, alpha, beta):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, K = a.shape
+    N = b.shape[1]
+    dc = dev(c)
+    b2.sgemm(M, N, K, alpha, dev(a), dev(b), beta, dc, path=path)
+    b2.check_status()
+    return dc.cpu().numpy()
+
+
+def test_config1_256_against_reference_cpu_gemm(cuda):
+    """BASELINE config 1: 256^3, alpha=1, beta=0, C zero-initialised, checked against the reference's
+    CPU row-major GEMM arithmetic (utils/utils.cu:93-103) with the reference's own verify_matrix rule
+    and with the north-star metric."""
+    a, b, c = mats(256, 256, 256, beta=0.0)
+    got = run_gpu(0, a, b, c, 1.0, 0.0)
+    ref = oracle.cpu_gemm(1.0, 0.0, a, b, c)
+    assert oracle.verify_matrix(ref, got)                       # |ref-got| <= 1e-2 everywhere
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.0, c)
+    assert oracle.gemm_error(got, c64, den) <= TOL_FFMA
+    assert np.array_equal(got, oracle.sgemm_fma(1.0, a, b, 0.0, c))
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("shape", [(128, 128, 32), (256, 384, 96), (512, 512, 512)])
+def test_ffma_variants_bit_exact(cuda, variant, shape):
+    import hpcdeepneuralnetworks_b200 as b2
+    b2.set_ffma_variant(variant)
+    try:
+        a, b, c = mats(*shape)
+        got = run_gpu(0, a, b, c, 1.0, 0.5)
+        assert np.array_equal(got, oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    finally:
+        b2.set_ffma_variant(2)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (2, 3, 4), (17, 13, 5), (127, 129, 31), (130, 260, 33), (64, 512, 1000),
+                                   (300, 100, 700), (1, 1024, 64), (1024, 4, 64), (129, 132, 4)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (1.0, 0.5), (-1.5, 1.0), (0.5, -1.5)])
+def test_ffma_odd_shapes(cuda, shape, alpha, beta):
+    M, N, K = shape
+    a, b, c = mats(M, N, K, beta=1.0)
+    got = run_gpu(0, a, b, c, alpha, beta)
+    assert np.array_equal(got, oracle.sgemm_fma(alpha, a, b, beta, c))
+    c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
+    assert oracle.gemm_error(got, c64, den) <= TOL_FFMA
+
+
+def test_ffma_beta_zero_does_not_read_c(cuda):
+    a, b, _ = mats(200, 136, 64)
+    c = np.full((200, 136), np.nan, np.float32)
+    got = run_gpu(0, a, b, c, 1.0, 0.0)
+    assert np.array_equal(got, oracle.sgemm_fma(1.0, a, b, 0.0, np.zeros_like(c)))
+
+
+def test_ffma_degenerate_k_and_alpha(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    c = oracle.fill_uniform(64 * 48, 3).reshape(64, 48)
+    dc = dev(c)
+    b2.sgemm(64, 48, 0, 1.0, None, None, 0.5, dc)           # K = 0: C = beta*C
+    assert np.array_equal(dc.cpu().numpy(), np.float32(0.5) * c)
+    a, b, _ = mats(64, 48, 32)
+    dc = dev(c)
+    b2.sgemm(64, 48, 32, 0.0, dev(a), dev(b), 0.0, dc)      # alpha = 0, beta = 0: zeros
+    assert not dc.cpu().numpy().any()
+    b2.sgemm(0, 48, 32, 1.0, dev(a), dev(b), 0.0, dc)       # empty: no-op
+
+
+def test_ffma_leading_dimensions_and_guards(cuda):
+    """Sub-matrix views (lda/ldb/ldc larger than the logical width); everything outside C's view is untouched."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K, lda, ldb, ldc = 150, 200, 70, 96, 256, 212
+    A = oracle.fill_uniform(M * lda, 1).reshape(M, lda)
+    B = oracle.fill_uniform(K * ldb, 2).reshape(K, ldb)
+    Cb = oracle.fill_uniform((M + 2) * ldc, 3).reshape(M + 2, ldc)
+    dC = dev(Cb)
+    b2.sgemm(M, N, K, 1.0, dev(A), dev(B), 0.5, dC[1:], lda=lda, ldb=ldb, ldc=ldc)
+    want = Cb.copy()
+    want[1:M + 1, :N] = oracle.sgemm_fma(1.0, A[:, :K], B[:, :N], 0.5, Cb[1:M + 1, :N])
+    assert np.array_equal(dC.cpu().numpy(), want)
+
+
+def test_ffma_unaligned_falls_back_to_generic_kernel(cuda):
+    """Leading dimensions that are not multiples of 4 floats and odd base offsets cannot be described to TMA."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 77, 91, 53
+    a, b, c = mats(M, N, K)
+    da = dev(np.concatenate([[0.0], a.ravel()]).astype(np.float32))[1:]      # 4-byte aligned only
+    dc = dev(c)
+    b2.sgemm(M, N, K, 1.0, da, dev(b), 0.5, dc)
+    assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+
+
+@pytest.mark.parametrize("kid,n,t", [(1, 96, 32), (1, 100, 16), (2, 128, 32), (2, 64, 16), (3, 128, 32), (4, 128, 32),
+                                     (5, 128, 32), (5, 64, 16), (6, 128, 32), (7, 128, 32), (8, 192, 32), (9, 256, 32),
+                                     (10, 256, 32), (11, 256, 32), (12, 384, 32), (13, 384, 32), (14, 384, 32)])
+def test_series_rungs_bit_exact(cuda, kid, n, t):
+    """sgemm_1 .. sgemm_14 with the reference's argument order (N, A, B, C, alpha, beta)."""
+    import hpcdeepneuralnetworks_b200 as b2
+    a, b, c = mats(n, n, n)
+    dc = dev(c)
+    b2.sgemm_series(kid, n, dev(a), dev(b), dc, 1.0, 0.5, threads_x=t)
+    got = dc.cpu().numpy()
+    assert np.array_equal(got, oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    assert oracle.verify_matrix(oracle.cpu_gemm(1.0, 0.5, a, b, c), got)
+
+
+def test_series_rejects_non_multiple(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    t = torch.zeros(200 * 200, device="cuda")
+    with pytest.raises(b2.B2Error) as e:
+        b2.sgemm_series(13, 200, t, t, t.clone(), 1.0, 0.0)
+    assert e.value.status == -2
+
+
+def test_reference_shaped_shims(cuda):
+    from hpcdeepneuralnetworks_b200 import _lib
+    import hpcdeepneuralnetworks_b200 as b2
+    L = _lib.load()
+    n = 256
+    a, b, c = mats(n, n, n)
+    da, db, dc = dev(a), dev(b), dev(c)
+    torch.cuda.synchronize()
+    p = lambda t: C.c_void_p(t.data_ptr())
+    assert L.ref_sgemm_rowmajor(n, p(da), p(db), p(dc), 1.0, 0.5) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    dc = dev(c)
+    torch.cuda.synchronize()
+    assert L.sgemm(n, n, n, 1.0, p(da), p(db), 0.5, p(dc)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    # column-major NT of kernel/ft_sgemm: A MxK (lda=M), B NxK (ldb=N), C MxN (ldc=M), beta = -1.5 as in its driver
+    for (M, N, K) in ((128, 128, 64), (200, 72, 96), (132, 260, 40)):
+        af = oracle.fill_uniform(M * K, 1)
+        bf = oracle.fill_uniform(N * K, 2)
+        cf = oracle.fill_uniform(M * N, 3)
+        dcf = dev(cf)
+        b2.sgemm_colmajor_nt(M, N, K, dev(af), dev(bf), dcf, 1.0, -1.5)
+        assert np.array_equal(dcf.cpu().numpy(), oracle.sgemm_colmajor_nt(M, N, K, 1.0, af, bf, -1.5, cf))
+
+
+@pytest.mark.parametrize("mn_major", [False, True])
+@pytest.mark.parametrize("shape", [(128, 256, 32), (128, 256, 64), (256, 512, 256), (1024, 1024, 1024), (130, 300, 70),
+                                   (17, 13, 5), (384, 128, 1000)])
+def test_3xtf32_path(cuda, mn_major, shape):
+    import hpcdeepneuralnetworks_b200 as b2
+    b2.set_tf32_b_layout(mn_major)
+    try:
+        M, N, K = shape
+        a, b, c = mats(M, N, K)
+        got = run_gpu(1, a, b, c, 1.0, 0.5)
+        c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+        err = oracle.gemm_error(got, c64, den)
+        assert err <= TOL_3XTF32, f"3xTF32 error {err:.3e} (B {'MN' if mn_major else 'K'}-major)"
+    finally:
+        b2.set_tf32_b_layout(False)
+
+
+def test_sweep_sizes_both_paths(cuda):
+    """BASELINE config 2 (alpha=1, beta=0.5) at a few sweep sizes, inputs generated on the device; checked on
+    sampled rows against the double reference."""
+    import hpcdeepneuralnetworks_b200 as b2
+    for n in (768, 2048):
+        A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+        B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+        C0 = b2.fill_uniform(torch.empty((n, n), device="cuda"), 3)
+        rows = np.array([0, 1, n // 2 - 1, n // 2, n - 1])
+        a, b, c0 = A.cpu().numpy(), B.cpu().numpy(), C0.cpu().numpy()
+        c64, den = oracle.sgemm_f64(1.0, a[rows], b, 0.5, c0[rows])
+        for path, tol in ((0, TOL_FFMA), (1, TOL_3XTF32)):
+            Cm = C0.clone()
+            b2.sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=path)
+            b2.check_status()
+            got = Cm.cpu().numpy()[rows]
+            assert oracle.gemm_error(got, c64, den) <= tol
+            if path == 0:
+                assert np.array_equal(got, oracle.sgemm_fma(1.0, a[rows], b, 0.5, c0[rows]))
+
+
+def test_full_size_6144_properties(cuda):
+    """6144^3 (the metric's size): linearity in alpha and agreement of the two math paths, plus sampled rows."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 6144
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    C1 = torch.zeros((n, n), device="cuda")
+    C2 = torch.zeros((n, n), device="cuda")
+    b2.sgemm(n, n, n, 1.0, A, B, 0.0, C1)
+    b2.sgemm(n, n, n, 2.0, A, B, 0.0, C2)
+    assert torch.equal(C2, 2.0 * C1)                          # scaling by 2 is exact
+    C3 = torch.zeros((n, n), device="cuda")
+    b2.sgemm(n, n, n, 1.0, A, B, 0.0, C3, path=1)
+    b2.check_status()
+    scale = n / 4.0                                           # E[(|A|.|B|)_ij] for uniform[-1,1]
+    assert float((C3 - C1).abs().max().item()) <= 3e-5 * scale
+    rows = np.array([5, 3071, 6143])
+    a, b = A[rows].cpu().numpy(), B.cpu().numpy()
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.0, np.zeros((3, n), np.float32))
+    assert oracle.gemm_error(C1[rows].cpu().numpy(), c64, den) <= TOL_FFMA
+    assert oracle.gemm_error(C3[rows].cpu().numpy(), c64, den) <= TOL_3XTF32
+
+
+def test_host_buffer_api(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 300, 260, 128
+    a, b, c = mats(M, N, K)
+    hs = b2.HostSgemm(M, N, K)
+    hs.hA.copy_(torch.from_numpy(a)); hs.hB.copy_(torch.from_numpy(b)); hs.hC.copy_(torch.from_numpy(c))
+    out = hs.run(1.0, 0.5).numpy()
+    assert np.array_equal(out, oracle.sgemm_fma(1.0, a, b, 0.5, c))

@@ -1,0 +1,152 @@
+"""GPU parity of SAXPY (bit-exact) and SDOT (1e-5 relative to sum|x*y|) against the CPU oracle,
+through the C ABI.  Covers empty, tiny, ragged and misaligned vectors and the harness fills."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 255, 1024, 4099, (1 << 20), (1 << 20) + 3, (1 << 24) + 1])
+def test_saxpy_bit_exact(cuda, n):
+    import hpcdeepneuralnetworks_b200 as b2
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    dx, dy = dev(x), dev(y)
+    b2.saxpy(n, 2.0, dx, dy)
+    assert np.array_equal(dy.cpu().numpy(), oracle.saxpy(2.0, x, y))
+    assert np.array_equal(dx.cpu().numpy(), x)
+
+
+@pytest.mark.parametrize("alpha", [0.0, 1.0, -1.5, 0.3333333])
+def test_saxpy_alpha_values_fused(cuda, alpha):
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 100003
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    dy = dev(y)
+    b2.saxpy(n, alpha, dev(x), dy)
+    assert np.array_equal(dy.cpu().numpy(), oracle.saxpy(alpha, x, y))   # one FMA per element
+
+
+@pytest.mark.parametrize("xoff,yoff", [(0, 0), (1, 1), (3, 3), (1, 0), (0, 2), (2, 3)])
+def test_saxpy_misaligned_views(cuda, xoff, yoff):
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 70001
+    xb, yb = oracle.fill_uniform(n + 8, 4), oracle.fill_uniform(n + 8, 5)
+    dxb, dyb = dev(xb), dev(yb)
+    b2.saxpy(n, 2.0, dxb[xoff:xoff + n], dyb[yoff:yoff + n])
+    want = yb.copy()
+    want[yoff:yoff + n] = oracle.saxpy(2.0, xb[xoff:xoff + n], yb[yoff:yoff + n])
+    assert np.array_equal(dyb.cpu().numpy(), want)          # guard elements either side untouched
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 1000, 4099, (1 << 20), (1 << 22) + 5, 1 << 26])
+def test_sdot_matches_oracle(cuda, n):
+    import hpcdeepneuralnetworks_b200 as b2
+    if n <= (1 << 22) + 5:
+        x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+        dx, dy = dev(x), dev(y)
+    else:   # generate on the device with the same hash, pull back for the oracle
+        dx = b2.fill_uniform(torch.empty(n, device="cuda"), 4)
+        dy = b2.fill_uniform(torch.empty(n, device="cuda"), 5)
+        x, y = dx.cpu().numpy(), dy.cpu().numpy()
+    out = torch.full((1,), 123.0, device="cuda")
+    b2.sdot(n, dx, dy, out)
+    want, scale = oracle.sdot(x, y)
+    got = float(out.item())
+    assert abs(got - want) <= 1e-5 * max(scale, 1e-30) + (0 if n else 1e-30)   # relative to sum|x*y|
+    if n:
+        assert abs(got - want) <= 1e-5 * abs(want) + 2e-7 * scale ** 0.5      # and tight against the value itself
+    # overwrites (does not accumulate) and is deterministic
+    b2.sdot(n, dx, dy, out)
+    assert float(out.item()) == got
+
+
+def test_sdot_misaligned(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 50001
+    xb, yb = oracle.fill_uniform(n + 4, 4), oracle.fill_uniform(n + 4, 5)
+    out = b2.sdot(n, dev(xb)[1:], dev(yb)[3:3 + n])
+    want, scale = oracle.sdot(xb[1:1 + n], yb[3:3 + n])
+    assert abs(float(out.item()) - want) <= 1e-5 * scale
+
+
+def test_sdot_partial_double(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    n = (1 << 21) + 17
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    out = torch.zeros(1, device="cuda")
+    p64 = torch.zeros(1, dtype=torch.float64, device="cuda")
+    b2.sdot_partial(n, dev(x), dev(y), out, p64)
+    want, scale = oracle.sdot(x, y)
+    assert abs(float(p64.item()) - want) <= 1e-6 * scale
+    assert float(out.item()) == np.float32(p64.item())
+
+
+def test_north_star_launchers_default_stream(cuda):
+    """`saxpy(n, alpha, x, y)` / `sdot(n, x, y, result)` exactly as declared (default stream, default handle)."""
+    from hpcdeepneuralnetworks_b200 import _lib
+    L = _lib.load()
+    n = 12345
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    dx, dy, out = dev(x), dev(y), torch.zeros(1, device="cuda")
+    torch.cuda.synchronize()
+    assert L.saxpy(n, 2.0, C.c_void_p(dx.data_ptr()), C.c_void_p(dy.data_ptr())) == 0
+    assert L.sdot(n, C.c_void_p(dx.data_ptr()), C.c_void_p(dy.data_ptr()), C.c_void_p(out.data_ptr())) == 0
+    torch.cuda.synchronize()
+    y2 = oracle.saxpy(2.0, x, y)
+    assert np.array_equal(dy.cpu().numpy(), y2)
+    want, scale = oracle.sdot(x, y2)
+    assert abs(float(out.item()) - want) <= 1e-5 * scale
+
+
+def test_device_fill_matches_host_hash(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    n = (1 << 20) + 7
+    t = b2.fill_uniform(torch.empty(n, device="cuda"), 9)
+    assert np.array_equal(t.cpu().numpy(), oracle.fill_uniform(n, 9))
+    c = b2.fill_const(torch.empty(1000, device="cuda"), 1.5)
+    assert bool((c == 1.5).all())
+
+
+def test_verify_matrix_and_timer(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    a = b2.fill_uniform(torch.empty((300, 200), device="cuda"), 1)
+    b = a.clone()
+    ok, mx = b2.verify_matrix(a, b)
+    assert ok and mx == 0.0
+    b[7, 9] += 0.02
+    ok, mx = b2.verify_matrix(a, b)
+    assert not ok and abs(mx - 0.02) < 1e-6
+    t = b2.EventTimer()
+    t.start()
+    b2.saxpy(a.numel(), 2.0, a.view(-1), b.view(-1))
+    t.stop()
+    assert t.elapsed_ms() > 0.0
+    info = b2.device_info()
+    assert info["sm_count"] > 0
+
+
+def test_large_vectors_properties(cuda):
+    """n = 2^28: full-size checks through size-independent properties (linearity, known sums)."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 1 << 28
+    x = b2.fill_uniform(torch.empty(n, device="cuda"), 4)
+    y = b2.fill_const(torch.empty(n, device="cuda"), 0.0)
+    b2.saxpy(n, 2.0, x, y)                      # y = 2x exactly
+    b2.saxpy(n, -2.0, x, y)                     # back to 0 exactly
+    assert float(y.abs().max().item()) == 0.0
+    ones = b2.fill_const(torch.empty(n, device="cuda"), 1.0)
+    half = b2.fill_const(torch.empty(n, device="cuda"), 0.5)
+    assert float(b2.sdot(n, ones, half).item()) == n * 0.5          # exactly representable
+    # sdot(x, 1) over chunks equals the sum of chunk dots (checksum of checksums)
+    whole = float(b2.sdot(n, x, ones).item())
+    parts = sum(float(b2.sdot(n // 4, x[i * (n // 4):], ones).item()) for i in range(4))
+    assert abs(whole - parts) <= 1e-5 * n / 2
