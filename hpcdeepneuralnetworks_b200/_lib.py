@@ -87,6 +87,7 @@ def load() -> C.CDLL:
     L.b2_timer_stop.argtypes = [vp, vp]
     L.b2_timer_elapsed_ms.argtypes = [vp, C.POINTER(f32)]
     L.b2_ffma_peak_probe.argtypes = [i32, i64, C.POINTER(C.c_double), vp]
+    L.b2_ffma2_peak_probe.argtypes = [i32, i64, C.POINTER(C.c_double), vp]
     L.b2_device_info.argtypes = [C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_size_t)]
     L.b2_check_status.argtypes = [vp, vp]
     L.b2_set_ffma_variant.argtypes = [i32]

@@ -250,15 +250,16 @@ class EventTimer:
             pass
 
 
-def ffma_peak_tflops(launches: int = 3, ffma_per_thread: int = 1 << 20) -> float:
+def ffma_peak_tflops(launches: int = 3, ffma_per_thread: int = 1 << 20, packed: bool = False) -> float:
     """Measured FP32 SIMT peak of the current device (register-only FMA stream), TFLOP/s."""
     L = _lib.load()
+    probe = L.b2_ffma2_peak_probe if packed else L.b2_ffma_peak_probe
     flops = C.c_double(0.0)
-    check(L.b2_ffma_peak_probe(1, ffma_per_thread, C.byref(flops), _stream()))  # warm-up
+    check(probe(1, ffma_per_thread, C.byref(flops), _stream()))  # warm-up
     torch.cuda.synchronize()
     t = EventTimer()
     t.start()
-    check(L.b2_ffma_peak_probe(launches, ffma_per_thread, C.byref(flops), _stream()))
+    check(probe(launches, ffma_per_thread, C.byref(flops), _stream()))
     t.stop()
     return flops.value / (t.elapsed_ms() * 1e-3) / 1e12
 

@@ -11,11 +11,16 @@
 //     swizzle; a thread reads a float4 ALONG K for each of its 8 rows, which costs the same
 //     number of 128-bit shared loads as the reference's transposed store scheme
 //     (kernel_9.cuh:37-40) and is bank-conflict free.
-//   * 8 warps as 4 (M) x 2 (N), lanes as 4 (M) x 8 (N): the warp tiling idea of
-//     kernel_11.cuh:22-27 with the lane shape chosen for the swizzled A reads.
-//   * Optionally the inner product uses the packed fma.rn.f32x2 instruction (two FP32
-//     FMAs per issue slot); per output the arithmetic is still one FMA per k in ascending k,
-//     so results are bit-identical to the scalar form.
+//   * 8 warps stacked along M, each spanning 16 rows x 128 columns, lanes as 4 (M) x 8 (N),
+//     4 x 16 outputs per thread: the warp tiling idea of kernel_11.cuh:22-27 with a shape
+//     chosen for the swizzled A reads and for the packed FMA below.
+//   * The inner product uses the packed fma.rn.f32x2 instruction (two FP32 FMAs per issue
+//     slot, pairs of adjacent columns).  The 4 A values a thread needs per k must sit in both
+//     halves of an operand; each warp writes them once per 8 k as (a,a) pairs into a private
+//     1 KB shared region, so the inner loop holds no register moves at all: per k it is
+//     32 packed FMAs, 4 + 2 128-bit shared loads, all fetched one k ahead.  Per output the
+//     arithmetic is still one FMA per k in ascending k, so results are bit-identical to the
+//     scalar form (kept as a variant).
 // Each output element is accumulated by exactly one thread in ascending k with one FMA per
 // k, and the epilogue is fma(alpha, acc, beta*c) (alpha*acc when beta == 0; C is then not
 // read).
@@ -28,7 +33,7 @@ namespace b2 {
 constexpr int FBM = 128, FBN = 128, FBK = 32, FSTAGES = 3;
 constexpr int kStageA = FBM * FBK * 4;  // 16 KB, 128 rows of 128 bytes, 128B-swizzled
 constexpr int kStageB = FBK * FBN * 4;  // 16 KB, 32 rows of 512 bytes, linear
-constexpr int kFfmaSmem = 1024 + FSTAGES * (kStageA + kStageB) + 128;
+constexpr int kFfmaSmem = 1024 + FSTAGES * (kStageA + kStageB) + 1024 + 8 * 1024;
 constexpr int kGroupM = 16;  // tile rasterisation: 16 tile-rows share their B panels in L2
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -44,6 +49,11 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
+__device__ __forceinline__ uint64_t ffma2v(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm volatile("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
 
 struct FfmaArgs {
   float *C;
@@ -53,54 +63,105 @@ struct FfmaArgs {
   int *status;  // device status word: set to B2_ERR_TIMEOUT if a bounded wait runs out
 };
 
-// Accumulators of one thread: 8 rows x 8 columns.  Row i is tile row  wm*32 + lm + 4*i,
-// column j is tile column  wn*64 + ln*4 + 32*(j/4) + j%4.
-template <bool PACKED>
+// Accumulators of one thread: 4 rows x 16 columns (a wide tile keeps the number of A values that
+// must be duplicated into both halves of a packed operand at 4 per k).  Row i is tile row
+// warp*16 + lm + 4*i (row-major A) or warp*16 + lm*4 + i (transposed A); column j is tile
+// column ln*4 + 32*(j/4) + j%4, so one warp spans all 128 columns of 16 rows.
+template <int PACKED>
 struct Acc;
 template <>
-struct Acc<false> {
-  float v[8][8];
+struct Acc<0> {
+  float v[4][16];
   __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
   }
-  __device__ __forceinline__ void step(const float (&a)[8], const float4 &b0, const float4 &b1) {
+  // aa: the thread's 4 A values, each duplicated (a,a); bb: 16 B values as 8 pairs
+  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
+    float a[4], b[16], dummy;
+    unpack2(aa[0].x, a[0], dummy);
+    unpack2(aa[0].y, a[1], dummy);
+    unpack2(aa[1].x, a[2], dummy);
+    unpack2(aa[1].y, a[3], dummy);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[i][0] = __fmaf_rn(a[i], b0.x, v[i][0]);
-      v[i][1] = __fmaf_rn(a[i], b0.y, v[i][1]);
-      v[i][2] = __fmaf_rn(a[i], b0.z, v[i][2]);
-      v[i][3] = __fmaf_rn(a[i], b0.w, v[i][3]);
-      v[i][4] = __fmaf_rn(a[i], b1.x, v[i][4]);
-      v[i][5] = __fmaf_rn(a[i], b1.y, v[i][5]);
-      v[i][6] = __fmaf_rn(a[i], b1.z, v[i][6]);
-      v[i][7] = __fmaf_rn(a[i], b1.w, v[i][7]);
+    for (int q = 0; q < 4; ++q) {
+      unpack2(bb[q].x, b[4 * q], b[4 * q + 1]);
+      unpack2(bb[q].y, b[4 * q + 2], b[4 * q + 3]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[i][j] = __fmaf_rn(a[i], b[j], v[i][j]);
   }
   __device__ __forceinline__ float get(int i, int j) const { return v[i][j]; }
   __device__ __forceinline__ void set(int i, int j, float x) { v[i][j] = x; }
 };
-template <>
-struct Acc<true> {
-  uint64_t v[8][4];  // pairs of adjacent columns
+struct AccPackedBase {
+  uint64_t v[4][8];  // pairs of adjacent columns
   __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[i][j] = 0ull;
+      for (int j = 0; j < 8; ++j) v[i][j] = 0ull;
   }
-  __device__ __forceinline__ void step(const float (&a)[8], const float4 &b0, const float4 &b1) {
-    const uint64_t bp0 = pack2(b0.x, b0.y), bp1 = pack2(b0.z, b0.w), bp2 = pack2(b1.x, b1.y), bp3 = pack2(b1.z, b1.w);
+  __device__ __forceinline__ float get(int i, int j) const {
+    float lo, hi;
+    unpack2(v[i][j >> 1], lo, hi);
+    return (j & 1) ? hi : lo;
+  }
+  __device__ __forceinline__ void set(int i, int j, float x) {
+    float lo, hi;
+    unpack2(v[i][j >> 1], lo, hi);
+    if (j & 1) hi = x; else lo = x;
+    v[i][j >> 1] = pack2(lo, hi);
+  }
+};
+template <>
+struct Acc<2> : AccPackedBase {
+  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
+    const uint64_t a[4] = {aa[0].x, aa[0].y, aa[1].x, aa[1].y};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint64_t aa = pack2(a[i], a[i]);
-      v[i][0] = ffma2(aa, bp0, v[i][0]);
-      v[i][1] = ffma2(aa, bp1, v[i][1]);
-      v[i][2] = ffma2(aa, bp2, v[i][2]);
-      v[i][3] = ffma2(aa, bp3, v[i][3]);
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        v[i][2 * q] = ffma2v(a[i], bb[q].x, v[i][2 * q]);
+        v[i][2 * q + 1] = ffma2v(a[i], bb[q].y, v[i][2 * q + 1]);
+      }
+  }
+};
+template <>
+struct Acc<3> : AccPackedBase {
+  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
+    const uint64_t a[4] = {aa[0].x, aa[0].y, aa[1].x, aa[1].y};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i][2 * q] = ffma2v(a[i], bb[q].x, v[i][2 * q]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i][2 * q + 1] = ffma2v(a[i], bb[q].y, v[i][2 * q + 1]);
     }
+  }
+};
+template <>
+struct Acc<1> {
+  uint64_t v[4][8];  // pairs of adjacent columns
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0ull;
+  }
+  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
+    const uint64_t a[4] = {aa[0].x, aa[0].y, aa[1].x, aa[1].y};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        v[i][2 * q] = ffma2(a[i], bb[q].x, v[i][2 * q]);
+        v[i][2 * q + 1] = ffma2(a[i], bb[q].y, v[i][2 * q + 1]);
+      }
   }
   __device__ __forceinline__ float get(int i, int j) const {
     float lo, hi;
@@ -124,27 +185,61 @@ __device__ __forceinline__ void tile_of_block(int bid, int tiles_m, int tiles_n,
   tn = r / gsz;
 }
 
-// Tile row of accumulator row i.  NN (A row-major, K contiguous): wm*32 + lm + 4*i, which makes
-// the swizzled float4-along-K reads conflict free.  TN (A given K x M, M contiguous, as in the
-// column-major family of kernel/ft_sgemm): wm*32 + lm*4 + (i&3) + 16*(i>>2), so that a thread
-// reads two float4 along M per k.
+// Tile row of accumulator row i of a thread (see Acc) and tile column of accumulator column j.
 template <bool TRANS_A>
-__device__ __forceinline__ int acc_row(int wm, int lm, int i) {
-  return TRANS_A ? (wm * 32 + lm * 4 + (i & 3) + 16 * (i >> 2)) : (wm * 32 + lm + 4 * i);
+__device__ __forceinline__ int acc_row(int warp, int lm, int i) {
+  return TRANS_A ? (warp * 16 + lm * 4 + i) : (warp * 16 + lm + 4 * i);
 }
+__device__ __forceinline__ int acc_col(int ln, int j) { return ln * 4 + 32 * (j >> 2) + (j & 3); }
 
-template <bool PACKED, int KCU, bool TRANS_A>
+// ---- ABFT additions (FT = true) ----------------------------------------------------------
+// Checksum algebra of kernel/ft_sgemm/README.md:4-14 per 128x128 output tile T = A_t * B_t:
+//   row checksum   T e   = A_t (B_t e)      one value per tile row
+//   col checksum   e^T T = (e^T A_t) B_t    one value per tile column
+// Encoding happens slab by slab inside the mainloop, on the shared-memory stage the FMAs are
+// about to consume (the reference encodes from the registers it prefetched,
+// kernel/ft_sgemm/include/ft_sgemm_tall.cuh:178-267):
+//   phase 1 (before the FMAs of the slab): warp w sums k-chunk w of the A slab over the 128
+//           rows and rows 4w..4w+3 of the B slab over the 128 columns -> 32 + 32 slab sums in
+//           shared memory, announced on a split-phase mbarrier;
+//   phase 2 (after the FMAs, when every warp's sums have long arrived): threads 0..127 add
+//           sum_k A[row][k] * Bsum[k] to their row checksum, threads 128..255 add
+//           Asum[k] * B[k][4 columns] for 8 k to their partial column checksums.
+// The epilogue compares the checksums with the row and column sums of the accumulators
+// (the reference does this every 256 of K, ft_sgemm_huge.cuh:143-271); a single row and a
+// single column out of tolerance locate the faulty accumulator, which is rebuilt as
+// row checksum - (sum of the other accumulators of that row).
+struct FtArgs {
+  const b2_fault *plan;
+  int n_faults;
+  float tau;
+  int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable
+};
+
+constexpr int kFtBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[3]
+constexpr int kFtSumOff = kFtBarOff + 128;                // float sAc[3][32], sBr[3][32]
+constexpr int kFtInjOff = kFtSumOff + 2 * FSTAGES * 32 * 4;  // int inj[8]
+constexpr int kDupOff = kFtBarOff + 1024;                 // 8 warps x 1 KB of duplicated A values
+
+template <int PACKED, bool TRANS_A, bool FT>
 __global__ void __launch_bounds__(256, 2)
-sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FfmaArgs p) {
+sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FfmaArgs p,
+                  const FtArgs ft) {
+  static_assert(!(FT && TRANS_A), "the ABFT encoder reads the row-major A stage");
   extern __shared__ unsigned char smem_raw[];
-  unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // round the dynamic shared window up to 1024 bytes without leaving the shared address space
+  unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char *sA = smem;
   unsigned char *sB = smem + FSTAGES * kStageA;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + FSTAGES * (kStageA + kStageB));
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + kFtBarOff);
   uint64_t *empty = full + FSTAGES;
+  uint64_t *sums_ready = empty + FSTAGES;
+  float *sAc = reinterpret_cast<float *>(smem + kFtSumOff);  // [stage][32] column sums of the A slab
+  float *sBr = sAc + FSTAGES * 32;                           // [stage][32] row sums of the B slab
+  int *inj = reinterpret_cast<int *>(smem + kFtInjOff);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wm = warp >> 1, wn = warp & 1, lm = lane >> 3, ln = lane & 7;
+  const int lm = lane >> 3, ln = lane & 7;
   const int tiles_m = (p.M + FBM - 1) / FBM, tiles_n = (p.N + FBN - 1) / FBN;
   int tile_m, tile_n;
   tile_of_block(blockIdx.x, tiles_m, tiles_n, tile_m, tile_n);
@@ -156,10 +251,28 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int s = 0; s < FSTAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 8);
+      if (FT) mbar_init(&sums_ready[s], 8);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+  }
+  if (FT && warp == 1) {
+    // first planned fault that names this tile (a plan holds at most one per tile)
+    int found = 0x7fffffff;
+    for (int f = lane; f < ft.n_faults; f += 32)
+      if (ft.plan[f].tile_m == tile_m && ft.plan[f].tile_n == tile_n && f < found) found = f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) found = min(found, __shfl_xor_sync(0xffffffffu, found, o));
+    if (lane == 0) {
+      inj[0] = (found != 0x7fffffff);
+      if (inj[0]) {
+        inj[1] = ft.plan[found].row;
+        inj[2] = ft.plan[found].col;
+        inj[3] = ft.plan[found].k_step;
+        inj[4] = ft.plan[found].bit;
+      }
+    }
   }
   __syncthreads();
   if (tid == 0) {
@@ -171,51 +284,169 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
 
+  // planned fault: which slab, and (for the owning thread only) which accumulator
+  int inj_kb = -1, inj_i = 0, inj_j = 0;
+  uint32_t inj_mask = 0;
+  if (FT && inj[0]) {
+    const int r = inj[1], c = inj[2];
+    const bool own = r >= 0 && r < FBM && c >= 0 && c < FBN && (r >> 4) == warp && (r & 3) == lm && ((c & 31) >> 2) == ln;
+    if (own) {
+      inj_kb = inj[3] < 0 ? 0 : (inj[3] >= nkb ? nkb - 1 : inj[3]);
+      inj_i = (r & 15) >> 2;
+      inj_j = (c >> 5) * 4 + (c & 3);
+      inj_mask = 1u << (inj[4] & 31);
+    }
+  }
+
   Acc<PACKED> acc;
   acc.zero();
-  // Byte offsets inside a stage.  A: row r at r*128, 16-byte chunk c of that row at
-  // ((c ^ (r & 7)) << 4); rows of this thread are wm*32 + lm + 4*i, so r & 7 is lm for even
-  // i and lm + 4 for odd i.  B: row k at k*512, column c at c*4.
-  const uint32_t a_thread = TRANS_A ? (uint32_t)(wm * 32 + lm * 4) * 4u : (uint32_t)(wm * 32 + lm) * 128u;
-  const uint32_t a_swz = (uint32_t)lm << 4;
-  const uint32_t b_thread = (uint32_t)(wn * 64 + ln * 4) * 4u;
+  float chk[4] = {0.f, 0.f, 0.f, 0.f};  // FT: [0] = row checksum (tid < 128) or 4 partial column checksums
+  // The packed FMA wants each A value in both halves of a 64-bit operand.  Instead of two
+  // register moves per value per thread, every warp re-writes the A values of its own 16 rows,
+  // 8 k at a time, into a private 1 KB region as (a,a) pairs; a thread then reads its 4 rows of
+  // one k as 32 contiguous bytes.  Slot of tile row r inside a k-row of that region:
+  // (r & 3) * 4 + (r >> 2) for row-major A (thread rows are lm + 4*i), r itself for transposed A.
+  unsigned char *D = smem + kDupOff + warp * 1024;
+  uint32_t dup_src, dup_dst;  // per-lane source (inside an A stage, chunk 0) and destination offsets
+  if (TRANS_A) {
+    const int ck = lane >> 2, rq = lane & 3;
+    dup_src = (uint32_t)ck * 512u + (uint32_t)(warp * 16 + rq * 4) * 4u;  // + chunk * 8 * 512
+    dup_dst = (uint32_t)(ck * 16 + rq * 4) * 8u;                           // 4 rows: + e * 8
+  } else {
+    const int crow = lane & 15, ckh = lane >> 4;
+    dup_src = (uint32_t)(warp * 16 + crow) * 128u;                         // + ((2*chunk + ckh) ^ (crow & 7)) << 4
+    dup_dst = (uint32_t)((ckh * 4) * 16 + (crow & 3) * 4 + (crow >> 2)) * 8u;  // 4 k: + e * 128
+  }
+  const uint32_t dup_swz = (uint32_t)(lane & 7), dup_kh = (uint32_t)(lane >> 4);
+  const unsigned char *Dr = D + lm * 32;           // this thread's 4 duplicated A values of k: + (k & 7) * 128
+  const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;  // B: row k at k*512, this thread's columns at ln*16 + q*128
   bool ok = true;
 
   for (int kb = 0; kb < nkb; ++kb) {
     const int s = kb % FSTAGES;
-    if (!mbar_wait(&full[s], (uint32_t)(kb / FSTAGES) & 1u)) {
+    const uint32_t parity = (uint32_t)(kb / FSTAGES) & 1u;
+    if (!mbar_wait(&full[s], parity)) {
       ok = false;
       break;
     }
-    const unsigned char *As = sA + s * kStageA + a_thread;
-    const unsigned char *Bs = sB + s * kStageB + b_thread;
-    if (TRANS_A) {
-#pragma unroll(KCU * 4)
-      for (int k = 0; k < FBK; ++k) {
-        const float4 a0 = *reinterpret_cast<const float4 *>(As + k * 512);
-        const float4 a1 = *reinterpret_cast<const float4 *>(As + k * 512 + 64);
-        const float4 b0 = *reinterpret_cast<const float4 *>(Bs + k * 512);
-        const float4 b1 = *reinterpret_cast<const float4 *>(Bs + k * 512 + 128);
-        const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-        acc.step(a, b0, b1);
+    const unsigned char *Ast = sA + s * kStageA;
+    const unsigned char *Bst = sB + s * kStageB;
+    if (FT) {
+      // ---- phase 1: slab sums ----
+      float4 pa = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4 *>(Ast + (lane + 32 * q) * 128 + ((warp ^ (lane & 7)) << 4));
+        pa.x += v.x; pa.y += v.y; pa.z += v.z; pa.w += v.w;
       }
-    } else {
-#pragma unroll(KCU)
-      for (int kc = 0; kc < FBK / 4; ++kc) {
-        const uint32_t y0 = ((uint32_t)kc << 4) ^ a_swz, y1 = y0 ^ 64u;
-        float4 a4[8];
+      // 4 components x 32 lanes -> 4 totals: halve the live components while folding lanes
+      const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
+      float k0 = h16 ? pa.z : pa.x, k1 = h16 ? pa.w : pa.y;
+      k0 += __shfl_xor_sync(0xffffffffu, h16 ? pa.x : pa.z, 16);
+      k1 += __shfl_xor_sync(0xffffffffu, h16 ? pa.y : pa.w, 16);
+      float ka = h8 ? k1 : k0;
+      ka += __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
+      ka += __shfl_xor_sync(0xffffffffu, ka, 4);
+      ka += __shfl_xor_sync(0xffffffffu, ka, 2);
+      ka += __shfl_xor_sync(0xffffffffu, ka, 1);
+      if ((lane & 7) == 0) sAc[s * 32 + warp * 4 + (h16 ? 2 : 0) + (h8 ? 1 : 0)] = ka;
+      const int kr = warp * 4 + (lane >> 3);
+      float sb = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          a4[i] = *reinterpret_cast<const float4 *>(As + ((i & 1) ? y1 : y0) + i * 512);
+      for (int q = 0; q < 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4 *>(Bst + kr * 512 + ((lane & 7) + 8 * q) * 16);
+        sb += (v.x + v.y) + (v.z + v.w);
+      }
+      sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+      sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+      sb += __shfl_xor_sync(0xffffffffu, sb, 4);
+      if ((lane & 7) == 0) sBr[s * 32 + kr] = sb;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sums_ready[s]);
+    }
+    const unsigned char *Bs = Bst + b_thread;
+    auto load_raw = [&](int chunk) -> float4 {
+      if (TRANS_A) return *reinterpret_cast<const float4 *>(Ast + dup_src + chunk * (8 * 512));
+      return *reinterpret_cast<const float4 *>(Ast + dup_src + ((((uint32_t)(2 * chunk) + dup_kh) ^ dup_swz) << 4));
+    };
+    auto store_dup = [&](const float4 &r) {
+      constexpr int step = TRANS_A ? 8 : 128;
+      *reinterpret_cast<float2 *>(D + dup_dst + 0 * step) = make_float2(r.x, r.x);
+      *reinterpret_cast<float2 *>(D + dup_dst + 1 * step) = make_float2(r.y, r.y);
+      *reinterpret_cast<float2 *>(D + dup_dst + 2 * step) = make_float2(r.z, r.z);
+      *reinterpret_cast<float2 *>(D + dup_dst + 3 * step) = make_float2(r.w, r.w);
+    };
+    float4 raw = load_raw(0);
+    __syncwarp();  // the last reads of the previous slab's pairs are done
+    store_dup(raw);
+    __syncwarp();
+    ulonglong2 a_cur[2], b_cur[4];
+    a_cur[0] = *reinterpret_cast<const ulonglong2 *>(Dr);
+    a_cur[1] = *reinterpret_cast<const ulonglong2 *>(Dr + 16);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const float4 b0 = *reinterpret_cast<const float4 *>(Bs + (kc * 4 + kk) * 512);
-          const float4 b1 = *reinterpret_cast<const float4 *>(Bs + (kc * 4 + kk) * 512 + 128);
-          float a[8];
+    for (int q = 0; q < 4; ++q) b_cur[q] = *reinterpret_cast<const ulonglong2 *>(Bs + q * 128);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) a[i] = (kk == 0) ? a4[i].x : (kk == 1) ? a4[i].y : (kk == 2) ? a4[i].z : a4[i].w;
-          acc.step(a, b0, b1);
+    for (int k = 0; k < FBK; ++k) {
+      ulonglong2 a_nxt[2], b_nxt[4];
+      if ((k & 7) == 3 && k + 5 < FBK) raw = load_raw((k >> 3) + 1);
+      if (k + 1 < FBK) {
+        if (((k + 1) & 7) == 0) {
+          __syncwarp();
+          store_dup(raw);
+          __syncwarp();
         }
+        a_nxt[0] = *reinterpret_cast<const ulonglong2 *>(Dr + ((k + 1) & 7) * 128);
+        a_nxt[1] = *reinterpret_cast<const ulonglong2 *>(Dr + ((k + 1) & 7) * 128 + 16);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) b_nxt[q] = *reinterpret_cast<const ulonglong2 *>(Bs + (k + 1) * 512 + q * 128);
+      }
+      acc.step(a_cur, b_cur);
+      if (k + 1 < FBK) {
+        a_cur[0] = a_nxt[0];
+        a_cur[1] = a_nxt[1];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) b_cur[q] = b_nxt[q];
+      }
+    }
+    if (FT) {
+      // ---- phase 2: fold the slab sums into the running checksums ----
+      if (!mbar_wait(&sums_ready[s], parity)) {
+        ok = false;
+        break;
+      }
+      if (warp < 4) {
+        const unsigned char *Arow = Ast + tid * 128;
+        const int sw = tid & 7;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float4 a = *reinterpret_cast<const float4 *>(Arow + ((c ^ sw) << 4));
+          const float4 b = *reinterpret_cast<const float4 *>(&sBr[s * 32 + c * 4]);
+          chk[0] = __fmaf_rn(a.x, b.x, chk[0]);
+          chk[0] = __fmaf_rn(a.y, b.y, chk[0]);
+          chk[0] = __fmaf_rn(a.z, b.z, chk[0]);
+          chk[0] = __fmaf_rn(a.w, b.w, chk[0]);
+        }
+      } else {
+        const int j = tid - 128, cg = j & 31, kg = j >> 5;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const int k = kg * 8 + kk;
+          const float4 b = *reinterpret_cast<const float4 *>(Bst + k * 512 + cg * 16);
+          const float ac = sAc[s * 32 + k];
+          chk[0] = __fmaf_rn(ac, b.x, chk[0]);
+          chk[1] = __fmaf_rn(ac, b.y, chk[1]);
+          chk[2] = __fmaf_rn(ac, b.z, chk[2]);
+          chk[3] = __fmaf_rn(ac, b.w, chk[3]);
+        }
+      }
+      // ---- simulated soft error: flip one bit of one accumulator after this slab ----
+      if (kb == inj_kb) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (i == inj_i && j == inj_j) acc.set(i, j, __uint_as_float(__float_as_uint(acc.get(i, j)) ^ inj_mask));
+        atomicAdd(&ft.report[1], 1);
       }
     }
     __syncwarp();
@@ -242,21 +473,128 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     return;
   }
 
-  // Epilogue straight from registers.
+  if (FT) {
+    // ---- verify, locate, correct (raw accumulators, before alpha/beta) ----
+    __syncthreads();  // every stage has been consumed by every warp: the ring is scratch now
+    float *scr = reinterpret_cast<float *>(sA);
+    float *rowsum_s = scr;            // [128]     row sums (a warp spans all columns of its rows)
+    float *colsum_s = scr + 128;      // [8][128]  partial column sums, one per warp
+    float *rowchk_s = scr + 1152;     // [128]
+    float *colchk_s = scr + 1280;     // [4][128]  partial column checksums, one per k-group
+    float *fix_part = scr + 1792;     // [8]
+    int *flags = reinterpret_cast<int *>(scr + 1800);  // nbad_r, nbad_c, bad_r, bad_c
+    float rs[4], cs[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) rs[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) cs[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float v = acc.get(i, j);
+        rs[i] += v;
+        cs[j] += v;
+      }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 1);
+      rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 2);
+      rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 4);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 8);
+      cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 16);
+    }
+    if (ln == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rowsum_s[acc_row<TRANS_A>(warp, lm, i)] = rs[i];
+    }
+    if (lm == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) colsum_s[warp * 128 + acc_col(ln, j)] = cs[j];
+    }
+    if (warp < 4) {
+      rowchk_s[tid] = chk[0];
+    } else {
+      const int j = tid - 128, cg = j & 31, kg = j >> 5;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) colchk_s[kg * 128 + cg * 4 + e] = chk[e];
+    }
+    if (tid < 4) flags[tid] = 0;
+    __syncthreads();
+    {
+      float actual, expect;
+      if (tid < 128) {
+        actual = rowsum_s[tid];
+        expect = rowchk_s[tid];
+      } else {
+        const int c = tid - 128;
+        actual = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) actual += colsum_s[w * 128 + c];
+        expect = (colchk_s[c] + colchk_s[128 + c]) + (colchk_s[256 + c] + colchk_s[384 + c]);
+      }
+      if (!(fabsf(actual - expect) <= ft.tau)) {  // NaN-safe: a NaN difference counts as out of tolerance
+        atomicAdd(&flags[tid < 128 ? 0 : 1], 1);
+        flags[tid < 128 ? 2 : 3] = tid & 127;
+      }
+    }
+    __syncthreads();
+    const int nbad_r = flags[0], nbad_c = flags[1];
+    if (nbad_r | nbad_c) {  // uniform over the block
+      if (nbad_r == 1 && nbad_c == 1) {
+        const int br = flags[2], bc = flags[3];
+        const bool own_row = (br >> 4) == warp && (br & 3) == lm;
+        const int bi = (br & 15) >> 2;
+        const bool own_col = own_row && ((bc & 31) >> 2) == ln;
+        const int bj = (bc >> 5) * 4 + (bc & 3);
+        if (own_row) {
+          float part = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (i == bi && !(own_col && j == bj)) part += acc.get(i, j);
+          fix_part[ln] = part;
+        }
+        __syncthreads();
+        if (own_col) {
+          float others = 0.f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) others += fix_part[q];
+          const float rebuilt = rowchk_s[br] - others;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (i == bi && j == bj) acc.set(i, j, rebuilt);
+          atomicAdd(&ft.report[2], 1);
+          atomicAdd(&ft.report[3], 1);
+        }
+      } else if (tid == 0) {
+        if (nbad_r >= 1 && nbad_c >= 1) atomicAdd(&ft.report[2], 1);
+        atomicAdd(&ft.report[4], 1);
+      }
+    }
+    if (tid == 0) atomicAdd(&ft.report[0], 1);
+  }
+
+  // Epilogue straight from registers: per row, 8 lanes x 16 bytes = 128 contiguous bytes per store.
   const bool read_c = (p.beta != 0.f);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int row = m0 + acc_row<TRANS_A>(wm, lm, i);
+  for (int i = 0; i < 4; ++i) {
+    const int row = m0 + acc_row<TRANS_A>(warp, lm, i);
     if (row >= p.M) continue;
     float *crow = p.C + (size_t)row * p.ldc;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int col = n0 + wn * 64 + ln * 4 + 32 * h;
+    for (int h = 0; h < 4; ++h) {
+      const int col = n0 + ln * 4 + 32 * h;
       if (p.vec_c && col + 3 < p.N) {
-        float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (read_c) c = *reinterpret_cast<const float4 *>(crow + col);
         float4 o;
         if (read_c) {
+          const float4 c = *reinterpret_cast<const float4 *>(crow + col);
           o.x = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 0), __fmul_rn(p.beta, c.x));
           o.y = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 1), __fmul_rn(p.beta, c.y));
           o.z = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 2), __fmul_rn(p.beta, c.z));
@@ -336,29 +674,40 @@ static int g_ffma_variant = -1;  // -1: pick from B2_FFMA_VARIANT (default packe
 static int ffma_variant() {
   if (g_ffma_variant < 0) {
     const char *e = getenv("B2_FFMA_VARIANT");
-    g_ffma_variant = e ? atoi(e) : 2;
-    if (g_ffma_variant < 0 || g_ffma_variant > 3) g_ffma_variant = 2;
+    g_ffma_variant = e ? atoi(e) : 1;
+    if (g_ffma_variant < 0 || g_ffma_variant > 3) g_ffma_variant = 1;
   }
   return g_ffma_variant;
 }
 
-template <bool PACKED, int KCU, bool TRANS_A>
-static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s) {
+template <int PACKED, bool TRANS_A, bool FT = false>
+static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s,
+                       const FtArgs &ft = FtArgs{nullptr, 0, 0.f, nullptr}) {
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, KCU, TRANS_A>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfmaSmem));
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, KCU, TRANS_A>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, TRANS_A, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfmaSmem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, TRANS_A, FT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     configured = true;
   }
-  sgemm_ffma_kernel<PACKED, KCU, TRANS_A><<<grid, 256, kFfmaSmem, s>>>(ta, tb, args);
+  sgemm_ffma_kernel<PACKED, TRANS_A, FT><<<grid, 256, kFfmaSmem, s>>>(ta, tb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
+
+int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
+                           const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
 
 // trans_a = 0: A is M x K row-major (lda >= K).  trans_a = 1: A is given as K x M row-major
 // (lda >= M), i.e. the column-major M x K operand of the kernel/ft_sgemm family.
 int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                         const float *B, int ldb, float beta, float *C, int ldc, cudaStream_t s) {
+  return sgemm_ffma_dispatch_ft(ctx, trans_a, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, nullptr, s);
+}
+
+// ft == nullptr: plain SGEMM.  Otherwise the ABFT kernel (row-major A only; operands must be
+// describable to TMA, i.e. 16-byte aligned with leading dimensions that are multiples of 4).
+int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
+                           const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s) {
   if (M == 0 || N == 0) return B2_OK;
   if (K == 0 || alpha == 0.f) {
     if (beta == 1.f) return B2_OK;
@@ -368,6 +717,10 @@ int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float al
   }
   const bool tma_ok = ((((uintptr_t)A | (uintptr_t)B) & 15) == 0) && (lda % 4 == 0) && (ldb % 4 == 0);
   (void)trans_a;
+  if (ft) {
+    B2_REQUIRE(tma_ok && !trans_a, B2_ERR_UNSUPPORTED,
+               "ft_sgemm: A and B must be 16-byte aligned with lda, ldb multiples of 4 (lda=%d ldb=%d)", lda, ldb);
+  }
   if (!tma_ok) {
     dim3 grid((N + 63) / 64, (M + 63) / 64);
     sgemm_generic_kernel<<<grid, 256, 0, s>>>(M, N, K, alpha, A, trans_a ? 1 : lda, trans_a ? lda : 1, B, ldb, beta, C, ldc);
@@ -385,15 +738,14 @@ int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float al
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
   const int grid = ((M + FBM - 1) / FBM) * ((N + FBN - 1) / FBN);
-  if (trans_a) {
-    return (ffma_variant() & 1) ? launch_ffma<true, 2, true>(ta, tb, args, grid, s)
-                                : launch_ffma<false, 2, true>(ta, tb, args, grid, s);
-  }
+  const bool packed = ffma_variant() != 0;
+  if (ft) return launch_ffma<1, false, true>(ta, tb, args, grid, s, *ft);
+  if (trans_a) return packed ? launch_ffma<1, true>(ta, tb, args, grid, s) : launch_ffma<0, true>(ta, tb, args, grid, s);
   switch (ffma_variant()) {
-    case 0: return launch_ffma<false, 8, false>(ta, tb, args, grid, s);
-    case 2: return launch_ffma<true, 2, false>(ta, tb, args, grid, s);
-    case 3: return launch_ffma<false, 2, false>(ta, tb, args, grid, s);
-    default: return launch_ffma<true, 8, false>(ta, tb, args, grid, s);
+    case 0: return launch_ffma<0, false>(ta, tb, args, grid, s);
+    case 2: return launch_ffma<2, false>(ta, tb, args, grid, s);
+    case 3: return launch_ffma<3, false>(ta, tb, args, grid, s);
+    default: return launch_ffma<1, false>(ta, tb, args, grid, s);
   }
 }
 
@@ -407,6 +759,37 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
 }
 
 extern "C" {
+
+int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
+                float beta, float *C, int ldc, const b2_fault *plan_dev, int n_faults, float tau, b2_ft_report *report_dev,
+                void *stream) {
+  B2_REQUIRE(path == B2_PATH_FFMA || path == B2_PATH_3XTF32, B2_ERR_INVALID_ARG, "b2_ft_sgemm: unknown path %d", path);
+  B2_REQUIRE(M >= 0 && N >= 0 && K >= 0, B2_ERR_INVALID_ARG, "b2_ft_sgemm: negative dimension (M=%d N=%d K=%d)", M, N, K);
+  B2_REQUIRE(n_faults >= 0 && (n_faults == 0 || plan_dev != nullptr), B2_ERR_INVALID_ARG, "b2_ft_sgemm: bad fault plan");
+  if (M == 0 || N == 0) return B2_OK;
+  B2_REQUIRE(C != nullptr, B2_ERR_INVALID_ARG, "b2_ft_sgemm: C is NULL");
+  B2_REQUIRE(ldc >= N, B2_ERR_INVALID_ARG, "b2_ft_sgemm: ldc = %d < N = %d", ldc, N);
+  if (K > 0) {
+    B2_REQUIRE(A != nullptr && B != nullptr, B2_ERR_INVALID_ARG, "b2_ft_sgemm: A or B is NULL");
+    B2_REQUIRE(lda >= K, B2_ERR_INVALID_ARG, "b2_ft_sgemm: lda = %d < K = %d", lda, K);
+    B2_REQUIRE(ldb >= N, B2_ERR_INVALID_ARG, "b2_ft_sgemm: ldb = %d < N = %d", ldb, N);
+  }
+  B2_REQUIRE(path == B2_PATH_FFMA, B2_ERR_UNSUPPORTED, "b2_ft_sgemm: ABFT is built on the FFMA path only");
+  Context *ctx = h ? (Context *)h : default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ft_sgemm: no context (%s)", b2_last_error());
+  FtArgs ft;
+  ft.plan = plan_dev;
+  ft.n_faults = n_faults;
+  // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the
+  // rounding noise between the two ways the checksums are summed
+  ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
+  ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
+  return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
+}
+
+int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C) {
+  return b2_ft_sgemm(nullptr, B2_PATH_FFMA, M, N, K, alpha, A, K, B, N, beta, C, N, nullptr, 0, 0.f, nullptr, nullptr);
+}
 
 // Selects the inner-loop variant of the FFMA kernel (0 scalar FFMA, 1 packed f32x2, 2/3 the
 // same with a shorter unrolled body).  For benchmarking; results are bit-identical.

@@ -217,6 +217,97 @@ __global__ void __launch_bounds__(256) ffma_probe_kernel(int64_t iters, float a,
   if (s == 123.456f) *sink = s;  // keeps the chains alive; practically never true
 }
 
+// The same stream with the packed fma.rn.f32x2 instruction: 8 independent 2-wide chains.
+__global__ void __launch_bounds__(256) ffma2_probe_kernel(int64_t iters, float a, float b, float *sink) {
+  uint64_t acc[8], av, bv;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(av) : "f"(a));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(bv) : "f"(b));
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x = (float)(threadIdx.x + i);
+    asm("mov.b64 %0, {%1, %1};" : "=l"(acc[i]) : "f"(x));
+  }
+  for (int64_t it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(acc[i]) : "l"(av), "l"(bv));
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[i]));
+    s += lo + hi;
+  }
+  if (s == 123.456f) *sink = s;
+}
+
+// Outer-product shaped FMA stream (4 x 16 accumulators from 4 + 16 operand registers, no memory
+// traffic): the register-operand pattern of the SGEMM inner loop, scalar or packed.
+template <bool PACKED>
+__global__ void __launch_bounds__(256, 2) ffma_outer_probe_kernel(int64_t iters, float seed, float *sink) {
+  float total = 0.f;
+  if (PACKED) {
+    uint64_t acc[4][8], a[4], b[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float x = seed * (float)(i + 1 + threadIdx.x);
+      asm("mov.b64 %0, {%1, %1};" : "=l"(a[i]) : "f"(x));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float x = seed * (float)(j + 3), y = seed * (float)(j + 5);
+      asm("mov.b64 %0, {%1, %2};" : "=l"(b[j]) : "f"(x), "f"(y));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
+    for (int64_t it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[i][j]) : "l"(a[i]), "l"(b[j]));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float lo, hi;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[i][j]));
+        total += lo + hi;
+      }
+  } else {
+    float acc[4][16], a[4], b[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = seed * (float)(i + 1 + threadIdx.x);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) b[j] = seed * (float)(j + 3);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[i][j] = 0.f;
+    for (int64_t it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) total += acc[i][j];
+  }
+  if (total == 123.456f) *sink = total;
+}
+
 static int vec_grid(Context *ctx, int64_t work_items, int per_block) {
   int64_t need = (work_items + per_block - 1) / per_block;
   int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 blocks of 256 threads fill an SM
@@ -324,14 +415,41 @@ int b2_verify_matrix(const float *ref_dev, const float *got_dev, int64_t rows, i
   return hostv[0] ? 1 : 0;
 }
 
+static int ffma_probe(bool packed, int launches, int64_t ffma_per_thread, double *flops_out, void *stream);
+
 int b2_ffma_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
+  return ffma_probe(false, launches, ffma_per_thread, flops_out, stream);
+}
+int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
+  return ffma_probe(true, launches, ffma_per_thread, flops_out, stream);
+}
+// experiment entry (not part of the public header): outer-product operand pattern
+int b2_ffma_outer_probe(int packed, int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
+  Context *ctx = default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "no context");
+  const int64_t iters = (ffma_per_thread + 255) / 256;
+  const int grid = ctx->sm_count * 2;
+  float *sink = (float *)((char *)ctx->fixed + kFixedVerify + 64);
+  for (int l = 0; l < launches; ++l) {
+    if (packed) ffma_outer_probe_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.001f, sink);
+    else ffma_outer_probe_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.001f, sink);
+  }
+  B2_CUDA(cudaGetLastError());
+  if (flops_out) *flops_out = 2.0 * (double)launches * (double)grid * 256.0 * (double)iters * 256.0;
+  return B2_OK;
+}
+
+static int ffma_probe(bool packed, int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
   Context *ctx = default_context();
   B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ffma_peak_probe: no context");
   B2_REQUIRE(launches > 0 && ffma_per_thread > 0, B2_ERR_INVALID_ARG, "b2_ffma_peak_probe: bad arguments");
   const int64_t iters = (ffma_per_thread + 127) / 128;
   const int grid = ctx->sm_count * 8;
   float *sink = (float *)((char *)ctx->fixed + kFixedVerify + 64);
-  for (int l = 0; l < launches; ++l) ffma_probe_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.999f, 0.001f, sink);
+  for (int l = 0; l < launches; ++l) {
+    if (packed) ffma2_probe_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.999f, 0.001f, sink);
+    else ffma_probe_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.999f, 0.001f, sink);
+  }
   B2_CUDA(cudaGetLastError());
   if (flops_out) *flops_out = 2.0 * (double)launches * (double)grid * 256.0 * (double)iters * 128.0;
   return B2_OK;

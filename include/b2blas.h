@@ -168,6 +168,16 @@ int b2_timer_elapsed_ms(b2_timer t, float *ms_out);
  * returns the total flop count (2 per FMA) in *flops_out.  Used to measure the FP32 SIMT
  * peak that SGEMM's roofline fraction is quoted against. */
 int b2_ffma_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream);
+/* The same probe issued as packed fma.rn.f32x2 (two FMAs per instruction). */
+int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream);
+/* Inner-loop variant of the FFMA SGEMM kernel (0 scalar FFMA, 1/2 packed f32x2, 3 scalar with a
+ * short unrolled body); results are bit-identical, used for benchmarking only. */
+int b2_set_ffma_variant(int v);
+/* 3xTF32 path: 0 = B planes written transposed (N x K) and fed K-major, 1 = planes as is, MN-major. */
+int b2_set_tf32_b_layout(int mn_major);
+/* Reads and clears the device status word that bounded waits set; synchronises the stream.
+ * Returns 0 or the recorded negative status. */
+int b2_check_status(b2_handle h, void *stream);
 
 /* getDetails (utils/utils.cu:21-26): SM count and clock of the current device. */
 int b2_device_info(int *sm_count, int *sm_clock_khz, size_t *global_mem_bytes);

@@ -1,0 +1,188 @@
+"""GPU tests of the ABFT SGEMM: clean runs are bit-identical to the plain kernel with zero false
+positives; every injected single fault above the threshold is detected, located and corrected so
+that the result meets the north-star tolerance; sub-threshold flips are benign by construction."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def mats(M, N, K):
+    a = oracle.fill_uniform(M * K, 1).reshape(M, K)
+    b = oracle.fill_uniform(K * N, 2).reshape(K, N)
+    c = oracle.fill_uniform(M * N, 3).reshape(M, N)
+    return a, b, c
+
+
+def default_tau(K):
+    return max(2e-6 * K, 4e-5)
+
+
+def classify(a, b, plan, tau):
+    """Per planned fault: |faulty - clean| of the final accumulator, from the exact CPU walk."""
+    must, gray, benign = 0, 0, 0
+    for f in plan:
+        clean, bad, ok = oracle.fault_effect(a, b, f)
+        assert ok
+        d = abs(np.float64(bad) - np.float64(clean))
+        if not np.isfinite(d) or d > 2 * tau:
+            must += 1
+        elif d < 0.5 * tau:
+            benign += 1
+        else:
+            gray += 1
+    return must, gray, benign
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 32), (256, 384, 96), (1024, 1024, 1024), (130, 260, 72), (64, 512, 1000)])
+def test_clean_run_no_false_positive_and_bit_identical(cuda, shape):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    rep = b2.new_report()
+    dc = dev(c)
+    b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    assert r == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0}
+    assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+
+
+@pytest.mark.parametrize("bit", [20, 22, 23, 25, 27, 29, 30, 31])
+@pytest.mark.parametrize("k_step", [0, 5, 10 ** 6])
+def test_single_fault_each_bit(cuda, bit, k_step):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 256, 256, 512
+    a, b, c = mats(M, N, K)
+    plan = np.array([[1, 0, 77, 101, k_step, bit]], dtype=np.int32)
+    tau = default_tau(K)
+    must, gray, benign = classify(a, b, plan, tau)
+    rep = b2.new_report()
+    dc = dev(c)
+    b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert r["tiles"] == 4 and r["injected"] == 1
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+    got = dc.cpu().numpy()
+    if must:
+        assert r["detected"] == 1 and r["corrected"] == 1 and r["uncorrectable"] == 0
+    if benign:
+        assert r["detected"] == 0 and r["uncorrectable"] == 0
+    if must or benign:
+        assert oracle.gemm_error(got, c64, den) <= TOL
+    # every element other than the struck one is bit-identical to the plain result
+    want = oracle.sgemm_fma(1.0, a, b, 0.5, c)
+    mask = np.ones_like(want, dtype=bool)
+    mask[128 + 77, 101] = False
+    assert np.array_equal(got[mask], want[mask])
+
+
+@pytest.mark.parametrize("seed", [6, 7, 8])
+def test_config3_1024_plan(cuda, seed):
+    """BASELINE config 3 at 1024^3: one flip (bit 20..30) per 64 tiles -- here also a denser plan, one per 2 tiles."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 1024
+    a, b, c = mats(n, n, n)
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+    for per in (64, 2):
+        plan = oracle.make_fault_plan(n, n, n, seed=seed, tiles_per_fault=per)
+        tau = default_tau(n)
+        must, gray, benign = classify(a, b, plan, tau)
+        rep = b2.new_report()
+        dc = dev(c)
+        b2.ft_sgemm(n, n, n, 1.0, dev(a), dev(b), 0.5, dc, plan=b2.make_plan(plan), report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert r["tiles"] == 64 and r["injected"] == len(plan)
+        assert must <= r["corrected"] <= must + gray
+        assert r["uncorrectable"] <= gray
+        if gray == 0:
+            assert oracle.gemm_error(dc.cpu().numpy(), c64, den) <= TOL
+
+
+def test_nan_and_inf_faults_are_rebuilt(cuda):
+    """A flip of bit 30 on a value in [1,2) makes Inf/NaN; the value must be rebuilt, not subtracted."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 128, 128, 256
+    a, b, c = mats(M, N, K)
+    clean = oracle.sgemm_fma(1.0, a, b, 0.0, np.zeros_like(c))
+    cand = np.argwhere((np.abs(clean) >= 1.0) & (np.abs(clean) < 2.0))
+    r0, c0 = (int(v) for v in cand[0])
+    plan = np.array([[0, 0, r0, c0, 10 ** 6, 30]], dtype=np.int32)
+    _, bad, _ = oracle.fault_effect(a, b, plan[0])
+    assert not np.isfinite(bad)
+    rep = b2.new_report()
+    dc = dev(c)
+    b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, plan=b2.make_plan(plan), report=rep)
+    r = b2.read_report(rep)
+    assert r["corrected"] == 1 and r["uncorrectable"] == 0
+    got = dc.cpu().numpy()
+    assert np.isfinite(got).all()
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+    assert oracle.gemm_error(got, c64, den) <= TOL
+
+
+def test_north_star_launcher_ft_sgemm(cuda):
+    import ctypes as C
+    from hpcdeepneuralnetworks_b200 import _lib
+    L = _lib.load()
+    n = 256
+    a, b, c = mats(n, n, n)
+    da, db, dc = dev(a), dev(b), dev(c)
+    torch.cuda.synchronize()
+    p = lambda t: C.c_void_p(t.data_ptr())
+    assert L.ft_sgemm(n, n, n, 1.0, p(da), p(db), 0.5, p(dc)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+
+
+def test_unsupported_operands_are_refused(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    t = torch.zeros(100 * 100 + 4, device="cuda")
+    with pytest.raises(b2.B2Error) as e:
+        b2.ft_sgemm(50, 50, 50, 1.0, t[1:], t, 0.0, t.clone())      # A not 16-byte aligned
+    assert e.value.status == -2
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_config3_large_sizes(cuda, n):
+    """BASELINE config 3 at 4096^3 and 8192^3: seeded plan (one flip per 64 tiles) and a clean run; checked
+    against the plain kernel on the device and against the exact CPU walk of each struck accumulator."""
+    import hpcdeepneuralnetworks_b200 as b2
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    plain = torch.zeros((n, n), device="cuda")
+    b2.sgemm(n, n, n, 1.0, A, B, 0.0, plain)
+    tiles = (n // 128) ** 2
+    rep = b2.new_report()
+    out = torch.zeros((n, n), device="cuda")
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, report=rep)
+    b2.check_status()
+    assert b2.read_report(rep) == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0}
+    assert torch.equal(out, plain)
+    plan = oracle.make_fault_plan(n, n, n, seed=6)
+    assert len(plan) == tiles // 64
+    a, b = A.cpu().numpy(), B.cpu().numpy()
+    tau = default_tau(n)
+    must, gray, benign = classify(a, b, plan, tau)
+    rep = b2.new_report()
+    out.zero_()
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert r["injected"] == len(plan) and must <= r["corrected"] <= must + gray and r["uncorrectable"] <= gray
+    diff = (out - plain).abs()
+    # untouched elements identical; struck ones within the tolerance scale 1e-5 * K/4 (+ the gray zone bound 2 tau)
+    assert int((diff > 0).sum().item()) <= len(plan)
+    assert float(diff.max().item()) <= max(1e-5 * n / 4.0, 2 * tau if gray else 0.0)
