@@ -15,12 +15,11 @@
 //     4 x 16 outputs per thread: the warp tiling idea of kernel_11.cuh:22-27 with a shape
 //     chosen for the swizzled A reads and for the packed FMA below.
 //   * The inner product uses the packed fma.rn.f32x2 instruction (two FP32 FMAs per issue
-//     slot, pairs of adjacent columns).  The 4 A values a thread needs per k must sit in both
-//     halves of an operand; each warp writes them once per 8 k as (a,a) pairs into a private
-//     1 KB shared region, so the inner loop holds no register moves at all: per k it is
-//     32 packed FMAs, 4 + 2 128-bit shared loads, all fetched one k ahead.  Per output the
-//     arithmetic is still one FMA per k in ascending k, so results are bit-identical to the
-//     scalar form (kept as a variant).
+//     slot, pairs of adjacent columns); only the 4 A values per k have to be duplicated into
+//     both halves of an operand.  Per output the arithmetic is still one FMA per k in
+//     ascending k, so results are bit-identical to the scalar form (kept as a variant).
+//     The K-slab body is fully unrolled: shorter unrolled bodies and register-free schemes
+//     for the duplication (a per-warp shared region of (a,a) pairs) both measured slower.
 // Each output element is accumulated by exactly one thread in ascending k with one FMA per
 // k, and the epilogue is fma(alpha, acc, beta*c) (alpha*acc when beta == 0; C is then not
 // read).
@@ -33,7 +32,7 @@ namespace b2 {
 constexpr int FBM = 128, FBN = 128, FBK = 32, FSTAGES = 3;
 constexpr int kStageA = FBM * FBK * 4;  // 16 KB, 128 rows of 128 bytes, 128B-swizzled
 constexpr int kStageB = FBK * FBN * 4;  // 16 KB, 32 rows of 512 bytes, linear
-constexpr int kFfmaSmem = 1024 + FSTAGES * (kStageA + kStageB) + 1024 + 8 * 1024;
+constexpr int kFfmaSmem = 1024 + FSTAGES * (kStageA + kStageB) + 1024;
 constexpr int kGroupM = 16;  // tile rasterisation: 16 tile-rows share their B panels in L2
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -49,11 +48,6 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
-__device__ __forceinline__ uint64_t ffma2v(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm volatile("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
 
 struct FfmaArgs {
   float *C;
@@ -67,10 +61,10 @@ struct FfmaArgs {
 // must be duplicated into both halves of a packed operand at 4 per k).  Row i is tile row
 // warp*16 + lm + 4*i (row-major A) or warp*16 + lm*4 + i (transposed A); column j is tile
 // column ln*4 + 32*(j/4) + j%4, so one warp spans all 128 columns of 16 rows.
-template <int PACKED>
+template <bool PACKED>
 struct Acc;
 template <>
-struct Acc<0> {
+struct Acc<false> {
   float v[4][16];
   __device__ __forceinline__ void zero() {
 #pragma unroll
@@ -78,27 +72,22 @@ struct Acc<0> {
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
   }
-  // aa: the thread's 4 A values, each duplicated (a,a); bb: 16 B values as 8 pairs
-  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
-    float a[4], b[16], dummy;
-    unpack2(aa[0].x, a[0], dummy);
-    unpack2(aa[0].y, a[1], dummy);
-    unpack2(aa[1].x, a[2], dummy);
-    unpack2(aa[1].y, a[3], dummy);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      unpack2(bb[q].x, b[4 * q], b[4 * q + 1]);
-      unpack2(bb[q].y, b[4 * q + 2], b[4 * q + 3]);
-    }
+  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[4]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[i][j] = __fmaf_rn(a[i], b[j], v[i][j]);
+      for (int q = 0; q < 4; ++q) {
+        v[i][4 * q + 0] = __fmaf_rn(a[i], b[q].x, v[i][4 * q + 0]);
+        v[i][4 * q + 1] = __fmaf_rn(a[i], b[q].y, v[i][4 * q + 1]);
+        v[i][4 * q + 2] = __fmaf_rn(a[i], b[q].z, v[i][4 * q + 2]);
+        v[i][4 * q + 3] = __fmaf_rn(a[i], b[q].w, v[i][4 * q + 3]);
+      }
   }
   __device__ __forceinline__ float get(int i, int j) const { return v[i][j]; }
   __device__ __forceinline__ void set(int i, int j, float x) { v[i][j] = x; }
 };
-struct AccPackedBase {
+template <>
+struct Acc<true> {
   uint64_t v[4][8];  // pairs of adjacent columns
   __device__ __forceinline__ void zero() {
 #pragma unroll
@@ -106,62 +95,19 @@ struct AccPackedBase {
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[i][j] = 0ull;
   }
-  __device__ __forceinline__ float get(int i, int j) const {
-    float lo, hi;
-    unpack2(v[i][j >> 1], lo, hi);
-    return (j & 1) ? hi : lo;
-  }
-  __device__ __forceinline__ void set(int i, int j, float x) {
-    float lo, hi;
-    unpack2(v[i][j >> 1], lo, hi);
-    if (j & 1) hi = x; else lo = x;
-    v[i][j >> 1] = pack2(lo, hi);
-  }
-};
-template <>
-struct Acc<2> : AccPackedBase {
-  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
-    const uint64_t a[4] = {aa[0].x, aa[0].y, aa[1].x, aa[1].y};
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        v[i][2 * q] = ffma2v(a[i], bb[q].x, v[i][2 * q]);
-        v[i][2 * q + 1] = ffma2v(a[i], bb[q].y, v[i][2 * q + 1]);
-      }
-  }
-};
-template <>
-struct Acc<3> : AccPackedBase {
-  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
-    const uint64_t a[4] = {aa[0].x, aa[0].y, aa[1].x, aa[1].y};
+  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[4]) {
+    uint64_t bp[8];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i][2 * q] = ffma2v(a[i], bb[q].x, v[i][2 * q]);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i][2 * q + 1] = ffma2v(a[i], bb[q].y, v[i][2 * q + 1]);
+      bp[2 * q] = pack2(b[q].x, b[q].y);
+      bp[2 * q + 1] = pack2(b[q].z, b[q].w);
     }
-  }
-};
-template <>
-struct Acc<1> {
-  uint64_t v[4][8];  // pairs of adjacent columns
-  __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t aa = pack2(a[i], a[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = 0ull;
-  }
-  __device__ __forceinline__ void step(const ulonglong2 (&aa)[2], const ulonglong2 (&bb)[4]) {
-    const uint64_t a[4] = {aa[0].x, aa[0].y, aa[1].x, aa[1].y};
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        v[i][2 * q] = ffma2(a[i], bb[q].x, v[i][2 * q]);
-        v[i][2 * q + 1] = ffma2(a[i], bb[q].y, v[i][2 * q + 1]);
-      }
+      for (int j = 0; j < 8; ++j) v[i][j] = ffma2(aa, bp[j], v[i][j]);
+    }
   }
   __device__ __forceinline__ float get(int i, int j) const {
     float lo, hi;
@@ -219,9 +165,8 @@ struct FtArgs {
 constexpr int kFtBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[3]
 constexpr int kFtSumOff = kFtBarOff + 128;                // float sAc[3][32], sBr[3][32]
 constexpr int kFtInjOff = kFtSumOff + 2 * FSTAGES * 32 * 4;  // int inj[8]
-constexpr int kDupOff = kFtBarOff + 1024;                 // 8 warps x 1 KB of duplicated A values
 
-template <int PACKED, bool TRANS_A, bool FT>
+template <bool PACKED, int KCU, bool TRANS_A, bool FT>
 __global__ void __launch_bounds__(256, 2)
 sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FfmaArgs p,
                   const FtArgs ft) {
@@ -301,25 +246,12 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   Acc<PACKED> acc;
   acc.zero();
   float chk[4] = {0.f, 0.f, 0.f, 0.f};  // FT: [0] = row checksum (tid < 128) or 4 partial column checksums
-  // The packed FMA wants each A value in both halves of a 64-bit operand.  Instead of two
-  // register moves per value per thread, every warp re-writes the A values of its own 16 rows,
-  // 8 k at a time, into a private 1 KB region as (a,a) pairs; a thread then reads its 4 rows of
-  // one k as 32 contiguous bytes.  Slot of tile row r inside a k-row of that region:
-  // (r & 3) * 4 + (r >> 2) for row-major A (thread rows are lm + 4*i), r itself for transposed A.
-  unsigned char *D = smem + kDupOff + warp * 1024;
-  uint32_t dup_src, dup_dst;  // per-lane source (inside an A stage, chunk 0) and destination offsets
-  if (TRANS_A) {
-    const int ck = lane >> 2, rq = lane & 3;
-    dup_src = (uint32_t)ck * 512u + (uint32_t)(warp * 16 + rq * 4) * 4u;  // + chunk * 8 * 512
-    dup_dst = (uint32_t)(ck * 16 + rq * 4) * 8u;                           // 4 rows: + e * 8
-  } else {
-    const int crow = lane & 15, ckh = lane >> 4;
-    dup_src = (uint32_t)(warp * 16 + crow) * 128u;                         // + ((2*chunk + ckh) ^ (crow & 7)) << 4
-    dup_dst = (uint32_t)((ckh * 4) * 16 + (crow & 3) * 4 + (crow >> 2)) * 8u;  // 4 k: + e * 128
-  }
-  const uint32_t dup_swz = (uint32_t)(lane & 7), dup_kh = (uint32_t)(lane >> 4);
-  const unsigned char *Dr = D + lm * 32;           // this thread's 4 duplicated A values of k: + (k & 7) * 128
-  const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;  // B: row k at k*512, this thread's columns at ln*16 + q*128
+  // Byte offsets inside a stage.  A: row r at r*128, 16-byte chunk c of that row at
+  // ((c ^ (r & 7)) << 4); rows of this thread are warp*16 + lm + 4*i, so r & 7 is lm for even
+  // i and lm + 4 for odd i.  B: row k at k*512, column c at c*4.
+  const uint32_t a_thread = TRANS_A ? (uint32_t)(warp * 16 + lm * 4) * 4u : (uint32_t)(warp * 16 + lm) * 128u;
+  const uint32_t a_swz = (uint32_t)lm << 4;
+  const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;
   bool ok = true;
 
   for (int kb = 0; kb < nkb; ++kb) {
@@ -364,48 +296,36 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&sums_ready[s]);
     }
+    const unsigned char *As = Ast + a_thread;
     const unsigned char *Bs = Bst + b_thread;
-    auto load_raw = [&](int chunk) -> float4 {
-      if (TRANS_A) return *reinterpret_cast<const float4 *>(Ast + dup_src + chunk * (8 * 512));
-      return *reinterpret_cast<const float4 *>(Ast + dup_src + ((((uint32_t)(2 * chunk) + dup_kh) ^ dup_swz) << 4));
-    };
-    auto store_dup = [&](const float4 &r) {
-      constexpr int step = TRANS_A ? 8 : 128;
-      *reinterpret_cast<float2 *>(D + dup_dst + 0 * step) = make_float2(r.x, r.x);
-      *reinterpret_cast<float2 *>(D + dup_dst + 1 * step) = make_float2(r.y, r.y);
-      *reinterpret_cast<float2 *>(D + dup_dst + 2 * step) = make_float2(r.z, r.z);
-      *reinterpret_cast<float2 *>(D + dup_dst + 3 * step) = make_float2(r.w, r.w);
-    };
-    float4 raw = load_raw(0);
-    __syncwarp();  // the last reads of the previous slab's pairs are done
-    store_dup(raw);
-    __syncwarp();
-    ulonglong2 a_cur[2], b_cur[4];
-    a_cur[0] = *reinterpret_cast<const ulonglong2 *>(Dr);
-    a_cur[1] = *reinterpret_cast<const ulonglong2 *>(Dr + 16);
+    if (TRANS_A) {
+#pragma unroll(KCU * 4)
+      for (int k = 0; k < FBK; ++k) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(As + k * 512);
+        float4 b[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) b_cur[q] = *reinterpret_cast<const ulonglong2 *>(Bs + q * 128);
-#pragma unroll
-    for (int k = 0; k < FBK; ++k) {
-      ulonglong2 a_nxt[2], b_nxt[4];
-      if ((k & 7) == 3 && k + 5 < FBK) raw = load_raw((k >> 3) + 1);
-      if (k + 1 < FBK) {
-        if (((k + 1) & 7) == 0) {
-          __syncwarp();
-          store_dup(raw);
-          __syncwarp();
-        }
-        a_nxt[0] = *reinterpret_cast<const ulonglong2 *>(Dr + ((k + 1) & 7) * 128);
-        a_nxt[1] = *reinterpret_cast<const ulonglong2 *>(Dr + ((k + 1) & 7) * 128 + 16);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) b_nxt[q] = *reinterpret_cast<const ulonglong2 *>(Bs + (k + 1) * 512 + q * 128);
+        for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + k * 512 + q * 128);
+        const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+        acc.step(a, b);
       }
-      acc.step(a_cur, b_cur);
-      if (k + 1 < FBK) {
-        a_cur[0] = a_nxt[0];
-        a_cur[1] = a_nxt[1];
+    } else {
+#pragma unroll(KCU)
+      for (int kc = 0; kc < FBK / 4; ++kc) {
+        const uint32_t y0 = ((uint32_t)kc << 4) ^ a_swz, y1 = y0 ^ 64u;
+        float4 a4[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) b_cur[q] = b_nxt[q];
+        for (int i = 0; i < 4; ++i)
+          a4[i] = *reinterpret_cast<const float4 *>(As + ((i & 1) ? y1 : y0) + i * 512);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          float4 b[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + (kc * 4 + kk) * 512 + q * 128);
+          float a[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) a[i] = (kk == 0) ? a4[i].x : (kk == 1) ? a4[i].y : (kk == 2) ? a4[i].z : a4[i].w;
+          acc.step(a, b);
+        }
       }
     }
     if (FT) {
@@ -675,21 +595,21 @@ static int ffma_variant() {
   if (g_ffma_variant < 0) {
     const char *e = getenv("B2_FFMA_VARIANT");
     g_ffma_variant = e ? atoi(e) : 1;
-    if (g_ffma_variant < 0 || g_ffma_variant > 3) g_ffma_variant = 1;
+    if (g_ffma_variant < 0 || g_ffma_variant > 1) g_ffma_variant = 1;
   }
   return g_ffma_variant;
 }
 
-template <int PACKED, bool TRANS_A, bool FT = false>
+template <bool PACKED, int KCU, bool TRANS_A, bool FT = false>
 static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s,
                        const FtArgs &ft = FtArgs{nullptr, 0, 0.f, nullptr}) {
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, TRANS_A, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfmaSmem));
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, TRANS_A, FT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, KCU, TRANS_A, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfmaSmem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, KCU, TRANS_A, FT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     configured = true;
   }
-  sgemm_ffma_kernel<PACKED, TRANS_A, FT><<<grid, 256, kFfmaSmem, s>>>(ta, tb, args, ft);
+  sgemm_ffma_kernel<PACKED, KCU, TRANS_A, FT><<<grid, 256, kFfmaSmem, s>>>(ta, tb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
@@ -739,14 +659,9 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
   const int grid = ((M + FBM - 1) / FBM) * ((N + FBN - 1) / FBN);
   const bool packed = ffma_variant() != 0;
-  if (ft) return launch_ffma<1, false, true>(ta, tb, args, grid, s, *ft);
-  if (trans_a) return packed ? launch_ffma<1, true>(ta, tb, args, grid, s) : launch_ffma<0, true>(ta, tb, args, grid, s);
-  switch (ffma_variant()) {
-    case 0: return launch_ffma<0, false>(ta, tb, args, grid, s);
-    case 2: return launch_ffma<2, false>(ta, tb, args, grid, s);
-    case 3: return launch_ffma<3, false>(ta, tb, args, grid, s);
-    default: return launch_ffma<1, false>(ta, tb, args, grid, s);
-  }
+  if (ft) return launch_ffma<true, 8, false, true>(ta, tb, args, grid, s, *ft);
+  if (trans_a) return packed ? launch_ffma<true, 8, true>(ta, tb, args, grid, s) : launch_ffma<false, 8, true>(ta, tb, args, grid, s);
+  return packed ? launch_ffma<true, 8, false>(ta, tb, args, grid, s) : launch_ffma<false, 8, false>(ta, tb, args, grid, s);
 }
 
 }  // namespace b2
@@ -791,10 +706,10 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
   return b2_ft_sgemm(nullptr, B2_PATH_FFMA, M, N, K, alpha, A, K, B, N, beta, C, N, nullptr, 0, 0.f, nullptr, nullptr);
 }
 
-// Selects the inner-loop variant of the FFMA kernel (0 scalar FFMA, 1 packed f32x2, 2/3 the
-// same with a shorter unrolled body).  For benchmarking; results are bit-identical.
+// Selects the inner-loop variant of the FFMA kernel (0 scalar FFMA, 1 packed f32x2).  For
+// benchmarking; results are bit-identical.
 int b2_set_ffma_variant(int v) {
-  B2_REQUIRE(v >= 0 && v <= 3, B2_ERR_INVALID_ARG, "b2_set_ffma_variant: %d not in 0..3", v);
+  B2_REQUIRE(v >= 0 && v <= 1, B2_ERR_INVALID_ARG, "b2_set_ffma_variant: %d not in 0..1", v);
   b2::g_ffma_variant = v;
   return B2_OK;
 }

@@ -244,70 +244,6 @@ __global__ void __launch_bounds__(256) ffma2_probe_kernel(int64_t iters, float a
   if (s == 123.456f) *sink = s;
 }
 
-// Outer-product shaped FMA stream (4 x 16 accumulators from 4 + 16 operand registers, no memory
-// traffic): the register-operand pattern of the SGEMM inner loop, scalar or packed.
-template <bool PACKED>
-__global__ void __launch_bounds__(256, 2) ffma_outer_probe_kernel(int64_t iters, float seed, float *sink) {
-  float total = 0.f;
-  if (PACKED) {
-    uint64_t acc[4][8], a[4], b[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float x = seed * (float)(i + 1 + threadIdx.x);
-      asm("mov.b64 %0, {%1, %1};" : "=l"(a[i]) : "f"(x));
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float x = seed * (float)(j + 3), y = seed * (float)(j + 5);
-      asm("mov.b64 %0, {%1, %2};" : "=l"(b[j]) : "f"(x), "f"(y));
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
-    for (int64_t it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int r = 0; r < 4; ++r)
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            asm volatile("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[i][j]) : "l"(a[i]), "l"(b[j]));
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float lo, hi;
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[i][j]));
-        total += lo + hi;
-      }
-  } else {
-    float acc[4][16], a[4], b[16];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = seed * (float)(i + 1 + threadIdx.x);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) b[j] = seed * (float)(j + 3);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 16; ++j) acc[i][j] = 0.f;
-    for (int64_t it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int r = 0; r < 4; ++r)
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int j = 0; j < 16; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 16; ++j) total += acc[i][j];
-  }
-  if (total == 123.456f) *sink = total;
-}
-
 static int vec_grid(Context *ctx, int64_t work_items, int per_block) {
   int64_t need = (work_items + per_block - 1) / per_block;
   int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 blocks of 256 threads fill an SM
@@ -422,21 +358,6 @@ int b2_ffma_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out,
 }
 int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
   return ffma_probe(true, launches, ffma_per_thread, flops_out, stream);
-}
-// experiment entry (not part of the public header): outer-product operand pattern
-int b2_ffma_outer_probe(int packed, int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {
-  Context *ctx = default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "no context");
-  const int64_t iters = (ffma_per_thread + 255) / 256;
-  const int grid = ctx->sm_count * 2;
-  float *sink = (float *)((char *)ctx->fixed + kFixedVerify + 64);
-  for (int l = 0; l < launches; ++l) {
-    if (packed) ffma_outer_probe_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.001f, sink);
-    else ffma_outer_probe_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(iters, 0.001f, sink);
-  }
-  B2_CUDA(cudaGetLastError());
-  if (flops_out) *flops_out = 2.0 * (double)launches * (double)grid * 256.0 * (double)iters * 256.0;
-  return B2_OK;
 }
 
 static int ffma_probe(bool packed, int launches, int64_t ffma_per_thread, double *flops_out, void *stream) {

@@ -170,8 +170,8 @@ int b2_timer_elapsed_ms(b2_timer t, float *ms_out);
 int b2_ffma_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream);
 /* The same probe issued as packed fma.rn.f32x2 (two FMAs per instruction). */
 int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out, void *stream);
-/* Inner-loop variant of the FFMA SGEMM kernel (0 scalar FFMA, 1/2 packed f32x2, 3 scalar with a
- * short unrolled body); results are bit-identical, used for benchmarking only. */
+/* Inner-loop variant of the FFMA SGEMM kernel (0 scalar FFMA, 1 packed f32x2, the default);
+ * results are bit-identical, used for benchmarking only. */
 int b2_set_ffma_variant(int v);
 /* 3xTF32 path: 0 = B planes written transposed (N x K) and fed K-major, 1 = planes as is, MN-major. */
 int b2_set_tf32_b_layout(int mn_major);

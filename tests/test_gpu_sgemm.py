@@ -51,7 +51,7 @@ def test_config1_256_against_reference_cpu_gemm(cuda):
     assert np.array_equal(got, oracle.sgemm_fma(1.0, a, b, 0.0, c))
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("shape", [(128, 128, 32), (256, 384, 96), (512, 512, 512)])
 def test_ffma_variants_bit_exact(cuda, variant, shape):
     import hpcdeepneuralnetworks_b200 as b2
