@@ -34,7 +34,8 @@ NMULTI = 32768
 CPU_SAMPLE_N = 1152          # reference CPU GEMM sample: 1152^3 = (3/16 * 6144)^3, about 1/152 of the flop
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the committed
 # ncu captures (profiles/), scaled to a full launch; None until a capture exists for that kernel.
-NCU_TRAFFIC = {"sgemm_ffma_6144": None, "sgemm_3xtf32_6144": None, "saxpy_2p28": None, "sdot_2p28": None}
+NCU_TRAFFIC = {"sgemm_ffma_6144": 1.442411e9 + 145.4656e6, "sgemm_3xtf32_6144": 2.906706e9 + 140.046848e6,
+               "saxpy_2p28": None, "sdot_2p28": 4 * (536.8855e6 + 4.07e6)}
 
 
 def load_peaks():
@@ -161,10 +162,10 @@ def run_reference(args):
     return 0
 
 
-def bench_vectors(b2, torch, peaks, steps, warmup):
+def bench_vectors(b2, torch, peaks, steps, warmup, log2n=28):
     """SAXPY / SDOT at n = 2^28 (1 GiB per vector, larger than L2): GB/s against the measured HBM copy peak."""
     out = {}
-    n = 1 << 28
+    n = 1 << log2n
     x = b2.fill_uniform(torch.empty(n, device="cuda"), 4)
     y = b2.fill_uniform(torch.empty(n, device="cuda"), 5)
     res = torch.zeros(1, device="cuda")
@@ -188,6 +189,9 @@ def run_single(args):
     import hpcdeepneuralnetworks_b200 as b2
     torch.cuda.set_device(0)
     peaks = load_peaks()
+    if args.only == "vectors":   # small-case command for profiling the streaming kernels
+        print(json.dumps(bench_vectors(b2, torch, peaks, args.steps, args.warmup, args.vec_log2n)))
+        return 0
     n = args.size or N1
     flop = 2.0 * n ** 3
     path = 1 if args.path == "3xtf32" else 0
@@ -349,6 +353,8 @@ def main():
     ap.add_argument("--path", default="ffma", choices=["ffma", "3xtf32"])
     ap.add_argument("--size", type=int, default=0, help="override the matrix size (profiling of small cases)")
     ap.add_argument("--panel", type=int, default=4096, help="K-panel of the B broadcast (multi-GPU)")
+    ap.add_argument("--only", default="all", choices=["all", "vectors"], help="vectors: SAXPY/SDOT only (profiling)")
+    ap.add_argument("--vec-log2n", type=int, default=28, help="log2 of the vector length of the SAXPY/SDOT leg")
     ap.add_argument("--quick", action="store_true", help="headline kernel only (no extras); used for profiling")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
