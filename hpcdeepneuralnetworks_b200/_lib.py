@@ -77,6 +77,7 @@ def load() -> C.CDLL:
     L.sdot.argtypes = [i32, vp, vp, vp]
     L.b2_sdot.argtypes = [vp, i64, vp, vp, vp, vp]
     L.b2_sdot_partial.argtypes = [vp, i64, vp, vp, vp, vp, vp]
+    L.b2_sdot_static.argtypes = [i64, vp, vp, vp, vp]
     L.b2_fill_uniform.argtypes = [vp, i64, u64, vp]
     L.b2_fill_uniform_host.argtypes = [vp, i64, u64]
     L.b2_fill_const.argtypes = [vp, i64, f32, vp]

@@ -165,6 +165,13 @@ def sdot(n, x, y, out=None, handle=None):
     return out
 
 
+def sdot_static(n, x, y, out):
+    """out[0] <- x . y through the entry point that allocates nothing (``b2_sdot_static``): no handle, scratch in
+    the library's own static device array, n <= 2**30.  ``out`` must be an existing 1-element device tensor."""
+    check(_lib.load().b2_sdot_static(n, _ptr(x), _ptr(y), _ptr(out), _stream()))
+    return out
+
+
 def sdot_partial(n, x, y, out, partial64, handle=None):
     h = handle or default_handle()
     check(_lib.load().b2_sdot_partial(h.raw, n, _ptr(x), _ptr(y), _ptr(out), _ptr(partial64), _stream()))

@@ -10,6 +10,8 @@
 // result is deterministic (the reference's atomicAdd of block sums is not).
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b2 {
@@ -170,6 +172,21 @@ __global__ void __launch_bounds__(kVecThreads) sdot_kernel(int64_t n, const floa
   sdot_finish(sdot_thread_sum<ALIGNED>(n, x, y), partials, ticket, result, result64);
 }
 
+// ---- SDOT without any allocation ---------------------------------------------------------
+// Scratch of b2_sdot_static: one double per block plus the ticket word, held in the module's
+// own device memory (every GPU that loads the library carries these 16.25 KB until exit).
+constexpr int kStaticSdotBlocks = 2048;
+constexpr int64_t kStaticSdotMaxN = (int64_t)1 << 30;
+static __device__ __align__(256) unsigned char g_sdot_static_scratch[kStaticSdotBlocks * sizeof(double) + 256];
+
+struct StaticSdotSetup {
+  bool ready = false;
+  unsigned char *scratch = nullptr;  // device address of g_sdot_static_scratch on this device
+  int sm_count = 0;
+};
+static StaticSdotSetup g_static_sdot[64];
+static std::mutex g_static_sdot_mu;
+
 __global__ void fill_uniform_kernel(float *dst, int64_t n, uint64_t mixed_seed) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
@@ -297,6 +314,49 @@ int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, floa
 
 int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, void *stream) {
   return b2_sdot_partial(h, n, x, y, result_dev, nullptr, stream);
+}
+
+int b2_sdot_static(int64_t n, const float *x, const float *y, float *result_dev, void *stream) {
+  B2_REQUIRE(n >= 0, B2_ERR_INVALID_ARG, "b2_sdot_static: n = %lld is negative", (long long)n);
+  B2_REQUIRE(n <= kStaticSdotMaxN, B2_ERR_UNSUPPORTED,
+             "b2_sdot_static: n = %lld exceeds the limit of %lld elements of the allocation-free entry point; use b2_sdot",
+             (long long)n, (long long)kStaticSdotMaxN);
+  B2_REQUIRE(result_dev != nullptr, B2_ERR_INVALID_ARG, "b2_sdot_static: result pointer is NULL");
+  B2_REQUIRE(n == 0 || (x != nullptr && y != nullptr), B2_ERR_INVALID_ARG, "b2_sdot_static: null vector");
+  B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_sdot_static: vectors must be 4-byte aligned");
+  int dev = 0;
+  B2_CUDA(cudaGetDevice(&dev));
+  B2_REQUIRE(dev >= 0 && dev < 64, B2_ERR_UNSUPPORTED, "b2_sdot_static: device ordinal %d not supported", dev);
+  StaticSdotSetup *st = &g_static_sdot[dev];
+  {
+    // First call on this device (with it current): resolve the device address of the scratch
+    // array.  The array's name in host code is only a handle for this lookup, not an address.
+    std::lock_guard<std::mutex> lk(g_static_sdot_mu);
+    if (!st->ready) {
+      void *p = nullptr;
+      B2_CUDA(cudaGetSymbolAddress(&p, g_sdot_static_scratch));
+      B2_REQUIRE(p != nullptr, B2_ERR_CUDA, "b2_sdot_static: the scratch symbol has no device address");
+      B2_CUDA(cudaDeviceGetAttribute(&st->sm_count, cudaDevAttrMultiProcessorCount, dev));
+      st->scratch = (unsigned char *)p;
+      st->ready = true;
+    }
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  double *partials = (double *)st->scratch;
+  unsigned int *ticket = (unsigned int *)(st->scratch + kStaticSdotBlocks * sizeof(double));
+  // The array keeps whatever the previous call left: the ticket has to start at zero (the
+  // partials need no clearing, every block writes its own before it takes a ticket).
+  B2_CUDA(cudaMemsetAsync(ticket, 0, sizeof(unsigned int), s));
+  int64_t need = ((n >> 2) + kVecThreads * kVecUnroll - 1) / (kVecThreads * kVecUnroll);
+  if (need < 1) need = 1;
+  int64_t grid = (int64_t)st->sm_count * 8;
+  if (grid > need) grid = need;
+  if (grid > kStaticSdotBlocks) grid = kStaticSdotBlocks;
+  const bool al = (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+  if (al) sdot_kernel<true><<<(int)grid, kVecThreads, 0, s>>>(n, x, y, partials, ticket, result_dev, nullptr);
+  else sdot_kernel<false><<<(int)grid, kVecThreads, 0, s>>>(n, x, y, partials, ticket, result_dev, nullptr);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
 }
 
 int saxpy(int n, float alpha, const float *x, float *y) { return b2_saxpy(nullptr, n, alpha, x, y, nullptr); }

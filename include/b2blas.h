@@ -137,6 +137,23 @@ int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *resul
 int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev,
                     double *partial_dev, void *stream);
 
+/* SDOT for callers that must not allocate.  This entry point has no counterpart in the
+ * reference.  It is meant for code that cannot call cudaMalloc at the point where it needs a dot
+ * product: a plugin running under a host framework that has already handed all device memory to its
+ * own pool, a callback on a latency-critical path where cudaMalloc's implicit device
+ * synchronisation is not acceptable, or a process whose memory budget is fixed at start-up.  It
+ * creates no handle and calls no cudaMalloc, cudaFree or other allocating routine: its scratch (one
+ * double per block and a ticket word, 16.25 KB) is a static device array inside the library, which
+ * every GPU that loads the library holds until the process exits.  Same arithmetic, same result
+ * and same determinism as b2_sdot; *result_dev is overwritten.
+ * Limits and rules:
+ *  - n may be at most 2^30 elements; larger n returns B2_ERR_UNSUPPORTED (use b2_sdot).
+ *  - The first call on each device looks up the device address of the scratch array (with that
+ *    device current); make that first call before starting any stream capture.
+ *  - All calls on a device share the one scratch array, so two calls that can overlap on the GPU
+ *    (different streams, no dependency) race with each other; serialise them. */
+int b2_sdot_static(int64_t n, const float *x, const float *y, float *result_dev, void *stream);
+
 /* ---- harness (rebuild of utils/utils.cu around CUDA events) ----------------------- */
 
 /* Element i of the stream `seed` is a counter-based hash of (seed, i) mapped to a
