@@ -204,7 +204,10 @@ def run_single(args):
     ffma_peak = b2.ffma_peak_tflops()
 
     def step(p=path):
-        b2.sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=p)
+        if args.abft:
+            b2.ft_sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=p)
+        else:
+            b2.sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=p)
 
     with ClockSampler(0) as clk:
         ms = timed(step, args.steps, args.warmup)
@@ -260,7 +263,7 @@ def run_single(args):
         "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": f"sgemm_rowmajor_{n}^3", "path": args.path, "alpha": 1.0, "beta": 0.5,
+        "config": {"workload": f"sgemm_rowmajor_{n}^3" + ("_abft" if args.abft else ""), "path": args.path, "alpha": 1.0, "beta": 0.5,
                    "inputs": "seeded uniform[-1,1) generated on the device", "l2": "A, B, C are 3 x %d MB, larger than the 126 MB L2" % (4 * n * n // 2 ** 20),
                    "parallelism": "1 GPU"},
         "roofline": roof(path, tflops), "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * (1 if path == 0 else 3),
@@ -355,6 +358,7 @@ def main():
     ap.add_argument("--panel", type=int, default=4096, help="K-panel of the B broadcast (multi-GPU)")
     ap.add_argument("--only", default="all", choices=["all", "vectors"], help="vectors: SAXPY/SDOT only (profiling)")
     ap.add_argument("--vec-log2n", type=int, default=28, help="log2 of the vector length of the SAXPY/SDOT leg")
+    ap.add_argument("--abft", action="store_true", help="time the fault-tolerant SGEMM as the headline step (profiling)")
     ap.add_argument("--quick", action="store_true", help="headline kernel only (no extras); used for profiling")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

@@ -49,6 +49,12 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 struct FfmaArgs {
   float *C;
   int M, N, K, ldc;
@@ -163,8 +169,8 @@ struct FtArgs {
 };
 
 constexpr int kFtBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[3]
-constexpr int kFtSumOff = kFtBarOff + 128;                // float sAc[3][32], sBr[3][32]
-constexpr int kFtInjOff = kFtSumOff + 2 * FSTAGES * 32 * 4;  // int inj[8]
+constexpr int kFtSumOff = kFtBarOff + 128;                // float2 sAc[3][32] (each sum twice), float sBr[3][32]
+constexpr int kFtInjOff = kFtSumOff + 3 * FSTAGES * 32 * 4;  // int inj[8]
 
 template <bool PACKED, int KCU, bool TRANS_A, bool FT>
 __global__ void __launch_bounds__(256, 2)
@@ -179,8 +185,8 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + kFtBarOff);
   uint64_t *empty = full + FSTAGES;
   uint64_t *sums_ready = empty + FSTAGES;
-  float *sAc = reinterpret_cast<float *>(smem + kFtSumOff);  // [stage][32] column sums of the A slab
-  float *sBr = sAc + FSTAGES * 32;                           // [stage][32] row sums of the B slab
+  unsigned char *sAc = smem + kFtSumOff;               // [stage][32] column sums of the A slab, as (s,s) pairs
+  unsigned char *sBr = sAc + FSTAGES * 256;            // [stage][32] row sums of the B slab
   int *inj = reinterpret_cast<int *>(smem + kFtInjOff);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -230,28 +236,28 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 
   // planned fault: which slab, and (for the owning thread only) which accumulator
-  int inj_kb = -1, inj_i = 0, inj_j = 0;
-  uint32_t inj_mask = 0;
+  int inj_kb = -1;  // slab after which this thread flips a bit (-1: never); the rest is re-read from inj[]
   if (FT && inj[0]) {
     const int r = inj[1], c = inj[2];
     const bool own = r >= 0 && r < FBM && c >= 0 && c < FBN && (r >> 4) == warp && (r & 3) == lm && ((c & 31) >> 2) == ln;
     if (own) {
       inj_kb = inj[3] < 0 ? 0 : (inj[3] >= nkb ? nkb - 1 : inj[3]);
-      inj_i = (r & 15) >> 2;
-      inj_j = (c >> 5) * 4 + (c & 3);
-      inj_mask = 1u << (inj[4] & 31);
     }
   }
 
   Acc<PACKED> acc;
   acc.zero();
-  float chk[4] = {0.f, 0.f, 0.f, 0.f};  // FT: [0] = row checksum (tid < 128) or 4 partial column checksums
   // Byte offsets inside a stage.  A: row r at r*128, 16-byte chunk c of that row at
   // ((c ^ (r & 7)) << 4); rows of this thread are warp*16 + lm + 4*i, so r & 7 is lm for even
   // i and lm + 4 for odd i.  B: row k at k*512, column c at c*4.
   const uint32_t a_thread = TRANS_A ? (uint32_t)(warp * 16 + lm * 4) * 4u : (uint32_t)(warp * 16 + lm) * 128u;
   const uint32_t a_swz = (uint32_t)lm << 4;
   const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;
+  // ABFT: per-thread byte offsets of the encoder, fixed for the whole kernel
+  const uint32_t p1a_off = (uint32_t)lane * 128u + (uint32_t)((warp ^ (lane & 7)) << 4);   // A: rows lane+32q, k-chunk = warp
+  const uint32_t p1b_off = (uint32_t)(warp * 4 + (lane >> 3)) * 512u + (uint32_t)(lane & 7) * 16u;  // B: row 4*warp + lane/8
+  const uint32_t p2_off = (warp < 4) ? (uint32_t)tid * 128u : (uint32_t)(((tid - 128) >> 5) * 8) * 512u + (uint32_t)((tid - 128) & 31) * 16u;
+  uint64_t chk2[2] = {0ull, 0ull};  // FT: packed running checksums (row: 2 pairs folded at the end; column: 4 columns)
   bool ok = true;
 
   for (int kb = 0; kb < nkb; ++kb) {
@@ -264,35 +270,42 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const unsigned char *Ast = sA + s * kStageA;
     const unsigned char *Bst = sB + s * kStageB;
     if (FT) {
-      // ---- phase 1: slab sums ----
-      float4 pa = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float4 v = *reinterpret_cast<const float4 *>(Ast + (lane + 32 * q) * 128 + ((warp ^ (lane & 7)) << 4));
-        pa.x += v.x; pa.y += v.y; pa.z += v.z; pa.w += v.w;
-      }
+      // ---- phase 1: slab sums (packed adds; offsets precomputed) ----
+      const unsigned char *pa_ptr = Ast + p1a_off;
+      ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(pa_ptr);
+      ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(pa_ptr + 32 * 128);
+      ulonglong2 v2 = *reinterpret_cast<const ulonglong2 *>(pa_ptr + 64 * 128);
+      ulonglong2 v3 = *reinterpret_cast<const ulonglong2 *>(pa_ptr + 96 * 128);
+      const uint64_t pxy = fadd2(fadd2(v0.x, v1.x), fadd2(v2.x, v3.x));
+      const uint64_t pzw = fadd2(fadd2(v0.y, v1.y), fadd2(v2.y, v3.y));
+      float px, py, pz, pw;
+      unpack2(pxy, px, py);
+      unpack2(pzw, pz, pw);
       // 4 components x 32 lanes -> 4 totals: halve the live components while folding lanes
       const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
-      float k0 = h16 ? pa.z : pa.x, k1 = h16 ? pa.w : pa.y;
-      k0 += __shfl_xor_sync(0xffffffffu, h16 ? pa.x : pa.z, 16);
-      k1 += __shfl_xor_sync(0xffffffffu, h16 ? pa.y : pa.w, 16);
+      float k0 = h16 ? pz : px, k1 = h16 ? pw : py;
+      k0 += __shfl_xor_sync(0xffffffffu, h16 ? px : pz, 16);
+      k1 += __shfl_xor_sync(0xffffffffu, h16 ? py : pw, 16);
       float ka = h8 ? k1 : k0;
       ka += __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
       ka += __shfl_xor_sync(0xffffffffu, ka, 4);
       ka += __shfl_xor_sync(0xffffffffu, ka, 2);
       ka += __shfl_xor_sync(0xffffffffu, ka, 1);
-      if ((lane & 7) == 0) sAc[s * 32 + warp * 4 + (h16 ? 2 : 0) + (h8 ? 1 : 0)] = ka;
-      const int kr = warp * 4 + (lane >> 3);
-      float sb = 0.f;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float4 v = *reinterpret_cast<const float4 *>(Bst + kr * 512 + ((lane & 7) + 8 * q) * 16);
-        sb += (v.x + v.y) + (v.z + v.w);
-      }
+      if ((lane & 7) == 0)
+        *reinterpret_cast<float2 *>(sAc + s * 256 + (warp * 4 + (h16 ? 2 : 0) + (h8 ? 1 : 0)) * 8) = make_float2(ka, ka);
+      const unsigned char *pb_ptr = Bst + p1b_off;
+      v0 = *reinterpret_cast<const ulonglong2 *>(pb_ptr);
+      v1 = *reinterpret_cast<const ulonglong2 *>(pb_ptr + 128);
+      v2 = *reinterpret_cast<const ulonglong2 *>(pb_ptr + 256);
+      v3 = *reinterpret_cast<const ulonglong2 *>(pb_ptr + 384);
+      const uint64_t sb2 = fadd2(fadd2(fadd2(v0.x, v0.y), fadd2(v1.x, v1.y)), fadd2(fadd2(v2.x, v2.y), fadd2(v3.x, v3.y)));
+      float sbx, sby;
+      unpack2(sb2, sbx, sby);
+      float sb = sbx + sby;
       sb += __shfl_xor_sync(0xffffffffu, sb, 1);
       sb += __shfl_xor_sync(0xffffffffu, sb, 2);
       sb += __shfl_xor_sync(0xffffffffu, sb, 4);
-      if ((lane & 7) == 0) sBr[s * 32 + kr] = sb;
+      if ((lane & 7) == 0) *reinterpret_cast<float *>(sBr + s * 128 + (warp * 4 + (lane >> 3)) * 4) = sb;
       __syncwarp();
       if (lane == 0) mbar_arrive(&sums_ready[s]);
     }
@@ -335,32 +348,36 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         break;
       }
       if (warp < 4) {
-        const unsigned char *Arow = Ast + tid * 128;
-        const int sw = tid & 7;
+        // row checksum of tile row tid: sum_k A[tid][k] * Bsum[k], two packed chains
+        const unsigned char *Arow = Ast + p2_off;
+        const uint32_t sw = (uint32_t)(tid & 7) << 4;
+        const unsigned char *br = sBr + s * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const float4 a = *reinterpret_cast<const float4 *>(Arow + ((c ^ sw) << 4));
-          const float4 b = *reinterpret_cast<const float4 *>(&sBr[s * 32 + c * 4]);
-          chk[0] = __fmaf_rn(a.x, b.x, chk[0]);
-          chk[0] = __fmaf_rn(a.y, b.y, chk[0]);
-          chk[0] = __fmaf_rn(a.z, b.z, chk[0]);
-          chk[0] = __fmaf_rn(a.w, b.w, chk[0]);
+          const ulonglong2 a = *reinterpret_cast<const ulonglong2 *>(Arow + (((uint32_t)c << 4) ^ sw));
+          const ulonglong2 b = *reinterpret_cast<const ulonglong2 *>(br + c * 16);
+          chk2[0] = ffma2(a.x, b.x, chk2[0]);
+          chk2[1] = ffma2(a.y, b.y, chk2[1]);
         }
       } else {
-        const int j = tid - 128, cg = j & 31, kg = j >> 5;
+        // partial checksums of 4 columns over 8 k: Asum[k] * B[k][4 columns]
+        const unsigned char *Bcol = Bst + p2_off;
+        const unsigned char *ac = sAc + s * 256 + ((tid - 128) >> 5) * 64;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const int k = kg * 8 + kk;
-          const float4 b = *reinterpret_cast<const float4 *>(Bst + k * 512 + cg * 16);
-          const float ac = sAc[s * 32 + k];
-          chk[0] = __fmaf_rn(ac, b.x, chk[0]);
-          chk[1] = __fmaf_rn(ac, b.y, chk[1]);
-          chk[2] = __fmaf_rn(ac, b.z, chk[2]);
-          chk[3] = __fmaf_rn(ac, b.w, chk[3]);
+        for (int kk = 0; kk < 8; kk += 2) {
+          const ulonglong2 a2 = *reinterpret_cast<const ulonglong2 *>(ac + kk * 8);  // (s_k, s_k, s_k+1, s_k+1)
+          const ulonglong2 b0 = *reinterpret_cast<const ulonglong2 *>(Bcol + kk * 512);
+          const ulonglong2 b1 = *reinterpret_cast<const ulonglong2 *>(Bcol + (kk + 1) * 512);
+          chk2[0] = ffma2(a2.x, b0.x, chk2[0]);
+          chk2[1] = ffma2(a2.x, b0.y, chk2[1]);
+          chk2[0] = ffma2(a2.y, b1.x, chk2[0]);
+          chk2[1] = ffma2(a2.y, b1.y, chk2[1]);
         }
       }
       // ---- simulated soft error: flip one bit of one accumulator after this slab ----
       if (kb == inj_kb) {
+        const int inj_i = (inj[1] & 15) >> 2, inj_j = (inj[2] >> 5) * 4 + (inj[2] & 3);
+        const uint32_t inj_mask = 1u << (inj[4] & 31);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -435,12 +452,16 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
       for (int j = 0; j < 16; ++j) colsum_s[warp * 128 + acc_col(ln, j)] = cs[j];
     }
-    if (warp < 4) {
-      rowchk_s[tid] = chk[0];
-    } else {
-      const int j = tid - 128, cg = j & 31, kg = j >> 5;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) colchk_s[kg * 128 + cg * 4 + e] = chk[e];
+    {
+      float c0, c1, c2, c3;
+      unpack2(chk2[0], c0, c1);
+      unpack2(chk2[1], c2, c3);
+      if (warp < 4) {
+        rowchk_s[tid] = (c0 + c1) + (c2 + c3);
+      } else {
+        const int j = tid - 128, cg = j & 31, kg = j >> 5;
+        *reinterpret_cast<float4 *>(&colchk_s[kg * 128 + cg * 4]) = make_float4(c0, c1, c2, c3);
+      }
     }
     if (tid < 4) flags[tid] = 0;
     __syncthreads();
