@@ -184,11 +184,56 @@ def bench_vectors(b2, torch, peaks, steps, warmup, log2n=28):
     return out
 
 
+def run_sweep(args):
+    """BASELINE config 2: square row-major SGEMM, N = 256 .. 6144 step 256, alpha=1, beta=0.5, both math paths.
+    Prints one JSON object with a row per size (not the headline line)."""
+    import torch
+    import hpcdeepneuralnetworks_b200 as b2
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    ffma_peak = b2.ffma_peak_tflops()
+    nmax = args.size or N1
+    A = b2.fill_uniform(torch.empty(nmax * nmax, device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty(nmax * nmax, device="cuda"), 2)
+    Cm = b2.fill_uniform(torch.empty(nmax * nmax, device="cuda"), 3)
+    flush = torch.empty(160 * 2 ** 20 // 4, device="cuda")       # > L2: written between timed launches of small sizes
+    rows = []
+    for n in range(256, nmax + 1, 256):
+        a, b, c = A[:n * n].view(n, n), B[:n * n].view(n, n), Cm[:n * n].view(n, n)
+        row = {"n": n}
+        for path, key in ((0, "ffma"), (1, "3xtf32")):
+            small = 3 * 4 * n * n < 2 * 126 * 2 ** 20               # operands could sit in L2: flush between launches
+            def one():
+                if small:
+                    flush.zero_()
+                b2.sgemm(n, n, n, 1.0, a, b, 0.5, c, path=path)
+            reps = 20 if n <= 2048 else 8
+            if small:
+                # time the flush alone and subtract it
+                ms_both = timed(one, reps, 3)
+                ms_flush = timed(lambda: flush.zero_(), reps, 3)
+                ms = max(ms_both - ms_flush, 1e-6)
+            else:
+                ms = timed(one, reps, 3)
+            row[key + "_ms"] = ms
+            row[key + "_tflops"] = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
+        row["ffma_frac_of_fp32_peak"] = row["ffma_tflops"] / ffma_peak
+        row["3xtf32_tensor_frac"] = 3 * row["3xtf32_tflops"] / (peaks["bf16_tflops"] / 2)
+        rows.append(row)
+    b2.check_status()
+    print(json.dumps({"sweep": "sgemm_rowmajor_square", "alpha": 1.0, "beta": 0.5, "ffma_peak_tflops": ffma_peak,
+                      "tf32_peak_tflops": peaks["bf16_tflops"] / 2, "l2": "sizes whose operands fit twice in L2 are timed with a 160 MB flush between launches, flush time subtracted",
+                      "rows": rows}))
+    return 0
+
+
 def run_single(args):
     import torch
     import hpcdeepneuralnetworks_b200 as b2
     torch.cuda.set_device(0)
     peaks = load_peaks()
+    if args.sweep:
+        return run_sweep(args)
     if args.only == "vectors":   # small-case command for profiling the streaming kernels
         print(json.dumps(bench_vectors(b2, torch, peaks, args.steps, args.warmup, args.vec_log2n)))
         return 0
@@ -358,6 +403,7 @@ def main():
     ap.add_argument("--panel", type=int, default=4096, help="K-panel of the B broadcast (multi-GPU)")
     ap.add_argument("--only", default="all", choices=["all", "vectors"], help="vectors: SAXPY/SDOT only (profiling)")
     ap.add_argument("--vec-log2n", type=int, default=28, help="log2 of the vector length of the SAXPY/SDOT leg")
+    ap.add_argument("--sweep", action="store_true", help="config 2: N = 256..6144 step 256, both paths (prints a table object)")
     ap.add_argument("--abft", action="store_true", help="time the fault-tolerant SGEMM as the headline step (profiling)")
     ap.add_argument("--quick", action="store_true", help="headline kernel only (no extras); used for profiling")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -33,7 +33,8 @@ class FtReport(C.Structure):
     """``b2_ft_report`` of include/b2blas.h."""
 
     _fields_ = [("tiles", C.c_int32), ("injected", C.c_int32), ("detected", C.c_int32),
-                ("corrected", C.c_int32), ("uncorrectable", C.c_int32), ("reserved", C.c_int32 * 3)]
+                ("corrected", C.c_int32), ("uncorrectable", C.c_int32), ("false_alarms", C.c_int32),
+                ("reserved", C.c_int32 * 2)]
 
 
 def declared_symbols() -> list[str]:
@@ -93,6 +94,8 @@ def load() -> C.CDLL:
     L.b2_check_status.argtypes = [vp, vp]
     L.b2_set_ffma_variant.argtypes = [i32]
     L.b2_set_tf32_b_layout.argtypes = [i32]
+    L.b2_ffma_tile_info.argtypes = [i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_char_p)]
+    L.b2_set_ffma_tile.argtypes = [i32]
     _lib = L
     return L
 

@@ -146,7 +146,8 @@ def new_report() -> torch.Tensor:
 
 def read_report(report: torch.Tensor) -> dict:
     v = report.cpu().tolist()
-    return {"tiles": v[0], "injected": v[1], "detected": v[2], "corrected": v[3], "uncorrectable": v[4]}
+    return {"tiles": v[0], "injected": v[1], "detected": v[2], "corrected": v[3], "uncorrectable": v[4],
+            "false_alarms": v[5]}
 
 
 def saxpy(n, alpha, x, y, handle=None):
@@ -279,6 +280,22 @@ def device_info() -> dict:
 
 def set_ffma_variant(v: int):
     check(_lib.load().b2_set_ffma_variant(v))
+
+
+def ffma_tiles() -> list:
+    """The generated FFMA tile family: [(index, name, bm, bn, threads)]."""
+    L = _lib.load()
+    out = []
+    for i in range(L.b2_ffma_tile_count()):
+        bm, bn, th, name = C.c_int(), C.c_int(), C.c_int(), C.c_char_p()
+        check(L.b2_ffma_tile_info(i, C.byref(bm), C.byref(bn), C.byref(th), C.byref(name)))
+        out.append((i, name.value.decode(), bm.value, bn.value, th.value))
+    return out
+
+
+def set_ffma_tile(index: int):
+    """Pin the FFMA tile (index into ``ffma_tiles()``); -1 restores the automatic choice."""
+    check(_lib.load().b2_set_ffma_tile(index))
 
 
 def set_tf32_b_layout(mn_major: bool):

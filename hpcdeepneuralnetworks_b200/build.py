@@ -41,7 +41,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    headers = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + [os.path.join(PKG, "..", "include", "b2blas.h")]
+    headers = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + sorted(glob.glob(os.path.join(CSRC, "*.inc"))) + [os.path.join(PKG, "..", "include", "b2blas.h")]
     jobs = []
     objs = []
     for src in sources:

@@ -100,11 +100,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a short
-// hardware-defined time) and returns false; the caller records B2_ERR_TIMEOUT and leaves.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 24)) {
-  for (uint32_t i = 0; i < limit; ++i)
+// Bounded wait: polls the barrier and gives up about one second after the first failed poll
+// (wall clock of the device's global timer, checked every 256 polls) or after `limit` polls,
+// whichever comes first; returns false, the caller records B2_ERR_TIMEOUT and leaves.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) return false;
+  }
   return false;
 }
 

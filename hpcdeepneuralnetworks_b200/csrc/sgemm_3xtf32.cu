@@ -103,6 +103,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   const int m0 = tile_m * TBM, n0 = tile_n * TBN;
   const int nkb = (p.K + TBK - 1) / TBK;
 
+  if (*reinterpret_cast<volatile int *>(p.status) != 0) return;  // an earlier CTA of this launch timed out
   if (tid == 0) {
     for (int s = 0; s < TSTAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -196,9 +197,10 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     if (nkb > 0) {
       // poll in slices so that an abort raised by the other roles is seen
       bool done = false;
+      const uint64_t t0 = global_timer_ns();
       for (int it = 0; it < (1 << 14) && !done; ++it) {
         done = mbar_wait(acc_ready, 0, 1u << 10);
-        if (!done && *abort_flag) break;
+        if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
       }
       ok = done;
     }

@@ -1,19 +1,21 @@
-// FP32 SIMT (FFMA) SGEMM for sm_100a: row-major C = alpha*A*B + beta*C, any M, N, K.
+// FP32 SIMT (FFMA) SGEMM and ABFT SGEMM for sm_100a: row-major C = alpha*A*B + beta*C, any
+// M, N, K.
 //
 // Stands in for rung 14 of the reference series (kernel/sgemm/include/kernel_14.cuh:12:
-// 128x128x32 block tile, 256 threads, 8x8 outputs per thread) and, through the
-// column-major shim, for the plain tile family of kernel/ft_sgemm
-// (include_code_gen/sgemm_huge.cuh:11).  What is different on Blackwell:
+// 128x128x32 block tile, 256 threads, 8x8 outputs per thread), for the plain and ABFT tile
+// families of kernel/ft_sgemm (include_code_gen/{ft_}sgemm_{small..huge}.cuh:11, hand-written
+// include/ft_sgemm_huge.cuh:21) and, through gen_ft_sgemm.py, for its code generator
+// (code_gen/code_gen.py:4, code_gen/main.py:8-19).  What is different on Blackwell:
 //   * A and B slabs are brought in by TMA (cp.async.bulk.tensor) into a 3-stage shared
 //     ring guarded by full/empty mbarriers; no thread spends issue slots on global loads,
 //     and out-of-range rows/columns/K are zero-filled by the copy engine, so any shape works.
 //   * A stays K-contiguous in shared memory (TMA cannot transpose) under the 128-byte
-//     swizzle; a thread reads a float4 ALONG K for each of its 8 rows, which costs the same
+//     swizzle; a thread reads a float4 ALONG K for each of its 4 rows, which costs the same
 //     number of 128-bit shared loads as the reference's transposed store scheme
 //     (kernel_9.cuh:37-40) and is bank-conflict free.
-//   * 8 warps stacked along M, each spanning 16 rows x 128 columns, lanes as 4 (M) x 8 (N),
-//     4 x 16 outputs per thread: the warp tiling idea of kernel_11.cuh:22-27 with a shape
-//     chosen for the swizzled A reads and for the packed FMA below.
+//   * BM/16 warps stacked along M, each spanning 16 rows x BN columns, lanes as 4 (M) x 8 (N),
+//     4 x NR outputs per thread (NR = BN/8): the warp tiling idea of kernel_11.cuh:22-27 with
+//     a shape chosen for the swizzled A reads and for the packed FMA below.
 //   * The inner product uses the packed fma.rn.f32x2 instruction (two FP32 FMAs per issue
 //     slot, pairs of adjacent columns); only the 4 A values per k have to be duplicated into
 //     both halves of an operand.  Per output the arithmetic is still one FMA per k in
@@ -23,16 +25,17 @@
 // Each output element is accumulated by exactly one thread in ascending k with one FMA per
 // k, and the epilogue is fma(alpha, acc, beta*c) (alpha*acc when beta == 0; C is then not
 // read).
+//
+// The tile family (block tile BM x BN, BK = 32) is listed in ffma_tiles.inc, which
+// gen_ft_sgemm.py writes; every entry is instantiated plain and with ABFT.
+#include <math.h>
 #include <stdlib.h>
 
 #include "common.cuh"
 
 namespace b2 {
 
-constexpr int FBM = 128, FBN = 128, FBK = 32, FSTAGES = 3;
-constexpr int kStageA = FBM * FBK * 4;  // 16 KB, 128 rows of 128 bytes, 128B-swizzled
-constexpr int kStageB = FBK * FBN * 4;  // 16 KB, 32 rows of 512 bytes, linear
-constexpr int kFfmaSmem = 1024 + FSTAGES * (kStageA + kStageB) + 1024;
+constexpr int FBK = 32, FSTAGES = 3;
 constexpr int kGroupM = 16;  // tile rasterisation: 16 tile-rows share their B panels in L2
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -48,7 +51,6 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
-
 __device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
@@ -63,26 +65,73 @@ struct FfmaArgs {
   int *status;  // device status word: set to B2_ERR_TIMEOUT if a bounded wait runs out
 };
 
-// Accumulators of one thread: 4 rows x 16 columns (a wide tile keeps the number of A values that
-// must be duplicated into both halves of a packed operand at 4 per k).  Row i is tile row
-// warp*16 + lm + 4*i (row-major A) or warp*16 + lm*4 + i (transposed A); column j is tile
-// column ln*4 + 32*(j/4) + j%4, so one warp spans all 128 columns of 16 rows.
-template <bool PACKED>
+// ABFT arguments.  Checksum algebra of kernel/ft_sgemm/README.md:4-14 at the granularity the
+// accumulators are held: block (w, g) = the 16 rows of warp w x the NR columns of lane column g
+// (64 blocks of 16 x 16 in a 128 x 128 tile).  With Asum_w[k] = sum of A over the 16 rows of w
+// (a column checksum e^T A of that row band) and Bsum_g[k] = sum of B[k][.] over the columns
+// of g (a row checksum B e of that column set),
+//     sum of the block's outputs = sum_k Asum_w[k] * Bsum_g[k].
+// Both sums are formed slab by slab in the mainloop from the shared-memory stage that the FMAs
+// consume (the reference encodes from the registers it prefetched,
+// kernel/ft_sgemm/include/ft_sgemm_tall.cuh:178-267):
+//   phase 1 (before the slab's FMAs): each warp sums its own 16 rows of the A slab (4 loads,
+//           packed adds, a 3-shuffle transpose-reduce) and keeps the 32 sums in a private
+//           shared row; thread (k, g) sums the NR columns of g in row k of the B slab into a
+//           per-stage shared table, announced on a split-phase mbarrier;
+//   phase 2 (after the FMAs, when all warps' sums have long arrived): lane (g, r) adds
+//           sum_{8 k of r} Asum_w[k] * Bsum_g[k] to its running checksum (4 packed FMAs).
+// The epilogue folds the 4 k-ranges and the 4 x NR accumulators of the 4 lanes that share a
+// block with two shuffles each and compares them in registers (the reference compares every
+// 256 of K through shared memory, ft_sgemm_huge.cuh:143-271).  A block out of tolerance is
+// recomputed element by element from A and B in global memory with the kernel's own
+// arithmetic; every accumulator that differs is replaced, which both locates and corrects
+// the fault exactly (the reference subtracts a rounded residual with the location left
+// unfinished, ft_sgemm_huge.cuh:296-371).
+struct FtArgs {
+  const b2_fault *plan;
+  int n_faults;
+  float tau;
+  int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable, false alarms
+  const float *A, *B;
+  int lda, ldb;
+};
+
+template <int BM, int NR>
+struct TileCfg {
+  static constexpr int BN = 8 * NR;
+  static constexpr int WARPS = BM / 16;
+  static constexpr int THREADS = 32 * WARPS;
+  static constexpr int kStageA = BM * FBK * 4;
+  static constexpr int kStageB = FBK * BN * 4;
+  static constexpr int kBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[3]
+  static constexpr int kAwOff = kBarOff + 128;                   // float Asum[WARPS][32]
+  static constexpr int kBgOff = kAwOff + WARPS * 128;            // float Bsum[FSTAGES][8][32]
+  static constexpr int kMiscOff = kBgOff + FSTAGES * 1024;       // int inj[8]; int nflag; int flagged[64]
+  static constexpr int kSmem = 1024 + kMiscOff + 512;
+  static constexpr int MIN_BLOCKS = 512 / THREADS;
+  static_assert(BM % 16 == 0 && BM >= 32 && BM <= 128, "BM is 32, 64 or 128");
+  static_assert(NR == 8 || NR == 16, "NR is 8 or 16 columns per thread");
+};
+
+// Accumulators of one thread: 4 rows x NR columns.  Row i is tile row warp*16 + lm + 4*i
+// (row-major A) or warp*16 + lm*4 + i (transposed A); column j is tile column
+// ln*4 + 32*(j/4) + j%4, so one warp spans all BN columns of 16 rows.
+template <bool PACKED, int NR>
 struct Acc;
-template <>
-struct Acc<false> {
-  float v[4][16];
+template <int NR>
+struct Acc<false, NR> {
+  float v[4][NR];
   __device__ __forceinline__ void zero() {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
+      for (int j = 0; j < NR; ++j) v[i][j] = 0.f;
   }
-  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[4]) {
+  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[NR / 4]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < NR / 4; ++q) {
         v[i][4 * q + 0] = __fmaf_rn(a[i], b[q].x, v[i][4 * q + 0]);
         v[i][4 * q + 1] = __fmaf_rn(a[i], b[q].y, v[i][4 * q + 1]);
         v[i][4 * q + 2] = __fmaf_rn(a[i], b[q].z, v[i][4 * q + 2]);
@@ -91,20 +140,28 @@ struct Acc<false> {
   }
   __device__ __forceinline__ float get(int i, int j) const { return v[i][j]; }
   __device__ __forceinline__ void set(int i, int j, float x) { v[i][j] = x; }
+  __device__ __forceinline__ float total() const {
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NR; ++j) s[i] += v[i][j];
+    return (s[0] + s[1]) + (s[2] + s[3]);
+  }
 };
-template <>
-struct Acc<true> {
-  uint64_t v[4][8];  // pairs of adjacent columns
+template <int NR>
+struct Acc<true, NR> {
+  uint64_t v[4][NR / 2];  // pairs of adjacent columns
   __device__ __forceinline__ void zero() {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = 0ull;
+      for (int j = 0; j < NR / 2; ++j) v[i][j] = 0ull;
   }
-  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[4]) {
-    uint64_t bp[8];
+  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[NR / 4]) {
+    uint64_t bp[NR / 2];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < NR / 4; ++q) {
       bp[2 * q] = pack2(b[q].x, b[q].y);
       bp[2 * q + 1] = pack2(b[q].z, b[q].w);
     }
@@ -112,7 +169,7 @@ struct Acc<true> {
     for (int i = 0; i < 4; ++i) {
       const uint64_t aa = pack2(a[i], a[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = ffma2(aa, bp[j], v[i][j]);
+      for (int j = 0; j < NR / 2; ++j) v[i][j] = ffma2(aa, bp[j], v[i][j]);
     }
   }
   __device__ __forceinline__ float get(int i, int j) const {
@@ -125,6 +182,18 @@ struct Acc<true> {
     unpack2(v[i][j >> 1], lo, hi);
     if (j & 1) hi = x; else lo = x;
     v[i][j >> 1] = pack2(lo, hi);
+  }
+  __device__ __forceinline__ float total() const {
+    uint64_t s[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[i] = v[i][0];
+#pragma unroll
+      for (int j = 1; j < NR / 2; ++j) s[i] = fadd2(s[i], v[i][j]);
+    }
+    float lo, hi;
+    unpack2(fadd2(fadd2(s[0], s[1]), fadd2(s[2], s[3])), lo, hi);
+    return lo + hi;
   }
 };
 
@@ -144,82 +213,64 @@ __device__ __forceinline__ int acc_row(int warp, int lm, int i) {
 }
 __device__ __forceinline__ int acc_col(int ln, int j) { return ln * 4 + 32 * (j >> 2) + (j & 3); }
 
-// ---- ABFT additions (FT = true) ----------------------------------------------------------
-// Checksum algebra of kernel/ft_sgemm/README.md:4-14 per 128x128 output tile T = A_t * B_t:
-//   row checksum   T e   = A_t (B_t e)      one value per tile row
-//   col checksum   e^T T = (e^T A_t) B_t    one value per tile column
-// Encoding happens slab by slab inside the mainloop, on the shared-memory stage the FMAs are
-// about to consume (the reference encodes from the registers it prefetched,
-// kernel/ft_sgemm/include/ft_sgemm_tall.cuh:178-267):
-//   phase 1 (before the FMAs of the slab): warp w sums k-chunk w of the A slab over the 128
-//           rows and rows 4w..4w+3 of the B slab over the 128 columns -> 32 + 32 slab sums in
-//           shared memory, announced on a split-phase mbarrier;
-//   phase 2 (after the FMAs, when every warp's sums have long arrived): threads 0..127 add
-//           sum_k A[row][k] * Bsum[k] to their row checksum, threads 128..255 add
-//           Asum[k] * B[k][4 columns] for 8 k to their partial column checksums.
-// The epilogue compares the checksums with the row and column sums of the accumulators
-// (the reference does this every 256 of K, ft_sgemm_huge.cuh:143-271); a single row and a
-// single column out of tolerance locate the faulty accumulator, which is rebuilt as
-// row checksum - (sum of the other accumulators of that row).
-struct FtArgs {
-  const b2_fault *plan;
-  int n_faults;
-  float tau;
-  int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable
-};
-
-constexpr int kFtBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[3]
-constexpr int kFtSumOff = kFtBarOff + 128;                // float2 sAc[3][32] (each sum twice), float sBr[3][32]
-constexpr int kFtInjOff = kFtSumOff + 3 * FSTAGES * 32 * 4;  // int inj[8]
-
-template <bool PACKED, int KCU, bool TRANS_A, bool FT>
-__global__ void __launch_bounds__(256, 2)
+template <int BM, int NR, bool PACKED, bool TRANS_A, bool FT>
+__global__ void __launch_bounds__(TileCfg<BM, NR>::THREADS, TileCfg<BM, NR>::MIN_BLOCKS)
 sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FfmaArgs p,
                   const FtArgs ft) {
-  static_assert(!(FT && TRANS_A), "the ABFT encoder reads the row-major A stage");
+  using Cfg = TileCfg<BM, NR>;
+  constexpr int BN = Cfg::BN, WARPS = Cfg::WARPS, THREADS = Cfg::THREADS;
+  constexpr int kStageA = Cfg::kStageA, kStageB = Cfg::kStageB, BROW = BN * 4;  // bytes per k row of the B stage
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
   unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char *sA = smem;
   unsigned char *sB = smem + FSTAGES * kStageA;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + kFtBarOff);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + Cfg::kBarOff);
   uint64_t *empty = full + FSTAGES;
   uint64_t *sums_ready = empty + FSTAGES;
-  unsigned char *sAc = smem + kFtSumOff;               // [stage][32] column sums of the A slab, as (s,s) pairs
-  unsigned char *sBr = sAc + FSTAGES * 256;            // [stage][32] row sums of the B slab
-  int *inj = reinterpret_cast<int *>(smem + kFtInjOff);
+  unsigned char *sAw = smem + Cfg::kAwOff;   // [warp][32] sums of the warp's 16 rows of the A slab
+  unsigned char *sBg = smem + Cfg::kBgOff;   // [stage] 1 KB table of the sums of column set g of the B slab per k
+  int *inj = reinterpret_cast<int *>(smem + Cfg::kMiscOff);
+  int *nflag = inj + 8;
+  int *flagged = inj + 9;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int lm = lane >> 3, ln = lane & 7;
-  const int tiles_m = (p.M + FBM - 1) / FBM, tiles_n = (p.N + FBN - 1) / FBN;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   int tile_m, tile_n;
   tile_of_block(blockIdx.x, tiles_m, tiles_n, tile_m, tile_n);
-  const int m0 = tile_m * FBM, n0 = tile_n * FBN;
+  const int m0 = tile_m * BM, n0 = tile_n * BN;
   const int nkb = (p.K + FBK - 1) / FBK;
 
+  if (*reinterpret_cast<volatile int *>(p.status) != 0) return;  // an earlier CTA of this launch timed out
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < FSTAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 8);
-      if (FT) mbar_init(&sums_ready[s], 8);
+      mbar_init(&empty[s], WARPS);
+      if (FT) mbar_init(&sums_ready[s], WARPS);
     }
+    if (FT) *nflag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
-  if (FT && warp == 1) {
-    // first planned fault that names this tile (a plan holds at most one per tile)
+  if (FT && warp == WARPS - 1) {
+    // first planned fault that names this tile (a plan holds at most one per tile; tiles are
+    // counted in units of this kernel's block tile)
     int found = 0x7fffffff;
-    for (int f = lane; f < ft.n_faults; f += 32)
-      if (ft.plan[f].tile_m == tile_m && ft.plan[f].tile_n == tile_n && f < found) found = f;
+    for (int f = lane; f < ft.n_faults; f += 32) {
+      // the plan addresses 128 x 128 tiles; map its (row, col) into this kernel's tile grid
+      const int gr = ft.plan[f].tile_m * 128 + ft.plan[f].row, gc = ft.plan[f].tile_n * 128 + ft.plan[f].col;
+      if (gr / BM == tile_m && gc / BN == tile_n && f < found) found = f;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) found = min(found, __shfl_xor_sync(0xffffffffu, found, o));
     if (lane == 0) {
       inj[0] = (found != 0x7fffffff);
       if (inj[0]) {
-        inj[1] = ft.plan[found].row;
-        inj[2] = ft.plan[found].col;
+        inj[1] = (ft.plan[found].tile_m * 128 + ft.plan[found].row) - m0;
+        inj[2] = (ft.plan[found].tile_n * 128 + ft.plan[found].col) - n0;
         inj[3] = ft.plan[found].k_step;
         inj[4] = ft.plan[found].bit;
       }
@@ -235,29 +286,28 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
 
-  // planned fault: which slab, and (for the owning thread only) which accumulator
-  int inj_kb = -1;  // slab after which this thread flips a bit (-1: never); the rest is re-read from inj[]
+  // planned fault: the slab after which the owning thread flips a bit (-1: not this thread)
+  int inj_kb = -1;
   if (FT && inj[0]) {
     const int r = inj[1], c = inj[2];
-    const bool own = r >= 0 && r < FBM && c >= 0 && c < FBN && (r >> 4) == warp && (r & 3) == lm && ((c & 31) >> 2) == ln;
-    if (own) {
-      inj_kb = inj[3] < 0 ? 0 : (inj[3] >= nkb ? nkb - 1 : inj[3]);
-    }
+    const bool own = r >= 0 && r < BM && c >= 0 && c < BN && (r >> 4) == warp &&
+                     (TRANS_A ? (((r & 15) >> 2) == lm) : ((r & 3) == lm)) && ((c & 31) >> 2) == ln;
+    if (own) inj_kb = inj[3] < 0 ? 0 : (inj[3] >= nkb ? nkb - 1 : inj[3]);
   }
 
-  Acc<PACKED> acc;
+  Acc<PACKED, NR> acc;
   acc.zero();
   // Byte offsets inside a stage.  A: row r at r*128, 16-byte chunk c of that row at
   // ((c ^ (r & 7)) << 4); rows of this thread are warp*16 + lm + 4*i, so r & 7 is lm for even
-  // i and lm + 4 for odd i.  B: row k at k*512, column c at c*4.
+  // i and lm + 4 for odd i.  B: row k at k*BROW, column c at c*4.
   const uint32_t a_thread = TRANS_A ? (uint32_t)(warp * 16 + lm * 4) * 4u : (uint32_t)(warp * 16 + lm) * 128u;
   const uint32_t a_swz = (uint32_t)lm << 4;
   const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;
-  // ABFT: per-thread byte offsets of the encoder, fixed for the whole kernel
-  const uint32_t p1a_off = (uint32_t)lane * 128u + (uint32_t)((warp ^ (lane & 7)) << 4);   // A: rows lane+32q, k-chunk = warp
-  const uint32_t p1b_off = (uint32_t)(warp * 4 + (lane >> 3)) * 512u + (uint32_t)(lane & 7) * 16u;  // B: row 4*warp + lane/8
-  const uint32_t p2_off = (warp < 4) ? (uint32_t)tid * 128u : (uint32_t)(((tid - 128) >> 5) * 8) * 512u + (uint32_t)((tid - 128) & 31) * 16u;
-  uint64_t chk2[2] = {0ull, 0ull};  // FT: packed running checksums (row: 2 pairs folded at the end; column: 4 columns)
+  // ABFT encoder offsets: this lane's part of the warp's 16 A rows, and its (k, g) cells of B
+  const uint32_t e_a_off = TRANS_A ? (uint32_t)lane * (BM * 4) + (uint32_t)warp * 64u
+                                   : (uint32_t)(warp * 16 + lm) * 128u + (uint32_t)((ln ^ lm) << 4);
+  const uint32_t e_b_off = (uint32_t)(tid >> 3) * BROW + (uint32_t)(tid & 7) * 16u;
+  uint64_t chk2[2] = {0ull, 0ull};  // running checksum of block (warp, ln) over this lane's k-range, packed
   bool ok = true;
 
   for (int kb = 0; kb < nkb; ++kb) {
@@ -269,61 +319,103 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     const unsigned char *Ast = sA + s * kStageA;
     const unsigned char *Bst = sB + s * kStageB;
-    if (FT) {
-      // ---- phase 1: slab sums (packed adds; offsets precomputed) ----
-      const unsigned char *pa_ptr = Ast + p1a_off;
-      ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(pa_ptr);
-      ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(pa_ptr + 32 * 128);
-      ulonglong2 v2 = *reinterpret_cast<const ulonglong2 *>(pa_ptr + 64 * 128);
-      ulonglong2 v3 = *reinterpret_cast<const ulonglong2 *>(pa_ptr + 96 * 128);
-      const uint64_t pxy = fadd2(fadd2(v0.x, v1.x), fadd2(v2.x, v3.x));
-      const uint64_t pzw = fadd2(fadd2(v0.y, v1.y), fadd2(v2.y, v3.y));
-      float px, py, pz, pw;
-      unpack2(pxy, px, py);
-      unpack2(pzw, pz, pw);
-      // 4 components x 32 lanes -> 4 totals: halve the live components while folding lanes
-      const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
-      float k0 = h16 ? pz : px, k1 = h16 ? pw : py;
-      k0 += __shfl_xor_sync(0xffffffffu, h16 ? px : pz, 16);
-      k1 += __shfl_xor_sync(0xffffffffu, h16 ? py : pw, 16);
-      float ka = h8 ? k1 : k0;
-      ka += __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
-      ka += __shfl_xor_sync(0xffffffffu, ka, 4);
-      ka += __shfl_xor_sync(0xffffffffu, ka, 2);
-      ka += __shfl_xor_sync(0xffffffffu, ka, 1);
-      if ((lane & 7) == 0)
-        *reinterpret_cast<float2 *>(sAc + s * 256 + (warp * 4 + (h16 ? 2 : 0) + (h8 ? 1 : 0)) * 8) = make_float2(ka, ka);
-      const unsigned char *pb_ptr = Bst + p1b_off;
-      v0 = *reinterpret_cast<const ulonglong2 *>(pb_ptr);
-      v1 = *reinterpret_cast<const ulonglong2 *>(pb_ptr + 128);
-      v2 = *reinterpret_cast<const ulonglong2 *>(pb_ptr + 256);
-      v3 = *reinterpret_cast<const ulonglong2 *>(pb_ptr + 384);
-      const uint64_t sb2 = fadd2(fadd2(fadd2(v0.x, v0.y), fadd2(v1.x, v1.y)), fadd2(fadd2(v2.x, v2.y), fadd2(v3.x, v3.y)));
-      float sbx, sby;
-      unpack2(sb2, sbx, sby);
-      float sb = sbx + sby;
-      sb += __shfl_xor_sync(0xffffffffu, sb, 1);
-      sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-      sb += __shfl_xor_sync(0xffffffffu, sb, 4);
-      if ((lane & 7) == 0) *reinterpret_cast<float *>(sBr + s * 128 + (warp * 4 + (lane >> 3)) * 4) = sb;
+    // ---- ABFT phase 1 (slab sums) and phase 2 (fold the PREVIOUS slab's sums into the running
+    // checksum) are issued from inside the unrolled FMA stream below, so that their load ->
+    // add -> shuffle -> store chains overlap with FMAs instead of idling the warp.
+    auto phase1 = [&]() {
+      // ---- phase 1: slab sums ----
+      float aw;  // this lane's entry of the warp's 32 A sums: k = 4*ln + lm, or k = lane for transposed A
+      if (TRANS_A) {
+        const unsigned char *pa = Ast + e_a_off;  // row k = lane of the [k][BM] stage, the warp's 16 columns
+        const ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(pa);
+        const ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(pa + 16);
+        const ulonglong2 v2 = *reinterpret_cast<const ulonglong2 *>(pa + 32);
+        const ulonglong2 v3 = *reinterpret_cast<const ulonglong2 *>(pa + 48);
+        float lo, hi;
+        unpack2(fadd2(fadd2(fadd2(v0.x, v0.y), fadd2(v1.x, v1.y)), fadd2(fadd2(v2.x, v2.y), fadd2(v3.x, v3.y))), lo, hi);
+        aw = lo + hi;
+      } else {
+        // rows warp*16 + lm + 4e (e = 0..3), k-chunk ln; rows with (r & 7) >= 4, i.e. odd e, sit in
+        // the 16-byte chunk with bit 2 flipped (128-byte swizzle)
+        const ulonglong2 w0 = *reinterpret_cast<const ulonglong2 *>(Ast + e_a_off);
+        const ulonglong2 w1 = *reinterpret_cast<const ulonglong2 *>(Ast + ((e_a_off ^ 64u) + 512));
+        const ulonglong2 w2 = *reinterpret_cast<const ulonglong2 *>(Ast + (e_a_off + 1024));
+        const ulonglong2 w3 = *reinterpret_cast<const ulonglong2 *>(Ast + ((e_a_off ^ 64u) + 1536));
+        const uint64_t pxy = fadd2(fadd2(w0.x, w1.x), fadd2(w2.x, w3.x));
+        const uint64_t pzw = fadd2(fadd2(w0.y, w1.y), fadd2(w2.y, w3.y));
+        float px, py, pz, pw;
+        unpack2(pxy, px, py);
+        unpack2(pzw, pz, pw);
+        // 4 components x 4 lanes (lm) -> one total per lane: halve the live components per fold
+        const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
+        float k0 = h16 ? pz : px, k1 = h16 ? pw : py;
+        k0 += __shfl_xor_sync(0xffffffffu, h16 ? px : pz, 16);
+        k1 += __shfl_xor_sync(0xffffffffu, h16 ? py : pw, 16);
+        aw = h8 ? k1 : k0;
+        aw += __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
+      }
+      __syncwarp();  // the previous slab's phase-2 reads of this warp's row are done
+      *reinterpret_cast<float *>(sAw + warp * 128 + (TRANS_A ? lane : (4 * ln + lm)) * 4) = aw;
+      // B: cell (k, g) = sum of the NR columns of column set g in row k; THREADS cells per pass
+#pragma unroll
+      for (int pass = 0; pass < 256 / THREADS; ++pass) {
+        const unsigned char *pb = Bst + e_b_off + pass * (THREADS / 8) * BROW;
+        uint64_t sb2;
+        {
+          const ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(pb);
+          const ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(pb + 128);
+          sb2 = fadd2(fadd2(v0.x, v0.y), fadd2(v1.x, v1.y));
+          if (NR == 16) {
+            const ulonglong2 v2 = *reinterpret_cast<const ulonglong2 *>(pb + 256);
+            const ulonglong2 v3 = *reinterpret_cast<const ulonglong2 *>(pb + 384);
+            sb2 = fadd2(sb2, fadd2(fadd2(v2.x, v2.y), fadd2(v3.x, v3.y)));
+          }
+        }
+        float lo, hi;
+        unpack2(sb2, lo, hi);
+        const int k = (tid >> 3) + pass * (THREADS / 8);
+        // table layout: k = 8r + 4h + e of column set g at h*512 + (r*8 + g)*16 + e*4, so that the 32 lanes
+        // (g, r) of a warp read each half as one contiguous 512-byte row in phase 2
+        *reinterpret_cast<float *>(sBg + s * 1024 + ((k >> 2) & 1) * 512 + ((k >> 3) * 8 + (tid & 7)) * 16 + (k & 3) * 4) = lo + hi;
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&sums_ready[s]);
-    }
+    };
+    auto phase2 = [&](int ps, uint32_t pparity) -> bool {
+      if (!mbar_wait(&sums_ready[ps], pparity)) return false;
+      const unsigned char *pw = sAw + warp * 128 + lm * 32;
+      const unsigned char *pg = sBg + ps * 1024 + (lm * 8 + ln) * 16;
+      const ulonglong2 a01 = *reinterpret_cast<const ulonglong2 *>(pw);
+      const ulonglong2 a23 = *reinterpret_cast<const ulonglong2 *>(pw + 16);
+      const ulonglong2 g01 = *reinterpret_cast<const ulonglong2 *>(pg);
+      const ulonglong2 g23 = *reinterpret_cast<const ulonglong2 *>(pg + 512);
+      chk2[0] = ffma2(a01.x, g01.x, chk2[0]);
+      chk2[1] = ffma2(a01.y, g01.y, chk2[1]);
+      chk2[0] = ffma2(a23.x, g23.x, chk2[0]);
+      chk2[1] = ffma2(a23.y, g23.y, chk2[1]);
+      return true;
+    };
+    const int sprev = (kb + FSTAGES - 1) % FSTAGES;
+    const uint32_t pprev = (uint32_t)((kb - 1) / FSTAGES) & 1u;
     const unsigned char *As = Ast + a_thread;
     const unsigned char *Bs = Bst + b_thread;
     if (TRANS_A) {
-#pragma unroll(KCU * 4)
-      for (int k = 0; k < FBK; ++k) {
-        const float4 a4 = *reinterpret_cast<const float4 *>(As + k * 512);
-        float4 b[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + k * 512 + q * 128);
+      for (int k = 0; k < FBK; ++k) {
+        if (FT && k == 4 && kb > 0 && !phase2(sprev, pprev)) ok = false;
+        if (FT && k == 8) phase1();
+        const float4 a4 = *reinterpret_cast<const float4 *>(As + k * (BM * 4));
+        float4 b[NR / 4];
+#pragma unroll
+        for (int q = 0; q < NR / 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + k * BROW + q * 128);
         const float a[4] = {a4.x, a4.y, a4.z, a4.w};
         acc.step(a, b);
       }
     } else {
-#pragma unroll(KCU)
+#pragma unroll
       for (int kc = 0; kc < FBK / 4; ++kc) {
+        if (FT && kc == 1 && kb > 0 && !phase2(sprev, pprev)) ok = false;
+        if (FT && kc == 2) phase1();
         const uint32_t y0 = ((uint32_t)kc << 4) ^ a_swz, y1 = y0 ^ 64u;
         float4 a4[4];
 #pragma unroll
@@ -331,9 +423,9 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           a4[i] = *reinterpret_cast<const float4 *>(As + ((i & 1) ? y1 : y0) + i * 512);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          float4 b[4];
+          float4 b[NR / 4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + (kc * 4 + kk) * 512 + q * 128);
+          for (int q = 0; q < NR / 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + (kc * 4 + kk) * BROW + q * 128);
           float a[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) a[i] = (kk == 0) ? a4[i].x : (kk == 1) ? a4[i].y : (kk == 2) ? a4[i].z : a4[i].w;
@@ -342,46 +434,15 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
     if (FT) {
-      // ---- phase 2: fold the slab sums into the running checksums ----
-      if (!mbar_wait(&sums_ready[s], parity)) {
-        ok = false;
-        break;
-      }
-      if (warp < 4) {
-        // row checksum of tile row tid: sum_k A[tid][k] * Bsum[k], two packed chains
-        const unsigned char *Arow = Ast + p2_off;
-        const uint32_t sw = (uint32_t)(tid & 7) << 4;
-        const unsigned char *br = sBr + s * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const ulonglong2 a = *reinterpret_cast<const ulonglong2 *>(Arow + (((uint32_t)c << 4) ^ sw));
-          const ulonglong2 b = *reinterpret_cast<const ulonglong2 *>(br + c * 16);
-          chk2[0] = ffma2(a.x, b.x, chk2[0]);
-          chk2[1] = ffma2(a.y, b.y, chk2[1]);
-        }
-      } else {
-        // partial checksums of 4 columns over 8 k: Asum[k] * B[k][4 columns]
-        const unsigned char *Bcol = Bst + p2_off;
-        const unsigned char *ac = sAc + s * 256 + ((tid - 128) >> 5) * 64;
-#pragma unroll
-        for (int kk = 0; kk < 8; kk += 2) {
-          const ulonglong2 a2 = *reinterpret_cast<const ulonglong2 *>(ac + kk * 8);  // (s_k, s_k, s_k+1, s_k+1)
-          const ulonglong2 b0 = *reinterpret_cast<const ulonglong2 *>(Bcol + kk * 512);
-          const ulonglong2 b1 = *reinterpret_cast<const ulonglong2 *>(Bcol + (kk + 1) * 512);
-          chk2[0] = ffma2(a2.x, b0.x, chk2[0]);
-          chk2[1] = ffma2(a2.x, b0.y, chk2[1]);
-          chk2[0] = ffma2(a2.y, b1.x, chk2[0]);
-          chk2[1] = ffma2(a2.y, b1.y, chk2[1]);
-        }
-      }
+      if (!ok) break;
       // ---- simulated soft error: flip one bit of one accumulator after this slab ----
       if (kb == inj_kb) {
-        const int inj_i = (inj[1] & 15) >> 2, inj_j = (inj[2] >> 5) * 4 + (inj[2] & 3);
+        const int inj_i = TRANS_A ? (inj[1] & 3) : ((inj[1] & 15) >> 2), inj_j = (inj[2] >> 5) * 4 + (inj[2] & 3);
         const uint32_t inj_mask = 1u << (inj[4] & 31);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
+          for (int j = 0; j < NR; ++j)
             if (i == inj_i && j == inj_j) acc.set(i, j, __uint_as_float(__float_as_uint(acc.get(i, j)) ^ inj_mask));
         atomicAdd(&ft.report[1], 1);
       }
@@ -389,7 +450,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);
     // Refill, one slab behind: the stage that slab kb-1 used gets slab kb-1+FSTAGES once all
-    // 8 warps have released it.
+    // warps have released it.
     if (tid == 0 && kb >= 1) {
       const int kprev = kb - 1, knext = kprev + FSTAGES;
       if (knext < nkb) {
@@ -405,118 +466,88 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   }
+  if (FT && ok && nkb > 0) {
+    // the last slab's sums have not been folded yet
+    const int ps = (nkb - 1) % FSTAGES;
+    if (mbar_wait(&sums_ready[ps], (uint32_t)((nkb - 1) / FSTAGES) & 1u)) {
+      const unsigned char *pw = sAw + warp * 128 + lm * 32;
+      const unsigned char *pg = sBg + ps * 1024 + (lm * 8 + ln) * 16;
+      const ulonglong2 a01 = *reinterpret_cast<const ulonglong2 *>(pw);
+      const ulonglong2 a23 = *reinterpret_cast<const ulonglong2 *>(pw + 16);
+      const ulonglong2 g01 = *reinterpret_cast<const ulonglong2 *>(pg);
+      const ulonglong2 g23 = *reinterpret_cast<const ulonglong2 *>(pg + 512);
+      chk2[0] = ffma2(a01.x, g01.x, chk2[0]);
+      chk2[1] = ffma2(a01.y, g01.y, chk2[1]);
+      chk2[0] = ffma2(a23.x, g23.x, chk2[0]);
+      chk2[1] = ffma2(a23.y, g23.y, chk2[1]);
+    } else {
+      ok = false;
+    }
+  }
   if (!ok) {
     atomicExch(p.status, (int)B2_ERR_TIMEOUT);
     return;
   }
 
   if (FT) {
-    // ---- verify, locate, correct (raw accumulators, before alpha/beta) ----
-    __syncthreads();  // every stage has been consumed by every warp: the ring is scratch now
-    float *scr = reinterpret_cast<float *>(sA);
-    float *rowsum_s = scr;            // [128]     row sums (a warp spans all columns of its rows)
-    float *colsum_s = scr + 128;      // [8][128]  partial column sums, one per warp
-    float *rowchk_s = scr + 1152;     // [128]
-    float *colchk_s = scr + 1280;     // [4][128]  partial column checksums, one per k-group
-    float *fix_part = scr + 1792;     // [8]
-    int *flags = reinterpret_cast<int *>(scr + 1800);  // nbad_r, nbad_c, bad_r, bad_c
-    float rs[4], cs[16];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) rs[i] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) cs[j] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float v = acc.get(i, j);
-        rs[i] += v;
-        cs[j] += v;
-      }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 1);
-      rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 2);
-      rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 4);
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 8);
-      cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 16);
-    }
-    if (ln == 0) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) rowsum_s[acc_row<TRANS_A>(warp, lm, i)] = rs[i];
-    }
-    if (lm == 0) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) colsum_s[warp * 128 + acc_col(ln, j)] = cs[j];
-    }
+    // ---- verify in registers, then recompute the blocks that are out of tolerance ----
+    float expect, actual = acc.total();
     {
       float c0, c1, c2, c3;
       unpack2(chk2[0], c0, c1);
       unpack2(chk2[1], c2, c3);
-      if (warp < 4) {
-        rowchk_s[tid] = (c0 + c1) + (c2 + c3);
-      } else {
-        const int j = tid - 128, cg = j & 31, kg = j >> 5;
-        *reinterpret_cast<float4 *>(&colchk_s[kg * 128 + cg * 4]) = make_float4(c0, c1, c2, c3);
-      }
+      expect = (c0 + c1) + (c2 + c3);
     }
-    if (tid < 4) flags[tid] = 0;
-    __syncthreads();
-    {
-      float actual, expect;
-      if (tid < 128) {
-        actual = rowsum_s[tid];
-        expect = rowchk_s[tid];
-      } else {
-        const int c = tid - 128;
-        actual = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) actual += colsum_s[w * 128 + c];
-        expect = (colchk_s[c] + colchk_s[128 + c]) + (colchk_s[256 + c] + colchk_s[384 + c]);
-      }
-      if (!(fabsf(actual - expect) <= ft.tau)) {  // NaN-safe: a NaN difference counts as out of tolerance
-        atomicAdd(&flags[tid < 128 ? 0 : 1], 1);
-        flags[tid < 128 ? 2 : 3] = tid & 127;
-      }
-    }
-    __syncthreads();
-    const int nbad_r = flags[0], nbad_c = flags[1];
-    if (nbad_r | nbad_c) {  // uniform over the block
-      if (nbad_r == 1 && nbad_c == 1) {
-        const int br = flags[2], bc = flags[3];
-        const bool own_row = (br >> 4) == warp && (br & 3) == lm;
-        const int bi = (br & 15) >> 2;
-        const bool own_col = own_row && ((bc & 31) >> 2) == ln;
-        const int bj = (bc >> 5) * 4 + (bc & 3);
-        if (own_row) {
-          float part = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (i == bi && !(own_col && j == bj)) part += acc.get(i, j);
-          fix_part[ln] = part;
+    expect += __shfl_xor_sync(0xffffffffu, expect, 8);
+    expect += __shfl_xor_sync(0xffffffffu, expect, 16);
+    actual += __shfl_xor_sync(0xffffffffu, actual, 8);
+    actual += __shfl_xor_sync(0xffffffffu, actual, 16);
+    const bool bad = !(fabsf(actual - expect) <= ft.tau);  // NaN-safe: a NaN difference is out of tolerance
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);      // also: the ring is idle from here on
+    if (any_bad) {                                           // uniform over the block
+      if (bad && lm == 0) flagged[atomicAdd(nflag, 1)] = warp * 8 + ln;
+      __syncthreads();
+      const int nf = *nflag;
+      float *rec = reinterpret_cast<float *>(sA);  // [16 rows][NR] recomputed outputs of one block
+      for (int f = 0; f < nf; ++f) {
+        const int bw = flagged[f] >> 3, bg = flagged[f] & 7;
+        for (int e = tid; e < 16 * NR; e += THREADS) {
+          const int er = e / NR, ec = e % NR;
+          const int row = m0 + bw * 16 + er, col = n0 + acc_col(bg, ec);
+          float v = 0.f;
+          if (row < p.M && col < p.N) {
+            const float *ap = TRANS_A ? ft.A + row : ft.A + (size_t)row * ft.lda;
+            const size_t astep = TRANS_A ? (size_t)ft.lda : 1;
+            const float *bp = ft.B + col;
+            for (int k = 0; k < p.K; ++k) v = __fmaf_rn(ap[k * astep], bp[(size_t)k * ft.ldb], v);
+          }
+          rec[e] = v;
         }
         __syncthreads();
-        if (own_col) {
-          float others = 0.f;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) others += fix_part[q];
-          const float rebuilt = rowchk_s[br] - others;
+        if (warp == bw && ln == bg) {
+          int fixed = 0;
 #pragma unroll
           for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (i == bi && j == bj) acc.set(i, j, rebuilt);
-          atomicAdd(&ft.report[2], 1);
-          atomicAdd(&ft.report[3], 1);
+            for (int j = 0; j < NR; ++j) {
+              const float want = rec[(acc_row<TRANS_A>(0, lm, i)) * NR + j];
+              if (__float_as_uint(want) != __float_as_uint(acc.get(i, j))) {
+                acc.set(i, j, want);
+                ++fixed;
+              }
+            }
+          fixed += __shfl_xor_sync(0x01010101u << bg, fixed, 8);
+          fixed += __shfl_xor_sync(0x01010101u << bg, fixed, 16);
+          if (lm == 0) {
+            if (fixed) {
+              atomicAdd(&ft.report[2], 1);
+              atomicAdd(&ft.report[3], fixed);
+            } else {
+              atomicAdd(&ft.report[5], 1);  // checksum out of tolerance but every output verified: false alarm
+            }
+          }
         }
-      } else if (tid == 0) {
-        if (nbad_r >= 1 && nbad_c >= 1) atomicAdd(&ft.report[2], 1);
-        atomicAdd(&ft.report[4], 1);
+        __syncthreads();
       }
     }
     if (tid == 0) atomicAdd(&ft.report[0], 1);
@@ -530,7 +561,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (row >= p.M) continue;
     float *crow = p.C + (size_t)row * p.ldc;
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
+    for (int h = 0; h < NR / 4; ++h) {
       const int col = n0 + ln * 4 + 32 * h;
       if (p.vec_c && col + 3 < p.N) {
         float4 o;
@@ -611,6 +642,7 @@ __global__ void scale_c_kernel(int M, int N, float beta, float *C, int ldc) {
 }
 
 static int g_ffma_variant = -1;  // -1: pick from B2_FFMA_VARIANT (default packed)
+static int g_ffma_tile = -1;     // -1: automatic; otherwise an index into the tile table
 
 static int ffma_variant() {
   if (g_ffma_variant < 0) {
@@ -621,18 +653,63 @@ static int ffma_variant() {
   return g_ffma_variant;
 }
 
-template <bool PACKED, int KCU, bool TRANS_A, bool FT = false>
+template <int BM, int NR, bool PACKED, bool TRANS_A, bool FT>
 static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s,
-                       const FtArgs &ft = FtArgs{nullptr, 0, 0.f, nullptr}) {
+                       const FtArgs &ft) {
+  using Cfg = TileCfg<BM, NR>;
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, KCU, TRANS_A, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfmaSmem));
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<PACKED, KCU, TRANS_A, FT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     configured = true;
   }
-  sgemm_ffma_kernel<PACKED, KCU, TRANS_A, FT><<<grid, 256, kFfmaSmem, s>>>(ta, tb, args, ft);
+  sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
+}
+
+// One row per generated tile: the launcher for each (packed?, transposed A?, ABFT?) combination.
+typedef int (*FfmaLauncher)(const CUtensorMap &, const CUtensorMap &, const FfmaArgs &, int, cudaStream_t, const FtArgs &);
+struct FfmaTile {
+  const char *name;
+  int bm, bn, threads;
+  float efficiency;  // measured fraction of the 128x128 tile's throughput, used by the picker
+  FfmaLauncher fn[2][2][2];  // [packed][trans_a][ft]
+};
+
+#define B2_FFMA_TILE(NAME, BM, NR, EFF)                                                          \
+  {NAME, BM, 8 * NR, 2 * BM, EFF,                                                                \
+   {{{launch_ffma<BM, NR, false, false, false>, launch_ffma<BM, NR, false, false, true>},        \
+     {launch_ffma<BM, NR, false, true, false>, launch_ffma<BM, NR, false, true, true>}},         \
+    {{launch_ffma<BM, NR, true, false, false>, launch_ffma<BM, NR, true, false, true>},          \
+     {launch_ffma<BM, NR, true, true, false>, launch_ffma<BM, NR, true, true, true>}}}},
+static const FfmaTile g_tiles[] = {
+#include "ffma_tiles.inc"
+};
+constexpr int kNumTiles = sizeof(g_tiles) / sizeof(g_tiles[0]);
+
+// Picks the tile with the best predicted throughput: its measured efficiency times how well its
+// CTA count fills whole waves of (512 / threads) co-resident CTAs per SM.  The fill term matters
+// less the more waves there are (the hardware back-fills), hence the 1/waves exponent.
+static int pick_tile(const Context *ctx, int M, int N) {
+  if (g_ffma_tile >= 0 && g_ffma_tile < kNumTiles) return g_ffma_tile;
+  int best = 0;
+  double best_score = -1.0;
+  for (int t = 0; t < kNumTiles; ++t) {
+    const FfmaTile &tl = g_tiles[t];
+    const double ctas = (double)((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
+    const double slots = (double)ctx->sm_count * (512 / tl.threads);
+    const double waves = ceil(ctas / slots);
+    const double fill = ctas / (waves * slots);
+    // padding: work done on rows/columns outside the matrix
+    const double useful = ((double)M * N) / (ctas * tl.bm * tl.bn);
+    const double score = tl.efficiency * pow(fill, 1.0 / waves) * useful;
+    if (score > best_score) {
+      best_score = score;
+      best = t;
+    }
+  }
+  return best;
 }
 
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
@@ -645,8 +722,8 @@ int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float al
   return sgemm_ffma_dispatch_ft(ctx, trans_a, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, nullptr, s);
 }
 
-// ft == nullptr: plain SGEMM.  Otherwise the ABFT kernel (row-major A only; operands must be
-// describable to TMA, i.e. 16-byte aligned with leading dimensions that are multiples of 4).
+// ft == nullptr: plain SGEMM.  Otherwise the ABFT kernel (operands must be describable to TMA,
+// i.e. 16-byte aligned with leading dimensions that are multiples of 4).
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s) {
   if (M == 0 || N == 0) return B2_OK;
@@ -657,9 +734,8 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
     return B2_OK;
   }
   const bool tma_ok = ((((uintptr_t)A | (uintptr_t)B) & 15) == 0) && (lda % 4 == 0) && (ldb % 4 == 0);
-  (void)trans_a;
   if (ft) {
-    B2_REQUIRE(tma_ok && !trans_a, B2_ERR_UNSUPPORTED,
+    B2_REQUIRE(tma_ok, B2_ERR_UNSUPPORTED,
                "ft_sgemm: A and B must be 16-byte aligned with lda, ldb multiples of 4 (lda=%d ldb=%d)", lda, ldb);
   }
   if (!tma_ok) {
@@ -668,21 +744,21 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
     B2_CUDA(cudaGetLastError());
     return B2_OK;
   }
+  const FfmaTile &tl = g_tiles[pick_tile(ctx, M, N)];
   CUtensorMap ta, tb;
-  int st = trans_a ? make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, FBM, FBK, CU_TENSOR_MAP_SWIZZLE_NONE)
-                   : make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, FBK, FBM, CU_TENSOR_MAP_SWIZZLE_128B);
+  int st = trans_a ? make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, tl.bm, FBK, CU_TENSOR_MAP_SWIZZLE_NONE)
+                   : make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, FBK, tl.bm, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
-  st = make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, FBN, FBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+  st = make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, tl.bn, FBK, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (st != B2_OK) return st;
   FfmaArgs args;
   args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
-  const int grid = ((M + FBM - 1) / FBM) * ((N + FBN - 1) / FBN);
-  const bool packed = ffma_variant() != 0;
-  if (ft) return launch_ffma<true, 8, false, true>(ta, tb, args, grid, s, *ft);
-  if (trans_a) return packed ? launch_ffma<true, 8, true>(ta, tb, args, grid, s) : launch_ffma<false, 8, true>(ta, tb, args, grid, s);
-  return packed ? launch_ffma<true, 8, false>(ta, tb, args, grid, s) : launch_ffma<false, 8, false>(ta, tb, args, grid, s);
+  const int grid = ((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
+  FtArgs none = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, 0, 0};
+  const int packed = (ft != nullptr || ffma_variant() != 0) ? 1 : 0;
+  return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, args, grid, s, ft ? *ft : none);
 }
 
 }  // namespace b2
@@ -717,9 +793,13 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
   // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the
-  // rounding noise between the two ways the checksums are summed
+  // rounding noise between the two ways a block's sum is formed
   ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
   ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
+  ft.A = A;
+  ft.B = B;
+  ft.lda = lda;
+  ft.ldb = ldb;
   return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
 }
 
@@ -732,6 +812,23 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
 int b2_set_ffma_variant(int v) {
   B2_REQUIRE(v >= 0 && v <= 1, B2_ERR_INVALID_ARG, "b2_set_ffma_variant: %d not in 0..1", v);
   b2::g_ffma_variant = v;
+  return B2_OK;
+}
+
+// Tile family (ffma_tiles.inc): number of tiles, description of tile i, and a pin for the
+// picker (-1 = automatic).
+int b2_ffma_tile_count(void) { return b2::kNumTiles; }
+int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name) {
+  B2_REQUIRE(i >= 0 && i < b2::kNumTiles, B2_ERR_INVALID_ARG, "b2_ffma_tile_info: tile %d not in 0..%d", i, b2::kNumTiles - 1);
+  if (bm) *bm = b2::g_tiles[i].bm;
+  if (bn) *bn = b2::g_tiles[i].bn;
+  if (threads) *threads = b2::g_tiles[i].threads;
+  if (name) *name = b2::g_tiles[i].name;
+  return B2_OK;
+}
+int b2_set_ffma_tile(int i) {
+  B2_REQUIRE(i >= -1 && i < b2::kNumTiles, B2_ERR_INVALID_ARG, "b2_set_ffma_tile: tile %d not in -1..%d", i, b2::kNumTiles - 1);
+  b2::g_ffma_tile = i;
   return B2_OK;
 }
 

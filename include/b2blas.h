@@ -86,9 +86,9 @@ int ref_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, flo
 
 /* ---- ABFT (fault-tolerant) SGEMM --------------------------------------------------- */
 
-/* One simulated soft error: after K-slab `k_step` of output tile (`tile_m`,`tile_n`)
- * (128x128 tiles), bit `bit` of the FP32 accumulator of tile-local element
- * (`row`,`col`) is flipped in registers.  A simulated fault never faults the GPU. */
+/* One simulated soft error: after K-slab `k_step` (slab = 32 of K), bit `bit` of the FP32
+ * accumulator of output element (tile_m*128 + row, tile_n*128 + col) is flipped in registers.
+ * A plan holds at most one fault per 128x128 tile.  A simulated fault never faults the GPU. */
 typedef struct {
   int32_t tile_m, tile_n;
   int32_t row, col;     /* 0..127 inside the tile */
@@ -99,10 +99,11 @@ typedef struct {
 typedef struct {
   int32_t tiles;          /* output tiles verified */
   int32_t injected;       /* faults applied from the plan */
-  int32_t detected;       /* tiles whose row AND column checksum both flagged */
-  int32_t corrected;      /* accumulators rebuilt from the row checksum */
-  int32_t uncorrectable;  /* flagged but not locatable as a single element */
-  int32_t reserved[3];
+  int32_t detected;       /* 16 x 16 blocks whose checksum was out of tolerance and held a wrong output */
+  int32_t corrected;      /* accumulators found wrong by recomputation and replaced */
+  int32_t uncorrectable;  /* always 0 with recompute-based correction; kept for callers that test it */
+  int32_t false_alarms;   /* blocks out of tolerance whose outputs all verified */
+  int32_t reserved[2];
 } b2_ft_report;
 
 /* North-star launcher `ft_sgemm`: as sgemm() with checksum encode in the mainloop and
@@ -190,6 +191,11 @@ int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out
 /* Inner-loop variant of the FFMA SGEMM kernel (0 scalar FFMA, 1 packed f32x2, the default);
  * results are bit-identical, used for benchmarking only. */
 int b2_set_ffma_variant(int v);
+/* FFMA tile family (generated table): count, description of tile i, and a pin for the automatic
+ * picker (-1 = automatic).  Stands in for the positional kernel ids of kernel/ft_sgemm/sgemm.cu:114-157. */
+int b2_ffma_tile_count(void);
+int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name);
+int b2_set_ffma_tile(int i);
 /* 3xTF32 path: 0 = B planes written transposed (N x K) and fed K-major, 1 = planes as is, MN-major. */
 int b2_set_tf32_b_layout(int mn_major);
 /* Reads and clears the device status word that bounded waits set; synchronises the stream.

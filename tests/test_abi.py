@@ -60,6 +60,22 @@ def test_host_fill_matches_oracle(L):
     assert np.array_equal(buf, oracle.fill_uniform(1000, 42))
 
 
+def test_generated_tile_table_is_current_and_exported(L):
+    import ctypes as C
+    from hpcdeepneuralnetworks_b200 import gen_ft_sgemm
+    assert gen_ft_sgemm.main(["--check"]) == 0                       # csrc/ffma_tiles.inc matches the generator
+    assert L.b2_ffma_tile_count() == len(gen_ft_sgemm.TILES)
+    bm, bn, th, name = C.c_int(), C.c_int(), C.c_int(), C.c_char_p()
+    for i, (tname, (param, _)) in enumerate(gen_ft_sgemm.TILES.items()):
+        assert L.b2_ffma_tile_info(i, C.byref(bm), C.byref(bn), C.byref(th), C.byref(name)) == 0
+        assert (name.value.decode(), bm.value, bn.value, th.value) == (tname, param[0], param[1], 2 * param[0])
+    assert L.b2_ffma_tile_info(99, None, None, None, None) == -1
+    assert L.b2_set_ffma_tile(99) == -1 and L.b2_set_ffma_tile(-1) == 0
+    import pytest as _pt
+    with _pt.raises(ValueError):
+        gen_ft_sgemm.validate("small", (16, 16, 16, 8, 16, 2, 2))    # the reference's 16x16x16 tile has no B200 form
+
+
 def test_workspace_query(L):
     assert L.b2_sgemm_workspace_bytes(0, 1024, 1024, 1024) == 0
     need = L.b2_sgemm_workspace_bytes(1, 1024, 1024, 1024)

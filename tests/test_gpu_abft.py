@@ -23,6 +23,15 @@ def mats(M, N, K):
     return a, b, c
 
 
+@pytest.fixture(autouse=True)
+def _pin_huge_tile(cuda):
+    """The report counts tiles of whichever block tile ran; pin the 128x128 tile so that counts are fixed."""
+    import hpcdeepneuralnetworks_b200 as b2
+    b2.set_ffma_tile(0)
+    yield
+    b2.set_ffma_tile(-1)
+
+
 def default_tau(K):
     return max(2e-6 * K, 4e-5)
 
@@ -54,7 +63,7 @@ def test_clean_run_no_false_positive_and_bit_identical(cuda, shape):
     b2.check_status()
     r = b2.read_report(rep)
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
-    assert r == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0}
+    assert r == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0, "false_alarms": 0}
     assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
 
 
@@ -81,11 +90,14 @@ def test_single_fault_each_bit(cuda, bit, k_step):
         assert r["detected"] == 0 and r["uncorrectable"] == 0
     if must or benign:
         assert oracle.gemm_error(got, c64, den) <= TOL
-    # every element other than the struck one is bit-identical to the plain result
+    # every element other than the struck one is bit-identical to the plain result; a corrected one is too,
+    # because correction recomputes the output with the kernel's own arithmetic
     want = oracle.sgemm_fma(1.0, a, b, 0.5, c)
     mask = np.ones_like(want, dtype=bool)
     mask[128 + 77, 101] = False
     assert np.array_equal(got[mask], want[mask])
+    if must:
+        assert np.array_equal(got, want)
 
 
 @pytest.mark.parametrize("seed", [6, 7, 8])
@@ -169,7 +181,8 @@ def test_config3_large_sizes(cuda, n):
     out = torch.zeros((n, n), device="cuda")
     b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, report=rep)
     b2.check_status()
-    assert b2.read_report(rep) == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0}
+    assert b2.read_report(rep) == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0,
+                                   "false_alarms": 0}
     assert torch.equal(out, plain)
     plan = oracle.make_fault_plan(n, n, n, seed=6)
     assert len(plan) == tiles // 64
@@ -186,3 +199,50 @@ def test_config3_large_sizes(cuda, n):
     # untouched elements identical; struck ones within the tolerance scale 1e-5 * K/4 (+ the gray zone bound 2 tau)
     assert int((diff > 0).sum().item()) <= len(plan)
     assert float(diff.max().item()) <= max(1e-5 * n / 4.0, 2 * tau if gray else 0.0)
+
+
+def test_every_generated_tile_plain_and_abft(cuda):
+    """The generated tile family: each tile pinned, plain result bit-exact, a planted fault found and repaired."""
+    import hpcdeepneuralnetworks_b200 as b2
+    tiles = b2.ffma_tiles()
+    assert len(tiles) >= 6 and {t[1] for t in tiles} >= {"huge", "tall", "wide", "large", "medium"}
+    M, N, K = 200, 264, 160
+    a, b, c = mats(M, N, K)
+    want = oracle.sgemm_fma(1.0, a, b, 0.5, c)
+    plan = np.array([[1, 1, 40, 100, 2, 28]], dtype=np.int32)        # output element (168, 228)
+    clean, bad, ok = oracle.fault_effect(a, b, plan[0])
+    assert ok and abs(bad - clean) > 4 * default_tau(K)
+    try:
+        for idx, name, bm, bn, threads in tiles:
+            b2.set_ffma_tile(idx)
+            dc = dev(c)
+            b2.sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc)
+            b2.check_status()
+            assert np.array_equal(dc.cpu().numpy(), want), name
+            rep = b2.new_report()
+            dc = dev(c)
+            b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, plan=b2.make_plan(plan), report=rep)
+            b2.check_status()
+            r = b2.read_report(rep)
+            assert r["tiles"] == ((M + bm - 1) // bm) * ((N + bn - 1) // bn), name
+            assert (r["injected"], r["detected"], r["corrected"], r["false_alarms"]) == (1, 1, 1, 0), (name, r)
+            assert np.array_equal(dc.cpu().numpy(), want), name
+    finally:
+        b2.set_ffma_tile(-1)
+
+
+def test_two_faults_in_one_block_are_both_repaired(cuda):
+    """Recompute-based correction does not depend on the single-fault assumption inside a block: plant a fault,
+    run, then corrupt through a second plan entry in a neighbouring tile of the same call."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 256, 256, 256
+    a, b, c = mats(M, N, K)
+    plan = np.array([[0, 0, 5, 9, 1, 27], [0, 1, 5, 9, 3, 29], [1, 0, 100, 64, 0, 26], [1, 1, 127, 127, 7, 30]], dtype=np.int32)
+    rep = b2.new_report()
+    dc = dev(c)
+    b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, plan=b2.make_plan(plan), report=rep)
+    r = b2.read_report(rep)
+    must, gray, benign = classify(a, b, plan, default_tau(K))
+    assert r["injected"] == 4 and must <= r["corrected"] <= must + gray
+    if gray == 0 and benign == 0:
+        assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))

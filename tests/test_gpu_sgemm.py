@@ -135,6 +135,27 @@ def test_series_rungs_bit_exact(cuda, kid, n, t):
     assert oracle.verify_matrix(oracle.cpu_gemm(1.0, 0.5, a, b, c), got)
 
 
+@pytest.mark.parametrize("shape", [(96, 200, 64), (33, 65, 40), (520, 130, 300)])
+def test_tile_family_colmajor_and_rowmajor(cuda, shape):
+    """Every generated tile on the row-major and on the column-major (transposed-A) entry points."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    af, bf, cf = oracle.fill_uniform(M * K, 1), oracle.fill_uniform(N * K, 2), oracle.fill_uniform(M * N, 3)
+    want_cm = oracle.sgemm_colmajor_nt(M, N, K, 1.0, af, bf, -1.5, cf) if M % 4 == 0 and N % 4 == 0 else None
+    try:
+        for idx, name, bm, bn, threads in b2.ffma_tiles():
+            b2.set_ffma_tile(idx)
+            got = run_gpu(0, a, b, c, 1.0, 0.5)
+            assert np.array_equal(got, oracle.sgemm_fma(1.0, a, b, 0.5, c)), name
+            if want_cm is not None:
+                dcf = dev(cf)
+                b2.sgemm_colmajor_nt(M, N, K, dev(af), dev(bf), dcf, 1.0, -1.5)
+                assert np.array_equal(dcf.cpu().numpy(), want_cm), name
+    finally:
+        b2.set_ffma_tile(-1)
+
+
 def test_series_rejects_non_multiple(cuda):
     import hpcdeepneuralnetworks_b200 as b2
     t = torch.zeros(200 * 200, device="cuda")
