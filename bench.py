@@ -184,6 +184,33 @@ def bench_vectors(b2, torch, peaks, steps, warmup, log2n=28):
     return out
 
 
+def cublas_abft_baseline_ms(torch, A, B, Cm, steps, warmup):
+    """The reference's NON-fused ABFT baseline ("Ding et al." line of its plots), reproduced step for step with
+    library calls (kernel/ft_sgemm/include/baseline_ft_sgemm.cuh:1-34): per 256-wide K panel one cuBLAS SGEMM,
+    six SGEMVs (row/col sums of C, A, B and their products), two AXPYs and two DOTs, with a device
+    synchronisation between the stages.  Comparison line only; nothing of the library runs here."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    n = A.shape[0]
+    e = torch.ones(n, device="cuda")
+
+    def one():
+        for k0 in range(0, n, 256):
+            a, b = A[:, k0:k0 + 256], B[k0:k0 + 256, :]
+            torch.addmm(Cm, a, b, beta=0.5, alpha=1.0, out=Cm)
+            torch.cuda.synchronize()
+            c_row, c_col = torch.mv(Cm, e), torch.mv(Cm.t(), e)
+            a_col, b_row = torch.mv(a.t(), e), torch.mv(b, e)
+            torch.cuda.synchronize()
+            ab_col, ba_row = torch.mv(b.t(), a_col), torch.mv(a, b_row)
+            torch.cuda.synchronize()
+            c_col.add_(ab_col, alpha=-1.0)
+            torch.dot(c_col, e)
+            torch.cuda.synchronize()
+            c_row.add_(ba_row, alpha=-1.0)
+            torch.dot(c_row, e)
+    return timed(one, steps, warmup)
+
+
 def run_sweep(args):
     """BASELINE config 2: square row-major SGEMM, N = 256 .. 6144 step 256, alpha=1, beta=0.5, both math paths.
     Prints one JSON object with a row per size (not the headline line)."""
@@ -285,6 +312,12 @@ def run_single(args):
                                    "overhead_pct": 100.0 * (ms_ft / ms_plain - 1.0)}
         except Exception as e:  # reported, not hidden
             extras["abft_ffma"] = {"error": str(e)}
+        try:
+            ms_cb = cublas_abft_baseline_ms(torch, A, B, Cm, 3, 1)
+            extras["abft_cublas_nonfused_baseline"] = {"ms": ms_cb, "value": flop / (ms_cb * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                                       "note": "cuBLAS gemm/gemv/axpy/dot per 256-K panel with syncs, as baseline_ft_sgemm.cuh"}
+        except Exception as e:
+            extras["abft_cublas_nonfused_baseline"] = {"error": str(e)}
         extras.update(bench_vectors(b2, torch, peaks, max(5, args.steps), 3))
 
     # end to end through the host-buffer API: pinned host A, B, C -> device -> SGEMM -> host C

@@ -298,5 +298,3 @@ def set_ffma_tile(index: int):
     check(_lib.load().b2_set_ffma_tile(index))
 
 
-def set_tf32_b_layout(mn_major: bool):
-    check(_lib.load().b2_set_tf32_b_layout(1 if mn_major else 0))

@@ -66,7 +66,23 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         cmd = [nvcc(), "-shared", "-cudart", "shared", "-o", LIB] + objs + \
               ["-Xlinker", "-rpath,/usr/local/cuda/lib64"]
         run(cmd)
+    build_driver()
     return LIB
+
+
+DRIVER_SRC = os.path.join(PKG, "drivers", "b2_driver.cpp")
+DRIVER_BIN = os.path.join(PKG, "drivers", "b2_driver")
+
+
+def build_driver() -> str:
+    """The C++ command-line driver (reference-shaped main() over the C ABI), linked against libb2blas.so."""
+    if _stale(DRIVER_BIN, [DRIVER_SRC, LIB, os.path.join(PKG, "..", "include", "b2blas.h")]):
+        cmd = [nvcc(), "-O2", "-std=c++17", "-I" + os.path.join(PKG, "..", "include"), DRIVER_SRC, "-o", DRIVER_BIN,
+               "-L" + PKG, "-lb2blas", "-cudart", "shared", "-Xlinker", "-rpath," + PKG, "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("driver build failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    return DRIVER_BIN
 
 
 if __name__ == "__main__":

@@ -9,9 +9,9 @@
 //
 // Two kernels:
 //   split_planes_kernel   one pass over A and B writing the hi/lo planes (low 13 mantissa
-//                         bits already zero, so the tensor core's own treatment of them is
-//                         irrelevant) into the workspace.  B is written either as is
-//                         (K x N, "MN-major" operand) or transposed (N x K, "K-major").
+//   split_planes_t_kernel bits already zero, so the tensor core's own treatment of them is
+//                         irrelevant) into the workspace.  B is written transposed (N x K) so
+//                         that both operands are K-major under the 128-byte swizzle.
 //   sgemm_3xtf32_kernel   one 128 x 256 output tile per CTA, K-slabs of 32; warp 0 = TMA
 //                         producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
 //                         epilogue (tcgen05.ld -> alpha/beta -> global).  2-stage ring of
@@ -37,41 +37,58 @@ __device__ __forceinline__ float tf32_rna(float x) {
   return __uint_as_float(r & 0xFFFFE000u);
 }
 
-// hi/lo planes of a rows x cols row-major matrix (pitch ld) into dense planes of pitch ldp.
-__global__ void split_planes_kernel(const float *__restrict__ X, int rows, int cols, int ld, float *__restrict__ hi,
-                                    float *__restrict__ lo, int ldp) {
-  const int64_t total = (int64_t)rows * ldp;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / ldp;
-    const int c = (int)(i - r * ldp);
-    float h = 0.f, l = 0.f;
-    if (c < cols) {
-      const float x = X[r * ld + c];
-      h = tf32_rna(x);
-      l = tf32_rna(x - h);
+// hi/lo planes of a rows x cols row-major matrix (pitch ld) into dense planes of pitch ldp
+// (a multiple of 4): one thread per 4 consecutive columns, 128-bit loads when the source allows.
+__global__ void __launch_bounds__(256) split_planes_kernel(const float *__restrict__ X, int rows, int cols, int ld,
+                                                           float *__restrict__ hi, float *__restrict__ lo, int ldp, int vec) {
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (c >= ldp) return;
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    const float *src = X + (size_t)r * ld + c;
+    float4 x;
+    if (vec && c + 3 < cols) {
+      x = __ldcs(reinterpret_cast<const float4 *>(src));
+    } else {
+      x.x = (c + 0 < cols) ? src[0] : 0.f;
+      x.y = (c + 1 < cols) ? src[1] : 0.f;
+      x.z = (c + 2 < cols) ? src[2] : 0.f;
+      x.w = (c + 3 < cols) ? src[3] : 0.f;
     }
-    hi[i] = h;
-    lo[i] = l;
+    float4 h, l;
+    h.x = tf32_rna(x.x); l.x = tf32_rna(x.x - h.x);
+    h.y = tf32_rna(x.y); l.y = tf32_rna(x.y - h.y);
+    h.z = tf32_rna(x.z); l.z = tf32_rna(x.z - h.z);
+    h.w = tf32_rna(x.w); l.w = tf32_rna(x.w - h.w);
+    *reinterpret_cast<float4 *>(hi + (size_t)r * ldp + c) = h;
+    *reinterpret_cast<float4 *>(lo + (size_t)r * ldp + c) = l;
   }
 }
 
-// Transposing variant: X is rows x cols (pitch ld); planes are cols x rows (pitch ldp >= rows).
-__global__ void split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld, float *__restrict__ hi,
-                                      float *__restrict__ lo, int ldp) {
-  __shared__ float t[32][33];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  for (int j = threadIdx.y; j < 32; j += 8) {
-    const int r = r0 + j, c = c0 + threadIdx.x;
-    t[j][threadIdx.x] = (r < rows && c < cols) ? X[(int64_t)r * ld + c] : 0.f;
+// Transposing variant: X is rows x cols (pitch ld); planes are cols x rows (pitch ldp >= rows,
+// a multiple of 4).  64 x 64 tiles through shared memory: coalesced reads along the columns of X,
+// 128-bit coalesced writes along the rows of X.
+__global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld,
+                                                             float *__restrict__ hi, float *__restrict__ lo, int ldp) {
+  __shared__ float t[64][65];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64, tid = threadIdx.x;
+  for (int e = tid; e < 64 * 64; e += 256) {
+    const int rr = e >> 6, cc = e & 63;
+    const int r = r0 + rr, c = c0 + cc;
+    t[rr][cc] = (r < rows && c < cols) ? X[(size_t)r * ld + c] : 0.f;
   }
   __syncthreads();
-  for (int j = threadIdx.y; j < 32; j += 8) {
-    const int c = c0 + j, r = r0 + threadIdx.x;  // output row = c, output column = r
+  for (int e = tid; e < 64 * 16; e += 256) {
+    const int cc = e >> 4, rq = (e & 15) * 4;   // output row c0 + cc, output columns r0 + rq .. +3
+    const int c = c0 + cc, r = r0 + rq;
     if (c < cols && r < ldp) {
-      const float x = (r < rows) ? t[threadIdx.x][j] : 0.f;
-      const float h = tf32_rna(x);
-      hi[(int64_t)c * ldp + r] = h;
-      lo[(int64_t)c * ldp + r] = tf32_rna(x - h);
+      float4 h, l;
+      const float x0 = t[rq + 0][cc], x1 = t[rq + 1][cc], x2 = t[rq + 2][cc], x3 = t[rq + 3][cc];
+      h.x = tf32_rna(x0); l.x = tf32_rna(x0 - h.x);
+      h.y = tf32_rna(x1); l.y = tf32_rna(x1 - h.y);
+      h.z = tf32_rna(x2); l.z = tf32_rna(x2 - h.z);
+      h.w = tf32_rna(x3); l.w = tf32_rna(x3 - h.w);
+      *reinterpret_cast<float4 *>(hi + (size_t)c * ldp + r) = h;
+      *reinterpret_cast<float4 *>(lo + (size_t)c * ldp + r) = l;
     }
   }
 }
@@ -84,7 +101,6 @@ struct Tf32Args {
   int *status;
 };
 
-template <bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
@@ -139,14 +155,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
         mbar_expect_tx(&full[s], kTStage);
         tma_load_2d(st, &tmAh, &full[s], kb * TBK, m0);
         tma_load_2d(st + kTA, &tmAl, &full[s], kb * TBK, m0);
-        if (B_MN) {
-          // planes are K x N: eight 32(n) x 32(k) boxes per plane, each 4 KB under the 128B swizzle
-#pragma unroll
-          for (int j = 0; j < TBN / 32; ++j) {
-            tma_load_2d(st + 2 * kTA + j * 4096, &tmBh, &full[s], n0 + j * 32, kb * TBK);
-            tma_load_2d(st + 2 * kTA + kTB + j * 4096, &tmBl, &full[s], n0 + j * 32, kb * TBK);
-          }
-        } else {
+        {
           tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * TBK, n0);
           tma_load_2d(st + 2 * kTA + kTB, &tmBl, &full[s], kb * TBK, n0);
         }
@@ -155,7 +164,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(TBM, TBN, 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = umma_idesc_tf32(TBM, TBN, 0, 0);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % TSTAGES;
@@ -172,16 +181,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           // 8 floats is 32 bytes further along the row.
           const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
           const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
-          uint64_t b_hi, b_lo;
-          if (B_MN) {
-            // MN-major, 128B swizzle: 32 n contiguous (128 bytes), next 32 n at LBO = 4096,
-            // 8-k groups at SBO = 1024; one K-step of 8 is one group.
-            b_hi = umma_smem_desc(st + 2 * kTA + k4 * 1024, 4096, 1024, 2);
-            b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 1024, 4096, 1024, 2);
-          } else {
-            b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
-            b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
-          }
+          const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
+          const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
           umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
@@ -260,23 +261,18 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
 }
 
-static int g_tf32_b_mn = -1;  // -1: from B2_TF32_B_MN (default 0: K-major planes of B)
-
 size_t tf32_workspace_bytes(int M, int N, int K) {
-  const size_t kp = ((size_t)K + 3) & ~(size_t)3, np = ((size_t)N + 3) & ~(size_t)3;
-  const size_t a = (size_t)M * kp, b1 = (size_t)N * kp, b2 = (size_t)K * np;
-  const size_t b = b1 > b2 ? b1 : b2;
-  return (2 * a + 2 * b) * sizeof(float) + 4 * 1024;
+  const size_t kp = ((size_t)K + 3) & ~(size_t)3;
+  return (2 * (size_t)M * kp + 2 * (size_t)N * kp) * sizeof(float) + 4 * 1024;
 }
 
-template <bool B_MN>
 static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTf32Smem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTf32Smem));
     configured = true;
   }
-  sgemm_3xtf32_kernel<B_MN><<<grid, 192, kTf32Smem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
+  sgemm_3xtf32_kernel<<<grid, 192, kTf32Smem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
@@ -288,29 +284,23 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
                           float beta, float *C, int ldc, cudaStream_t s) {
   if (M == 0 || N == 0) return B2_OK;
   if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, s);
-  if (g_tf32_b_mn < 0) {
-    const char *e = getenv("B2_TF32_B_MN");
-    g_tf32_b_mn = (e && atoi(e) != 0) ? 1 : 0;
-  }
-  const bool b_mn = g_tf32_b_mn != 0;
   int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
   if (st != B2_OK) return st;
-  const int kp = (K + 3) & ~3, np = (N + 3) & ~3;
+  const int kp = (K + 3) & ~3;
   char *w = (char *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023);
-  const size_t a_elems = (size_t)M * kp, b_elems = b_mn ? (size_t)K * np : (size_t)N * kp;
+  const size_t a_elems = (size_t)M * kp, b_elems = (size_t)N * kp;
   auto align1k = [](size_t bytes) { return (bytes + 1023) & ~(size_t)1023; };
   float *Ah = (float *)w;
   float *Al = (float *)(w + align1k(a_elems * 4));
   float *Bh = (float *)(w + 2 * align1k(a_elems * 4));
   float *Bl = (float *)(w + 2 * align1k(a_elems * 4) + align1k(b_elems * 4));
 
-  const int blocks = ctx->sm_count * 8;
-  split_planes_kernel<<<blocks, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp);
-  if (b_mn) {
-    split_planes_kernel<<<blocks, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, np);
-  } else {
-    dim3 g((N + 31) / 32, (kp + 31) / 32), blk(32, 8);
-    split_planes_t_kernel<<<g, blk, 0, s>>>(B, K, N, ldb, Bh, Bl, kp);
+  {
+    const int vec = ((((uintptr_t)A) & 15) == 0 && (lda % 4) == 0) ? 1 : 0;
+    dim3 g((kp / 4 + 255) / 256, M < 16384 ? M : 16384);
+    split_planes_kernel<<<g, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp, vec);
+    dim3 gt((N + 63) / 64, (kp + 63) / 64);
+    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp);
   }
   B2_CUDA(cudaGetLastError());
 
@@ -319,15 +309,9 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, TBK, TBM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
-  if (b_mn) {
-    st = make_tmap_2d(&maps[2], Bh, (uint64_t)N, (uint64_t)K, (uint64_t)np, 32, TBK, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st != B2_OK) return st;
-    st = make_tmap_2d(&maps[3], Bl, (uint64_t)N, (uint64_t)K, (uint64_t)np, 32, TBK, CU_TENSOR_MAP_SWIZZLE_128B);
-  } else {
-    st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st != B2_OK) return st;
-    st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
-  }
+  st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != B2_OK) return st;
+  st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
 
   Tf32Args args;
@@ -335,7 +319,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
   const int grid = ((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN);
-  return b_mn ? launch_tf32<true>(maps, args, grid, s) : launch_tf32<false>(maps, args, grid, s);
+  return launch_tf32(maps, args, grid, s);
 }
 
 }  // namespace b2
@@ -347,12 +331,6 @@ extern "C" {
 size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K) {
   if (path != B2_PATH_3XTF32 || M <= 0 || N <= 0 || K <= 0) return 0;
   return tf32_workspace_bytes(M, N, K);
-}
-
-// 0: B planes written transposed (N x K) and fed K-major; 1: B planes as is (K x N), fed MN-major.
-int b2_set_tf32_b_layout(int mn_major) {
-  b2::g_tf32_b_mn = mn_major ? 1 : 0;
-  return B2_OK;
 }
 
 }  // extern "C"

@@ -196,8 +196,6 @@ int b2_set_ffma_variant(int v);
 int b2_ffma_tile_count(void);
 int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name);
 int b2_set_ffma_tile(int i);
-/* 3xTF32 path: 0 = B planes written transposed (N x K) and fed K-major, 1 = planes as is, MN-major. */
-int b2_set_tf32_b_layout(int mn_major);
 /* Reads and clears the device status word that bounded waits set; synchronises the stream.
  * Returns 0 or the recorded negative status. */
 int b2_check_status(b2_handle h, void *stream);

@@ -191,21 +191,33 @@ def test_reference_shaped_shims(cuda):
         assert np.array_equal(dcf.cpu().numpy(), oracle.sgemm_colmajor_nt(M, N, K, 1.0, af, bf, -1.5, cf))
 
 
-@pytest.mark.parametrize("mn_major", [False, True])
 @pytest.mark.parametrize("shape", [(128, 256, 32), (128, 256, 64), (256, 512, 256), (1024, 1024, 1024), (130, 300, 70),
-                                   (17, 13, 5), (384, 128, 1000)])
-def test_3xtf32_path(cuda, mn_major, shape):
+                                   (17, 13, 5), (384, 128, 1000), (200, 520, 36)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.5), (-1.5, 0.0)])
+def test_3xtf32_path(cuda, shape, alpha, beta):
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    got = run_gpu(1, a, b, c, alpha, beta)
+    c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
+    err = oracle.gemm_error(got, c64, den)
+    assert err <= TOL_3XTF32, f"3xTF32 error {err:.3e}"
+
+
+def test_3xtf32_leading_dimensions(cuda):
     import hpcdeepneuralnetworks_b200 as b2
-    b2.set_tf32_b_layout(mn_major)
-    try:
-        M, N, K = shape
-        a, b, c = mats(M, N, K)
-        got = run_gpu(1, a, b, c, 1.0, 0.5)
-        c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
-        err = oracle.gemm_error(got, c64, den)
-        assert err <= TOL_3XTF32, f"3xTF32 error {err:.3e} (B {'MN' if mn_major else 'K'}-major)"
-    finally:
-        b2.set_tf32_b_layout(False)
+    M, N, K, lda, ldb, ldc = 150, 200, 70, 96, 256, 212
+    A = oracle.fill_uniform(M * lda, 1).reshape(M, lda)
+    B = oracle.fill_uniform(K * ldb, 2).reshape(K, ldb)
+    Cb = oracle.fill_uniform((M + 2) * ldc, 3).reshape(M + 2, ldc)
+    dC = dev(Cb)
+    b2.sgemm(M, N, K, 1.0, dev(A), dev(B), 0.5, dC[1:], path=1, lda=lda, ldb=ldb, ldc=ldc)
+    b2.check_status()
+    got = dC.cpu().numpy()
+    c64, den = oracle.sgemm_f64(1.0, A[:, :K], B[:, :N], 0.5, Cb[1:M + 1, :N])
+    assert oracle.gemm_error(np.ascontiguousarray(got[1:M + 1, :N]), c64, den) <= TOL_3XTF32
+    mask = np.ones_like(Cb, dtype=bool)
+    mask[1:M + 1, :N] = False
+    assert np.array_equal(got[mask], Cb[mask])          # nothing outside the view was touched
 
 
 def test_sweep_sizes_both_paths(cuda):
