@@ -298,3 +298,8 @@ def set_ffma_tile(index: int):
     check(_lib.load().b2_set_ffma_tile(index))
 
 
+
+
+def set_tf32_tile_n(n: int):
+    """Pin the 3xTF32 tile width (128 or 256; 0 = automatic)."""
+    check(_lib.load().b2_set_tf32_tile_n(n))

@@ -12,24 +12,31 @@
 //   split_planes_t_kernel bits already zero, so the tensor core's own treatment of them is
 //                         irrelevant) into the workspace.  B is written transposed (N x K) so
 //                         that both operands are K-major under the 128-byte swizzle.
-//   sgemm_3xtf32_kernel   one 128 x 256 output tile per CTA, K-slabs of 32; warp 0 = TMA
+//   sgemm_3xtf32_kernel   one 128 x 256 (or 128 x 128) output tile per CTA, K-slabs of 32; warp 0 = TMA
 //                         producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
 //                         epilogue (tcgen05.ld -> alpha/beta -> global).  2-stage ring of
 //                         96 KB (A_hi, A_lo: 128x32; B_hi, B_lo: 256x32), all tiles under the
 //                         128-byte swizzle.
 // Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
+#include <math.h>
 #include <stdlib.h>
 
 #include "common.cuh"
 
 namespace b2 {
 
-constexpr int TBM = 128, TBN = 256, TBK = 32, TSTAGES = 2;
+constexpr int TBM = 128, TBK = 32;
 constexpr int kTA = TBM * TBK * 4;                 // 16 KB per A plane tile
-constexpr int kTB = TBN * TBK * 4;                 // 32 KB per B plane tile
-constexpr int kTStage = 2 * kTA + 2 * kTB;         // 96 KB
-constexpr int kTf32Smem = 1024 + TSTAGES * kTStage + 256;
-constexpr int kTmemCols = 256;
+// Two tile widths: 128 x 256 (2 stages of 96 KB) and 128 x 128 (3 stages of 64 KB) for problem
+// sizes whose 128 x 256 tile grid fills the last wave of 148 SMs badly.
+template <int TBN>
+struct Tf32Cfg {
+  static constexpr int kStages = (TBN == 256) ? 2 : 3;
+  static constexpr int kTB = TBN * TBK * 4;          // bytes per B plane tile
+  static constexpr int kStage = 2 * kTA + 2 * kTB;
+  static constexpr int kSmem = 1024 + kStages * kStage + 256;
+  static constexpr int kTmemCols = TBN;              // FP32 accumulator: one TMEM column per output column
+};
 
 __device__ __forceinline__ float tf32_rna(float x) {
   uint32_t r;
@@ -101,9 +108,12 @@ struct Tf32Args {
   int *status;
 };
 
+template <int TBN>
 __global__ void __launch_bounds__(192, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
+  constexpr int TSTAGES = Tf32Cfg<TBN>::kStages, kTB = Tf32Cfg<TBN>::kTB, kTStage = Tf32Cfg<TBN>::kStage;
+  constexpr int kTmemCols = Tf32Cfg<TBN>::kTmemCols;
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
   unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -261,18 +271,21 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
 }
 
+static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
+
 size_t tf32_workspace_bytes(int M, int N, int K) {
   const size_t kp = ((size_t)K + 3) & ~(size_t)3;
   return (2 * (size_t)M * kp + 2 * (size_t)N * kp) * sizeof(float) + 4 * 1024;
 }
 
+template <int TBN>
 static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTf32Smem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<TBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tf32Cfg<TBN>::kSmem));
     configured = true;
   }
-  sgemm_3xtf32_kernel<<<grid, 192, kTf32Smem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
+  sgemm_3xtf32_kernel<TBN><<<grid, 192, Tf32Cfg<TBN>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
@@ -309,17 +322,23 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, TBK, TBM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
-  st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
+  // tile width: whole waves of one CTA per SM; a 128-wide tile costs ~0.55 of a 256-wide one
+  const double sms = (double)ctx->sm_count;
+  const double tm = (double)((M + TBM - 1) / TBM);
+  const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
+  int tbn = (t128 < t256) ? 128 : 256;
+  if (g_tf32_tile_n == 128 || g_tf32_tile_n == 256) tbn = g_tf32_tile_n;
+  st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, tbn, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
-  st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
+  st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, tbn, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
 
   Tf32Args args;
   args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
-  const int grid = ((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN);
-  return launch_tf32(maps, args, grid, s);
+  const int grid = ((M + TBM - 1) / TBM) * ((N + tbn - 1) / tbn);
+  return tbn == 128 ? launch_tf32<128>(maps, args, grid, s) : launch_tf32<256>(maps, args, grid, s);
 }
 
 }  // namespace b2
@@ -331,6 +350,13 @@ extern "C" {
 size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K) {
   if (path != B2_PATH_3XTF32 || M <= 0 || N <= 0 || K <= 0) return 0;
   return tf32_workspace_bytes(M, N, K);
+}
+
+// Pins the 3xTF32 tile width (128 or 256 columns; 0 = automatic).  For benchmarking.
+int b2_set_tf32_tile_n(int n) {
+  B2_REQUIRE(n == 0 || n == 128 || n == 256, B2_ERR_INVALID_ARG, "b2_set_tf32_tile_n: %d is not 0, 128 or 256", n);
+  b2::g_tf32_tile_n = n;
+  return B2_OK;
 }
 
 }  // extern "C"

@@ -203,6 +203,20 @@ def test_3xtf32_path(cuda, shape, alpha, beta):
     assert err <= TOL_3XTF32, f"3xTF32 error {err:.3e}"
 
 
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_3xtf32_both_tile_widths(cuda, tile_n):
+    import hpcdeepneuralnetworks_b200 as b2
+    b2.set_tf32_tile_n(tile_n)
+    try:
+        for shape in ((256, 512, 96), (130, 300, 70), (640, 384, 200)):
+            a, b, c = mats(*shape)
+            got = run_gpu(1, a, b, c, 1.0, 0.5)
+            c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+            assert oracle.gemm_error(got, c64, den) <= TOL_3XTF32
+    finally:
+        b2.set_tf32_tile_n(0)
+
+
 def test_3xtf32_leading_dimensions(cuda):
     import hpcdeepneuralnetworks_b200 as b2
     M, N, K, lda, ldb, ldc = 150, 200, 70, 96, 256, 212
