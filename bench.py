@@ -370,9 +370,11 @@ def run_multi(args):
         b2.fill_uniform(B, 2)
     Cm = torch.zeros((rows, n), device="cuda")
     comm = torch.cuda.Stream()
+    report = b2.new_report() if args.abft else None
 
     def step():
-        b2dist.sharded_sgemm(n, n, n, 1.0, A, B, 0.0, Cm, src=0, panel=args.panel, path=path, comm_stream=comm)
+        b2dist.sharded_sgemm(n, n, n, 1.0, A, B, 0.0, Cm, src=0, panel=args.panel, path=path, comm_stream=comm,
+                             abft=args.abft, report=report)
 
     def barrier():
         dist.barrier()
@@ -404,7 +406,7 @@ def run_multi(args):
             "metric": METRIC.replace("6144", str(n)), "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"sgemm_rowmajor_{n}^3_rowblock_sharded", "path": args.path, "alpha": 1.0, "beta": 0.0,
+            "config": {"workload": f"sgemm_rowmajor_{n}^3_rowblock_sharded" + ("_abft" if args.abft else ""), "path": args.path, "alpha": 1.0, "beta": 0.0,
                        "parallelism": f"A,C row blocks over {world} GPUs; B broadcast from rank 0 per GEMM in K-panels of {args.panel} (NCCL)",
                        "l2": "operands are GBs per GPU, far larger than L2"},
             "roofline": {"bound": "fp32_simt" if path == 0 else "tensor", "achieved": per_gpu if path == 0 else 3 * per_gpu,
@@ -416,6 +418,7 @@ def run_multi(args):
                     "note": "operands of 32768^3 are generated on the device; no host copy is part of this workload"},
             "gpu_launches": args.steps * len(b2dist.k_panels(n, args.panel)) * (1 if path == 0 else 3),
             "clocks": clk.summary(),
+            "abft_report": (b2.read_report(report) if args.abft else None),
             "extra": {"sdot_sharded": {"n_total": nloc * world, "ms": ms_dot, "value": 8.0 * nloc * world / (ms_dot * 1e-3) / 1e9,
                                        "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_dot * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
         }
