@@ -211,6 +211,31 @@ def cublas_abft_baseline_ms(torch, A, B, Cm, steps, warmup):
     return timed(one, steps, warmup)
 
 
+def run_series(args):
+    """The reference's step-wise series sgemm_1 .. sgemm_14 (kernel/sgemm/include/kernel_*.cuh) at one size, GFLOPS per
+    rung as in its README table and fig/ABFT_GEMM/bar_graph/fig9_plot_step_wise.py.  Prints one JSON object."""
+    import torch
+    import hpcdeepneuralnetworks_b200 as b2
+    torch.cuda.set_device(0)
+    n = args.size or 2048
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    Cm = b2.fill_uniform(torch.empty((n, n), device="cuda"), 3)
+    flush = torch.empty(160 * 2 ** 20 // 4, device="cuda")
+    ms_flush = timed(lambda: flush.zero_(), 10, 3)
+    rows = []
+    for kid in range(1, 15):
+        def one():
+            flush.zero_()
+            b2.sgemm_series(kid, n, A, B, Cm, 1.0, 0.5)
+        reps = 3 if kid <= 2 else 8
+        ms = max(timed(one, reps, 2) - ms_flush, 1e-6)
+        rows.append({"kernel": kid, "ms": ms, "gflops": 2.0 * n ** 3 / (ms * 1e-3) / 1e9})
+    print(json.dumps({"series": "sgemm_1..14", "n": n, "alpha": 1.0, "beta": 0.5,
+                      "l2": "160 MB flush between launches, flush time subtracted", "rows": rows}))
+    return 0
+
+
 def run_sweep(args):
     """BASELINE config 2: square row-major SGEMM, N = 256 .. 6144 step 256, alpha=1, beta=0.5, both math paths.
     Prints one JSON object with a row per size (not the headline line)."""
@@ -261,6 +286,8 @@ def run_single(args):
     peaks = load_peaks()
     if args.sweep:
         return run_sweep(args)
+    if args.series:
+        return run_series(args)
     if args.only == "vectors":   # small-case command for profiling the streaming kernels
         print(json.dumps(bench_vectors(b2, torch, peaks, args.steps, args.warmup, args.vec_log2n)))
         return 0
@@ -439,6 +466,7 @@ def main():
     ap.add_argument("--panel", type=int, default=4096, help="K-panel of the B broadcast (multi-GPU)")
     ap.add_argument("--only", default="all", choices=["all", "vectors"], help="vectors: SAXPY/SDOT only (profiling)")
     ap.add_argument("--vec-log2n", type=int, default=28, help="log2 of the vector length of the SAXPY/SDOT leg")
+    ap.add_argument("--series", action="store_true", help="the reference's rungs sgemm_1..14 at --size (default 2048)")
     ap.add_argument("--sweep", action="store_true", help="config 2: N = 256..6144 step 256, both paths (prints a table object)")
     ap.add_argument("--abft", action="store_true", help="time the fault-tolerant SGEMM as the headline step (profiling)")
     ap.add_argument("--quick", action="store_true", help="headline kernel only (no extras); used for profiling")
