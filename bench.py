@@ -128,6 +128,26 @@ def cpu_reference_gemm_tflops(n, reps):
     return 2.0 * n ** 3 / (sum(times) / len(times)) / 1e12, ("reference" if use_ref else "port"), times
 
 
+def reference_gpu_kernel_tflops(kernel_id=11, n=N1):
+    """The reference's own kernel/sgemm driver, compiled unmodified for sm_100a (oracle/_ref/ref_sgemm), run on this
+    GPU: its sgemm_<kernel_id> at one size.  Only kernels without the one-slab over-read (9, 11) are ever run.
+    Returns TFLOP/s or None when the binary or a GPU is missing."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_sgemm")
+    if kernel_id not in (9, 11) or not os.path.exists(exe):
+        return None
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        r = subprocess.run([exe, str(kernel_id), str(n), str(n), "32"], capture_output=True, text=True, timeout=300)
+        if r.returncode != 0:
+            return None
+        vals = [v for v in r.stdout.strip().splitlines()[-1].split(",") if v.strip()]
+        return float(vals[-1]) / 1e3
+    except Exception:
+        return None
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU GEMM on the host cores, same metric and unit."""
     rank = int(os.environ.get("RANK", "0"))
@@ -157,6 +177,9 @@ def run_reference(args):
                          "all_cores_port": {"value": 2.0 * n ** 3 / t_all / 1e12, "cores": os.cpu_count()}},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # context only: the reference's Turing kernel sgemm_11 recompiled for sm_100a on this GPU, 6144^3
+        "reference_gpu_kernel": {"kernel": "sgemm_11 (kernel/sgemm/include/kernel_11.cuh:15), unmodified, -arch=sm_100a",
+                                 "value": reference_gpu_kernel_tflops(11), "unit": "TFLOP/s"},
     }
     print(json.dumps(line))
     return 0

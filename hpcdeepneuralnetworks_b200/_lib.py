@@ -73,6 +73,8 @@ def load() -> C.CDLL:
     L.ref_sgemm_rowmajor.argtypes = [i32, vp, vp, vp, f32, f32]
     L.ref_sgemm_colmajor_nt.argtypes = [i32, i32, i32, vp, vp, vp, f32, f32]
     L.b2_ft_sgemm.argtypes = [vp, i32, i32, i32, i32, f32, vp, i32, vp, i32, f32, vp, i32, vp, i32, f32, vp, vp]
+    L.b2_ft_sgemm_colmajor_nt.argtypes = [vp, i32, i32, i32, f32, vp, vp, f32, vp, vp, i32, f32, vp, vp]
+    L.ref_ft_sgemm_colmajor_nt.argtypes = [i32, i32, i32, vp, vp, vp, f32, f32]
     L.saxpy.argtypes = [i32, f32, vp, vp]
     L.b2_saxpy.argtypes = [vp, i64, f32, vp, vp, vp]
     L.sdot.argtypes = [i32, vp, vp, vp]

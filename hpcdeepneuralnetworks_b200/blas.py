@@ -140,6 +140,16 @@ def ft_sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, plan=None, tau=0
     return Cm
 
 
+def ft_sgemm_colmajor_nt(M, N, K, A, B, Cm, alpha, beta, *, plan=None, tau=0.0, report=None, handle=None):
+    """ABFT SGEMM in the kernel/ft_sgemm layout (column-major A MxK, B NxK, C MxN; C = alpha*A*B^T + beta*C).
+    A planned fault's (row, col) address C^T."""
+    h = handle or default_handle()
+    nf = 0 if plan is None else int(plan.shape[0])
+    check(_lib.load().b2_ft_sgemm_colmajor_nt(h.raw, M, N, K, alpha, _ptr(A), _ptr(B), beta, _ptr(Cm), _ptr(plan), nf, tau,
+                                              _ptr(report), _stream()))
+    return Cm
+
+
 def new_report() -> torch.Tensor:
     return torch.zeros(8, dtype=torch.int32, device="cuda")
 
@@ -182,16 +192,24 @@ def sdot_partial(n, x, y, out, partial64, handle=None):
 # ---- host-buffer forms: what a caller holding host arrays (the reference drivers' situation
 # before their cudaMemcpy calls, kernel/sgemm/sgemm.cu:50-58) would use -------------------------
 class HostSgemm:
-    """Pinned staging + device buffers for repeated row-major SGEMM calls on host arrays."""
+    """Row-major SGEMM on HOST arrays: pinned staging buffers, device buffers and a three-stream pipeline.
 
-    def __init__(self, M, N, K, path=PATH_FFMA):
+    ``run`` copies B once, then walks row panels of A and C: the panel p+1 travels host->device while panel p is
+    multiplied and panel p-1 travels device->host, so the PCIe transfers hide behind the kernel (or the other way
+    round).  Panels are whole GEMM calls of the library (``panel_rows`` x N x K); results are bit-identical to one
+    call, because every output row is still accumulated in ascending k by one thread."""
+
+    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=1024):
         self.M, self.N, self.K, self.path = M, N, K, path
+        self.panel_rows = max(128, (min(panel_rows, M) + 127) // 128 * 128) if M >= 128 else M
         self.hA = torch.empty((M, K), dtype=torch.float32).pin_memory()
         self.hB = torch.empty((K, N), dtype=torch.float32).pin_memory()
         self.hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
         self.dA = torch.empty((M, K), dtype=torch.float32, device="cuda")
         self.dB = torch.empty((K, N), dtype=torch.float32, device="cuda")
         self.dC = torch.empty((M, N), dtype=torch.float32, device="cuda")
+        self._h2d = torch.cuda.Stream()
+        self._d2h = torch.cuda.Stream()
 
     def h2d_bytes(self):
         return 4 * (self.M * self.K + self.K * self.N + self.M * self.N)
@@ -200,16 +218,32 @@ class HostSgemm:
         return 4 * self.M * self.N
 
     def run(self, alpha, beta, ft=False):
-        """hC <- alpha*hA*hB + beta*hC through the device; returns hC (pinned) after sync."""
-        self.dA.copy_(self.hA, non_blocking=True)
-        self.dB.copy_(self.hB, non_blocking=True)
-        self.dC.copy_(self.hC, non_blocking=True)
-        if ft:
-            ft_sgemm(self.M, self.N, self.K, alpha, self.dA, self.dB, beta, self.dC, path=self.path)
-        else:
-            sgemm(self.M, self.N, self.K, alpha, self.dA, self.dB, beta, self.dC, path=self.path)
-        self.hC.copy_(self.dC, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        """hC <- alpha*hA*hB + beta*hC through the device; returns hC (pinned) after everything has landed."""
+        compute = torch.cuda.current_stream()
+        h2d, d2h = self._h2d, self._d2h
+        h2d.wait_stream(compute)          # earlier work on the device buffers is finished
+        d2h.wait_stream(compute)
+        M, N, K, P = self.M, self.N, self.K, max(1, self.panel_rows)
+        if self.path == PATH_3XTF32:      # sized once, outside the pipeline
+            (default_handle()).reserve(_lib.load().b2_sgemm_workspace_bytes(self.path, min(P, M), N, K))
+        with torch.cuda.stream(h2d):
+            self.dB.copy_(self.hB, non_blocking=True)
+        for r0 in range(0, max(M, 1), P):
+            r1 = min(M, r0 + P)
+            with torch.cuda.stream(h2d):
+                self.dA[r0:r1].copy_(self.hA[r0:r1], non_blocking=True)
+                if beta != 0.0:
+                    self.dC[r0:r1].copy_(self.hC[r0:r1], non_blocking=True)
+                landed = h2d.record_event()
+            compute.wait_event(landed)
+            fn = ft_sgemm if ft else sgemm
+            fn(r1 - r0, N, K, alpha, self.dA[r0:r1], self.dB, beta, self.dC[r0:r1], path=self.path)
+            done = compute.record_event()
+            d2h.wait_event(done)
+            with torch.cuda.stream(d2h):
+                self.hC[r0:r1].copy_(self.dC[r0:r1], non_blocking=True)
+        compute.wait_stream(d2h)
+        compute.synchronize()
         return self.hC
 
 

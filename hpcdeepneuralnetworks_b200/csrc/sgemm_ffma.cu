@@ -803,6 +803,37 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
   return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
 }
 
+// Column-major NT form of the ABFT SGEMM (the layout of the reference's ft_sgemm_* kernels):
+// A is M x K (lda = M), B is stored N x K (ldb = N), C is M x N (ldc = M), C = alpha*A*B^T + beta*C.
+// Computed as the row-major product C^T = B * A^T with the transposed-A tile, so a fault planned
+// at (row, col) of a 128 x 128 tile addresses C^T: row runs along N, col along M.
+int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const float *A, const float *B, float beta,
+                            float *C, const b2_fault *plan_dev, int n_faults, float tau, b2_ft_report *report_dev,
+                            void *stream) {
+  B2_REQUIRE(M >= 0 && N >= 0 && K >= 0, B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: negative dimension");
+  B2_REQUIRE(n_faults >= 0 && (n_faults == 0 || plan_dev != nullptr), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: bad fault plan");
+  if (M == 0 || N == 0) return B2_OK;
+  B2_REQUIRE(C != nullptr && (K == 0 || (A != nullptr && B != nullptr)), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: null matrix");
+  Context *ctx = h ? (Context *)h : default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ft_sgemm_colmajor_nt: no context (%s)", b2_last_error());
+  FtArgs ft;
+  ft.plan = plan_dev;
+  ft.n_faults = n_faults;
+  ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
+  ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
+  ft.A = B;   // left operand of C^T = B * A^T, held K x N in memory
+  ft.B = A;   // right operand, held K x M in memory
+  ft.lda = N;
+  ft.ldb = M;
+  return sgemm_ffma_dispatch_ft(ctx, 1, N, M, K, alpha, B, N, A, M, beta, C, M, &ft, (cudaStream_t)stream);
+}
+
+// Reference-shaped shim: ft_sgemm_<tile>(M, N, K, A, B, C, alpha, beta) of kernel/ft_sgemm
+// (include/ft_sgemm_huge.cuh:21), default stream, no injection.
+int ref_ft_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, float alpha, float beta) {
+  return b2_ft_sgemm_colmajor_nt(nullptr, M, N, K, alpha, A, B, beta, C, nullptr, 0, 0.f, nullptr, nullptr);
+}
+
 int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C) {
   return b2_ft_sgemm(nullptr, B2_PATH_FFMA, M, N, K, alpha, A, K, B, N, beta, C, N, nullptr, 0, 0.f, nullptr, nullptr);
 }

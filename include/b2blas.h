@@ -120,6 +120,15 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
                 const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
                 int n_faults, float tau, b2_ft_report *report_dev, void *stream);
 
+/* The same in the reference's own ABFT layout, column-major NT (A MxK lda=M, B NxK ldb=N, C MxN
+ * ldc=M): ft_sgemm_<tile>(M, N, K, A, B, C, alpha, beta) of kernel/ft_sgemm/include/ft_sgemm_huge.cuh:21
+ * and include_code_gen/ft_sgemm_wide.cuh:11.  The product is computed as C^T = B * A^T, so a planned
+ * fault's (row, col) address C^T (row along N, col along M). */
+int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const float *A, const float *B,
+                            float beta, float *C, const b2_fault *plan_dev, int n_faults, float tau,
+                            b2_ft_report *report_dev, void *stream);
+int ref_ft_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, float alpha, float beta);
+
 /* ---- SAXPY / SDOT ----------------------------------------------------------------- */
 
 /* y <- alpha*x + y, one fused multiply-add per element (bit-exact with fmaf on the host).

@@ -16,7 +16,8 @@ def test_exports_every_declared_symbol(L):
     names = _lib.declared_symbols()
     assert len(names) >= 28
     for required in ("sgemm", "ft_sgemm", "saxpy", "sdot", "b2_sgemm", "b2_ft_sgemm", "b2_saxpy", "b2_sdot",
-                     "b2_sgemm_series", "ref_sgemm_rowmajor", "ref_sgemm_colmajor_nt"):
+                     "b2_sgemm_series", "ref_sgemm_rowmajor", "ref_sgemm_colmajor_nt", "ref_ft_sgemm_colmajor_nt",
+                     "b2_sdot_static"):
         assert required in names
     missing = [n for n in names if not hasattr(L, n)]
     assert missing == []

@@ -246,3 +246,29 @@ def test_two_faults_in_one_block_are_both_repaired(cuda):
     assert r["injected"] == 4 and must <= r["corrected"] <= must + gray
     if gray == 0 and benign == 0:
         assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (260, 136, 96), (512, 384, 256)])
+def test_colmajor_nt_abft(cuda, shape):
+    """The reference's own ABFT layout (column-major NT): clean run bit-identical, a planted fault repaired."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    af, bf, cf = oracle.fill_uniform(M * K, 1), oracle.fill_uniform(N * K, 2), oracle.fill_uniform(M * N, 3)
+    want = oracle.sgemm_colmajor_nt(M, N, K, 1.0, af, bf, -1.5, cf)
+    rep = b2.new_report()
+    dc = dev(cf)
+    b2.ft_sgemm_colmajor_nt(M, N, K, dev(af), dev(bf), dc, 1.0, -1.5, report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert (r["injected"], r["detected"], r["corrected"], r["false_alarms"]) == (0, 0, 0, 0) and r["tiles"] >= 1
+    assert np.array_equal(dc.cpu().numpy(), want)
+    # C^T is N x M: plant a flip of bit 28 at C^T[(N-1), (M-2)] after slab 1
+    gr, gc = N - 1, M - 2
+    plan = np.array([[gr // 128, gc // 128, gr % 128, gc % 128, 1, 28]], dtype=np.int32)
+    rep = b2.new_report()
+    dc = dev(cf)
+    b2.ft_sgemm_colmajor_nt(M, N, K, dev(af), dev(bf), dc, 1.0, -1.5, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert (r["injected"], r["detected"], r["corrected"]) == (1, 1, 1), r
+    assert np.array_equal(dc.cpu().numpy(), want)

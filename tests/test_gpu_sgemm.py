@@ -278,11 +278,17 @@ def test_full_size_6144_properties(cuda):
     assert oracle.gemm_error(C3[rows].cpu().numpy(), c64, den) <= TOL_3XTF32
 
 
-def test_host_buffer_api(cuda):
+@pytest.mark.parametrize("shape,panel", [((300, 260, 128), 1024), ((700, 260, 128), 256), ((64, 40, 32), 1024)])
+@pytest.mark.parametrize("beta", [0.5, 0.0])
+def test_host_buffer_api(cuda, shape, panel, beta):
+    """Host arrays in, host array out, through the pipelined three-stream path; bit-identical to one device call."""
     import hpcdeepneuralnetworks_b200 as b2
-    M, N, K = 300, 260, 128
+    M, N, K = shape
     a, b, c = mats(M, N, K)
-    hs = b2.HostSgemm(M, N, K)
+    hs = b2.HostSgemm(M, N, K, panel_rows=panel)
     hs.hA.copy_(torch.from_numpy(a)); hs.hB.copy_(torch.from_numpy(b)); hs.hC.copy_(torch.from_numpy(c))
-    out = hs.run(1.0, 0.5).numpy()
-    assert np.array_equal(out, oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    out = hs.run(1.0, beta).numpy().copy()
+    assert np.array_equal(out, oracle.sgemm_fma(1.0, a, b, beta, c))
+    hs.hC.copy_(torch.from_numpy(c))
+    out2 = hs.run(1.0, beta, ft=(M >= 128)).numpy()          # second run on the same buffers, ABFT kernel
+    assert np.array_equal(out2, out)
