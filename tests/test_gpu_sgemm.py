@@ -278,17 +278,25 @@ def test_full_size_6144_properties(cuda):
     assert oracle.gemm_error(C3[rows].cpu().numpy(), c64, den) <= TOL_3XTF32
 
 
-@pytest.mark.parametrize("shape,panel", [((300, 260, 128), 1024), ((700, 260, 128), 256), ((64, 40, 32), 1024)])
+@pytest.mark.parametrize("shape,panel,panel_k", [((300, 260, 128), 1024, 1024), ((700, 260, 512), 256, 128), ((64, 40, 32), 1024, 1024),
+                                                 ((520, 384, 300), 128, 1024)])
 @pytest.mark.parametrize("beta", [0.5, 0.0])
-def test_host_buffer_api(cuda, shape, panel, beta):
-    """Host arrays in, host array out, through the pipelined three-stream path; bit-identical to one device call."""
+def test_host_buffer_api(cuda, shape, panel, panel_k, beta):
+    """Host arrays in, host array out, through the pipelined three-stream path.  One K panel: bit-identical to one
+    device call; several K panels: bit-identical to the same panel schedule on the CPU, and within the tolerance."""
     import hpcdeepneuralnetworks_b200 as b2
     M, N, K = shape
     a, b, c = mats(M, N, K)
-    hs = b2.HostSgemm(M, N, K, panel_rows=panel)
+    hs = b2.HostSgemm(M, N, K, panel_rows=panel, panel_k=panel_k)
     hs.hA.copy_(torch.from_numpy(a)); hs.hB.copy_(torch.from_numpy(b)); hs.hC.copy_(torch.from_numpy(c))
     out = hs.run(1.0, beta).numpy().copy()
-    assert np.array_equal(out, oracle.sgemm_fma(1.0, a, b, beta, c))
+    want = c.copy()
+    for i, k0 in enumerate(range(0, K, hs.pk)):
+        k1 = min(K, k0 + hs.pk)
+        want = oracle.sgemm_fma(1.0, np.ascontiguousarray(a[:, k0:k1]), np.ascontiguousarray(b[k0:k1]), beta if i == 0 else 1.0, want)
+    assert np.array_equal(out, want)
+    c64, den = oracle.sgemm_f64(1.0, a, b, beta, c)
+    assert oracle.gemm_error(out, c64, den) <= TOL_FFMA
     hs.hC.copy_(torch.from_numpy(c))
     out2 = hs.run(1.0, beta, ft=(M >= 128)).numpy()          # second run on the same buffers, ABFT kernel
     assert np.array_equal(out2, out)
