@@ -234,6 +234,43 @@ def cublas_abft_baseline_ms(torch, A, B, Cm, steps, warmup):
     return timed(one, steps, warmup)
 
 
+def run_vec_sweep(args):
+    """BASELINE config 4: SAXPY and SDOT at n = 2^20, 2^24, 2^28, 2^30 (alpha = 2).  The two small sizes fit in the
+    126 MB L2; they are timed twice: back to back on the same vectors (L2-resident) and rotating through enough
+    distinct vector pairs to exceed L2 (the reference's own trick, kernel/saxpy/saxpy.cu:79-80,126)."""
+    import torch
+    import hpcdeepneuralnetworks_b200 as b2
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    rows = []
+    res = torch.zeros(1, device="cuda")
+    for log2n in (20, 24, 28, 30):
+        n = 1 << log2n
+        pairs = max(1, min(64, (512 * 2 ** 20) // (8 * n)))          # distinct (x, y) pairs: >= 512 MB in rotation
+        xs = b2.fill_uniform(torch.empty(pairs * n, device="cuda"), 4)
+        ys = b2.fill_uniform(torch.empty(pairs * n, device="cuda"), 5)
+        state = {"i": 0}
+
+        def rot(fn):
+            def f():
+                i = state["i"] = (state["i"] + 1) % pairs
+                fn(xs[i * n:(i + 1) * n], ys[i * n:(i + 1) * n])
+            return f
+        reps = 200 if log2n <= 24 else 10
+        row = {"n": n, "log2n": log2n, "pairs_in_rotation": pairs}
+        for name, per_elt, fn in (("saxpy", 12.0, lambda x, y: b2.saxpy(n, 2.0, x, y)), ("sdot", 8.0, lambda x, y: b2.sdot(n, x, y, res))):
+            ms = timed(rot(fn), reps, 5)
+            row[name + "_gbs"] = per_elt * n / (ms * 1e-3) / 1e9
+            row[name + "_frac_of_measured_hbm"] = row[name + "_gbs"] / peaks["hbm_gbs"]
+            if pairs > 1:
+                ms_hot = timed(lambda: fn(xs[:n], ys[:n]), reps, 5)
+                row[name + "_gbs_l2_resident"] = per_elt * n / (ms_hot * 1e-3) / 1e9
+        rows.append(row)
+        del xs, ys
+    print(json.dumps({"sweep": "saxpy_sdot_config4", "alpha": 2.0, "hbm_peak_gbs": peaks["hbm_gbs"], "rows": rows}))
+    return 0
+
+
 def run_series(args):
     """The reference's step-wise series sgemm_1 .. sgemm_14 (kernel/sgemm/include/kernel_*.cuh) at one size, GFLOPS per
     rung as in its README table and fig/ABFT_GEMM/bar_graph/fig9_plot_step_wise.py.  Prints one JSON object."""
@@ -311,6 +348,8 @@ def run_single(args):
         return run_sweep(args)
     if args.series:
         return run_series(args)
+    if args.vec_sweep:
+        return run_vec_sweep(args)
     if args.only == "vectors":   # small-case command for profiling the streaming kernels
         print(json.dumps(bench_vectors(b2, torch, peaks, args.steps, args.warmup, args.vec_log2n)))
         return 0
@@ -489,6 +528,7 @@ def main():
     ap.add_argument("--panel", type=int, default=4096, help="K-panel of the B broadcast (multi-GPU)")
     ap.add_argument("--only", default="all", choices=["all", "vectors"], help="vectors: SAXPY/SDOT only (profiling)")
     ap.add_argument("--vec-log2n", type=int, default=28, help="log2 of the vector length of the SAXPY/SDOT leg")
+    ap.add_argument("--vec-sweep", action="store_true", help="config 4: SAXPY/SDOT at n = 2^20, 2^24, 2^28, 2^30")
     ap.add_argument("--series", action="store_true", help="the reference's rungs sgemm_1..14 at --size (default 2048)")
     ap.add_argument("--sweep", action="store_true", help="config 2: N = 256..6144 step 256, both paths (prints a table object)")
     ap.add_argument("--abft", action="store_true", help="time the fault-tolerant SGEMM as the headline step (profiling)")

@@ -134,10 +134,12 @@ def test_verify_matrix_and_timer(cuda):
     assert info["sm_count"] > 0
 
 
-def test_large_vectors_properties(cuda):
-    """n = 2^28: full-size checks through size-independent properties (linearity, known sums)."""
+@pytest.mark.parametrize("log2n", [28, 30])
+def test_large_vectors_properties(cuda, log2n):
+    """n = 2^28 and 2^30 (the largest configured size, 4 GiB per vector): full-size checks through size-independent
+    properties (linearity, known sums, a checksum of checksums)."""
     import hpcdeepneuralnetworks_b200 as b2
-    n = 1 << 28
+    n = 1 << log2n
     x = b2.fill_uniform(torch.empty(n, device="cuda"), 4)
     y = b2.fill_const(torch.empty(n, device="cuda"), 0.0)
     b2.saxpy(n, 2.0, x, y)                      # y = 2x exactly
