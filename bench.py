@@ -376,6 +376,31 @@ def run_single(args):
     clocks = clk.summary()
     tflops = flop / (ms * 1e-3) / 1e12
 
+    def tf32_library_peak():
+        """cuBLAS TF32 GEMM 8192^3 through torch, best of 5 (the same recipe as the pool's bf16 peak): context for
+        the tensor-path fraction, since TF32 is not in MEASURED_PEAKS.json."""
+        old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            m = 8192
+            x = torch.rand(m, m, device="cuda")
+            y = torch.rand(m, m, device="cuda")
+            for _ in range(2):
+                x @ y
+            best = 1e30
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                x @ y
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            return 2.0 * m ** 3 / (best * 1e-3) / 1e12
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = old
+
+    tf32_lib = None if args.quick else tf32_library_peak()
+
     def roof(p, tf):
         if p == 0:
             return {"bound": "fp32_simt", "achieved": tf, "peak": ffma_peak, "unit": "TFLOP/s", "frac": tf / ffma_peak,
@@ -384,7 +409,8 @@ def run_single(args):
         tf32_peak = peaks["bf16_tflops"] / 2.0       # dense TF32 runs at half the bf16 rate
         return {"bound": "tensor", "achieved": 3.0 * tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": 3.0 * tf / tf32_peak,
                 "traffic": NCU_TRAFFIC["sgemm_3xtf32_6144"], "peak_source": f"{peaks['source']} bf16 GEMM / 2",
-                "useful_tflops": tf, "algorithmic_flop": 3.0 * flop}
+                "useful_tflops": tf, "algorithmic_flop": 3.0 * flop,
+                "cublas_tf32_gemm_tflops_same_run": tf32_lib, "frac_of_cublas_tf32": (3.0 * tf / tf32_lib) if tf32_lib else None}
 
     extras = {}
     if not args.quick:

@@ -94,6 +94,7 @@ def load() -> C.CDLL:
     L.b2_ffma2_peak_probe.argtypes = [i32, i64, C.POINTER(C.c_double), vp]
     L.b2_device_info.argtypes = [C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_size_t)]
     L.b2_check_status.argtypes = [vp, vp]
+    L.b2_selftest_wait_timeout.argtypes = [vp, i32, vp]
     L.b2_set_ffma_variant.argtypes = [i32]
     L.b2_ffma_tile_info.argtypes = [i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_char_p)]
     L.b2_set_ffma_tile.argtypes = [i32]

@@ -108,12 +108,13 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22),
+                                          uint64_t limit_ns = 1000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) return false;
+    if ((i & 255u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
   }
   return false;
 }

@@ -105,6 +105,21 @@ int make_tmap_2d(CUtensorMap *out, const float *base, uint64_t inner, uint64_t o
 
 }  // namespace b2
 
+namespace b2 {
+// One block waits on an mbarrier that nothing will ever arrive on, with a short time limit, and
+// reports the timeout through the status word: the path every bounded wait of the GEMM kernels
+// takes when a copy or a peer never shows up.  The context stays usable.
+__global__ void wait_timeout_selftest_kernel(uint64_t limit_ns, int *status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait(&bar, 0, 1u << 22, limit_ns)) atomicExch(status, (int)B2_ERR_TIMEOUT);
+}
+}  // namespace b2
+
 using namespace b2;
 
 struct b2_context : public Context {};
@@ -195,6 +210,16 @@ int b2_timer_elapsed_ms(b2_timer t, float *ms_out) {
   B2_REQUIRE(t != nullptr && ms_out != nullptr, B2_ERR_INVALID_ARG, "timer or output is NULL");
   B2_CUDA(cudaEventSynchronize(t->end));
   B2_CUDA(cudaEventElapsedTime(ms_out, t->beg, t->end));
+  return B2_OK;
+}
+
+int b2_selftest_wait_timeout(b2_handle h, int timeout_us, void *stream) {
+  Context *c = h ? (Context *)h : default_context();
+  B2_REQUIRE(c != nullptr, B2_ERR_CUDA, "b2_selftest_wait_timeout: no context");
+  B2_REQUIRE(timeout_us >= 1 && timeout_us <= 100000, B2_ERR_INVALID_ARG, "b2_selftest_wait_timeout: %d us not in 1..100000", timeout_us);
+  wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((uint64_t)timeout_us * 1000ull,
+                                                                    (int *)((char *)c->fixed + kFixedStatus));
+  B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
 

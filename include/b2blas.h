@@ -211,6 +211,11 @@ int b2_set_tf32_tile_n(int n);
  * Returns 0 or the recorded negative status. */
 int b2_check_status(b2_handle h, void *stream);
 
+/* Self-test of the bounded-wait path: one block waits `timeout_us` (1..100000) on a barrier that
+ * nothing completes, gives up and records B2_ERR_TIMEOUT in the handle's status word, which
+ * b2_check_status then returns.  The GPU context stays usable; nothing faults or hangs. */
+int b2_selftest_wait_timeout(b2_handle h, int timeout_us, void *stream);
+
 /* getDetails (utils/utils.cu:21-26): SM count and clock of the current device. */
 int b2_device_info(int *sm_count, int *sm_clock_khz, size_t *global_mem_bytes);
 

@@ -300,3 +300,22 @@ def test_host_buffer_api(cuda, shape, panel, panel_k, beta):
     hs.hC.copy_(torch.from_numpy(c))
     out2 = hs.run(1.0, beta, ft=(M >= 128)).numpy()          # second run on the same buffers, ABFT kernel
     assert np.array_equal(out2, out)
+
+
+def test_bounded_wait_times_out_and_context_survives(cuda):
+    """A device-side wait that nothing satisfies gives up after its limit, the host reads B2_ERR_TIMEOUT, and the
+    next launches run normally (no trap, no hang, no lost context)."""
+    import time
+    import hpcdeepneuralnetworks_b200 as b2
+    from hpcdeepneuralnetworks_b200 import _lib
+    L = _lib.load()
+    h = b2.default_handle()
+    t0 = time.time()
+    assert L.b2_selftest_wait_timeout(h.raw, 2000, None) == 0          # 2 ms limit
+    with pytest.raises(b2.B2Error) as e:
+        b2.check_status()
+    assert e.value.status == -4 and time.time() - t0 < 5.0
+    b2.check_status()                                                   # the status word was cleared
+    a, b, c = mats(128, 128, 64)
+    assert np.array_equal(run_gpu(0, a, b, c, 1.0, 0.5), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    assert L.b2_selftest_wait_timeout(h.raw, 0, None) == -1
