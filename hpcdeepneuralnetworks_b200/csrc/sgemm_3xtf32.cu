@@ -129,7 +129,13 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   const int m0 = tile_m * TBM, n0 = tile_n * TBN;
   const int nkb = (p.K + TBK - 1) / TBK;
 
-  if (*reinterpret_cast<volatile int *>(p.status) != 0) return;  // an earlier CTA of this launch timed out
+  {
+    // an earlier CTA of this launch timed out: leave at once (one thread reads, so the whole CTA agrees)
+    __shared__ int launch_aborted;
+    if (threadIdx.x == 0) launch_aborted = *reinterpret_cast<volatile int *>(p.status);
+    __syncthreads();
+    if (launch_aborted != 0) return;
+  }
   if (tid == 0) {
     for (int s = 0; s < TSTAGES; ++s) {
       mbar_init(&full[s], 1);

@@ -242,7 +242,13 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int m0 = tile_m * BM, n0 = tile_n * BN;
   const int nkb = (p.K + FBK - 1) / FBK;
 
-  if (*reinterpret_cast<volatile int *>(p.status) != 0) return;  // an earlier CTA of this launch timed out
+  {
+    // an earlier CTA of this launch timed out: leave at once (one thread reads, so the whole CTA agrees)
+    __shared__ int launch_aborted;
+    if (threadIdx.x == 0) launch_aborted = *reinterpret_cast<volatile int *>(p.status);
+    __syncthreads();
+    if (launch_aborted != 0) return;
+  }
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < FSTAGES; ++s) {
