@@ -371,3 +371,8 @@ def set_ffma_tile(index: int):
 def set_tf32_tile_n(n: int):
     """Pin the 3xTF32 tile width (128 or 256; 0 = automatic)."""
     check(_lib.load().b2_set_tf32_tile_n(n))
+
+
+def set_tf32_slab_k(k: int):
+    """K-slab depth of the 3xTF32 kernel (16 or 32)."""
+    check(_lib.load().b2_set_tf32_slab_k(k))

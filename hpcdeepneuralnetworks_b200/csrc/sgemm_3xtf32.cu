@@ -25,17 +25,21 @@
 
 namespace b2 {
 
-constexpr int TBM = 128, TBK = 32;
-constexpr int kTA = TBM * TBK * 4;                 // 16 KB per A plane tile
-// Two tile widths: 128 x 256 (2 stages of 96 KB) and 128 x 128 (3 stages of 64 KB) for problem
-// sizes whose 128 x 256 tile grid fills the last wave of 148 SMs badly.
-template <int TBN>
+constexpr int TBM = 128;
+// Two tile widths: 128 x 256 and 128 x 128 (for problem sizes whose 128 x 256 tile grid fills the
+// last wave of 148 SMs badly).  K-slab depth TBK: 32 floats = one 128-byte swizzled row, or 16
+// floats = one 64-byte swizzled row; the shallower slab doubles the number of stages that fit
+// (more TMA bytes in flight for the same shared memory).
+template <int TBN, int TBK>
 struct Tf32Cfg {
-  static constexpr int kStages = (TBN == 256) ? 2 : 3;
+  static constexpr int kTA = TBM * TBK * 4;          // bytes per A plane tile
   static constexpr int kTB = TBN * TBK * 4;          // bytes per B plane tile
   static constexpr int kStage = 2 * kTA + 2 * kTB;
+  static constexpr int kStages = (192 * 1024) / kStage;
   static constexpr int kSmem = 1024 + kStages * kStage + 256;
   static constexpr int kTmemCols = TBN;              // FP32 accumulator: one TMEM column per output column
+  static constexpr uint32_t kSwizzle = (TBK == 32) ? 2u : 4u;   // descriptor layout type: 128-byte / 64-byte swizzle
+  static constexpr uint32_t kSbo = 8 * TBK * 4;                 // bytes between 8-row groups
 };
 
 __device__ __forceinline__ float tf32_rna(float x) {
@@ -108,12 +112,13 @@ struct Tf32Args {
   int *status;
 };
 
-template <int TBN>
+template <int TBN, int TBK>
 __global__ void __launch_bounds__(192, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
-  constexpr int TSTAGES = Tf32Cfg<TBN>::kStages, kTB = Tf32Cfg<TBN>::kTB, kTStage = Tf32Cfg<TBN>::kStage;
-  constexpr int kTmemCols = Tf32Cfg<TBN>::kTmemCols;
+  using Cfg = Tf32Cfg<TBN, TBK>;
+  constexpr int TSTAGES = Cfg::kStages, kTA = Cfg::kTA, kTB = Cfg::kTB, kTStage = Cfg::kStage;
+  constexpr int kTmemCols = Cfg::kTmemCols;
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
   unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -195,10 +200,10 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
         for (int k4 = 0; k4 < TBK / 8; ++k4) {
           // K-major, 128B swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart; a K-step of
           // 8 floats is 32 bytes further along the row.
-          const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
-          const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
-          const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
-          const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
+          const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+          const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+          const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+          const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
           umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
@@ -278,20 +283,21 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 }
 
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
+static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 
 size_t tf32_workspace_bytes(int M, int N, int K) {
   const size_t kp = ((size_t)K + 3) & ~(size_t)3;
   return (2 * (size_t)M * kp + 2 * (size_t)N * kp) * sizeof(float) + 4 * 1024;
 }
 
-template <int TBN>
+template <int TBN, int TBK>
 static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<TBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tf32Cfg<TBN>::kSmem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<TBN, TBK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tf32Cfg<TBN, TBK>::kSmem));
     configured = true;
   }
-  sgemm_3xtf32_kernel<TBN><<<grid, 192, Tf32Cfg<TBN>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
+  sgemm_3xtf32_kernel<TBN, TBK><<<grid, 192, Tf32Cfg<TBN, TBK>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
@@ -324,9 +330,11 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   B2_CUDA(cudaGetLastError());
 
   CUtensorMap maps[4];
-  st = make_tmap_2d(&maps[0], Ah, (uint64_t)K, (uint64_t)M, (uint64_t)kp, TBK, TBM, CU_TENSOR_MAP_SWIZZLE_128B);
+  const int tbk = (g_tf32_slab_k == 32) ? 32 : 16;
+  const CUtensorMapSwizzle swz = (tbk == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  st = make_tmap_2d(&maps[0], Ah, (uint64_t)K, (uint64_t)M, (uint64_t)kp, tbk, TBM, swz);
   if (st != B2_OK) return st;
-  st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, TBK, TBM, CU_TENSOR_MAP_SWIZZLE_128B);
+  st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, tbk, TBM, swz);
   if (st != B2_OK) return st;
   // tile width: whole waves of one CTA per SM; a 128-wide tile costs ~0.55 of a 256-wide one
   const double sms = (double)ctx->sm_count;
@@ -334,9 +342,9 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
   int tbn = (t128 < t256) ? 128 : 256;
   if (g_tf32_tile_n == 128 || g_tf32_tile_n == 256) tbn = g_tf32_tile_n;
-  st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, tbn, CU_TENSOR_MAP_SWIZZLE_128B);
+  st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
   if (st != B2_OK) return st;
-  st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, TBK, tbn, CU_TENSOR_MAP_SWIZZLE_128B);
+  st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
   if (st != B2_OK) return st;
 
   Tf32Args args;
@@ -344,7 +352,8 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
   const int grid = ((M + TBM - 1) / TBM) * ((N + tbn - 1) / tbn);
-  return tbn == 128 ? launch_tf32<128>(maps, args, grid, s) : launch_tf32<256>(maps, args, grid, s);
+  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32>(maps, args, grid, s) : launch_tf32<256, 32>(maps, args, grid, s);
+  return tbn == 128 ? launch_tf32<128, 16>(maps, args, grid, s) : launch_tf32<256, 16>(maps, args, grid, s);
 }
 
 }  // namespace b2
@@ -362,6 +371,12 @@ size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K) {
 int b2_set_tf32_tile_n(int n) {
   B2_REQUIRE(n == 0 || n == 128 || n == 256, B2_ERR_INVALID_ARG, "b2_set_tf32_tile_n: %d is not 0, 128 or 256", n);
   b2::g_tf32_tile_n = n;
+  return B2_OK;
+}
+// K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.
+int b2_set_tf32_slab_k(int k) {
+  B2_REQUIRE(k == 16 || k == 32, B2_ERR_INVALID_ARG, "b2_set_tf32_slab_k: %d is not 16 or 32", k);
+  b2::g_tf32_slab_k = k;
   return B2_OK;
 }
 

@@ -207,6 +207,8 @@ int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name);
 int b2_set_ffma_tile(int i);
 /* Pins the tile width of the 3xTF32 kernel (128 or 256 output columns per CTA; 0 = automatic). */
 int b2_set_tf32_tile_n(int n);
+/* K-slab depth of the 3xTF32 kernel: 16 (64-byte swizzle, 4-6 stages) or 32 (128-byte swizzle, 2-3 stages). */
+int b2_set_tf32_slab_k(int k);
 /* Reads and clears the device status word that bounded waits set; synchronises the stream.
  * Returns 0 or the recorded negative status. */
 int b2_check_status(b2_handle h, void *stream);

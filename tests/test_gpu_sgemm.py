@@ -203,10 +203,12 @@ def test_3xtf32_path(cuda, shape, alpha, beta):
     assert err <= TOL_3XTF32, f"3xTF32 error {err:.3e}"
 
 
+@pytest.mark.parametrize("slab_k", [32, 16])
 @pytest.mark.parametrize("tile_n", [128, 256])
-def test_3xtf32_both_tile_widths(cuda, tile_n):
+def test_3xtf32_both_tile_widths(cuda, tile_n, slab_k):
     import hpcdeepneuralnetworks_b200 as b2
     b2.set_tf32_tile_n(tile_n)
+    b2.set_tf32_slab_k(slab_k)
     try:
         for shape in ((256, 512, 96), (130, 300, 70), (640, 384, 200)):
             a, b, c = mats(*shape)
@@ -215,6 +217,7 @@ def test_3xtf32_both_tile_widths(cuda, tile_n):
             assert oracle.gemm_error(got, c64, den) <= TOL_3XTF32
     finally:
         b2.set_tf32_tile_n(0)
+        b2.set_tf32_slab_k(32)
 
 
 def test_3xtf32_leading_dimensions(cuda):
