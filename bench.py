@@ -428,6 +428,13 @@ def run_single(args):
         except Exception as e:  # reported, not hidden
             extras["abft_ffma"] = {"error": str(e)}
         try:
+            ms_ft3 = timed(lambda: b2.ft_sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=1), max(3, args.steps // 2), 3)
+            ms_plain3 = ms if path == 1 else ms_o
+            extras["abft_3xtf32"] = {"ms": ms_ft3, "value": flop / (ms_ft3 * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                     "overhead_pct": 100.0 * (ms_ft3 / ms_plain3 - 1.0)}
+        except Exception as e:
+            extras["abft_3xtf32"] = {"error": str(e)}
+        try:
             ms_cb = cublas_abft_baseline_ms(torch, A, B, Cm, 3, 1)
             extras["abft_cublas_nonfused_baseline"] = {"ms": ms_cb, "value": flop / (ms_cb * 1e-3) / 1e12, "unit": "TFLOP/s",
                                                        "note": "cuBLAS gemm/gemv/axpy/dot per 256-K panel with syncs, as baseline_ft_sgemm.cuh"}

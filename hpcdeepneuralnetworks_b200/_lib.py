@@ -34,7 +34,7 @@ class FtReport(C.Structure):
 
     _fields_ = [("tiles", C.c_int32), ("injected", C.c_int32), ("detected", C.c_int32),
                 ("corrected", C.c_int32), ("uncorrectable", C.c_int32), ("false_alarms", C.c_int32),
-                ("reserved", C.c_int32 * 2)]
+                ("max_residual_bits", C.c_int32), ("reserved", C.c_int32)]
 
 
 def declared_symbols() -> list[str]:

@@ -156,8 +156,9 @@ def new_report() -> torch.Tensor:
 
 def read_report(report: torch.Tensor) -> dict:
     v = report.cpu().tolist()
+    import struct
     return {"tiles": v[0], "injected": v[1], "detected": v[2], "corrected": v[3], "uncorrectable": v[4],
-            "false_alarms": v[5]}
+            "false_alarms": v[5], "max_residual": struct.unpack("f", struct.pack("i", v[6]))[0]}
 
 
 def saxpy(n, alpha, x, y, handle=None):

@@ -75,6 +75,16 @@ __host__ __device__ inline float uniform_at(uint64_t mixed_seed, uint64_t i) {
   return (float)u * (1.0f / 8388608.0f) - 1.0f;
 }
 
+// What an ABFT launch needs beyond the plain SGEMM arguments (both math paths).
+struct FtArgs {
+  const b2_fault *plan;
+  int n_faults;
+  float tau;
+  int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable, false alarms, max residual bits
+  const float *A, *B;
+  int lda, ldb;
+};
+
 #ifdef __CUDACC__
 // ---- device: mbarrier --------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -174,6 +184,12 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
+}
+// 32 lanes x 1 column.
+__device__ __forceinline__ uint32_t tmem_ld_32x1(uint32_t taddr) {
+  uint32_t v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr) : "memory");
+  return v;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

@@ -20,6 +20,7 @@
 // Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -30,14 +31,31 @@ constexpr int TBM = 128;
 // last wave of 148 SMs badly).  K-slab depth TBK: 32 floats = one 128-byte swizzled row, or 16
 // floats = one 64-byte swizzled row; the shallower slab doubles the number of stages that fit
 // (more TMA bytes in flight for the same shared memory).
-template <int TBN, int TBK>
+//
+// FT adds the ABFT checksum operand.  A checksum covers one row of a group of 32 output columns.
+// With s_g[k] = sum_{j<32} B[k][32g + j] split into hi and lo parts like B itself, the operand is,
+// per 256-column tile and K-slab, a 32 x TBK tile S (K-major like the B planes):
+//     rows 0..7 s_hi of groups 0..7, rows 8..15 s_lo, rows 16..23 s_hi again, rows 24..31 zero.
+// Two more MMAs of N = 16 per K-step multiply it by the A tiles the main MMAs already use, both
+// into the same 16 extra TMEM columns:
+//     A_lo x S[16..31]  -> column TBN + g     += A_lo*s_hi
+//     A_hi x S[0..15]   -> column TBN + g     += A_hi*s_hi,   column TBN + 8 + g += A_hi*s_lo
+// and the expected sum of a row's group g is column TBN + g plus column TBN + 8 + g.  A small-N
+// MMA costs about as much as fetching its A operand again, so two of them rather than three
+// matter; keeping both s_hi terms in one accumulator makes its truncation error follow that of
+// the data accumulators more closely (smaller clean residual) than three separate columns do.
+constexpr int kFtGroup = 32;                         // output columns per checksum
+constexpr int kFtRows = 32;                          // rows of S per 256-column tile
+template <int TBN, int TBK, bool FT = false>
 struct Tf32Cfg {
   static constexpr int kTA = TBM * TBK * 4;          // bytes per A plane tile
   static constexpr int kTB = TBN * TBK * 4;          // bytes per B plane tile
-  static constexpr int kStage = 2 * kTA + 2 * kTB;
-  static constexpr int kStages = (192 * 1024) / kStage;
+  static constexpr int kTS = FT ? kFtRows * TBK * 4 : 0;  // bytes per checksum tile
+  static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;
+  static constexpr int kStages = ((FT ? 208 : 192) * 1024) / kStage;
   static constexpr int kSmem = 1024 + kStages * kStage + 256;
-  static constexpr int kTmemCols = TBN;              // FP32 accumulator: one TMEM column per output column
+  // FP32 accumulator: one TMEM column per output column; FT: 16 more, rounded to a power of two
+  static constexpr int kTmemCols = FT ? 2 * TBN : TBN;
   static constexpr uint32_t kSwizzle = (TBK == 32) ? 2u : 4u;   // descriptor layout type: 128-byte / 64-byte swizzle
   static constexpr uint32_t kSbo = 8 * TBK * 4;                 // bytes between 8-row groups
 };
@@ -78,8 +96,12 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float *__restri
 // Transposing variant: X is rows x cols (pitch ld); planes are cols x rows (pitch ldp >= rows,
 // a multiple of 4).  64 x 64 tiles through shared memory: coalesced reads along the columns of X,
 // 128-bit coalesced writes along the rows of X.
+// With S != NULL it also writes the ABFT checksum plane (pitch ldp, 24 rows per 256 columns of X):
+// for every row r of X and group g of 32 columns inside 256-column tile t, S[24t + g][r] and
+// S[24t + 8 + g][r] are the lo/hi split of sum_{j<32} X[r][256t + 32g + j]; S[24t + 16 + g][r] = 0.
 __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld,
-                                                             float *__restrict__ hi, float *__restrict__ lo, int ldp) {
+                                                             float *__restrict__ hi, float *__restrict__ lo, int ldp,
+                                                             float *__restrict__ S) {
   __shared__ float t[64][65];
   const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64, tid = threadIdx.x;
   for (int e = tid; e < 64 * 64; e += 256) {
@@ -102,6 +124,23 @@ __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__rest
       *reinterpret_cast<float4 *>(lo + (size_t)c * ldp + r) = l;
     }
   }
+  if (S != nullptr) {
+    const int rr = tid & 63, gg = (tid >> 6) & 1;   // row r0 + rr of X, columns c0 + 32gg .. +31
+    const size_t o = ((size_t)(c0 / 256) * kFtRows + (c0 % 256) / 32 + gg) * ldp + r0 + rr;
+    if (r0 + rr < ldp) {
+      if (tid < 128) {
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum += t[rr][32 * gg + j];
+        const float h = tf32_rna(sum);
+        S[o] = h;
+        S[o + (size_t)8 * ldp] = tf32_rna(sum - h);
+        S[o + (size_t)16 * ldp] = h;
+      } else {
+        S[o + (size_t)24 * ldp] = 0.f;
+      }
+    }
+  }
 }
 
 struct Tf32Args {
@@ -110,14 +149,35 @@ struct Tf32Args {
   float alpha, beta;
   int vec_c;
   int *status;
+  FtArgs ft;        // used by the FT instantiations only
+  float tau_elem;   // an output further than this from its recomputed value is replaced
 };
 
-template <int TBN, int TBK>
+// FP32 dot product of row `row` of A with column col0 + lane of B, from global memory (two
+// interleaved chains over K).  Called by whole warps.
+__device__ __forceinline__ float ft_recompute32(const Tf32Args &p, int row, int col0, int lane) {
+  const int col = col0 + lane;
+  float acc0 = 0.f, acc1 = 0.f;
+  if (row < p.M && col < p.N) {
+    const float *a = p.ft.A + (size_t)row * p.ft.lda;
+    const float *b = p.ft.B + col;
+    int k = 0;
+    for (; k + 1 < p.K; k += 2) {
+      acc0 = __fmaf_rn(a[k], b[(size_t)k * p.ft.ldb], acc0);
+      acc1 = __fmaf_rn(a[k + 1], b[(size_t)(k + 1) * p.ft.ldb], acc1);
+    }
+    if (k < p.K) acc0 = __fmaf_rn(a[k], b[(size_t)k * p.ft.ldb], acc0);
+  }
+  return acc0 + acc1;
+}
+
+template <int TBN, int TBK, bool FT>
 __global__ void __launch_bounds__(192, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
-                    const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
-  using Cfg = Tf32Cfg<TBN, TBK>;
-  constexpr int TSTAGES = Cfg::kStages, kTA = Cfg::kTA, kTB = Cfg::kTB, kTStage = Cfg::kStage;
+                    const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                    const __grid_constant__ CUtensorMap tmS, const Tf32Args p) {
+  using Cfg = Tf32Cfg<TBN, TBK, FT>;
+  constexpr int TSTAGES = Cfg::kStages, kTA = Cfg::kTA, kTB = Cfg::kTB, kTS = Cfg::kTS, kTStage = Cfg::kStage;
   constexpr int kTmemCols = Cfg::kTmemCols;
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
@@ -153,6 +213,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     tma_prefetch_desc(&tmAl);
     tma_prefetch_desc(&tmBh);
     tma_prefetch_desc(&tmBl);
+    if (FT) tma_prefetch_desc(&tmS);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -180,12 +241,14 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * TBK, n0);
           tma_load_2d(st + 2 * kTA + kTB, &tmBl, &full[s], kb * TBK, n0);
         }
+        if (FT) tma_load_2d(st + 2 * kTA + 2 * kTB, &tmS, &full[s], kb * TBK, tile_n * kFtRows);
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(TBM, TBN, 0, 0);
+      constexpr uint32_t idesc_s = umma_idesc_tf32(TBM, 16, 0, 0);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % TSTAGES;
@@ -207,6 +270,12 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
+          if (FT) {
+            const uint64_t s_lohi = umma_smem_desc(st + 2 * kTA + 2 * kTB + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+            const uint64_t s_hi0 = umma_smem_desc(st + 2 * kTA + 2 * kTB + 16 * TBK * 4 + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+            umma_tf32(tmem_base + TBN, a_lo, s_hi0, idesc_s, (kb > 0 || k4 > 0) ? 1u : 0u);
+            umma_tf32(tmem_base + TBN, a_hi, s_lohi, idesc_s, 1u);
+          }
         }
         umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
       }
@@ -216,6 +285,25 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 -------------------------------
     const int q = warp & 3;
     bool ok = true;
+    // planned faults that land in this thread's row of this tile: at most one per 128 columns
+    int inj_col0 = -1, inj_col1 = -1;
+    uint32_t inj_mask0 = 0u, inj_mask1 = 0u;
+    if (FT) {
+      const int my_row = m0 + q * 32 + lane;
+      for (int f = 0; f < p.ft.n_faults; ++f) {
+        const b2_fault ff = p.ft.plan[f];
+        const int gr = ff.tile_m * 128 + ff.row, gc = ff.tile_n * 128 + ff.col;
+        if (gr == my_row && gr < p.M && gc >= n0 && gc < n0 + TBN && gc < p.N) {
+          if (gc - n0 < 128) {
+            if (inj_col0 < 0) { inj_col0 = gc - n0; inj_mask0 = 1u << (ff.bit & 31); }
+          } else if (inj_col1 < 0) {
+            inj_col1 = gc - n0; inj_mask1 = 1u << (ff.bit & 31);
+          }
+        }
+      }
+    }
+    float worst = 0.f;          // largest in-tolerance |group sum - checksum| this thread saw
+    int n_inj = 0, n_det = 0, n_cor = 0, n_false = 0;
     if (nkb > 0) {
       // poll in slices so that an abort raised by the other roles is seen
       bool done = false;
@@ -226,6 +314,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
       }
       ok = done;
     }
+    ok = __all_sync(0xffffffffu, ok);   // the checksum pass below uses warp collectives
     if (!ok) *abort_flag = 1;
     tc_fence_after();
     const int row = m0 + q * 32 + lane;
@@ -234,12 +323,61 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 #pragma unroll 1
     for (int c = 0; c < TBN / 32; ++c) {
       uint32_t v[32];
+      float expect = 0.f;
       if (ok && nkb > 0) {
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        if (FT) {
+          const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(TBN + c);
+          const uint32_t e0 = tmem_ld_32x1(t0), e1 = tmem_ld_32x1(t0 + 8);
+          tmem_ld_wait();
+          expect = __uint_as_float(e0) + __uint_as_float(e1);
+        }
         tmem_ld_wait();
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      if (FT && ok && nkb > 0) {
+        // simulated soft errors: flip one bit of an accumulator as it leaves TMEM
+        if (inj_col0 >= 0 && (inj_col0 >> 5) == c) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j == (inj_col0 & 31)) v[j] ^= inj_mask0;
+          ++n_inj;
+        }
+        if (TBN > 128 && inj_col1 >= 0 && (inj_col1 >> 5) == c) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j == (inj_col1 & 31)) v[j] ^= inj_mask1;
+          ++n_inj;
+        }
+        {
+          float g = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) g += __uint_as_float(v[j]);
+          const float resid = fabsf(g - expect);
+          const bool bad = !(resid <= p.ft.tau);
+          if (!bad) worst = fmaxf(worst, resid);
+          unsigned m = __ballot_sync(0xffffffffu, bad);
+          while (m) {
+            const int L = __ffs(m) - 1;
+            m &= m - 1;
+            const int rowL = __shfl_sync(0xffffffffu, m0 + q * 32 + lane, L);
+            const float ref = ft_recompute32(p, rowL, n0 + c * 32, lane);
+            int replaced = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float r = __shfl_sync(0xffffffffu, ref, j);
+              if (lane == L && !(fabsf(__uint_as_float(v[j]) - r) <= p.tau_elem)) {
+                v[j] = __float_as_uint(r);
+                ++replaced;
+              }
+            }
+            if (lane == L) {
+              if (replaced) { ++n_det; n_cor += replaced; } else { ++n_false; }
+            }
+          }
+        }
       }
       if (!ok || row >= p.M) continue;
       const int col0 = n0 + c * 32;
@@ -271,6 +409,25 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
         }
       }
     }
+    if (FT) {
+      // one set of atomics per warp
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        n_inj += __shfl_xor_sync(0xffffffffu, n_inj, o);
+        n_det += __shfl_xor_sync(0xffffffffu, n_det, o);
+        n_cor += __shfl_xor_sync(0xffffffffu, n_cor, o);
+        n_false += __shfl_xor_sync(0xffffffffu, n_false, o);
+        worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+      }
+      if (lane == 0) {
+        if (q == 0) atomicAdd(&p.ft.report[0], 1);
+        if (n_inj) atomicAdd(&p.ft.report[1], n_inj);
+        if (n_det) atomicAdd(&p.ft.report[2], n_det);
+        if (n_cor) atomicAdd(&p.ft.report[3], n_cor);
+        if (n_false) atomicAdd(&p.ft.report[5], n_false);
+        atomicMax(&p.ft.report[6], __float_as_int(worst));
+      }
+    }
   }
 
   tc_fence_before();
@@ -285,30 +442,38 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
 static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 
+// hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
+// (24 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
 size_t tf32_workspace_bytes(int M, int N, int K) {
   const size_t kp = ((size_t)K + 3) & ~(size_t)3;
-  return (2 * (size_t)M * kp + 2 * (size_t)N * kp) * sizeof(float) + 4 * 1024;
+  const size_t srows = (((size_t)N + 255) / 256) * kFtRows;
+  return (2 * (size_t)M * kp + 2 * (size_t)N * kp + srows * kp) * sizeof(float) + 8 * 1024;
 }
 
-template <int TBN, int TBK>
+template <int TBN, int TBK, bool FT>
 static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<TBN, TBK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tf32Cfg<TBN, TBK>::kSmem));
+    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<TBN, TBK, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Tf32Cfg<TBN, TBK, FT>::kSmem));
     configured = true;
   }
-  sgemm_3xtf32_kernel<TBN, TBK><<<grid, 192, Tf32Cfg<TBN, TBK>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], args);
+  sgemm_3xtf32_kernel<TBN, TBK, FT><<<grid, 192, Tf32Cfg<TBN, TBK, FT>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3],
+                                                                                      maps[4], args);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
 
-int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
-                        const float *B, int ldb, float beta, float *C, int ldc, cudaStream_t s);
+int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
+                           const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
 
+// ft == NULL: plain 3xTF32 SGEMM; otherwise the ABFT form (checksum operand, verification and
+// recompute-based repair in the epilogue).
 int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
-                          float beta, float *C, int ldc, cudaStream_t s) {
+                          float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s) {
   if (M == 0 || N == 0) return B2_OK;
-  if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, s);
+  // nothing for the tensor cores to do: the FFMA path's scaling pass covers it
+  if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s);
   int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
   if (st != B2_OK) return st;
   const int kp = (K + 3) & ~3;
@@ -319,18 +484,21 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   float *Al = (float *)(w + align1k(a_elems * 4));
   float *Bh = (float *)(w + 2 * align1k(a_elems * 4));
   float *Bl = (float *)(w + 2 * align1k(a_elems * 4) + align1k(b_elems * 4));
+  const int srows = ((N + 255) / 256) * kFtRows;
+  float *S = (float *)(w + 2 * align1k(a_elems * 4) + 2 * align1k(b_elems * 4));
 
   {
     const int vec = ((((uintptr_t)A) & 15) == 0 && (lda % 4) == 0) ? 1 : 0;
     dim3 g((kp / 4 + 255) / 256, M < 16384 ? M : 16384);
     split_planes_kernel<<<g, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp, vec);
-    dim3 gt((N + 63) / 64, (kp + 63) / 64);
-    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp);
+    // the ABFT form covers whole 256-column tiles so that every checksum row is written
+    dim3 gt(ft ? ((N + 255) / 256) * 4 : (N + 63) / 64, (kp + 63) / 64);
+    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp, ft ? S : nullptr);
   }
   B2_CUDA(cudaGetLastError());
 
-  CUtensorMap maps[4];
-  const int tbk = (g_tf32_slab_k == 32) ? 32 : 16;
+  CUtensorMap maps[5];
+  const int tbk = (g_tf32_slab_k == 32 || ft) ? 32 : 16;   // the ABFT form is built for the 32-deep slab only
   const CUtensorMapSwizzle swz = (tbk == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   st = make_tmap_2d(&maps[0], Ah, (uint64_t)K, (uint64_t)M, (uint64_t)kp, tbk, TBM, swz);
   if (st != B2_OK) return st;
@@ -342,18 +510,32 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
   int tbn = (t128 < t256) ? 128 : 256;
   if (g_tf32_tile_n == 128 || g_tf32_tile_n == 256) tbn = g_tf32_tile_n;
+  if (ft) tbn = 256;   // the checksum operand is laid out for 256-column tiles
   st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
   if (st != B2_OK) return st;
 
+  if (ft) {
+    st = make_tmap_2d(&maps[4], S, (uint64_t)K, (uint64_t)srows, (uint64_t)kp, tbk, kFtRows, swz);
+    if (st != B2_OK) return st;
+  } else {
+    maps[4] = maps[2];
+  }
+
   Tf32Args args;
+  memset(&args, 0, sizeof(args));
   args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
   const int grid = ((M + TBM - 1) / TBM) * ((N + tbn - 1) / tbn);
-  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32>(maps, args, grid, s) : launch_tf32<256, 32>(maps, args, grid, s);
-  return tbn == 128 ? launch_tf32<128, 16>(maps, args, grid, s) : launch_tf32<256, 16>(maps, args, grid, s);
+  if (ft) {
+    args.ft = *ft;
+    args.tau_elem = 0.5f * ft->tau;
+    return launch_tf32<256, 32, true>(maps, args, grid, s);
+  }
+  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, false>(maps, args, grid, s) : launch_tf32<256, 32, false>(maps, args, grid, s);
+  return tbn == 128 ? launch_tf32<128, 16, false>(maps, args, grid, s) : launch_tf32<256, 16, false>(maps, args, grid, s);
 }
 
 }  // namespace b2

@@ -87,14 +87,6 @@ struct FfmaArgs {
 // arithmetic; every accumulator that differs is replaced, which both locates and corrects
 // the fault exactly (the reference subtracts a rounded residual with the location left
 // unfinished, ft_sgemm_huge.cuh:296-371).
-struct FtArgs {
-  const b2_fault *plan;
-  int n_faults;
-  float tau;
-  int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable, false alarms
-  const float *A, *B;
-  int lda, ldb;
-};
 
 template <int BM, int NR>
 struct TileCfg {
@@ -773,7 +765,8 @@ using namespace b2;
 
 namespace b2 {
 int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
-                          float beta, float *C, int ldc, cudaStream_t s);
+                          float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
+constexpr float kTf32TauPerK = 1e-5f;     // default ABFT threshold of the 3xTF32 path per unit of K
 }
 
 extern "C" {
@@ -792,20 +785,26 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
     B2_REQUIRE(lda >= K, B2_ERR_INVALID_ARG, "b2_ft_sgemm: lda = %d < K = %d", lda, K);
     B2_REQUIRE(ldb >= N, B2_ERR_INVALID_ARG, "b2_ft_sgemm: ldb = %d < N = %d", ldb, N);
   }
-  B2_REQUIRE(path == B2_PATH_FFMA, B2_ERR_UNSUPPORTED, "b2_ft_sgemm: ABFT is built on the FFMA path only");
   Context *ctx = h ? (Context *)h : default_context();
   B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ft_sgemm: no context (%s)", b2_last_error());
   FtArgs ft;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
-  // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the
-  // rounding noise between the two ways a block's sum is formed
-  ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
   ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
   ft.A = A;
   ft.B = B;
   ft.lda = lda;
   ft.ldb = ldb;
+  if (path == B2_PATH_3XTF32) {
+    // the tensor cores' accumulation error grows in proportion to K and is well above the FFMA
+    // path's rounding noise, so the threshold is wider: about 4.5x the largest residual of a clean
+    // 8192^3 product of unit-scale operands, more at smaller K
+    ft.tau = tau > 0.f ? tau : fmaxf(kTf32TauPerK * (float)K, 2e-4f);
+    return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
+  }
+  // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the
+  // rounding noise between the two ways a block's sum is formed
+  ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
   return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
 }
 
@@ -900,7 +899,7 @@ int b2_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const floa
   Context *ctx = h ? (Context *)h : default_context();
   B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_sgemm: no context (%s)", b2_last_error());
   if (path == B2_PATH_3XTF32)
-    return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, (cudaStream_t)stream);
+    return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, nullptr, (cudaStream_t)stream);
   return sgemm_ffma_dispatch(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, (cudaStream_t)stream);
 }
 

@@ -88,7 +88,9 @@ int ref_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, flo
 
 /* One simulated soft error: after K-slab `k_step` (slab = 32 of K), bit `bit` of the FP32
  * accumulator of output element (tile_m*128 + row, tile_n*128 + col) is flipped in registers.
- * A plan holds at most one fault per 128x128 tile.  A simulated fault never faults the GPU. */
+ * A plan holds at most one fault per 128x128 tile.  A simulated fault never faults the GPU.
+ * On the 3xTF32 path the accumulators live in tensor memory for the whole K loop, so the bit is
+ * flipped as the accumulator is read back after the last slab and `k_step` is ignored. */
 typedef struct {
   int32_t tile_m, tile_n;
   int32_t row, col;     /* 0..127 inside the tile */
@@ -103,7 +105,8 @@ typedef struct {
   int32_t corrected;      /* accumulators found wrong by recomputation and replaced */
   int32_t uncorrectable;  /* always 0 with recompute-based correction; kept for callers that test it */
   int32_t false_alarms;   /* blocks out of tolerance whose outputs all verified */
-  int32_t reserved[2];
+  int32_t max_residual_bits; /* 3xTF32 path: bit pattern of the largest in-tolerance |sum - checksum| (a float >= 0) */
+  int32_t reserved;
 } b2_ft_report;
 
 /* North-star launcher `ft_sgemm`: as sgemm() with checksum encode in the mainloop and
@@ -115,7 +118,12 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
 /* Full form.  `plan_dev`/`n_faults`: optional device array of faults to inject (NULL/0 =
  * clean run).  `tau` <= 0 selects the default threshold 2e-6*K (inputs of unit scale);
  * the reference uses a fixed 0.1 (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:30).
- * `report_dev`: optional device b2_ft_report that this call ADDS to (caller zeroes it). */
+ * `report_dev`: optional device b2_ft_report that this call ADDS to (caller zeroes it).
+ * path = B2_PATH_3XTF32: the checksums ride on the tensor cores (one per output row and group
+ * of 32 columns), a group out of tolerance is recomputed in FP32 from A and B and every output
+ * further than tau/2 from its recomputed value is replaced.  Default tau there is 1e-5*K: the
+ * tensor cores' truncating accumulation leaves a residual of about 2e-6*K on clean data.
+ * Needs the workspace of b2_sgemm_workspace_bytes(B2_PATH_3XTF32, ...). */
 int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda,
                 const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
                 int n_faults, float tau, b2_ft_report *report_dev, void *stream);

@@ -62,6 +62,7 @@ def test_clean_run_no_false_positive_and_bit_identical(cuda, shape):
     b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, report=rep)
     b2.check_status()
     r = b2.read_report(rep)
+    r.pop("max_residual")
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     assert r == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0, "false_alarms": 0}
     assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
@@ -181,8 +182,9 @@ def test_config3_large_sizes(cuda, n):
     out = torch.zeros((n, n), device="cuda")
     b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, report=rep)
     b2.check_status()
-    assert b2.read_report(rep) == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0,
-                                   "false_alarms": 0}
+    r = b2.read_report(rep)
+    r.pop("max_residual")
+    assert r == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0, "false_alarms": 0}
     assert torch.equal(out, plain)
     plan = oracle.make_fault_plan(n, n, n, seed=6)
     assert len(plan) == tiles // 64

@@ -1,0 +1,265 @@
+"""GPU tests of the ABFT SGEMM on the 3xTF32 tensor-core path: a clean run is bit-identical to the plain
+3xTF32 kernel with no detection and no false alarm; a flipped accumulator bit whose effect is above the
+threshold is found and the output rebuilt so that the result meets the 3xTF32 tolerance; a flip below the
+threshold is left alone.  The accumulators live in tensor memory, so what a fault does to one of them is
+known from the plain kernel's own output (alpha = 1, beta = 0)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-5          # max|C - C_ref| / (|A| |B|) that the 3xTF32 path has to meet
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def mats(M, N, K):
+    a = oracle.fill_uniform(M * K, 1).reshape(M, K)
+    b = oracle.fill_uniform(K * N, 2).reshape(K, N)
+    c = oracle.fill_uniform(M * N, 3).reshape(M, N)
+    return a, b, c
+
+
+def default_tau(K):
+    return max(1e-5 * K, 2e-4)
+
+
+def flip(x, bit):
+    """float32 array/scalar with one bit flipped."""
+    return (np.asarray(x, dtype=np.float32).view(np.uint32) ^ np.uint32(1 << bit)).view(np.float32)
+
+
+def classify(acc, plan, tau):
+    """(must, gray, benign) index lists of a plan, from the size of each flip on the accumulator `acc`."""
+    must, gray, benign = [], [], []
+    for i, f in enumerate(plan):
+        r, c = f[0] * 128 + f[2], f[1] * 128 + f[3]
+        with np.errstate(all="ignore"):
+            d = abs(np.float64(flip(acc[r, c], int(f[5]))) - np.float64(acc[r, c]))
+        (must if (not np.isfinite(d) or d > 2 * tau) else benign if d < 0.5 * tau else gray).append(i)
+    return must, gray, benign
+
+
+def counts(r):
+    return {k: r[k] for k in ("tiles", "injected", "detected", "corrected", "uncorrectable", "false_alarms")}
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 32), (256, 384, 96), (1024, 1024, 1024), (130, 260, 72), (64, 512, 1000),
+                                   (300, 100, 40), (129, 257, 33)])
+def test_clean_run_bit_identical_to_plain_3xtf32(cuda, shape):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    da, db = dev(a), dev(b)
+    plain, out = dev(c), dev(c)
+    b2.set_tf32_tile_n(256)
+    try:
+        b2.sgemm(M, N, K, 1.25, da, db, 0.5, plain, path=b2.PATH_3XTF32)
+    finally:
+        b2.set_tf32_tile_n(0)
+    rep = b2.new_report()
+    b2.ft_sgemm(M, N, K, 1.25, da, db, 0.5, out, path=b2.PATH_3XTF32, report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    assert counts(r) == {"tiles": tiles, "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0, "false_alarms": 0}
+    assert 0.0 <= r["max_residual"] <= 0.25 * default_tau(K)
+    assert torch.equal(out, plain)
+    c64, den = oracle.sgemm_f64(1.25, a, b, 0.5, c)
+    assert oracle.gemm_error(out.cpu().numpy(), c64, den) <= TOL
+
+
+@pytest.mark.parametrize("bit", [12, 18, 21, 23, 25, 27, 29, 30, 31])
+def test_single_fault_each_bit(cuda, bit):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 256, 512, 512
+    a, b, _ = mats(M, N, K)
+    da, db = dev(a), dev(b)
+    acc = torch.zeros((M, N), device="cuda")
+    b2.sgemm(M, N, K, 1.0, da, db, 0.0, acc, path=b2.PATH_3XTF32)
+    acc = acc.cpu().numpy()
+    plan = np.array([[1, 2, 77, 101, 0, bit]], dtype=np.int32)      # element (205, 357)
+    tau = default_tau(K)
+    must, gray, benign = classify(acc, plan, tau)
+    rep = b2.new_report()
+    out = torch.zeros((M, N), device="cuda")
+    b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    got = out.cpu().numpy()
+    assert r["tiles"] == 4 and r["injected"] == 1 and r["false_alarms"] == 0
+    mask = np.ones_like(acc, dtype=bool)
+    mask[205, 357] = False
+    assert np.array_equal(got[mask], acc[mask])                      # nothing else moved
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.0, np.zeros_like(acc))
+    if must:
+        assert r["detected"] == 1 and r["corrected"] == 1
+        assert abs(float(got[205, 357]) - float(acc[205, 357])) <= 0.5 * tau
+        assert oracle.gemm_error(got, c64, den) <= TOL
+    if benign:
+        assert r["detected"] == 0 and r["corrected"] == 0
+        assert got[205, 357].view(np.uint32) == flip(acc[205, 357], bit).view(np.uint32)
+
+
+@pytest.mark.parametrize("seed", [6, 7, 8])
+def test_config3_1024_plan(cuda, seed):
+    """BASELINE config 3 at 1024^3 on the tensor-core path: one flip (bit 20..30) per 64 tiles of 128 x 128, and a
+    denser plan of one per 2 tiles."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 1024
+    a, b, _ = mats(n, n, n)
+    da, db = dev(a), dev(b)
+    acc_d = torch.zeros((n, n), device="cuda")
+    b2.sgemm(n, n, n, 1.0, da, db, 0.0, acc_d, path=b2.PATH_3XTF32)
+    acc = acc_d.cpu().numpy()
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.0, np.zeros_like(acc))
+    tau = default_tau(n)
+    for per in (64, 2):
+        plan = oracle.make_fault_plan(n, n, n, seed=seed, tiles_per_fault=per)
+        must, gray, benign = classify(acc, plan, tau)
+        rep = b2.new_report()
+        out = torch.zeros((n, n), device="cuda")
+        b2.ft_sgemm(n, n, n, 1.0, da, db, 0.0, out, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert r["tiles"] == 32 and r["injected"] == len(plan) and r["false_alarms"] == 0
+        assert len(must) <= r["corrected"] <= len(must) + len(gray)
+        got = out.cpu().numpy()
+        changed = np.argwhere(got.view(np.uint32) != acc.view(np.uint32))
+        struck = {(int(f[0]) * 128 + int(f[2]), int(f[1]) * 128 + int(f[3])) for f in plan}
+        assert {tuple(int(v) for v in rc) for rc in changed} <= struck
+        for i in must:
+            f = plan[i]
+            rr, cc = f[0] * 128 + f[2], f[1] * 128 + f[3]
+            assert abs(float(got[rr, cc]) - float(acc[rr, cc])) <= 0.5 * tau
+        if not gray:
+            # benign flips stay in the output: each is below tau / 2 by construction
+            assert np.abs(got.astype(np.float64) - acc.astype(np.float64)).max() <= 0.5 * tau
+        if not gray and not benign:
+            assert oracle.gemm_error(got, c64, den) <= TOL
+
+
+def test_nan_and_inf_faults_are_rebuilt(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 128, 256, 256
+    a, b, _ = mats(M, N, K)
+    da, db = dev(a), dev(b)
+    acc_d = torch.zeros((M, N), device="cuda")
+    b2.sgemm(M, N, K, 1.0, da, db, 0.0, acc_d, path=b2.PATH_3XTF32)
+    acc = acc_d.cpu().numpy()
+    cand = np.argwhere((np.abs(acc) >= 1.0) & (np.abs(acc) < 2.0))
+    r0, c0 = (int(v) for v in cand[0])
+    with np.errstate(all="ignore"):
+        assert not np.isfinite(flip(acc[r0, c0], 30))
+    plan = np.array([[0, c0 // 128, r0, c0 % 128, 0, 30]], dtype=np.int32)
+    rep = b2.new_report()
+    out = torch.zeros((M, N), device="cuda")
+    b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), report=rep)
+    r = b2.read_report(rep)
+    assert r["injected"] == 1 and r["detected"] == 1 and r["corrected"] == 1
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.0, np.zeros_like(acc))
+    assert oracle.gemm_error(got, c64, den) <= TOL
+
+
+def test_faults_in_both_halves_of_a_tile_and_in_one_group(cuda):
+    """Two planned tiles of 128 columns share one 256-column kernel tile; two struck rows share one group of 32
+    columns.  All four flips are applied and repaired."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 128, 256, 384
+    a, b, _ = mats(M, N, K)
+    da, db = dev(a), dev(b)
+    acc = torch.zeros((M, N), device="cuda")
+    b2.sgemm(M, N, K, 1.0, da, db, 0.0, acc, path=b2.PATH_3XTF32)
+    plan = np.array([[0, 0, 5, 40, 0, 29], [0, 1, 5, 9, 0, 28], [0, 0, 17, 33, 0, 29], [0, 1, 90, 127, 0, 27]], dtype=np.int32)
+    rep = b2.new_report()
+    out = torch.zeros((M, N), device="cuda")
+    b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert counts(r) == {"tiles": 1, "injected": 4, "detected": 4, "corrected": 4, "uncorrectable": 0, "false_alarms": 0}
+    assert float((out - acc).abs().max().item()) <= 0.5 * default_tau(K)
+
+
+def test_threshold_override_leaves_small_faults_alone(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 128, 256, 128
+    a, b, _ = mats(M, N, K)
+    da, db = dev(a), dev(b)
+    acc_d = torch.zeros((M, N), device="cuda")
+    b2.sgemm(M, N, K, 1.0, da, db, 0.0, acc_d, path=b2.PATH_3XTF32)
+    acc = acc_d.cpu().numpy()
+    r0, c0 = (int(v) for v in np.unravel_index(np.argmax(np.abs(acc)), acc.shape))
+    bad = flip(acc[r0, c0], 22)                                     # top mantissa bit: a quarter of the value or more
+    assert abs(float(bad) - float(acc[r0, c0])) > 2 * default_tau(K)
+    plan = np.array([[0, c0 // 128, r0, c0 % 128, 0, 22]], dtype=np.int32)
+    for tau, found in ((1e9, 0), (0.0, 1)):
+        rep = b2.new_report()
+        out = torch.zeros((M, N), device="cuda")
+        b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), tau=tau, report=rep)
+        r = b2.read_report(rep)
+        assert r["injected"] == 1 and r["detected"] == found and r["corrected"] == found and r["false_alarms"] == 0
+        got = out.cpu().numpy()
+        if found:
+            assert abs(float(got[r0, c0]) - float(acc[r0, c0])) <= 0.5 * default_tau(K)
+        else:
+            assert got[r0, c0].view(np.uint32) == bad.view(np.uint32)
+
+
+def test_degenerate_products_take_the_scaling_route(cuda):
+    """K = 0 or alpha = 0: C <- beta*C without touching the tensor cores, still through b2_ft_sgemm."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N = 96, 160
+    _, _, c = mats(M, N, 8)
+    a, b, _ = mats(M, N, 64)
+    out = dev(c)
+    b2.ft_sgemm(M, N, 0, 1.0, dev(a), dev(b), 0.5, out, path=b2.PATH_3XTF32, lda=64, ldb=N)
+    assert np.array_equal(out.cpu().numpy(), (np.float32(0.5) * c).astype(np.float32))
+    out = dev(c)
+    b2.ft_sgemm(M, N, 64, 0.0, dev(a), dev(b), -2.0, out, path=b2.PATH_3XTF32)
+    assert np.array_equal(out.cpu().numpy(), (np.float32(-2.0) * c).astype(np.float32))
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_config3_large_sizes(cuda, n):
+    """BASELINE config 3 at 4096^3 and 8192^3: a clean run and the seeded plan (one flip per 64 tiles), checked
+    against the plain 3xTF32 kernel on the device."""
+    import hpcdeepneuralnetworks_b200 as b2
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    plain = torch.zeros((n, n), device="cuda")
+    b2.set_tf32_tile_n(256)
+    try:
+        b2.sgemm(n, n, n, 1.0, A, B, 0.0, plain, path=b2.PATH_3XTF32)
+    finally:
+        b2.set_tf32_tile_n(0)
+    tau = default_tau(n)
+    rep = b2.new_report()
+    out = torch.zeros((n, n), device="cuda")
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, path=b2.PATH_3XTF32, report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert counts(r) == {"tiles": (n // 128) * (n // 256), "injected": 0, "detected": 0, "corrected": 0, "uncorrectable": 0,
+                         "false_alarms": 0}
+    assert r["max_residual"] <= 0.4 * tau                         # margin of the default threshold on clean data
+    assert torch.equal(out, plain)
+    plan = oracle.make_fault_plan(n, n, n, seed=6)
+    acc = plain.cpu().numpy()
+    must, gray, benign = classify(acc, plan, tau)
+    rep = b2.new_report()
+    out.zero_()
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert r["injected"] == len(plan) and r["false_alarms"] == 0
+    assert len(must) <= r["corrected"] <= len(must) + len(gray)
+    diff = (out - plain).abs()
+    assert int((diff > 0).sum().item()) <= len(plan)
+    # repaired outputs carry the FP32 recomputation (within tau/2 of the tensor-core value); flips that stay are below 2 tau
+    assert float(diff.max().item()) <= (2 * tau if gray else 0.5 * tau)
