@@ -374,6 +374,11 @@ def set_tf32_tile_n(n: int):
     check(_lib.load().b2_set_tf32_tile_n(n))
 
 
+def set_tf32_pair(on: int):
+    """1: 3xTF32 on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2); 0: one CTA per tile."""
+    check(_lib.load().b2_set_tf32_pair(on))
+
+
 def set_tf32_slab_k(k: int):
     """K-slab depth of the 3xTF32 kernel (16 or 32)."""
     check(_lib.load().b2_set_tf32_slab_k(k))

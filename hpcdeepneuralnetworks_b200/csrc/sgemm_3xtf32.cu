@@ -439,8 +439,181 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
 }
 
+// ---- CTA-pair form: one 256 x 256 output tile per cluster of two CTAs (tcgen05 cta_group::2) ----
+// CTA r of the pair stages rows m0 + 128r.. of the A planes and columns n0 + 128r.. of the B planes
+// (64 KB per K-slab instead of 96 KB, so three stages fit and each SM pulls a third fewer bytes out
+// of L2 per flop); the leader (r = 0) issues MMAs of M = 256 that read both CTAs' tiles and write
+// 128 accumulator rows into each CTA's TMEM.  Every TMA load is a plain per-CTA load that signals
+// the leader's "full" barrier; the leader's commits free the stage in both CTAs.
+struct PairCfg {
+  static constexpr int kTA = TBM * 32 * 4;           // bytes per A plane tile (128 rows)
+  static constexpr int kTB = 128 * 32 * 4;           // bytes per B plane half tile (128 columns)
+  static constexpr int kStage = 2 * kTA + 2 * kTB;   // 64 KB
+  static constexpr int kStages = 3;
+  static constexpr int kSmem = 1024 + kStages * kStage + 256;
+  static constexpr int kTmemCols = 256;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                         const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
+  constexpr int S = PairCfg::kStages, kTA = PairCfg::kTA, kTB = PairCfg::kTB, kStage = PairCfg::kStage;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + S * kStage);
+  uint64_t *empty = full + S;
+  uint64_t *acc_ready = empty + S;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int tiles_n = (p.N + 255) / 256;
+  const int pair = blockIdx.x >> 1;
+  const int m0 = (pair / tiles_n) * 256 + (int)rank * 128, n0 = (pair % tiles_n) * 256;
+  const int nkb = (p.K + 31) / 32;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmAh);
+    tma_prefetch_desc(&tmAl);
+    tma_prefetch_desc(&tmBh);
+    tma_prefetch_desc(&tmBl);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, PairCfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();      // barriers of both CTAs are initialised before anything remote signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (one per CTA) ------------------------------------------------------
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S;
+        if (!mbar_wait(&empty[s], ((uint32_t)(kb / S) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        unsigned char *st = smem + s * kStage;
+        const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
+        if (rank == 0) mbar_expect_tx(&full[s], 2 * kStage);   // the bytes of both CTAs
+        tma_load_2d_pair(st, &tmAh, leader_full, kb * 32, m0);
+        tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
+        tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
+        tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the leader CTA only -------------------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % S;
+        if (!mbar_wait(&full[s], (uint32_t)(kb / S) & 1u)) {
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + s * kStage);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
+          const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
+          const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
+          const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
+          umma_tf32_pair(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          umma_tf32_pair(tmem_base, a_hi, b_lo, idesc, 1u);
+          umma_tf32_pair(tmem_base, a_hi, b_hi, idesc, 1u);
+        }
+        umma_commit_pair(&empty[s], (uint16_t)3);   // frees the stage in both CTAs
+      }
+      if (ok) umma_commit_pair(acc_ready, (uint16_t)3);
+    }
+  } else {
+    // ---- epilogue: warps 2..5 of each CTA, its own 128 accumulator rows ---------------------
+    const int q = warp & 3;
+    bool ok = true;
+    if (nkb > 0) {
+      bool done = false;
+      const uint64_t t0 = global_timer_ns();
+      for (int it = 0; it < (1 << 14) && !done; ++it) {
+        done = mbar_wait(acc_ready, 0, 1u << 10);
+        if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+      }
+      ok = done;
+    }
+    if (!ok) *abort_flag = 1;
+    tc_fence_after();
+    const int row = m0 + q * 32 + lane;
+    const bool read_c = (p.beta != 0.f);
+    float *crow = p.C + (size_t)row * p.ldc;
+#pragma unroll 1
+    for (int c = 0; c < 8; ++c) {
+      uint32_t v[32];
+      if (ok && nkb > 0) {
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      if (!ok || row >= p.M) continue;
+      const int col0 = n0 + c * 32;
+      if (p.vec_c && col0 + 31 < p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 o;
+          if (read_c) {
+            const float4 cc = *reinterpret_cast<const float4 *>(crow + col0 + j);
+            o.x = __fmaf_rn(p.alpha, __uint_as_float(v[j + 0]), __fmul_rn(p.beta, cc.x));
+            o.y = __fmaf_rn(p.alpha, __uint_as_float(v[j + 1]), __fmul_rn(p.beta, cc.y));
+            o.z = __fmaf_rn(p.alpha, __uint_as_float(v[j + 2]), __fmul_rn(p.beta, cc.z));
+            o.w = __fmaf_rn(p.alpha, __uint_as_float(v[j + 3]), __fmul_rn(p.beta, cc.w));
+          } else {
+            o.x = __fmul_rn(p.alpha, __uint_as_float(v[j + 0]));
+            o.y = __fmul_rn(p.alpha, __uint_as_float(v[j + 1]));
+            o.z = __fmul_rn(p.alpha, __uint_as_float(v[j + 2]));
+            o.w = __fmul_rn(p.alpha, __uint_as_float(v[j + 3]));
+          }
+          *reinterpret_cast<float4 *>(crow + col0 + j) = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < p.N) {
+            const float a = __uint_as_float(v[j]);
+            crow[col0 + j] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col0 + j])) : __fmul_rn(p.alpha, a);
+          }
+        }
+      }
+    }
+  }
+
+  // neither CTA leaves (or frees tensor memory) while the other may still be read by an MMA
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, PairCfg::kTmemCols);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+}
+
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
 static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
+static int g_tf32_pair = 0;    // 1: 256 x 256 tiles on CTA pairs (cta_group::2)
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
 // (24 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
@@ -504,6 +677,26 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, tbk, TBM, swz);
   if (st != B2_OK) return st;
+  if (g_tf32_pair && !ft && tbk == 32) {
+    st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
+    if (st != B2_OK) return st;
+    st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
+    if (st != B2_OK) return st;
+    Tf32Args pa;
+    memset(&pa, 0, sizeof(pa));
+    pa.C = C; pa.M = M; pa.N = N; pa.K = K; pa.ldc = ldc; pa.alpha = alpha; pa.beta = beta;
+    pa.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
+    pa.status = (int *)((char *)ctx->fixed + kFixedStatus);
+    static bool pair_configured = false;
+    if (!pair_configured) {
+      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmem));
+      pair_configured = true;
+    }
+    const int pairs = ((M + 255) / 256) * ((N + 255) / 256);
+    sgemm_3xtf32_pair_kernel<<<2 * pairs, 192, PairCfg::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], pa);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+  }
   // tile width: whole waves of one CTA per SM; a 128-wide tile costs ~0.55 of a 256-wide one
   const double sms = (double)ctx->sm_count;
   const double tm = (double)((M + TBM - 1) / TBM);
@@ -553,6 +746,12 @@ size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K) {
 int b2_set_tf32_tile_n(int n) {
   B2_REQUIRE(n == 0 || n == 128 || n == 256, B2_ERR_INVALID_ARG, "b2_set_tf32_tile_n: %d is not 0, 128 or 256", n);
   b2::g_tf32_tile_n = n;
+  return B2_OK;
+}
+// 1: the 3xTF32 SGEMM runs 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2); 0: one CTA per tile.
+int b2_set_tf32_pair(int on) {
+  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_tf32_pair: %d is not 0 or 1", on);
+  b2::g_tf32_pair = on;
   return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.
