@@ -375,7 +375,7 @@ def set_tf32_tile_n(n: int):
 
 
 def set_tf32_pair(on: int):
-    """1: 3xTF32 on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2); 0: one CTA per tile."""
+    """3xTF32 on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2): 0 never, 1 automatic (default), 2 always."""
     check(_lib.load().b2_set_tf32_pair(on))
 
 

@@ -44,7 +44,6 @@ constexpr int TBM = 128;
 // MMA costs about as much as fetching its A operand again, so two of them rather than three
 // matter; keeping both s_hi terms in one accumulator makes its truncation error follow that of
 // the data accumulators more closely (smaller clean residual) than three separate columns do.
-constexpr int kFtGroup = 32;                         // output columns per checksum
 constexpr int kFtRows = 32;                          // rows of S per 256-column tile
 template <int TBN, int TBK, bool FT = false>
 struct Tf32Cfg {
@@ -171,13 +170,159 @@ __device__ __forceinline__ float ft_recompute32(const Tf32Args &p, int row, int 
   return acc0 + acc1;
 }
 
+// Planned faults that land in this thread's row of this tile: at most one per 128 columns.
+struct FtInj {
+  int col0 = -1, col1 = -1;
+  uint32_t mask0 = 0u, mask1 = 0u;
+};
+template <int TBN>
+__device__ __forceinline__ FtInj ft_scan_plan(const Tf32Args &p, int my_row, int n0) {
+  FtInj inj;
+  for (int f = 0; f < p.ft.n_faults; ++f) {
+    const b2_fault ff = p.ft.plan[f];
+    const int gr = ff.tile_m * 128 + ff.row, gc = ff.tile_n * 128 + ff.col;
+    if (gr == my_row && gr < p.M && gc >= n0 && gc < n0 + TBN && gc < p.N) {
+      if (gc - n0 < 128) {
+        if (inj.col0 < 0) { inj.col0 = gc - n0; inj.mask0 = 1u << (ff.bit & 31); }
+      } else if (inj.col1 < 0) {
+        inj.col1 = gc - n0; inj.mask1 = 1u << (ff.bit & 31);
+      }
+    }
+  }
+  return inj;
+}
+
+// Epilogue of one warp (TMEM lane quarter q): 32 rows x TBN columns of the accumulator tile ->
+// alpha/beta -> global.  FT: each 32-column chunk is summed and compared with its two checksum
+// columns first; a row-group out of tolerance is recomputed and repaired (see the file header).
+// `ok` (warp-uniform) says the accumulator is complete; called by whole warps.
+template <int TBN, bool FT>
+__device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_base, int q, int lane, int m0, int n0, bool ok,
+                                              int nkb, const FtInj &inj) {
+  const int inj_col0 = inj.col0, inj_col1 = inj.col1;
+  const uint32_t inj_mask0 = inj.mask0, inj_mask1 = inj.mask1;
+  float worst = 0.f;          // largest in-tolerance |group sum - checksum| this thread saw
+  int n_inj = 0, n_det = 0, n_cor = 0, n_false = 0;
+  const int row = m0 + q * 32 + lane;
+  const bool read_c = (p.beta != 0.f);
+  float *crow = p.C + (size_t)row * p.ldc;
+#pragma unroll 1
+  for (int c = 0; c < TBN / 32; ++c) {
+    uint32_t v[32];
+    float expect = 0.f;
+    if (ok && nkb > 0) {
+      tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+      if (FT) {
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(TBN + c);
+        const uint32_t e0 = tmem_ld_32x1(t0), e1 = tmem_ld_32x1(t0 + 8);
+        tmem_ld_wait();
+        expect = __uint_as_float(e0) + __uint_as_float(e1);
+      }
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0u;
+    }
+    if (FT && ok && nkb > 0) {
+      // simulated soft errors: flip one bit of an accumulator as it leaves TMEM
+      if (inj_col0 >= 0 && (inj_col0 >> 5) == c) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j == (inj_col0 & 31)) v[j] ^= inj_mask0;
+        ++n_inj;
+      }
+      if (TBN > 128 && inj_col1 >= 0 && (inj_col1 >> 5) == c) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j == (inj_col1 & 31)) v[j] ^= inj_mask1;
+        ++n_inj;
+      }
+      {
+        float g = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) g += __uint_as_float(v[j]);
+        const float resid = fabsf(g - expect);
+        const bool bad = !(resid <= p.ft.tau);
+        if (!bad) worst = fmaxf(worst, resid);
+        unsigned m = __ballot_sync(0xffffffffu, bad);
+        while (m) {
+          const int L = __ffs(m) - 1;
+          m &= m - 1;
+          const int rowL = __shfl_sync(0xffffffffu, m0 + q * 32 + lane, L);
+          const float ref = ft_recompute32(p, rowL, n0 + c * 32, lane);
+          int replaced = 0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float r = __shfl_sync(0xffffffffu, ref, j);
+            if (lane == L && !(fabsf(__uint_as_float(v[j]) - r) <= p.tau_elem)) {
+              v[j] = __float_as_uint(r);
+              ++replaced;
+            }
+          }
+          if (lane == L) {
+            if (replaced) { ++n_det; n_cor += replaced; } else { ++n_false; }
+          }
+        }
+      }
+    }
+    if (!ok || row >= p.M) continue;
+    const int col0 = n0 + c * 32;
+    if (p.vec_c && col0 + 31 < p.N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o;
+        if (read_c) {
+          const float4 cc = *reinterpret_cast<const float4 *>(crow + col0 + j);
+          o.x = __fmaf_rn(p.alpha, __uint_as_float(v[j + 0]), __fmul_rn(p.beta, cc.x));
+          o.y = __fmaf_rn(p.alpha, __uint_as_float(v[j + 1]), __fmul_rn(p.beta, cc.y));
+          o.z = __fmaf_rn(p.alpha, __uint_as_float(v[j + 2]), __fmul_rn(p.beta, cc.z));
+          o.w = __fmaf_rn(p.alpha, __uint_as_float(v[j + 3]), __fmul_rn(p.beta, cc.w));
+        } else {
+          o.x = __fmul_rn(p.alpha, __uint_as_float(v[j + 0]));
+          o.y = __fmul_rn(p.alpha, __uint_as_float(v[j + 1]));
+          o.z = __fmul_rn(p.alpha, __uint_as_float(v[j + 2]));
+          o.w = __fmul_rn(p.alpha, __uint_as_float(v[j + 3]));
+        }
+        *reinterpret_cast<float4 *>(crow + col0 + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (col0 + j < p.N) {
+          const float a = __uint_as_float(v[j]);
+          crow[col0 + j] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col0 + j])) : __fmul_rn(p.alpha, a);
+        }
+      }
+    }
+  }
+  if (FT) {
+    // one set of atomics per warp
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      n_inj += __shfl_xor_sync(0xffffffffu, n_inj, o);
+      n_det += __shfl_xor_sync(0xffffffffu, n_det, o);
+      n_cor += __shfl_xor_sync(0xffffffffu, n_cor, o);
+      n_false += __shfl_xor_sync(0xffffffffu, n_false, o);
+      worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+    }
+    if (lane == 0) {
+      if (q == 0 && m0 < p.M) atomicAdd(&p.ft.report[0], 1);   // a pair's second CTA may lie wholly below the matrix
+      if (n_inj) atomicAdd(&p.ft.report[1], n_inj);
+      if (n_det) atomicAdd(&p.ft.report[2], n_det);
+      if (n_cor) atomicAdd(&p.ft.report[3], n_cor);
+      if (n_false) atomicAdd(&p.ft.report[5], n_false);
+      atomicMax(&p.ft.report[6], __float_as_int(worst));
+    }
+  }
+}
+
 template <int TBN, int TBK, bool FT>
 __global__ void __launch_bounds__(192, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                     const __grid_constant__ CUtensorMap tmS, const Tf32Args p) {
   using Cfg = Tf32Cfg<TBN, TBK, FT>;
-  constexpr int TSTAGES = Cfg::kStages, kTA = Cfg::kTA, kTB = Cfg::kTB, kTS = Cfg::kTS, kTStage = Cfg::kStage;
+  constexpr int TSTAGES = Cfg::kStages, kTA = Cfg::kTA, kTB = Cfg::kTB, kTStage = Cfg::kStage;
   constexpr int kTmemCols = Cfg::kTmemCols;
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
@@ -285,25 +430,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 -------------------------------
     const int q = warp & 3;
     bool ok = true;
-    // planned faults that land in this thread's row of this tile: at most one per 128 columns
-    int inj_col0 = -1, inj_col1 = -1;
-    uint32_t inj_mask0 = 0u, inj_mask1 = 0u;
-    if (FT) {
-      const int my_row = m0 + q * 32 + lane;
-      for (int f = 0; f < p.ft.n_faults; ++f) {
-        const b2_fault ff = p.ft.plan[f];
-        const int gr = ff.tile_m * 128 + ff.row, gc = ff.tile_n * 128 + ff.col;
-        if (gr == my_row && gr < p.M && gc >= n0 && gc < n0 + TBN && gc < p.N) {
-          if (gc - n0 < 128) {
-            if (inj_col0 < 0) { inj_col0 = gc - n0; inj_mask0 = 1u << (ff.bit & 31); }
-          } else if (inj_col1 < 0) {
-            inj_col1 = gc - n0; inj_mask1 = 1u << (ff.bit & 31);
-          }
-        }
-      }
-    }
-    float worst = 0.f;          // largest in-tolerance |group sum - checksum| this thread saw
-    int n_inj = 0, n_det = 0, n_cor = 0, n_false = 0;
+    FtInj inj;
+    if (FT) inj = ft_scan_plan<TBN>(p, m0 + q * 32 + lane, n0);
     if (nkb > 0) {
       // poll in slices so that an abort raised by the other roles is seen
       bool done = false;
@@ -317,117 +445,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     ok = __all_sync(0xffffffffu, ok);   // the checksum pass below uses warp collectives
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    const int row = m0 + q * 32 + lane;
-    const bool read_c = (p.beta != 0.f);
-    float *crow = p.C + (size_t)row * p.ldc;
-#pragma unroll 1
-    for (int c = 0; c < TBN / 32; ++c) {
-      uint32_t v[32];
-      float expect = 0.f;
-      if (ok && nkb > 0) {
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-        if (FT) {
-          const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(TBN + c);
-          const uint32_t e0 = tmem_ld_32x1(t0), e1 = tmem_ld_32x1(t0 + 8);
-          tmem_ld_wait();
-          expect = __uint_as_float(e0) + __uint_as_float(e1);
-        }
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0u;
-      }
-      if (FT && ok && nkb > 0) {
-        // simulated soft errors: flip one bit of an accumulator as it leaves TMEM
-        if (inj_col0 >= 0 && (inj_col0 >> 5) == c) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j == (inj_col0 & 31)) v[j] ^= inj_mask0;
-          ++n_inj;
-        }
-        if (TBN > 128 && inj_col1 >= 0 && (inj_col1 >> 5) == c) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j == (inj_col1 & 31)) v[j] ^= inj_mask1;
-          ++n_inj;
-        }
-        {
-          float g = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) g += __uint_as_float(v[j]);
-          const float resid = fabsf(g - expect);
-          const bool bad = !(resid <= p.ft.tau);
-          if (!bad) worst = fmaxf(worst, resid);
-          unsigned m = __ballot_sync(0xffffffffu, bad);
-          while (m) {
-            const int L = __ffs(m) - 1;
-            m &= m - 1;
-            const int rowL = __shfl_sync(0xffffffffu, m0 + q * 32 + lane, L);
-            const float ref = ft_recompute32(p, rowL, n0 + c * 32, lane);
-            int replaced = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float r = __shfl_sync(0xffffffffu, ref, j);
-              if (lane == L && !(fabsf(__uint_as_float(v[j]) - r) <= p.tau_elem)) {
-                v[j] = __float_as_uint(r);
-                ++replaced;
-              }
-            }
-            if (lane == L) {
-              if (replaced) { ++n_det; n_cor += replaced; } else { ++n_false; }
-            }
-          }
-        }
-      }
-      if (!ok || row >= p.M) continue;
-      const int col0 = n0 + c * 32;
-      if (p.vec_c && col0 + 31 < p.N) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float4 o;
-          if (read_c) {
-            const float4 cc = *reinterpret_cast<const float4 *>(crow + col0 + j);
-            o.x = __fmaf_rn(p.alpha, __uint_as_float(v[j + 0]), __fmul_rn(p.beta, cc.x));
-            o.y = __fmaf_rn(p.alpha, __uint_as_float(v[j + 1]), __fmul_rn(p.beta, cc.y));
-            o.z = __fmaf_rn(p.alpha, __uint_as_float(v[j + 2]), __fmul_rn(p.beta, cc.z));
-            o.w = __fmaf_rn(p.alpha, __uint_as_float(v[j + 3]), __fmul_rn(p.beta, cc.w));
-          } else {
-            o.x = __fmul_rn(p.alpha, __uint_as_float(v[j + 0]));
-            o.y = __fmul_rn(p.alpha, __uint_as_float(v[j + 1]));
-            o.z = __fmul_rn(p.alpha, __uint_as_float(v[j + 2]));
-            o.w = __fmul_rn(p.alpha, __uint_as_float(v[j + 3]));
-          }
-          *reinterpret_cast<float4 *>(crow + col0 + j) = o;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (col0 + j < p.N) {
-            const float a = __uint_as_float(v[j]);
-            crow[col0 + j] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col0 + j])) : __fmul_rn(p.alpha, a);
-          }
-        }
-      }
-    }
-    if (FT) {
-      // one set of atomics per warp
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        n_inj += __shfl_xor_sync(0xffffffffu, n_inj, o);
-        n_det += __shfl_xor_sync(0xffffffffu, n_det, o);
-        n_cor += __shfl_xor_sync(0xffffffffu, n_cor, o);
-        n_false += __shfl_xor_sync(0xffffffffu, n_false, o);
-        worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
-      }
-      if (lane == 0) {
-        if (q == 0) atomicAdd(&p.ft.report[0], 1);
-        if (n_inj) atomicAdd(&p.ft.report[1], n_inj);
-        if (n_det) atomicAdd(&p.ft.report[2], n_det);
-        if (n_cor) atomicAdd(&p.ft.report[3], n_cor);
-        if (n_false) atomicAdd(&p.ft.report[5], n_false);
-        atomicMax(&p.ft.report[6], __float_as_int(worst));
-      }
-    }
+    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj);
   }
 
   tc_fence_before();
@@ -445,19 +463,29 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 // of L2 per flop); the leader (r = 0) issues MMAs of M = 256 that read both CTAs' tiles and write
 // 128 accumulator rows into each CTA's TMEM.  Every TMA load is a plain per-CTA load that signals
 // the leader's "full" barrier; the leader's commits free the stage in both CTAs.
+//
+// FT: the checksum operand of an MMA with N = 16 is split between the CTAs like any B operand, 8
+// rows each.  CTA 0 stages rows 0..7 (s_hi) and 16..23 (s_hi) of the tile's 32-row S block, CTA 1
+// rows 8..15 (s_lo) and 24..31 (zero), so the two extra MMAs see [s_hi | s_lo] and [s_hi | 0] as
+// in the single-CTA kernel and the 16 checksum columns mean the same.
+template <bool FT>
 struct PairCfg {
   static constexpr int kTA = TBM * 32 * 4;           // bytes per A plane tile (128 rows)
   static constexpr int kTB = 128 * 32 * 4;           // bytes per B plane half tile (128 columns)
-  static constexpr int kStage = 2 * kTA + 2 * kTB;   // 64 KB
+  static constexpr int kTS = FT ? 2 * 8 * 32 * 4 : 0;   // two 8-row checksum slots
+  static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;   // 64 KB (+2 KB)
   static constexpr int kStages = 3;
   static constexpr int kSmem = 1024 + kStages * kStage + 256;
-  static constexpr int kTmemCols = 256;
+  static constexpr int kTmemCols = FT ? 512 : 256;
 };
 
+template <bool FT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
-                         const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl, const Tf32Args p) {
-  constexpr int S = PairCfg::kStages, kTA = PairCfg::kTA, kTB = PairCfg::kTB, kStage = PairCfg::kStage;
+                         const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                         const __grid_constant__ CUtensorMap tmS, const Tf32Args p) {
+  using PC = PairCfg<FT>;
+  constexpr int S = PC::kStages, kTA = PC::kTA, kTB = PC::kTB, kStage = PC::kStage;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + S * kStage);
@@ -485,9 +513,10 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     tma_prefetch_desc(&tmAl);
     tma_prefetch_desc(&tmBh);
     tma_prefetch_desc(&tmBl);
+    if (FT) tma_prefetch_desc(&tmS);
   }
   if (warp == 1) {
-    tmem_alloc_pair(tmem_slot, PairCfg::kTmemCols);
+    tmem_alloc_pair(tmem_slot, PC::kTmemCols);
     tmem_relinquish_pair();
   }
   tc_fence_before();
@@ -511,12 +540,18 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
         tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
         tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
+        if (FT) {
+          const int srow = (pair % tiles_n) * kFtRows + 8 * (int)rank;
+          tma_load_2d_pair(st + 2 * kTA + 2 * kTB, &tmS, leader_full, kb * 32, srow);
+          tma_load_2d_pair(st + 2 * kTA + 2 * kTB + 1024, &tmS, leader_full, kb * 32, srow + 16);
+        }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer: the leader CTA only -------------------------------------------------
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
+      constexpr uint32_t idesc_s = umma_idesc_tf32(256, 16, 0, 0);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % S;
@@ -536,6 +571,12 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
           umma_tf32_pair(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32_pair(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32_pair(tmem_base, a_hi, b_hi, idesc, 1u);
+          if (FT) {
+            const uint64_t w1 = umma_smem_desc(st + 2 * kTA + 2 * kTB + k4 * 32, 16, 1024, 2);
+            const uint64_t w2 = umma_smem_desc(st + 2 * kTA + 2 * kTB + 1024 + k4 * 32, 16, 1024, 2);
+            umma_tf32_pair(tmem_base + 256, a_lo, w2, idesc_s, (kb > 0 || k4 > 0) ? 1u : 0u);
+            umma_tf32_pair(tmem_base + 256, a_hi, w1, idesc_s, 1u);
+          }
         }
         umma_commit_pair(&empty[s], (uint16_t)3);   // frees the stage in both CTAs
       }
@@ -545,6 +586,8 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     // ---- epilogue: warps 2..5 of each CTA, its own 128 accumulator rows ---------------------
     const int q = warp & 3;
     bool ok = true;
+    FtInj inj;
+    if (FT) inj = ft_scan_plan<256>(p, m0 + q * 32 + lane, n0);
     if (nkb > 0) {
       bool done = false;
       const uint64_t t0 = global_timer_ns();
@@ -554,51 +597,10 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       }
       ok = done;
     }
+    ok = __all_sync(0xffffffffu, ok);
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    const int row = m0 + q * 32 + lane;
-    const bool read_c = (p.beta != 0.f);
-    float *crow = p.C + (size_t)row * p.ldc;
-#pragma unroll 1
-    for (int c = 0; c < 8; ++c) {
-      uint32_t v[32];
-      if (ok && nkb > 0) {
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0u;
-      }
-      if (!ok || row >= p.M) continue;
-      const int col0 = n0 + c * 32;
-      if (p.vec_c && col0 + 31 < p.N) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float4 o;
-          if (read_c) {
-            const float4 cc = *reinterpret_cast<const float4 *>(crow + col0 + j);
-            o.x = __fmaf_rn(p.alpha, __uint_as_float(v[j + 0]), __fmul_rn(p.beta, cc.x));
-            o.y = __fmaf_rn(p.alpha, __uint_as_float(v[j + 1]), __fmul_rn(p.beta, cc.y));
-            o.z = __fmaf_rn(p.alpha, __uint_as_float(v[j + 2]), __fmul_rn(p.beta, cc.z));
-            o.w = __fmaf_rn(p.alpha, __uint_as_float(v[j + 3]), __fmul_rn(p.beta, cc.w));
-          } else {
-            o.x = __fmul_rn(p.alpha, __uint_as_float(v[j + 0]));
-            o.y = __fmul_rn(p.alpha, __uint_as_float(v[j + 1]));
-            o.z = __fmul_rn(p.alpha, __uint_as_float(v[j + 2]));
-            o.w = __fmul_rn(p.alpha, __uint_as_float(v[j + 3]));
-          }
-          *reinterpret_cast<float4 *>(crow + col0 + j) = o;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (col0 + j < p.N) {
-            const float a = __uint_as_float(v[j]);
-            crow[col0 + j] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col0 + j])) : __fmul_rn(p.alpha, a);
-          }
-        }
-      }
-    }
+    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj);
   }
 
   // neither CTA leaves (or frees tensor memory) while the other may still be read by an MMA
@@ -606,14 +608,14 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc_pair(tmem_base, PairCfg::kTmemCols);
+    tmem_dealloc_pair(tmem_base, PC::kTmemCols);
   }
   if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
 }
 
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
 static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
-static int g_tf32_pair = 0;    // 1: 256 x 256 tiles on CTA pairs (cta_group::2)
+static int g_tf32_pair = 1;    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
 // (24 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
@@ -639,6 +641,33 @@ static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, 
 
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
+
+// How many CTA pairs the device runs at once (one CTA per SM; a pair needs two SMs of one cluster
+// domain).  Asked of the occupancy API once per process; half the SM count if it will not say.
+static int max_resident_pairs(Context *ctx) {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  int n = 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * ctx->sm_count, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg<true>::kSmem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true>::kSmem) != cudaSuccess ||
+      cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = ctx->sm_count / 2;
+  }
+  cached = n > 0 ? n : 1;
+  return cached;
+}
 
 // ft == NULL: plain 3xTF32 SGEMM; otherwise the ABFT form (checksum operand, verification and
 // recompute-based repair in the epilogue).
@@ -677,30 +706,48 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, tbk, TBM, swz);
   if (st != B2_OK) return st;
-  if (g_tf32_pair && !ft && tbk == 32) {
+  // Tile shape by whole waves: a pair tile (256 x 256 on two SMs) costs about 0.9 of a 128 x 256 tile
+  // per SM, a 128 x 128 tile about 0.55; a pinned width selects the single-CTA kernel of that width.
+  const double sms = (double)ctx->sm_count;
+  const double tm = (double)((M + TBM - 1) / TBM);
+  const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
+  const int pairs = ((M + 255) / 256) * ((N + 255) / 256);
+  const double tpair = 0.9 * ceil((double)pairs / (double)max_resident_pairs(ctx));
+  const bool pinned = (g_tf32_tile_n == 128 || g_tf32_tile_n == 256);
+  // (the ABFT form has no 128-wide kernel: pairs against 128 x 256 tiles)
+  const bool use_pair = tbk == 32 && !pinned &&
+                        (g_tf32_pair == 2 || (g_tf32_pair == 1 && tpair <= t256 && (ft != nullptr || tpair <= t128)));
+  if (use_pair) {
     st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
     if (st != B2_OK) return st;
     st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
     if (st != B2_OK) return st;
+    if (ft) {
+      st = make_tmap_2d(&maps[4], S, (uint64_t)K, (uint64_t)srows, (uint64_t)kp, 32, 8, swz);
+      if (st != B2_OK) return st;
+    } else {
+      maps[4] = maps[2];
+    }
     Tf32Args pa;
     memset(&pa, 0, sizeof(pa));
     pa.C = C; pa.M = M; pa.N = N; pa.K = K; pa.ldc = ldc; pa.alpha = alpha; pa.beta = beta;
     pa.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
     pa.status = (int *)((char *)ctx->fixed + kFixedStatus);
+    if (ft) {
+      pa.ft = *ft;
+      pa.tau_elem = 0.5f * ft->tau;
+    }
     static bool pair_configured = false;
     if (!pair_configured) {
-      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmem));
+      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<false>::kSmem));
+      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true>::kSmem));
       pair_configured = true;
     }
-    const int pairs = ((M + 255) / 256) * ((N + 255) / 256);
-    sgemm_3xtf32_pair_kernel<<<2 * pairs, 192, PairCfg::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], pa);
+    if (ft) sgemm_3xtf32_pair_kernel<true><<<2 * pairs, 192, PairCfg<true>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
+    else sgemm_3xtf32_pair_kernel<false><<<2 * pairs, 192, PairCfg<false>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
   }
-  // tile width: whole waves of one CTA per SM; a 128-wide tile costs ~0.55 of a 256-wide one
-  const double sms = (double)ctx->sm_count;
-  const double tm = (double)((M + TBM - 1) / TBM);
-  const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
   int tbn = (t128 < t256) ? 128 : 256;
   if (g_tf32_tile_n == 128 || g_tf32_tile_n == 256) tbn = g_tf32_tile_n;
   if (ft) tbn = 256;   // the checksum operand is laid out for 256-column tiles
@@ -748,9 +795,9 @@ int b2_set_tf32_tile_n(int n) {
   b2::g_tf32_tile_n = n;
   return B2_OK;
 }
-// 1: the 3xTF32 SGEMM runs 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2); 0: one CTA per tile.
+// CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) in the 3xTF32 SGEMM: 0 never, 1 automatic (default), 2 always.
 int b2_set_tf32_pair(int on) {
-  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_tf32_pair: %d is not 0 or 1", on);
+  B2_REQUIRE(on >= 0 && on <= 2, B2_ERR_INVALID_ARG, "b2_set_tf32_pair: %d is not 0, 1 or 2", on);
   b2::g_tf32_pair = on;
   return B2_OK;
 }

@@ -217,8 +217,9 @@ int b2_set_ffma_tile(int i);
 int b2_set_tf32_tile_n(int n);
 /* K-slab depth of the 3xTF32 kernel: 16 (64-byte swizzle, 4-6 stages) or 32 (128-byte swizzle, 2-3 stages). */
 int b2_set_tf32_slab_k(int k);
-/* 1: the 3xTF32 SGEMM runs 256x256 tiles on pairs of CTAs (tcgen05 cta_group::2, a cluster of two); 0: one CTA
- * per 128x256 or 128x128 tile. */
+/* 256x256 tiles on pairs of CTAs (tcgen05 cta_group::2, a cluster of two) in the 3xTF32 SGEMM: 0 never, 1 chosen
+ * against 128x128 single-CTA tiles by whole waves (default), 2 always.  A width pinned with b2_set_tf32_tile_n
+ * selects the single-CTA kernel of that width. */
 int b2_set_tf32_pair(int on);
 /* Reads and clears the device status word that bounded waits set; synchronises the stream.
  * Returns 0 or the recorded negative status. */

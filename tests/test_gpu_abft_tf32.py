@@ -14,6 +14,15 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-5          # max|C - C_ref| / (|A| |B|) that the 3xTF32 path has to meet
 
 
+@pytest.fixture(autouse=True, params=[0, 2], ids=["single_cta", "cta_pair"])
+def _kernel_form(request, cuda):
+    """Every test runs on the single-CTA kernel (128 x 256 tiles) and on the CTA-pair kernel (256 x 256 tiles)."""
+    import hpcdeepneuralnetworks_b200 as b2
+    b2.set_tf32_pair(request.param)
+    yield
+    b2.set_tf32_pair(1)
+
+
 def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 

@@ -220,6 +220,47 @@ def test_3xtf32_both_tile_widths(cuda, tile_n, slab_k):
         b2.set_tf32_slab_k(32)
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 32), (128, 256, 64), (256, 512, 256), (1024, 1024, 1024), (130, 300, 70),
+                                   (17, 13, 5), (384, 128, 1000), (200, 520, 36), (257, 255, 33), (1, 1, 1)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.5), (-1.5, 0.0)])
+def test_3xtf32_cta_pair_kernel_matches_single_cta(cuda, shape, alpha, beta):
+    """The cta_group::2 kernel (256 x 256 tiles on two CTAs) accumulates every output in the same order as the
+    single-CTA kernel, so the two agree bit for bit; both meet the tolerance against the double reference."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    try:
+        b2.set_tf32_pair(2)
+        pair = run_gpu(1, a, b, c, alpha, beta)
+        b2.set_tf32_pair(0)
+        single = run_gpu(1, a, b, c, alpha, beta)
+    finally:
+        b2.set_tf32_pair(1)
+    assert np.array_equal(pair, single)
+    c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
+    assert oracle.gemm_error(pair, c64, den) <= TOL_3XTF32
+
+
+def test_3xtf32_cta_pair_large_and_strided(cuda):
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 2304
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    C0 = b2.fill_uniform(torch.empty((n, n + 12), device="cuda"), 3)
+    out = {}
+    try:
+        for mode in (2, 0):
+            b2.set_tf32_pair(mode)
+            Cm = C0.clone()
+            b2.sgemm(n - 3, n - 5, n - 8, 0.75, A, B, -0.25, Cm, path=1, lda=n, ldb=n, ldc=n + 12)
+            b2.check_status()
+            out[mode] = Cm
+    finally:
+        b2.set_tf32_pair(1)
+    assert torch.equal(out[2], out[0])
+    assert torch.equal(out[2][:, n - 5:], C0[:, n - 5:]) and torch.equal(out[2][n - 3:], C0[n - 3:])
+
+
 def test_3xtf32_leading_dimensions(cuda):
     import hpcdeepneuralnetworks_b200 as b2
     M, N, K, lda, ldb, ldc = 150, 200, 70, 96, 256, 212
