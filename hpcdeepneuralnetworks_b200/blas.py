@@ -379,6 +379,11 @@ def set_tf32_pair(on: int):
     check(_lib.load().b2_set_tf32_pair(on))
 
 
+def set_tf32_abft_mode(mode: int):
+    """Where the 3xTF32 ABFT checksums are formed: 2 CUDA cores (default), 1 tensor cores."""
+    check(_lib.load().b2_set_tf32_abft_mode(mode))
+
+
 def set_tf32_slab_k(k: int):
     """K-slab depth of the 3xTF32 kernel (16 or 32)."""
     check(_lib.load().b2_set_tf32_slab_k(k))

@@ -44,17 +44,26 @@ constexpr int TBM = 128;
 // MMA costs about as much as fetching its A operand again, so two of them rather than three
 // matter; keeping both s_hi terms in one accumulator makes its truncation error follow that of
 // the data accumulators more closely (smaller clean residual) than three separate columns do.
-constexpr int kFtRows = 32;                          // rows of S per 256-column tile
-template <int TBN, int TBK, bool FT = false>
+//
+// FT = 1 is that form (checksums on the tensor cores).  FT = 2 forms the checksums on the CUDA
+// cores instead: S is then 8 rows of plain FP32 sums s_g[k] per 256-column tile, and the four
+// epilogue warps, idle during the mainloop, read each stage next to the MMAs (their own row of
+// A_hi and A_lo, all of S) and keep chk_g += (a_hi + a_lo) * s_g[k] for the 8 groups in registers.
+// No extra MMA, so the cost is a few percent instead of ~20 %, but an exact checksum does not
+// follow the truncation of the tensor cores' accumulators: the clean residual is 2.6x larger and
+// so is the default threshold.
+constexpr int kFtRows = 32;                          // rows of S per 256-column tile (FT = 1; FT = 2 uses the first 8)
+constexpr int kFtTensor = 1, kFtCuda = 2;
+template <int TBN, int TBK, int FT = 0>
 struct Tf32Cfg {
   static constexpr int kTA = TBM * TBK * 4;          // bytes per A plane tile
   static constexpr int kTB = TBN * TBK * 4;          // bytes per B plane tile
-  static constexpr int kTS = FT ? kFtRows * TBK * 4 : 0;  // bytes per checksum tile
+  static constexpr int kTS = FT == kFtTensor ? kFtRows * TBK * 4 : FT == kFtCuda ? 8 * TBK * 4 : 0;  // bytes per checksum tile
   static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;
   static constexpr int kStages = ((FT ? 208 : 192) * 1024) / kStage;
-  static constexpr int kSmem = 1024 + kStages * kStage + 256;
-  // FP32 accumulator: one TMEM column per output column; FT: 16 more, rounded to a power of two
-  static constexpr int kTmemCols = FT ? 2 * TBN : TBN;
+  static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 4096 : 0);   // + checksum table
+  // FP32 accumulator: one TMEM column per output column; FT = 1: 16 more, rounded to a power of two
+  static constexpr int kTmemCols = FT == kFtTensor ? 2 * TBN : TBN;
   static constexpr uint32_t kSwizzle = (TBK == 32) ? 2u : 4u;   // descriptor layout type: 128-byte / 64-byte swizzle
   static constexpr uint32_t kSbo = 8 * TBK * 4;                 // bytes between 8-row groups
 };
@@ -95,12 +104,14 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float *__restri
 // Transposing variant: X is rows x cols (pitch ld); planes are cols x rows (pitch ldp >= rows,
 // a multiple of 4).  64 x 64 tiles through shared memory: coalesced reads along the columns of X,
 // 128-bit coalesced writes along the rows of X.
-// With S != NULL it also writes the ABFT checksum plane (pitch ldp, 24 rows per 256 columns of X):
-// for every row r of X and group g of 32 columns inside 256-column tile t, S[24t + g][r] and
-// S[24t + 8 + g][r] are the lo/hi split of sum_{j<32} X[r][256t + 32g + j]; S[24t + 16 + g][r] = 0.
+// With S != NULL it also writes the ABFT checksum plane (pitch ldp): for every row r of X and group
+// g of 32 columns inside 256-column tile t, with sum = sum_{j<32} X[r][256t + 32g + j],
+//   smode 1 (32 rows per tile): S[32t + g][r] = S[32t + 16 + g][r] = hi(sum), S[32t + 8 + g][r] = lo(sum),
+//                               S[32t + 24 + g][r] = 0;
+//   smode 2 (8 rows per tile):  S[8t + g][r] = sum.
 __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld,
                                                              float *__restrict__ hi, float *__restrict__ lo, int ldp,
-                                                             float *__restrict__ S) {
+                                                             float *__restrict__ S, int smode) {
   __shared__ float t[64][65];
   const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64, tid = threadIdx.x;
   for (int e = tid; e < 64 * 64; e += 256) {
@@ -123,7 +134,16 @@ __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__rest
       *reinterpret_cast<float4 *>(lo + (size_t)c * ldp + r) = l;
     }
   }
-  if (S != nullptr) {
+  if (S != nullptr && smode == kFtCuda) {
+    // plain FP32 sums, 8 rows per 256 columns
+    const int rr = tid & 63, gg = (tid >> 6) & 1;
+    if (tid < 128 && r0 + rr < ldp) {
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sum += t[rr][32 * gg + j];
+      S[((size_t)(c0 / 256) * 8 + (c0 % 256) / 32 + gg) * ldp + r0 + rr] = sum;
+    }
+  } else if (S != nullptr) {
     const int rr = tid & 63, gg = (tid >> 6) & 1;   // row r0 + rr of X, columns c0 + 32gg .. +31
     const size_t o = ((size_t)(c0 / 256) * kFtRows + (c0 % 256) / 32 + gg) * ldp + r0 + rr;
     if (r0 + rr < ldp) {
@@ -192,13 +212,61 @@ __device__ __forceinline__ FtInj ft_scan_plan(const Tf32Args &p, int my_row, int
   return inj;
 }
 
+// CUDA-core checksums (FT = 2).  A warp owns 32 tile rows; lane (rb, kc) = (lane >> 3, lane & 7)
+// takes rows rb + 4i (i = 0..7) and the four k of 16-byte chunk kc of each K-slab, so that a warp
+// reads every A row once (8 lanes x 16 bytes = one 128-byte row, conflict-free) and S once per
+// lane octet, and keeps 8 rows x 8 groups of partial sums in registers for the whole K loop.
+// The tiles are K-major under the 128-byte swizzle: chunk j of row x sits at chunk j ^ (x & 7).
+struct FtCudaAcc {
+  float v[8][8];   // [row i][group g]
+};
+__device__ __forceinline__ void ft_cuda_slab(const unsigned char *a_hi, const unsigned char *a_lo, const unsigned char *sg,
+                                             int row0, int lane, FtCudaAcc &acc) {
+  const int rb = lane >> 3, kc = lane & 7;
+  float4 s4[8];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) s4[g] = *reinterpret_cast<const float4 *>(sg + g * 128 + ((kc ^ g) << 4));
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = row0 + rb + 4 * i;
+    const int off = r * 128 + ((kc ^ (r & 7)) << 4);
+    const float4 h = *reinterpret_cast<const float4 *>(a_hi + off);
+    const float4 l = *reinterpret_cast<const float4 *>(a_lo + off);
+    const float a0 = h.x + l.x, a1 = h.y + l.y, a2 = h.z + l.z, a3 = h.w + l.w;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float t = acc.v[i][g];
+      t = __fmaf_rn(a0, s4[g].x, t);
+      t = __fmaf_rn(a1, s4[g].y, t);
+      t = __fmaf_rn(a2, s4[g].z, t);
+      acc.v[i][g] = __fmaf_rn(a3, s4[g].w, t);
+    }
+  }
+}
+// End of the K loop: fold the eight k-chunk lanes of each row and leave chk[row][g] in the warp's
+// rows of the shared table (float [128][8]); the epilogue thread of a row reads its own entries.
+__device__ __forceinline__ void ft_cuda_finish(FtCudaAcc &acc, float *table, int row0, int lane) {
+  const int rb = lane >> 3, kc = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float t = acc.v[i][g];
+      t += __shfl_xor_sync(0xffffffffu, t, 1);
+      t += __shfl_xor_sync(0xffffffffu, t, 2);
+      t += __shfl_xor_sync(0xffffffffu, t, 4);
+      if (kc == g) table[(row0 + rb + 4 * i) * 8 + g] = t;
+    }
+  __syncwarp();
+}
+
 // Epilogue of one warp (TMEM lane quarter q): 32 rows x TBN columns of the accumulator tile ->
 // alpha/beta -> global.  FT: each 32-column chunk is summed and compared with its two checksum
 // columns first; a row-group out of tolerance is recomputed and repaired (see the file header).
 // `ok` (warp-uniform) says the accumulator is complete; called by whole warps.
-template <int TBN, bool FT>
+template <int TBN, int FT>
 __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_base, int q, int lane, int m0, int n0, bool ok,
-                                              int nkb, const FtInj &inj) {
+                                              int nkb, const FtInj &inj, const float *chk_row) {
   const int inj_col0 = inj.col0, inj_col1 = inj.col1;
   const uint32_t inj_mask0 = inj.mask0, inj_mask1 = inj.mask1;
   float worst = 0.f;          // largest in-tolerance |group sum - checksum| this thread saw
@@ -212,11 +280,13 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
     float expect = 0.f;
     if (ok && nkb > 0) {
       tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-      if (FT) {
+      if (FT == kFtTensor) {
         const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(TBN + c);
         const uint32_t e0 = tmem_ld_32x1(t0), e1 = tmem_ld_32x1(t0 + 8);
         tmem_ld_wait();
         expect = __uint_as_float(e0) + __uint_as_float(e1);
+      } else if (FT == kFtCuda) {
+        expect = chk_row[c];   // this row's entry of the shared table
       }
       tmem_ld_wait();
     } else {
@@ -316,7 +386,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
   }
 }
 
-template <int TBN, int TBK, bool FT>
+template <int TBN, int TBK, int FT>
 __global__ void __launch_bounds__(192, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
@@ -349,7 +419,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   if (tid == 0) {
     for (int s = 0; s < TSTAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], FT == kFtCuda ? 5 : 1);   // the MMA commit, and the four checksum warps
     }
     mbar_init(acc_ready, 1);
     *abort_flag = 0;
@@ -386,7 +456,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * TBK, n0);
           tma_load_2d(st + 2 * kTA + kTB, &tmBl, &full[s], kb * TBK, n0);
         }
-        if (FT) tma_load_2d(st + 2 * kTA + 2 * kTB, &tmS, &full[s], kb * TBK, tile_n * kFtRows);
+        if (FT == kFtTensor) tma_load_2d(st + 2 * kTA + 2 * kTB, &tmS, &full[s], kb * TBK, tile_n * kFtRows);
+        if (FT == kFtCuda) tma_load_2d(st + 2 * kTA + 2 * kTB, &tmS, &full[s], kb * TBK, tile_n * 8);
       }
     }
   } else if (warp == 1) {
@@ -415,7 +486,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
-          if (FT) {
+          if (FT == kFtTensor) {
             const uint64_t s_lohi = umma_smem_desc(st + 2 * kTA + 2 * kTB + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
             const uint64_t s_hi0 = umma_smem_desc(st + 2 * kTA + 2 * kTB + 16 * TBK * 4 + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
             umma_tf32(tmem_base + TBN, a_lo, s_hi0, idesc_s, (kb > 0 || k4 > 0) ? 1u : 0u);
@@ -432,6 +503,27 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     bool ok = true;
     FtInj inj;
     if (FT) inj = ft_scan_plan<TBN>(p, m0 + q * 32 + lane, n0);
+    float *table = reinterpret_cast<float *>(smem + TSTAGES * kTStage + 256);
+    if (FT == kFtCuda) {
+      // checksums on the CUDA cores: follow the stages next to the MMA issuer
+      FtCudaAcc acc;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int g = 0; g < 8; ++g) acc.v[i][g] = 0.f;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % TSTAGES;
+        if (!mbar_wait(&full[s], (uint32_t)(kb / TSTAGES) & 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        const unsigned char *st = smem + s * kTStage;
+        ft_cuda_slab(st, st + kTA, st + 2 * kTA + 2 * kTB, q * 32, lane, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      ft_cuda_finish(acc, table, q * 32, lane);
+    }
     if (nkb > 0) {
       // poll in slices so that an abort raised by the other roles is seen
       bool done = false;
@@ -445,7 +537,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     ok = __all_sync(0xffffffffu, ok);   // the checksum pass below uses warp collectives
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj);
+    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 8);
   }
 
   tc_fence_before();
@@ -468,18 +560,19 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 // rows each.  CTA 0 stages rows 0..7 (s_hi) and 16..23 (s_hi) of the tile's 32-row S block, CTA 1
 // rows 8..15 (s_lo) and 24..31 (zero), so the two extra MMAs see [s_hi | s_lo] and [s_hi | 0] as
 // in the single-CTA kernel and the 16 checksum columns mean the same.
-template <bool FT>
+constexpr int kPairBand = 8;   // tile rows per band of the pair kernel's tile order
+template <int FT>
 struct PairCfg {
   static constexpr int kTA = TBM * 32 * 4;           // bytes per A plane tile (128 rows)
   static constexpr int kTB = 128 * 32 * 4;           // bytes per B plane half tile (128 columns)
-  static constexpr int kTS = FT ? 2 * 8 * 32 * 4 : 0;   // two 8-row checksum slots
+  static constexpr int kTS = FT == kFtTensor ? 2 * 8 * 32 * 4 : FT == kFtCuda ? 8 * 32 * 4 : 0;   // two 8-row slots / one S tile
   static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;   // 64 KB (+2 KB)
   static constexpr int kStages = 3;
-  static constexpr int kSmem = 1024 + kStages * kStage + 256;
-  static constexpr int kTmemCols = FT ? 512 : 256;
+  static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 4096 : 0);   // + checksum table
+  static constexpr int kTmemCols = FT == kFtTensor ? 512 : 256;
 };
 
-template <bool FT>
+template <int FT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                          const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
@@ -491,20 +584,27 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + S * kStage);
   uint64_t *empty = full + S;
   uint64_t *acc_ready = empty + S;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  uint64_t *landed = acc_ready + 1;     // FT = 2, CTA 1: the leader's word that stage s is complete in both CTAs
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(landed + S);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
-  const int tiles_n = (p.N + 255) / 256;
+  // Tile order: bands of kPairBand tile rows, walked column by column, so that the pairs resident at one
+  // time share few distinct A and B panels (more L2 hits than a row-major walk over all columns).
+  const int tiles_n = (p.N + 255) / 256, tiles_m = (p.M + 255) / 256;
   const int pair = blockIdx.x >> 1;
-  const int m0 = (pair / tiles_n) * 256 + (int)rank * 128, n0 = (pair % tiles_n) * 256;
+  const int band = pair / (kPairBand * tiles_n), within = pair % (kPairBand * tiles_n);
+  const int band_rows = min(kPairBand, tiles_m - band * kPairBand);
+  const int tile_m = band * kPairBand + within % band_rows, tile_n = within / band_rows;
+  const int m0 = tile_m * 256 + (int)rank * 128, n0 = tile_n * 256;
   const int nkb = (p.K + 31) / 32;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], FT == kFtCuda ? 5 : 1);
+      mbar_init(&landed[s], 1);
     }
     mbar_init(acc_ready, 1);
     *abort_flag = 0;
@@ -540,8 +640,9 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
         tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
         tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
-        if (FT) {
-          const int srow = (pair % tiles_n) * kFtRows + 8 * (int)rank;
+        if (FT == kFtCuda) tma_load_2d_pair(st + 2 * kTA + 2 * kTB, &tmS, leader_full, kb * 32, tile_n * 8);
+        if (FT == kFtTensor) {
+          const int srow = tile_n * kFtRows + 8 * (int)rank;
           tma_load_2d_pair(st + 2 * kTA + 2 * kTB, &tmS, leader_full, kb * 32, srow);
           tma_load_2d_pair(st + 2 * kTA + 2 * kTB + 1024, &tmS, leader_full, kb * 32, srow + 16);
         }
@@ -561,6 +662,9 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
           break;
         }
         tc_fence_after();
+        // Tell CTA 1's checksum warps.  Its tiles were written by its own TMA loads, whose completion
+        // this thread has just observed on the "full" barrier, so they are in place before the arrival.
+        if (FT == kFtCuda) mbar_arrive_remote(mapa_u32(smem_u32(&landed[s]), 1));
         const uint32_t st = smem_u32(smem + s * kStage);
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
@@ -571,7 +675,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
           umma_tf32_pair(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32_pair(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32_pair(tmem_base, a_hi, b_hi, idesc, 1u);
-          if (FT) {
+          if (FT == kFtTensor) {
             const uint64_t w1 = umma_smem_desc(st + 2 * kTA + 2 * kTB + k4 * 32, 16, 1024, 2);
             const uint64_t w2 = umma_smem_desc(st + 2 * kTA + 2 * kTB + 1024 + k4 * 32, 16, 1024, 2);
             umma_tf32_pair(tmem_base + 256, a_lo, w2, idesc_s, (kb > 0 || k4 > 0) ? 1u : 0u);
@@ -588,6 +692,29 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     bool ok = true;
     FtInj inj;
     if (FT) inj = ft_scan_plan<256>(p, m0 + q * 32 + lane, n0);
+    float *table = reinterpret_cast<float *>(smem + S * kStage + 256);
+    if (FT == kFtCuda) {
+      // checksums on the CUDA cores: the leader's warps watch its "full" barrier, CTA 1's the word the
+      // leader forwards once the stage is complete in both CTAs
+      uint64_t *data_bar = (rank == 0) ? full : landed;
+      FtCudaAcc acc;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int g = 0; g < 8; ++g) acc.v[i][g] = 0.f;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S;
+        if (!mbar_wait(&data_bar[s], (uint32_t)(kb / S) & 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        const unsigned char *st = smem + s * kStage;
+        ft_cuda_slab(st, st + kTA, st + 2 * kTA + 2 * kTB, q * 32, lane, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      ft_cuda_finish(acc, table, q * 32, lane);
+    }
     if (nkb > 0) {
       bool done = false;
       const uint64_t t0 = global_timer_ns();
@@ -600,7 +727,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj);
+    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 8);
   }
 
   // neither CTA leaves (or frees tensor memory) while the other may still be read by an MMA
@@ -615,6 +742,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
 
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
 static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
+static int g_tf32_abft = kFtCuda;  // where the ABFT checksums are formed: 1 tensor cores, 2 CUDA cores
 static int g_tf32_pair = 1;    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
@@ -625,7 +753,7 @@ size_t tf32_workspace_bytes(int M, int N, int K) {
   return (2 * (size_t)M * kp + 2 * (size_t)N * kp + srows * kp) * sizeof(float) + 8 * 1024;
 }
 
-template <int TBN, int TBK, bool FT>
+template <int TBN, int TBK, int FT>
 static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
@@ -652,7 +780,7 @@ static int max_resident_pairs(Context *ctx) {
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * ctx->sm_count, 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
-  cfg.dynamicSmemBytes = PairCfg<true>::kSmem;
+  cfg.dynamicSmemBytes = PairCfg<kFtTensor>::kSmem;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 2;
@@ -660,8 +788,8 @@ static int max_resident_pairs(Context *ctx) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true>::kSmem) != cudaSuccess ||
-      cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
+  if (cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtTensor>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtTensor>::kSmem) != cudaSuccess ||
+      cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<kFtTensor>, &cfg) != cudaSuccess || n <= 0) {
     (void)cudaGetLastError();
     n = ctx->sm_count / 2;
   }
@@ -678,6 +806,16 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s);
   int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
   if (st != B2_OK) return st;
+  const int ftm = ft ? g_tf32_abft : 0;
+  FtArgs ftl;
+  if (ft) {
+    // Default thresholds for operands of unit scale, each about 4.5x the largest residual of a clean
+    // 8192^3 product (more at smaller K): checksums accumulated by the tensor cores follow their
+    // truncation (residual 2.2e-6*K), exact checksums from the CUDA cores do not (5.8e-6*K).
+    ftl = *ft;
+    if (!(ftl.tau > 0.f)) ftl.tau = fmaxf((ftm == kFtTensor ? 1e-5f : 2.6e-5f) * (float)K, 2e-4f);
+    ft = &ftl;
+  }
   const int kp = (K + 3) & ~3;
   char *w = (char *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023);
   const size_t a_elems = (size_t)M * kp, b_elems = (size_t)N * kp;
@@ -686,7 +824,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   float *Al = (float *)(w + align1k(a_elems * 4));
   float *Bh = (float *)(w + 2 * align1k(a_elems * 4));
   float *Bl = (float *)(w + 2 * align1k(a_elems * 4) + align1k(b_elems * 4));
-  const int srows = ((N + 255) / 256) * kFtRows;
+  const int srows = ((N + 255) / 256) * (g_tf32_abft == kFtTensor ? kFtRows : 8);
   float *S = (float *)(w + 2 * align1k(a_elems * 4) + 2 * align1k(b_elems * 4));
 
   {
@@ -695,7 +833,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     split_planes_kernel<<<g, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp, vec);
     // the ABFT form covers whole 256-column tiles so that every checksum row is written
     dim3 gt(ft ? ((N + 255) / 256) * 4 : (N + 63) / 64, (kp + 63) / 64);
-    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp, ft ? S : nullptr);
+    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp, ft ? S : nullptr, ftm);
   }
   B2_CUDA(cudaGetLastError());
 
@@ -739,12 +877,14 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     }
     static bool pair_configured = false;
     if (!pair_configured) {
-      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<false>::kSmem));
-      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true>::kSmem));
+      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<0>::kSmem));
+      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtTensor>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtTensor>::kSmem));
+      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtCuda>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtCuda>::kSmem));
       pair_configured = true;
     }
-    if (ft) sgemm_3xtf32_pair_kernel<true><<<2 * pairs, 192, PairCfg<true>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
-    else sgemm_3xtf32_pair_kernel<false><<<2 * pairs, 192, PairCfg<false>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
+    if (ftm == kFtTensor) sgemm_3xtf32_pair_kernel<kFtTensor><<<2 * pairs, 192, PairCfg<kFtTensor>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
+    else if (ftm == kFtCuda) sgemm_3xtf32_pair_kernel<kFtCuda><<<2 * pairs, 192, PairCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
+    else sgemm_3xtf32_pair_kernel<0><<<2 * pairs, 192, PairCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
   }
@@ -757,7 +897,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
 
   if (ft) {
-    st = make_tmap_2d(&maps[4], S, (uint64_t)K, (uint64_t)srows, (uint64_t)kp, tbk, kFtRows, swz);
+    st = make_tmap_2d(&maps[4], S, (uint64_t)K, (uint64_t)srows, (uint64_t)kp, tbk, ftm == kFtTensor ? kFtRows : 8, swz);
     if (st != B2_OK) return st;
   } else {
     maps[4] = maps[2];
@@ -772,10 +912,10 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (ft) {
     args.ft = *ft;
     args.tau_elem = 0.5f * ft->tau;
-    return launch_tf32<256, 32, true>(maps, args, grid, s);
+    return ftm == kFtTensor ? launch_tf32<256, 32, kFtTensor>(maps, args, grid, s) : launch_tf32<256, 32, kFtCuda>(maps, args, grid, s);
   }
-  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, false>(maps, args, grid, s) : launch_tf32<256, 32, false>(maps, args, grid, s);
-  return tbn == 128 ? launch_tf32<128, 16, false>(maps, args, grid, s) : launch_tf32<256, 16, false>(maps, args, grid, s);
+  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, 0>(maps, args, grid, s) : launch_tf32<256, 32, 0>(maps, args, grid, s);
+  return tbn == 128 ? launch_tf32<128, 16, 0>(maps, args, grid, s) : launch_tf32<256, 16, 0>(maps, args, grid, s);
 }
 
 }  // namespace b2
@@ -799,6 +939,12 @@ int b2_set_tf32_tile_n(int n) {
 int b2_set_tf32_pair(int on) {
   B2_REQUIRE(on >= 0 && on <= 2, B2_ERR_INVALID_ARG, "b2_set_tf32_pair: %d is not 0, 1 or 2", on);
   b2::g_tf32_pair = on;
+  return B2_OK;
+}
+// Where the ABFT checksums of the 3xTF32 path are formed: 1 on the tensor cores, 2 on the CUDA cores (default).
+int b2_set_tf32_abft_mode(int mode) {
+  B2_REQUIRE(mode == 1 || mode == 2, B2_ERR_INVALID_ARG, "b2_set_tf32_abft_mode: %d is not 1 or 2", mode);
+  b2::g_tf32_abft = mode;
   return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.

@@ -766,7 +766,6 @@ using namespace b2;
 namespace b2 {
 int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
                           float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
-constexpr float kTf32TauPerK = 1e-5f;     // default ABFT threshold of the 3xTF32 path per unit of K
 }
 
 extern "C" {
@@ -796,10 +795,7 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
   ft.lda = lda;
   ft.ldb = ldb;
   if (path == B2_PATH_3XTF32) {
-    // the tensor cores' accumulation error grows in proportion to K and is well above the FFMA
-    // path's rounding noise, so the threshold is wider: about 4.5x the largest residual of a clean
-    // 8192^3 product of unit-scale operands, more at smaller K
-    ft.tau = tau > 0.f ? tau : fmaxf(kTf32TauPerK * (float)K, 2e-4f);
+    ft.tau = tau;   // <= 0: the path's own default, which depends on where the checksums are formed
     return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
   }
   // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the

@@ -119,10 +119,11 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
  * clean run).  `tau` <= 0 selects the default threshold 2e-6*K (inputs of unit scale);
  * the reference uses a fixed 0.1 (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:30).
  * `report_dev`: optional device b2_ft_report that this call ADDS to (caller zeroes it).
- * path = B2_PATH_3XTF32: the checksums ride on the tensor cores (one per output row and group
- * of 32 columns), a group out of tolerance is recomputed in FP32 from A and B and every output
- * further than tau/2 from its recomputed value is replaced.  Default tau there is 1e-5*K: the
- * tensor cores' truncating accumulation leaves a residual of about 2e-6*K on clean data.
+ * path = B2_PATH_3XTF32: one checksum per output row and group of 32 columns, formed during the
+ * mainloop; a group out of tolerance is recomputed in FP32 from A and B and every output
+ * further than tau/2 from its recomputed value is replaced.  Default tau there is 2.6e-5*K (1e-5*K
+ * with b2_set_tf32_abft_mode(1)): the tensor cores' truncating accumulation leaves a residual of up
+ * to 5.8e-6*K (2.2e-6*K) on clean data of unit scale.
  * Needs the workspace of b2_sgemm_workspace_bytes(B2_PATH_3XTF32, ...). */
 int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda,
                 const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
@@ -221,6 +222,10 @@ int b2_set_tf32_slab_k(int k);
  * against 128x128 single-CTA tiles by whole waves (default), 2 always.  A width pinned with b2_set_tf32_tile_n
  * selects the single-CTA kernel of that width. */
 int b2_set_tf32_pair(int on);
+/* Where b2_ft_sgemm(path = B2_PATH_3XTF32) forms its checksums: 2 (default) on the CUDA cores beside the MMAs
+ * (few percent overhead, default tau 2.6e-5*K), 1 on the tensor cores as two extra small MMAs per K-step
+ * (about +20 %, default tau 1e-5*K: such checksums follow the accumulators' truncation more closely). */
+int b2_set_tf32_abft_mode(int mode);
 /* Reads and clears the device status word that bounded waits set; synchronises the stream.
  * Returns 0 or the recorded negative status. */
 int b2_check_status(b2_handle h, void *stream);

@@ -14,13 +14,25 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-5          # max|C - C_ref| / (|A| |B|) that the 3xTF32 path has to meet
 
 
-@pytest.fixture(autouse=True, params=[0, 2], ids=["single_cta", "cta_pair"])
+TAU_PER_K = {1: 1e-5, 2: 2.6e-5}     # default thresholds: checksums on the tensor cores / on the CUDA cores
+_mode = {"abft": 2}
+
+
+@pytest.fixture(autouse=True, params=[(0, 2), (2, 2), (0, 1), (2, 1)],
+                ids=["single_cta-cuda_checksums", "cta_pair-cuda_checksums", "single_cta-tensor_checksums",
+                     "cta_pair-tensor_checksums"])
 def _kernel_form(request, cuda):
-    """Every test runs on the single-CTA kernel (128 x 256 tiles) and on the CTA-pair kernel (256 x 256 tiles)."""
+    """Every test runs on the single-CTA kernel (128 x 256 tiles) and on the CTA-pair kernel (256 x 256 tiles),
+    with the checksums formed on the CUDA cores (the default) and on the tensor cores."""
     import hpcdeepneuralnetworks_b200 as b2
-    b2.set_tf32_pair(request.param)
+    pair, abft = request.param
+    b2.set_tf32_pair(pair)
+    b2.set_tf32_abft_mode(abft)
+    _mode["abft"] = abft
     yield
     b2.set_tf32_pair(1)
+    b2.set_tf32_abft_mode(2)
+    _mode["abft"] = 2
 
 
 def dev(a):
@@ -35,7 +47,7 @@ def mats(M, N, K):
 
 
 def default_tau(K):
-    return max(1e-5 * K, 2e-4)
+    return max(TAU_PER_K[_mode["abft"]] * K, 2e-4)
 
 
 def flip(x, bit):
