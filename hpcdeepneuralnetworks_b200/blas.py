@@ -129,7 +129,8 @@ def make_plan(plan) -> torch.Tensor | None:
 def ft_sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, plan=None, tau=0.0, report=None, lda=None, ldb=None,
              ldc=None, handle=None):
     """ABFT SGEMM.  ``plan``: device int32 tensor (n,6) from ``make_plan`` or None.  ``report``: device
-    int32 tensor of 8 words that the call adds to (see ``FtReport``) or None.  Returns ``Cm``."""
+    int32 tensor of 8 words that the call adds to (see ``FtReport``) or None.  ``tau``: > 0 absolute threshold,
+    0 the default for operands of unit scale, < 0 that default scaled by 3*rms(A)*rms(B).  Returns ``Cm``."""
     L = _lib.load()
     h = handle or default_handle()
     if path == PATH_3XTF32:

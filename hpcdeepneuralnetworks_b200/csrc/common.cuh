@@ -42,6 +42,11 @@ struct Context {
 };
 Context *default_context();           // process-wide, created on first use for the current device
 int ensure_workspace(Context *ctx, size_t bytes, cudaStream_t s);
+// Enqueues the reduction that leaves 3 * rms(X1) * rms(X2) in the context's scratch (1 for operands uniform in
+// [-1, 1)) and returns the device address of that float: the factor by which rounding noise, and so an ABFT
+// threshold, grows with the operands' scale.
+int ft_data_scale(Context *ctx, const float *X1, int rows1, int cols1, int ld1, const float *X2, int rows2, int cols2,
+                  int ld2, cudaStream_t s, const float **scale_dev);
 
 // Layout of Context::fixed (all offsets 256-byte aligned).
 constexpr size_t kSdotMaxBlocks = 4096;
@@ -50,7 +55,8 @@ constexpr size_t kFixedSdotTicket = kSdotMaxBlocks * sizeof(double);      // uns
 constexpr size_t kFixedStatus = kFixedSdotTicket + 256;                   // int status word of bounded waits
 constexpr size_t kFixedVerify = kFixedStatus + 256;                       // verify_matrix result {uint fails, uint maxbits}
 constexpr size_t kFixedFtReport = kFixedVerify + 256;                     // b2_ft_report scratch
-constexpr size_t kFixedBytes = kFixedFtReport + 256;
+constexpr size_t kFixedFtScale = kFixedFtReport + 256;                    // double ssA, ssB; float scale (ABFT threshold scaling)
+constexpr size_t kFixedBytes = kFixedFtScale + 256;
 
 // cuTensorMapEncodeTiled fetched through the runtime (no link-time libcuda dependency, so
 // the shared object still loads on a machine without a driver).
@@ -79,7 +85,8 @@ __host__ __device__ inline float uniform_at(uint64_t mixed_seed, uint64_t i) {
 struct FtArgs {
   const b2_fault *plan;
   int n_faults;
-  float tau;
+  float tau;                // threshold for operands of unit scale (uniform in [-1, 1))
+  const float *tau_scale;   // device float that multiplies tau and follows the operands' scale, or NULL
   int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable, false alarms, max residual bits
   const float *A, *B;
   int lda, ldb;

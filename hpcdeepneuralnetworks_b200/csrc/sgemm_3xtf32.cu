@@ -269,6 +269,8 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
                                               int nkb, const FtInj &inj, const float *chk_row) {
   const int inj_col0 = inj.col0, inj_col1 = inj.col1;
   const uint32_t inj_mask0 = inj.mask0, inj_mask1 = inj.mask1;
+  const float tscale = (FT && p.ft.tau_scale) ? __ldg(p.ft.tau_scale) : 1.f;
+  const float tau = p.ft.tau * tscale, tau_elem = p.tau_elem * tscale;
   float worst = 0.f;          // largest in-tolerance |group sum - checksum| this thread saw
   int n_inj = 0, n_det = 0, n_cor = 0, n_false = 0;
   const int row = m0 + q * 32 + lane;
@@ -312,7 +314,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
 #pragma unroll
         for (int j = 0; j < 32; ++j) g += __uint_as_float(v[j]);
         const float resid = fabsf(g - expect);
-        const bool bad = !(resid <= p.ft.tau);
+        const bool bad = !(resid <= tau);
         if (!bad) worst = fmaxf(worst, resid);
         unsigned m = __ballot_sync(0xffffffffu, bad);
         while (m) {
@@ -324,7 +326,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float r = __shfl_sync(0xffffffffu, ref, j);
-            if (lane == L && !(fabsf(__uint_as_float(v[j]) - r) <= p.tau_elem)) {
+            if (lane == L && !(fabsf(__uint_as_float(v[j]) - r) <= tau_elem)) {
               v[j] = __float_as_uint(r);
               ++replaced;
             }

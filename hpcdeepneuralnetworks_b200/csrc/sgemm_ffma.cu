@@ -500,7 +500,8 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     expect += __shfl_xor_sync(0xffffffffu, expect, 16);
     actual += __shfl_xor_sync(0xffffffffu, actual, 8);
     actual += __shfl_xor_sync(0xffffffffu, actual, 16);
-    const bool bad = !(fabsf(actual - expect) <= ft.tau);  // NaN-safe: a NaN difference is out of tolerance
+    const float tau = ft.tau_scale ? ft.tau * __ldg(ft.tau_scale) : ft.tau;
+    const bool bad = !(fabsf(actual - expect) <= tau);  // NaN-safe: a NaN difference is out of tolerance
     const int any_bad = __syncthreads_or(bad ? 1 : 0);      // also: the ring is idle from here on
     if (any_bad) {                                           // uniform over the block
       if (bad && lm == 0) flagged[atomicAdd(nflag, 1)] = warp * 8 + ln;
@@ -766,6 +767,44 @@ using namespace b2;
 namespace b2 {
 int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
                           float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
+
+// Sum of squares of a rows x cols matrix (pitch ld) added to *out: one block per row stripe.
+__global__ void __launch_bounds__(256) sumsq_kernel(const float *__restrict__ X, int rows, int cols, int ld, double *out) {
+  float acc = 0.f;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float *row = X + (size_t)r * ld;
+    for (int c = threadIdx.x; c < cols; c += 256) acc = __fmaf_rn(row[c], row[c], acc);
+  }
+  double d = (double)acc;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+  __shared__ double part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = d;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < 8; ++w) t += part[w];
+    atomicAdd(out, t);
+  }
+}
+__global__ void ft_scale_kernel(double *ss, double n1, double n2, float *scale) {
+  const double r1 = sqrt(ss[0] / n1), r2 = sqrt(ss[1] / n2);
+  *scale = (float)(3.0 * r1 * r2);   // uniform [-1, 1) has mean square 1/3
+}
+
+int ft_data_scale(Context *ctx, const float *X1, int rows1, int cols1, int ld1, const float *X2, int rows2, int cols2,
+                  int ld2, cudaStream_t s, const float **scale_dev) {
+  double *ss = (double *)((char *)ctx->fixed + kFixedFtScale);
+  float *scale = (float *)(ss + 2);
+  B2_CUDA(cudaMemsetAsync(ss, 0, 2 * sizeof(double), s));
+  const int g1 = rows1 < 1184 ? rows1 : 1184, g2 = rows2 < 1184 ? rows2 : 1184;
+  sumsq_kernel<<<g1, 256, 0, s>>>(X1, rows1, cols1, ld1, ss);
+  sumsq_kernel<<<g2, 256, 0, s>>>(X2, rows2, cols2, ld2, ss + 1);
+  ft_scale_kernel<<<1, 1, 0, s>>>(ss, (double)rows1 * cols1, (double)rows2 * cols2, scale);
+  B2_CUDA(cudaGetLastError());
+  *scale_dev = scale;
+  return B2_OK;
+}
 }
 
 extern "C" {
@@ -794,8 +833,14 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
   ft.B = B;
   ft.lda = lda;
   ft.ldb = ldb;
+  ft.tau_scale = nullptr;
+  if (tau < 0.f && K > 0) {
+    // scale-aware default: one pass over A and B for their root mean squares
+    int st = ft_data_scale(ctx, A, M, K, lda, B, K, N, ldb, (cudaStream_t)stream, &ft.tau_scale);
+    if (st != B2_OK) return st;
+  }
   if (path == B2_PATH_3XTF32) {
-    ft.tau = tau;   // <= 0: the path's own default, which depends on where the checksums are formed
+    ft.tau = tau > 0.f ? tau : 0.f;   // 0: the path's own default, which depends on where the checksums are formed
     return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
   }
   // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the
@@ -821,6 +866,11 @@ int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
   ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
+  ft.tau_scale = nullptr;
+  if (tau < 0.f && K > 0) {
+    int st = ft_data_scale(ctx, A, K, M, M, B, K, N, N, (cudaStream_t)stream, &ft.tau_scale);
+    if (st != B2_OK) return st;
+  }
   ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
   ft.A = B;   // left operand of C^T = B * A^T, held K x N in memory
   ft.B = A;   // right operand, held K x M in memory

@@ -116,8 +116,10 @@ typedef struct {
 int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C);
 
 /* Full form.  `plan_dev`/`n_faults`: optional device array of faults to inject (NULL/0 =
- * clean run).  `tau` <= 0 selects the default threshold 2e-6*K (inputs of unit scale);
- * the reference uses a fixed 0.1 (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:30).
+ * clean run).  `tau` > 0 is an absolute threshold; `tau` == 0 selects the default 2e-6*K, right for
+ * operands of unit scale (uniform in [-1, 1)); `tau` < 0 selects the same default multiplied by
+ * 3*rms(A)*rms(B), measured by one extra pass over A and B, for operands of any scale.  The
+ * reference uses a fixed 0.1 (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:30).
  * `report_dev`: optional device b2_ft_report that this call ADDS to (caller zeroes it).
  * path = B2_PATH_3XTF32: one checksum per output row and group of 32 columns, formed during the
  * mainloop; a group out of tolerance is recomputed in FP32 from A and B and every output

@@ -274,3 +274,47 @@ def test_colmajor_nt_abft(cuda, shape):
     r = b2.read_report(rep)
     assert (r["injected"], r["detected"], r["corrected"]) == (1, 1, 1), r
     assert np.array_equal(dc.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("sa,sb", [(100.0, 1.0), (0.01, 0.5), (7.0, 300.0)])
+def test_scale_aware_threshold(cuda, path, sa, sb):
+    """Operands far from unit scale: tau < 0 measures 3*rms(A)*rms(B) and scales the default threshold with it, so a
+    clean run raises no alarm and a planted flip is still found; the unit-scale default (tau = 0) would flag clean
+    blocks when the data is large."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 256, 512, 768
+    a, b, c = mats(M, N, K)
+    a, b = (a * np.float32(sa)).astype(np.float32), (b * np.float32(sb)).astype(np.float32)
+    da, db = dev(a), dev(b)
+    plain = torch.zeros((M, N), device="cuda")
+    b2.sgemm(M, N, K, 1.0, da, db, 0.0, plain, path=path)
+    rep = b2.new_report()
+    out = torch.zeros((M, N), device="cuda")
+    b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=path, tau=-1.0, report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert r["detected"] == 0 and r["false_alarms"] == 0 and r["corrected"] == 0
+    assert torch.equal(out, plain)
+    # a flip of the top exponent bit of the largest accumulator is far above any scaled threshold
+    acc = plain.cpu().numpy()
+    r0, c0 = (int(v) for v in np.unravel_index(np.argmax(np.abs(acc)), acc.shape))
+    plan = np.array([[r0 // 128, c0 // 128, r0 % 128, c0 % 128, 10 ** 6, 29]], dtype=np.int32)
+    rep = b2.new_report()
+    out.zero_()
+    b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=path, tau=-1.0, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    assert r["injected"] == 1 and r["detected"] == 1 and r["corrected"] >= 1 and r["false_alarms"] == 0
+    scale = 3.0 * float(np.sqrt(np.mean(a.astype(np.float64) ** 2)) * np.sqrt(np.mean(b.astype(np.float64) ** 2)))
+    assert float((out - plain).abs().max().item()) <= 2.6e-5 * K * scale
+    if sa * sb >= 100.0:
+        # the unit-scale default is too tight for this data: clean blocks are flagged (and found clean)
+        rep = b2.new_report()
+        out.zero_()
+        b2.ft_sgemm(M, N, K, 1.0, da, db, 0.0, out, path=path, tau=0.0, report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert r["false_alarms"] + r["detected"] > 0
+        if path == 0:
+            assert r["corrected"] == 0 and torch.equal(out, plain)      # recomputation is bit-exact on the FFMA path
