@@ -47,7 +47,8 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons while the timed region runs: through NVML (read-only, every few
+    milliseconds) when the bindings are there, else with nvidia-smi (about ten samples a second)."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -55,7 +56,40 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index, self.samples, self.stop_flag, self.thread = index, [], False, None
 
+    def _nvml_handle(self):
+        """NVML handle of this process's CUDA device `index` (by PCI bus id, so that CUDA_VISIBLE_DEVICES does not
+        matter), or None when NVML cannot be used.  NVML is only read here, never written."""
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            pr = torch.cuda.get_device_properties(self.index)
+            try:
+                bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+                return pynvml, pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        except Exception:
+            return None, None
+
     def _run(self):
+        nv, h = self._nvml_handle()
+        if h is not None:
+            # a few milliseconds per sample: a timed region of tens of milliseconds still gets several
+            bits = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+            try:
+                mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+                while not self.stop_flag:
+                    mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                    try:
+                        rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                    except Exception:
+                        rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    self.samples.append([str(mhz), str(mx)] + [("Active" if rs & b else "Not Active") for _, b in bits])
+                    time.sleep(0.004)
+                return
+            except Exception:
+                pass
         while not self.stop_flag:
             try:
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],

@@ -102,60 +102,61 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float *__restri
 }
 
 // Transposing variant: X is rows x cols (pitch ld); planes are cols x rows (pitch ldp >= rows,
-// a multiple of 4).  64 x 64 tiles through shared memory: coalesced reads along the columns of X,
-// 128-bit coalesced writes along the rows of X.
+// a multiple of 4).  Tiles of 128 rows x 64 columns of X through shared memory: reads run 256
+// bytes along a row of X, writes 512 bytes along a row of the planes (the writes are two thirds of
+// the traffic).
 // With S != NULL it also writes the ABFT checksum plane (pitch ldp): for every row r of X and group
 // g of 32 columns inside 256-column tile t, with sum = sum_{j<32} X[r][256t + 32g + j],
 //   smode 1 (32 rows per tile): S[32t + g][r] = S[32t + 16 + g][r] = hi(sum), S[32t + 8 + g][r] = lo(sum),
 //                               S[32t + 24 + g][r] = 0;
 //   smode 2 (8 rows per tile):  S[8t + g][r] = sum.
+constexpr int kSplitTK = 128, kSplitTN = 64;
 __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld,
                                                              float *__restrict__ hi, float *__restrict__ lo, int ldp,
                                                              float *__restrict__ S, int smode) {
-  __shared__ float t[64][65];
-  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64, tid = threadIdx.x;
-  for (int e = tid; e < 64 * 64; e += 256) {
-    const int rr = e >> 6, cc = e & 63;
+  __shared__ float t[kSplitTK][kSplitTN + 1];
+  const int c0 = blockIdx.x * kSplitTN, r0 = blockIdx.y * kSplitTK, tid = threadIdx.x;
+#pragma unroll 8
+  for (int e = tid; e < kSplitTK * kSplitTN; e += 256) {
+    const int rr = e / kSplitTN, cc = e % kSplitTN;
     const int r = r0 + rr, c = c0 + cc;
-    t[rr][cc] = (r < rows && c < cols) ? X[(size_t)r * ld + c] : 0.f;
+    t[rr][cc] = (r < rows && c < cols) ? __ldcs(X + (size_t)r * ld + c) : 0.f;
   }
   __syncthreads();
-  for (int e = tid; e < 64 * 16; e += 256) {
-    const int cc = e >> 4, rq = (e & 15) * 4;   // output row c0 + cc, output columns r0 + rq .. +3
-    const int c = c0 + cc, r = r0 + rq;
-    if (c < cols && r < ldp) {
-      float4 h, l;
-      const float x0 = t[rq + 0][cc], x1 = t[rq + 1][cc], x2 = t[rq + 2][cc], x3 = t[rq + 3][cc];
-      h.x = tf32_rna(x0); l.x = tf32_rna(x0 - h.x);
-      h.y = tf32_rna(x1); l.y = tf32_rna(x1 - h.y);
-      h.z = tf32_rna(x2); l.z = tf32_rna(x2 - h.z);
-      h.w = tf32_rna(x3); l.w = tf32_rna(x3 - h.w);
-      *reinterpret_cast<float4 *>(hi + (size_t)c * ldp + r) = h;
-      *reinterpret_cast<float4 *>(lo + (size_t)c * ldp + r) = l;
+  // A warp takes 4 output rows x 8 quads of k at a time: lane (kq, nn) = (lane & 7, lane >> 3) reads
+  // t[4kq + i][nn], 32 distinct banks under the pitch of 65, and each output row gets 128 contiguous bytes.
+  {
+    const int lane = tid & 31, warp = tid >> 5, kq = lane & 7, nn = lane >> 3;
+    for (int w = warp; w < (kSplitTN / 4) * (kSplitTK / 32); w += 8) {
+      const int cc = (w / (kSplitTK / 32)) * 4 + nn, rq = ((w % (kSplitTK / 32)) * 8 + kq) * 4;
+      const int c = c0 + cc, r = r0 + rq;   // output row c, output columns r .. r+3
+      if (c < cols && r < ldp) {
+        float4 h, l;
+        const float x0 = t[rq + 0][cc], x1 = t[rq + 1][cc], x2 = t[rq + 2][cc], x3 = t[rq + 3][cc];
+        h.x = tf32_rna(x0); l.x = tf32_rna(x0 - h.x);
+        h.y = tf32_rna(x1); l.y = tf32_rna(x1 - h.y);
+        h.z = tf32_rna(x2); l.z = tf32_rna(x2 - h.z);
+        h.w = tf32_rna(x3); l.w = tf32_rna(x3 - h.w);
+        __stcs(reinterpret_cast<float4 *>(hi + (size_t)c * ldp + r), h);
+        __stcs(reinterpret_cast<float4 *>(lo + (size_t)c * ldp + r), l);
+      }
     }
   }
-  if (S != nullptr && smode == kFtCuda) {
-    // plain FP32 sums, 8 rows per 256 columns
-    const int rr = tid & 63, gg = (tid >> 6) & 1;
-    if (tid < 128 && r0 + rr < ldp) {
+  if (S != nullptr) {
+    const int rr = tid & (kSplitTK - 1), gg = tid >> 7;   // row r0 + rr of X, columns c0 + 32gg .. +31
+    if (r0 + rr < ldp) {
       float sum = 0.f;
 #pragma unroll
       for (int j = 0; j < 32; ++j) sum += t[rr][32 * gg + j];
-      S[((size_t)(c0 / 256) * 8 + (c0 % 256) / 32 + gg) * ldp + r0 + rr] = sum;
-    }
-  } else if (S != nullptr) {
-    const int rr = tid & 63, gg = (tid >> 6) & 1;   // row r0 + rr of X, columns c0 + 32gg .. +31
-    const size_t o = ((size_t)(c0 / 256) * kFtRows + (c0 % 256) / 32 + gg) * ldp + r0 + rr;
-    if (r0 + rr < ldp) {
-      if (tid < 128) {
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) sum += t[rr][32 * gg + j];
+      const int g = (c0 % 256) / 32 + gg;
+      if (smode == kFtCuda) {
+        S[((size_t)(c0 / 256) * 8 + g) * ldp + r0 + rr] = sum;
+      } else {
         const float h = tf32_rna(sum);
+        const size_t o = ((size_t)(c0 / 256) * kFtRows + g) * ldp + r0 + rr;
         S[o] = h;
         S[o + (size_t)8 * ldp] = tf32_rna(sum - h);
         S[o + (size_t)16 * ldp] = h;
-      } else {
         S[o + (size_t)24 * ldp] = 0.f;
       }
     }
@@ -773,10 +774,11 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
 
 // How many CTA pairs the device runs at once (one CTA per SM; a pair needs two SMs of one cluster
-// domain).  Asked of the occupancy API once per process; half the SM count if it will not say.
+// domain).  Asked of the occupancy API once per process; 0 (pairs are then not chosen automatically)
+// if it will not say, e.g. on a partition that cannot schedule clusters.
 static int max_resident_pairs(Context *ctx) {
-  static int cached = 0;
-  if (cached > 0) return cached;
+  static int cached = -1;
+  if (cached >= 0) return cached;
   int n = 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -793,9 +795,9 @@ static int max_resident_pairs(Context *ctx) {
   if (cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtTensor>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtTensor>::kSmem) != cudaSuccess ||
       cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<kFtTensor>, &cfg) != cudaSuccess || n <= 0) {
     (void)cudaGetLastError();
-    n = ctx->sm_count / 2;
+    n = 0;
   }
-  cached = n > 0 ? n : 1;
+  cached = n;
   return cached;
 }
 
@@ -834,7 +836,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     dim3 g((kp / 4 + 255) / 256, M < 16384 ? M : 16384);
     split_planes_kernel<<<g, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp, vec);
     // the ABFT form covers whole 256-column tiles so that every checksum row is written
-    dim3 gt(ft ? ((N + 255) / 256) * 4 : (N + 63) / 64, (kp + 63) / 64);
+    dim3 gt(ft ? ((N + 255) / 256) * (256 / kSplitTN) : (N + kSplitTN - 1) / kSplitTN, (kp + kSplitTK - 1) / kSplitTK);
     split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp, ft ? S : nullptr, ftm);
   }
   B2_CUDA(cudaGetLastError());
@@ -852,7 +854,8 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   const double tm = (double)((M + TBM - 1) / TBM);
   const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
   const int pairs = ((M + 255) / 256) * ((N + 255) / 256);
-  const double tpair = 0.9 * ceil((double)pairs / (double)max_resident_pairs(ctx));
+  const int slots = max_resident_pairs(ctx);
+  const double tpair = slots > 0 ? 0.9 * ceil((double)pairs / (double)slots) : 1e30;
   const bool pinned = (g_tf32_tile_n == 128 || g_tf32_tile_n == 256);
   // (the ABFT form has no 128-wide kernel: pairs against 128 x 256 tiles)
   const bool use_pair = tbk == 32 && !pinned &&
