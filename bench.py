@@ -498,7 +498,7 @@ def run_single(args):
         "config": {"workload": f"sgemm_rowmajor_{n}^3" + ("_abft" if args.abft else ""), "path": args.path, "alpha": 1.0, "beta": 0.5,
                    "inputs": "seeded uniform[-1,1) generated on the device", "l2": "A, B, C are 3 x %d MB, larger than the 126 MB L2" % (4 * n * n // 2 ** 20),
                    "parallelism": "1 GPU"},
-        "roofline": roof(path, tflops), "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * (1 if path == 0 else 3),
+        "roofline": roof(path, tflops), "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * ((2 if b2.sgemm_workspace_bytes(0, n, n, n) > 0 else 1) if path == 0 else 3),
         "clocks": clocks, "extra": extras,
     }
     print(json.dumps(line))
@@ -570,7 +570,8 @@ def run_multi(args):
             "cpu_baseline": None,
             "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "operands of 32768^3 are generated on the device; no host copy is part of this workload"},
-            "gpu_launches": args.steps * len(b2dist.k_panels(n, args.panel)) * (1 if path == 0 else 3),
+            # per K-panel: the GEMM kernel, plus the transpose of the A panel (FFMA) or the two split kernels (3xTF32)
+            "gpu_launches": args.steps * len(b2dist.k_panels(n, args.panel)) * (2 if path == 0 else 3),
             "clocks": clk.summary(),
             "abft_report": (b2.read_report(report) if args.abft else None),
             "extra": {"sdot_sharded": {"n_total": nloc * world, "ms": ms_dot, "value": 8.0 * nloc * world / (ms_dot * 1e-3) / 1e9,

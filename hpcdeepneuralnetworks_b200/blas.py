@@ -96,8 +96,7 @@ def sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, lda=None, ldb=None,
     """Row-major C = alpha*A*B + beta*C on device tensors (in place on ``Cm``)."""
     L = _lib.load()
     h = handle or default_handle()
-    if path == PATH_3XTF32:
-        h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))
+    h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))   # required by the 3xTF32 path, optional speed-up for FFMA
     check(L.b2_sgemm(h.raw, path, M, N, K, alpha, _ptr(A), lda or K, _ptr(B), ldb or N, beta, _ptr(Cm), ldc or N,
                      _stream()))
     return Cm
@@ -133,8 +132,7 @@ def ft_sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, plan=None, tau=0
     0 the default for operands of unit scale, < 0 that default scaled by 3*rms(A)*rms(B).  Returns ``Cm``."""
     L = _lib.load()
     h = handle or default_handle()
-    if path == PATH_3XTF32:
-        h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))
+    h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))
     nf = 0 if plan is None else int(plan.shape[0])
     check(L.b2_ft_sgemm(h.raw, path, M, N, K, alpha, _ptr(A), lda or K, _ptr(B), ldb or N, beta, _ptr(Cm), ldc or N,
                         _ptr(plan), nf, tau, _ptr(report), _stream()))
@@ -373,6 +371,16 @@ def set_ffma_tile(index: int):
 def set_tf32_tile_n(n: int):
     """Pin the 3xTF32 tile width (128 or 256; 0 = automatic)."""
     check(_lib.load().b2_set_tf32_tile_n(n))
+
+
+def sgemm_workspace_bytes(path: int, M: int, N: int, K: int) -> int:
+    """Bytes of workspace an M x N x K SGEMM uses on ``path`` (required for 3xTF32, optional for FFMA)."""
+    return int(_lib.load().b2_sgemm_workspace_bytes(path, M, N, K))
+
+
+def set_ffma_transpose_a(on: int):
+    """1 (default): the FFMA path may transpose a row-major A into the workspace first; 0: never."""
+    check(_lib.load().b2_set_ffma_transpose_a(on))
 
 
 def set_tf32_pair(on: int):

@@ -772,6 +772,7 @@ static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, 
 
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
+size_t ffma_workspace_bytes(int M, int N, int K);
 
 // How many CTA pairs the device runs at once (one CTA per SM; a pair needs two SMs of one cluster
 // domain).  Asked of the occupancy API once per process; 0 (pairs are then not chosen automatically)
@@ -930,7 +931,9 @@ using namespace b2;
 extern "C" {
 
 size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K) {
-  if (path != B2_PATH_3XTF32 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (path == B2_PATH_FFMA) return ffma_workspace_bytes(M, N, K);   // optional: used when there, never required
+  if (path != B2_PATH_3XTF32) return 0;
   return tf32_workspace_bytes(M, N, K);
 }
 

@@ -302,8 +302,9 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t a_swz = (uint32_t)lm << 4;
   const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;
   // ABFT encoder offsets: this lane's part of the warp's 16 A rows, and its (k, g) cells of B
-  const uint32_t e_a_off = TRANS_A ? (uint32_t)lane * (BM * 4) + (uint32_t)warp * 64u
+  const uint32_t e_a_off = TRANS_A ? (uint32_t)(lane >> 2) * (BM * 4) + (uint32_t)warp * 64u + (uint32_t)(lane & 3) * 16u
                                    : (uint32_t)(warp * 16 + lm) * 128u + (uint32_t)((ln ^ lm) << 4);
+  const int ta_k = 8 * (2 * (lane & 1) + ((lane >> 1) & 1)) + (lane >> 2);   // the k whose A sum this lane ends up with
   const uint32_t e_b_off = (uint32_t)(tid >> 3) * BROW + (uint32_t)(tid & 7) * 16u;
   uint64_t chk2[2] = {0ull, 0ull};  // running checksum of block (warp, ln) over this lane's k-range, packed
   bool ok = true;
@@ -322,16 +323,26 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // add -> shuffle -> store chains overlap with FMAs instead of idling the warp.
     auto phase1 = [&]() {
       // ---- phase 1: slab sums ----
-      float aw;  // this lane's entry of the warp's 32 A sums: k = 4*ln + lm, or k = lane for transposed A
+      float aw;  // this lane's entry of the warp's 32 A sums: k = 4*ln + lm, or k = ta_k for transposed A
       if (TRANS_A) {
-        const unsigned char *pa = Ast + e_a_off;  // row k = lane of the [k][BM] stage, the warp's 16 columns
-        const ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(pa);
-        const ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(pa + 16);
-        const ulonglong2 v2 = *reinterpret_cast<const ulonglong2 *>(pa + 32);
-        const ulonglong2 v3 = *reinterpret_cast<const ulonglong2 *>(pa + 48);
-        float lo, hi;
-        unpack2(fadd2(fadd2(fadd2(v0.x, v0.y), fadd2(v1.x, v1.y)), fadd2(fadd2(v2.x, v2.y), fadd2(v3.x, v3.y))), lo, hi);
-        aw = lo + hi;
+        // [k][BM] stage: the warp's 16 columns are 64 bytes of each 512-byte row, always the same 16
+        // banks.  Lane (ksub, c4) = (lane >> 2, lane & 3) reads chunk c4 of rows 8j + ksub (8 rows per
+        // load instead of 32: a quarter of the bank conflicts), then the four chunk lanes fold.
+        const unsigned char *pa = Ast + e_a_off;
+        float p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(pa + j * 8 * (BM * 4));
+          float lo, hi;
+          unpack2(fadd2(v.x, v.y), lo, hi);
+          p[j] = lo + hi;
+        }
+        const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+        float k0 = b0 ? p[2] : p[0], k1 = b0 ? p[3] : p[1];
+        k0 += __shfl_xor_sync(0xffffffffu, b0 ? p[0] : p[2], 1);
+        k1 += __shfl_xor_sync(0xffffffffu, b0 ? p[1] : p[3], 1);
+        aw = b1 ? k1 : k0;
+        aw += __shfl_xor_sync(0xffffffffu, b1 ? k0 : k1, 2);
       } else {
         // rows warp*16 + lm + 4e (e = 0..3), k-chunk ln; rows with (r & 7) >= 4, i.e. odd e, sit in
         // the 16-byte chunk with bit 2 flipped (128-byte swizzle)
@@ -353,7 +364,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         aw += __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
       }
       __syncwarp();  // the previous slab's phase-2 reads of this warp's row are done
-      *reinterpret_cast<float *>(sAw + warp * 128 + (TRANS_A ? lane : (4 * ln + lm)) * 4) = aw;
+      *reinterpret_cast<float *>(sAw + warp * 128 + (TRANS_A ? ta_k : (4 * ln + lm)) * 4) = aw;
       // B: cell (k, g) = sum of the NR columns of column set g in row k; THREADS cells per pass
 #pragma unroll
       for (int pass = 0; pass < 256 / THREADS; ++pass) {
@@ -714,6 +725,35 @@ static int pick_tile(const Context *ctx, int M, int N) {
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
 
+// Y[c][r] = X[r][c] for a rows x cols matrix X (pitch ld) into Y (pitch ldy): 64 x 64 tiles through
+// shared memory, both sides coalesced.
+__global__ void __launch_bounds__(256) transpose_kernel(const float *__restrict__ X, int rows, int cols, int ld,
+                                                        float *__restrict__ Y, int ldy) {
+  __shared__ float t[64][65];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64, tid = threadIdx.x;
+#pragma unroll 4
+  for (int e = tid; e < 64 * 64; e += 256) {
+    const int rr = e >> 6, cc = e & 63;
+    t[rr][cc] = (r0 + rr < rows && c0 + cc < cols) ? __ldcs(X + (size_t)(r0 + rr) * ld + c0 + cc) : 0.f;
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int e = tid; e < 64 * 64; e += 256) {
+    const int cc = e >> 6, rr = e & 63;
+    if (c0 + cc < cols && r0 + rr < ldy) Y[(size_t)(c0 + cc) * ldy + r0 + rr] = t[rr][cc];
+  }
+}
+
+// The FFMA kernels run about 3.5 % faster with the A tile K-major in shared memory (one 128-bit load
+// fetches four rows of one k instead of four k of one row, which frees the inner loop of the
+// component selects).  A row-major A is therefore transposed into the workspace first when the
+// pass pays for itself (it moves 8*M*K bytes; the gain grows with N) and scratch can be had.
+static int g_ffma_transpose_a = 1;
+size_t ffma_workspace_bytes(int M, int N, int K) {
+  if (!g_ffma_transpose_a || N < 2048 || M < 128 || K < 32) return 0;
+  return (size_t)K * (((size_t)M + 3) & ~(size_t)3) * sizeof(float) + 2048;
+}
+
 // trans_a = 0: A is M x K row-major (lda >= K).  trans_a = 1: A is given as K x M row-major
 // (lda >= M), i.e. the column-major M x K operand of the kernel/ft_sgemm family.
 int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
@@ -742,6 +782,27 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
     sgemm_generic_kernel<<<grid, 256, 0, s>>>(M, N, K, alpha, A, trans_a ? 1 : lda, trans_a ? lda : 1, B, ldb, beta, C, ldc);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
+  }
+  if (!trans_a) {
+    const size_t want = ffma_workspace_bytes(M, N, K);
+    const bool fixed_too_small = ctx->ws != nullptr && !ctx->ws_owned && ctx->ws_bytes < want;
+    if (want != 0 && !fixed_too_small) {
+      if (ensure_workspace(ctx, want, s) == B2_OK) {
+        const int mp = (M + 3) & ~3;
+        float *AT = (float *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023);
+        dim3 g((K + 63) / 64, (M + 63) / 64);
+        transpose_kernel<<<g, 256, 0, s>>>(A, M, K, lda, AT, mp);
+        B2_CUDA(cudaGetLastError());
+        if (ft) {
+          FtArgs ft2 = *ft;
+          ft2.A = AT;     // the recomputation reads the operand the kernel used
+          ft2.lda = mp;
+          return sgemm_ffma_dispatch_ft(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, &ft2, s);
+        }
+        return sgemm_ffma_dispatch_ft(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, nullptr, s);
+      }
+      set_error("");   // no scratch to be had: the row-major kernel needs none
+    }
   }
   const FfmaTile &tl = g_tiles[pick_tile(ctx, M, N)];
   CUtensorMap ta, tb;
@@ -889,6 +950,12 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
   return b2_ft_sgemm(nullptr, B2_PATH_FFMA, M, N, K, alpha, A, K, B, N, beta, C, N, nullptr, 0, 0.f, nullptr, nullptr);
 }
 
+// 1 (default): a row-major A is transposed into the workspace first when that pays; 0: never.
+int b2_set_ffma_transpose_a(int on) {
+  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_ffma_transpose_a: %d is not 0 or 1", on);
+  b2::g_ffma_transpose_a = on;
+  return B2_OK;
+}
 // Selects the inner-loop variant of the FFMA kernel (0 scalar FFMA, 1 packed f32x2).  For
 // benchmarking; results are bit-identical.
 int b2_set_ffma_variant(int v) {

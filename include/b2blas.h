@@ -52,7 +52,10 @@ int b2_version(void);
 int b2_create(b2_handle *out);
 int b2_destroy(b2_handle h);
 int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
-/* Bytes of workspace b2_sgemm(path=3xTF32) needs for an MxNxK problem. */
+/* Bytes of workspace an MxNxK problem uses.  path = B2_PATH_3XTF32: required (hi/lo planes of A and B).
+ * path = B2_PATH_FFMA: optional; when that much scratch is there (or the handle may grow its own) a
+ * row-major A is transposed into it first, which makes large products about 3 % faster; 0 when the
+ * pass would not pay.  Results are bit-identical either way. */
 size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K);
 
 /* ---- SGEMM: row-major C = alpha*A*B + beta*C --------------------------------------- */
@@ -211,6 +214,9 @@ int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out
 /* Inner-loop variant of the FFMA SGEMM kernel (0 scalar FFMA, 1 packed f32x2, the default);
  * results are bit-identical, used for benchmarking only. */
 int b2_set_ffma_variant(int v);
+/* 1 (default): the FFMA path may transpose a row-major A into the workspace first (see
+ * b2_sgemm_workspace_bytes); 0: never. */
+int b2_set_ffma_transpose_a(int on);
 /* FFMA tile family (generated table): count, description of tile i, and a pin for the automatic
  * picker (-1 = automatic).  Stands in for the positional kernel ids of kernel/ft_sgemm/sgemm.cu:114-157. */
 int b2_ffma_tile_count(void);

@@ -363,3 +363,49 @@ def test_bounded_wait_times_out_and_context_survives(cuda):
     a, b, c = mats(128, 128, 64)
     assert np.array_equal(run_gpu(0, a, b, c, 1.0, 0.5), oracle.sgemm_fma(1.0, a, b, 0.5, c))
     assert L.b2_selftest_wait_timeout(h.raw, 0, None) == -1
+
+
+@pytest.mark.parametrize("shape", [(128, 2048, 32), (130, 2052, 70), (257, 2304, 129), (1024, 3072, 512)])
+def test_ffma_transposed_a_route_is_bit_identical(cuda, shape):
+    """With scratch available the FFMA path first transposes a row-major A (K-major A tiles are faster); every output
+    still sums its k in the same order, so the result is bit-identical to the direct route and to the oracle."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    assert b2.sgemm_workspace_bytes(0, M, N, K) > 0
+    a, b, c = mats(M, N, K)
+    out = {}
+    try:
+        for mode in (1, 0):
+            b2.set_ffma_transpose_a(mode)
+            out[mode] = run_gpu(0, a, b, c, -1.5, 0.5)
+    finally:
+        b2.set_ffma_transpose_a(1)
+    assert np.array_equal(out[1], out[0])
+    if M * N * K <= 130 * 2052 * 70:
+        assert np.array_equal(out[1], oracle.sgemm_fma(-1.5, a, b, 0.5, c))
+
+
+def test_ffma_transposed_a_route_needs_no_workspace(cuda):
+    """A caller-supplied workspace that is too small is not an error for the FFMA path: the direct kernel runs."""
+    import ctypes as C
+    import hpcdeepneuralnetworks_b200 as b2
+    from hpcdeepneuralnetworks_b200 import _lib
+    L = _lib.load()
+    M, N, K = 256, 2048, 64
+    a, b, c = mats(M, N, K)
+    h = C.c_void_p()
+    assert L.b2_create(C.byref(h)) == 0
+    small = torch.empty(4096, dtype=torch.uint8, device="cuda")
+    base = (small.data_ptr() + 1023) & ~1023
+    try:
+        assert L.b2_set_workspace(h, C.c_void_p(base), 1024) == 0
+        da, db, dc = dev(a), dev(b), dev(c)
+        torch.cuda.synchronize()
+        st = L.b2_sgemm(h, 0, M, N, K, 1.0, C.c_void_p(da.data_ptr()), K, C.c_void_p(db.data_ptr()), N, 0.5,
+                        C.c_void_p(dc.data_ptr()), N, None)
+        assert st == 0, L.b2_last_error()
+        torch.cuda.synchronize()
+        assert np.array_equal(dc.cpu().numpy(), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    finally:
+        L.b2_set_workspace(h, None, 0)
+        L.b2_destroy(h)
