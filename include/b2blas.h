@@ -48,7 +48,10 @@ int b2_version(void);
 /* A handle owns per-device scratch (SDOT block partials, 3xTF32 split planes, ABFT
  * report words).  b2_create allocates a small fixed scratch with cudaMalloc on the
  * current device; larger scratch is either grown on demand (cudaMalloc, synchronising)
- * or supplied by the caller with b2_set_workspace (no allocation inside the library). */
+ * or supplied by the caller with b2_set_workspace (no allocation inside the library).
+ * The scratch is shared by every call made on the handle: calls on one handle must be ordered
+ * on one stream (or otherwise serialised); work on several streams takes one handle per stream.
+ * A NULL handle means a default handle per device, with the same rule. */
 int b2_create(b2_handle *out);
 int b2_destroy(b2_handle h);
 int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
