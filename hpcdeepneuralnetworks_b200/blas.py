@@ -378,6 +378,11 @@ def sgemm_workspace_bytes(path: int, M: int, N: int, K: int) -> int:
     return int(_lib.load().b2_sgemm_workspace_bytes(path, M, N, K))
 
 
+def set_ft_level(level: int):
+    """ABFT encode granularity of the FFMA path: 1 block-level (default), 2 thread-level (128 x 128 tile)."""
+    check(_lib.load().b2_set_ft_level(level))
+
+
 def set_ffma_transpose_a(on: int):
     """1 (default): the FFMA path may transpose a row-major A into the workspace first; 0: never."""
     check(_lib.load().b2_set_ffma_transpose_a(on))

@@ -205,7 +205,22 @@ __device__ __forceinline__ int acc_row(int warp, int lm, int i) {
 }
 __device__ __forceinline__ int acc_col(int ln, int j) { return ln * 4 + 32 * (j >> 2) + (j & 3); }
 
-template <int BM, int NR, bool PACKED, bool TRANS_A, bool FT>
+// Thread-level encode (the idea of the reference's ft_sgemm_huge_thread, kernel/ft_sgemm/include/
+// ft_sgemm_huge_thread.cuh:37): every thread keeps the checksum of its own 4 x NR outputs,
+// chk += (sum of its 4 A values) * (sum of its NR B values) at every k, all in registers -- no
+// shared-memory encoder, no extra barrier, but about 13 more instructions per k beside the 32
+// packed FMAs.  Kept as a measured alternative to the block-level encoder (FT = 1).
+template <int NR>
+__device__ __forceinline__ float thread_checksum_step(const float (&a)[4], const float4 (&b)[NR / 4], float chk) {
+  uint64_t s2 = fadd2(pack2(b[0].x, b[0].y), pack2(b[0].z, b[0].w));
+#pragma unroll
+  for (int q = 1; q < NR / 4; ++q) s2 = fadd2(s2, fadd2(pack2(b[q].x, b[q].y), pack2(b[q].z, b[q].w)));
+  float lo, hi;
+  unpack2(s2, lo, hi);
+  return __fmaf_rn((a[0] + a[1]) + (a[2] + a[3]), lo + hi, chk);
+}
+
+template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
 __global__ void __launch_bounds__(TileCfg<BM, NR>::THREADS, TileCfg<BM, NR>::MIN_BLOCKS)
 sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FfmaArgs p,
                   const FtArgs ft) {
@@ -246,7 +261,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int s = 0; s < FSTAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], WARPS);
-      if (FT) mbar_init(&sums_ready[s], WARPS);
+      if (FT == 1) mbar_init(&sums_ready[s], WARPS);
     }
     if (FT) *nflag = 0;
     mbar_fence_init();
@@ -307,6 +322,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int ta_k = 8 * (2 * (lane & 1) + ((lane >> 1) & 1)) + (lane >> 2);   // the k whose A sum this lane ends up with
   const uint32_t e_b_off = (uint32_t)(tid >> 3) * BROW + (uint32_t)(tid & 7) * 16u;
   uint64_t chk2[2] = {0ull, 0ull};  // running checksum of block (warp, ln) over this lane's k-range, packed
+  float tchk = 0.f;                 // FT = 2: running checksum of this thread's own 4 x NR outputs
   bool ok = true;
 
   for (int kb = 0; kb < nkb; ++kb) {
@@ -411,20 +427,21 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (TRANS_A) {
 #pragma unroll
       for (int k = 0; k < FBK; ++k) {
-        if (FT && k == 4 && kb > 0 && !phase2(sprev, pprev)) ok = false;
-        if (FT && k == 8) phase1();
+        if (FT == 1 && k == 4 && kb > 0 && !phase2(sprev, pprev)) ok = false;
+        if (FT == 1 && k == 8) phase1();
         const float4 a4 = *reinterpret_cast<const float4 *>(As + k * (BM * 4));
         float4 b[NR / 4];
 #pragma unroll
         for (int q = 0; q < NR / 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + k * BROW + q * 128);
         const float a[4] = {a4.x, a4.y, a4.z, a4.w};
         acc.step(a, b);
+        if (FT == 2) tchk = thread_checksum_step<NR>(a, b, tchk);
       }
     } else {
 #pragma unroll
       for (int kc = 0; kc < FBK / 4; ++kc) {
-        if (FT && kc == 1 && kb > 0 && !phase2(sprev, pprev)) ok = false;
-        if (FT && kc == 2) phase1();
+        if (FT == 1 && kc == 1 && kb > 0 && !phase2(sprev, pprev)) ok = false;
+        if (FT == 1 && kc == 2) phase1();
         const uint32_t y0 = ((uint32_t)kc << 4) ^ a_swz, y1 = y0 ^ 64u;
         float4 a4[4];
 #pragma unroll
@@ -439,6 +456,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 4; ++i) a[i] = (kk == 0) ? a4[i].x : (kk == 1) ? a4[i].y : (kk == 2) ? a4[i].z : a4[i].w;
           acc.step(a, b);
+          if (FT == 2) tchk = thread_checksum_step<NR>(a, b, tchk);
         }
       }
     }
@@ -475,7 +493,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   }
-  if (FT && ok && nkb > 0) {
+  if (FT == 1 && ok && nkb > 0) {
     // the last slab's sums have not been folded yet
     const int ps = (nkb - 1) % FSTAGES;
     if (mbar_wait(&sums_ready[ps], (uint32_t)((nkb - 1) / FSTAGES) & 1u)) {
@@ -501,7 +519,9 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (FT) {
     // ---- verify in registers, then recompute the blocks that are out of tolerance ----
     float expect, actual = acc.total();
-    {
+    if (FT == 2) {
+      expect = tchk;
+    } else {
       float c0, c1, c2, c3;
       unpack2(chk2[0], c0, c1);
       unpack2(chk2[1], c2, c3);
@@ -663,7 +683,7 @@ static int ffma_variant() {
   return g_ffma_variant;
 }
 
-template <int BM, int NR, bool PACKED, bool TRANS_A, bool FT>
+template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
 static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s,
                        const FtArgs &ft) {
   using Cfg = TileCfg<BM, NR>;
@@ -748,6 +768,7 @@ __global__ void __launch_bounds__(256) transpose_kernel(const float *__restrict_
 // fetches four rows of one k instead of four k of one row, which frees the inner loop of the
 // component selects).  A row-major A is therefore transposed into the workspace first when the
 // pass pays for itself (it moves 8*M*K bytes; the gain grows with N) and scratch can be had.
+static int g_ft_level = 1;   // ABFT encode granularity of the FFMA path: 1 block (16 x NR per warp slice), 2 thread
 static int g_ffma_transpose_a = 1;
 size_t ffma_workspace_bytes(int M, int N, int K) {
   if (!g_ffma_transpose_a || N < 2048 || M < 128 || K < 32) return 0;
@@ -818,6 +839,9 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   const int grid = ((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
   FtArgs none = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, 0, 0};
   const int packed = (ft != nullptr || ffma_variant() != 0) ? 1 : 0;
+  if (ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128)   // thread-level encode: built for the 128 x 128 tile only
+    return trans_a ? launch_ffma<128, 16, true, true, 2>(ta, tb, args, grid, s, *ft)
+                   : launch_ffma<128, 16, true, false, 2>(ta, tb, args, grid, s, *ft);
   return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, args, grid, s, ft ? *ft : none);
 }
 
@@ -950,6 +974,13 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
   return b2_ft_sgemm(nullptr, B2_PATH_FFMA, M, N, K, alpha, A, K, B, N, beta, C, N, nullptr, 0, 0.f, nullptr, nullptr);
 }
 
+// ABFT encode granularity of the FFMA path: 1 block-level through shared memory (default), 2 thread-level in
+// registers (128 x 128 tile only; other tiles keep the block-level encoder).
+int b2_set_ft_level(int level) {
+  B2_REQUIRE(level == 1 || level == 2, B2_ERR_INVALID_ARG, "b2_set_ft_level: %d is not 1 or 2", level);
+  b2::g_ft_level = level;
+  return B2_OK;
+}
 // 1 (default): a row-major A is transposed into the workspace first when that pays; 0: never.
 int b2_set_ffma_transpose_a(int on) {
   B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_ffma_transpose_a: %d is not 0 or 1", on);

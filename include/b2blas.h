@@ -217,6 +217,11 @@ int b2_ffma2_peak_probe(int launches, int64_t ffma_per_thread, double *flops_out
 /* Inner-loop variant of the FFMA SGEMM kernel (0 scalar FFMA, 1 packed f32x2, the default);
  * results are bit-identical, used for benchmarking only. */
 int b2_set_ffma_variant(int v);
+/* ABFT encode granularity of the FFMA path: 1 (default) block-level, the checksums of a warp's 16 x 16 blocks formed
+ * through shared memory beside the FMAs; 2 thread-level, every thread keeps the checksum of its own outputs in
+ * registers (kernel/ft_sgemm/include/ft_sgemm_huge_thread.cuh:37; 128x128 tile only).  Detection, location and
+ * correction are the same. */
+int b2_set_ft_level(int level);
 /* 1 (default): the FFMA path may transpose a row-major A into the workspace first (see
  * b2_sgemm_workspace_bytes); 0: never. */
 int b2_set_ffma_transpose_a(int on);

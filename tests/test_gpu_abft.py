@@ -318,3 +318,39 @@ def test_scale_aware_threshold(cuda, path, sa, sb):
         assert r["false_alarms"] + r["detected"] > 0
         if path == 0:
             assert r["corrected"] == 0 and torch.equal(out, plain)      # recomputation is bit-exact on the FFMA path
+
+
+@pytest.mark.parametrize("transpose_a", [0, 1])
+def test_thread_level_encoder(cuda, transpose_a):
+    """The thread-level encoder (every thread checks its own 4 x 16 outputs, the reference's ft_sgemm_huge_thread idea)
+    finds and repairs the same faults as the block-level one, bit-identically, with no false alarm."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 1024
+    M, N, K = 512, 2048, 1024           # N >= 2048: the K-major route is eligible when transpose_a = 1
+    a, b, c = mats(M, N, K)
+    want = oracle.sgemm_fma(1.0, a, b, 0.5, c)
+    plan = oracle.make_fault_plan(M, N, K, seed=9, tiles_per_fault=4, bit_lo=25, bit_hi=30)
+    tau = default_tau(K)
+    must, gray, benign = classify(a, b, plan, tau)
+    try:
+        b2.set_ft_level(2)
+        b2.set_ffma_transpose_a(transpose_a)
+        rep = b2.new_report()
+        dc = dev(c)
+        b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert (r["tiles"], r["injected"], r["detected"], r["corrected"], r["false_alarms"]) == (64, 0, 0, 0, 0)
+        assert np.array_equal(dc.cpu().numpy(), want)
+        rep = b2.new_report()
+        dc = dev(c)
+        b2.ft_sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dc, plan=b2.make_plan(plan), report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert r["injected"] == len(plan) and r["false_alarms"] == 0
+        assert must <= r["corrected"] <= must + gray
+        if gray == 0 and benign == 0:
+            assert np.array_equal(dc.cpu().numpy(), want)
+    finally:
+        b2.set_ft_level(1)
+        b2.set_ffma_transpose_a(1)
