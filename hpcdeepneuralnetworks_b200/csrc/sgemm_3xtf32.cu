@@ -7,16 +7,22 @@
 // Three tcgen05.mma.kind::tf32 per K-step accumulate into one FP32 accumulator tile in TMEM,
 // small terms first.
 //
-// Two kernels:
-//   split_planes_kernel   one pass over A and B writing the hi/lo planes (low 13 mantissa
-//   split_planes_t_kernel bits already zero, so the tensor core's own treatment of them is
-//                         irrelevant) into the workspace.  B is written transposed (N x K) so
-//                         that both operands are K-major under the 128-byte swizzle.
-//   sgemm_3xtf32_kernel   one 128 x 256 (or 128 x 128) output tile per CTA, K-slabs of 32; warp 0 = TMA
-//                         producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
-//                         epilogue (tcgen05.ld -> alpha/beta -> global).  2-stage ring of
-//                         96 KB (A_hi, A_lo: 128x32; B_hi, B_lo: 256x32), all tiles under the
-//                         128-byte swizzle.
+// Kernels:
+//   split_planes_kernel      one pass over A and B writing the hi/lo planes (low 13 mantissa
+//   split_planes_t_kernel    bits already zero, so the tensor core's own treatment of them is
+//                            irrelevant) into the workspace.  B is written transposed (N x K) so
+//                            that both operands are K-major under the 128-byte swizzle.
+//   sgemm_3xtf32_kernel      one 128 x 256 (or 128 x 128) output tile per CTA, K-slabs of 32; warp 0 =
+//                            TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
+//                            epilogue (tcgen05.ld -> alpha/beta -> global).  2-stage ring of
+//                            96 KB (A_hi, A_lo: 128x32; B_hi, B_lo: 256x32), all tiles under the
+//                            128-byte swizzle.
+//   sgemm_3xtf32_pair_kernel one 256 x 256 tile per cluster of two CTAs (tcgen05 cta_group::2): each CTA
+//                            stages half of the A rows and half of the B columns (64 KB per slab, 3
+//                            stages), the leader issues MMAs of M = 256 over both CTAs' tiles.  The
+//                            form chosen for large problems; same warp roles, same epilogue.
+// Both GEMM kernels have ABFT forms (template FT: checksums on the tensor cores or on the CUDA
+// cores, verification and repair in the shared epilogue).
 // Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
 #include <math.h>
 #include <stdlib.h>
