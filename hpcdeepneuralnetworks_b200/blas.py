@@ -194,20 +194,23 @@ def sdot_partial(n, x, y, out, partial64, handle=None):
 class HostSgemm:
     """Row-major SGEMM on HOST arrays: pinned staging buffers, device buffers and a three-stream pipeline.
 
-    The work is cut into blocks (row panel p of A and C) x (K panel q: columns of A, rows of B), all of them
-    contiguous pieces of the host arrays.  ``run`` sends row panels and K panels alternately over PCIe, so that
-    after i row panels and j K panels i*j blocks are computable; each block is one GEMM call of the library
-    (rows_p x N x K_q, accumulating into C_p with beta on the first K panel and 1 afterwards), issued as soon as
-    both of its panels have landed; a row panel of C travels back on a third stream when its last block is done.
-    Transfers in both directions overlap the kernels.  With a single K panel the result is bit-identical to one
-    call; with several, each output is the sum of per-panel partial sums (same tolerance, different rounding)."""
+    Default schedule (one K panel, bit-identical to a single call): C is cut into row panels; B has to be on the
+    device before any full-width row panel can be computed, so the FIRST row panel is cut further into column
+    panels and computed tile by tile while the column panels of B (and of C) arrive -- pitched copies through
+    ``b2_copy_matrix_async`` -- and the following row panels are one full-width GEMM each, issued as soon as their
+    rows of A and C have landed; a row panel of C travels back on a third stream when it is done.  Transfers in
+    both directions overlap the kernels.  ``panel_rows`` defaults to 1536: a 1536 x 6144 panel is 576 tiles of
+    128 x 128, 1.95 waves of the 296 resident CTAs, where 1024 rows would leave the second wave a third full.
 
-    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=1024, panel_k=0):
+    With ``panel_k > 0`` the second cut is along K instead (rows of B, contiguous): row panels and K panels are sent
+    alternately and block (p, q) accumulates into C_p with beta on the first K panel and 1 afterwards; each output
+    is then a sum of per-panel partial sums (same tolerance, different rounding)."""
+
+    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=1536, panel_k=0, panel_cols=1536):
         self.M, self.N, self.K, self.path = M, N, K, path
         self.pr = M if M < 128 else max(128, (min(panel_rows, M) + 127) // 128 * 128)
-        # panel_k = 0: one K panel (bit-identical to a single call; measured within 7 % of the best split at 6144^3,
-        # where the step is bound by the PCIe transfers at ~35 GB/s, not by the kernels)
         self.pk = K if (K < 128 or panel_k <= 0) else max(128, (min(panel_k, K) + 127) // 128 * 128)
+        self.pc = N if N < 256 else max(128, (min(panel_cols, N) + 127) // 128 * 128)
         self.hA = torch.empty((M, K), dtype=torch.float32).pin_memory()
         self.hB = torch.empty((K, N), dtype=torch.float32).pin_memory()
         self.hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
@@ -223,17 +226,73 @@ class HostSgemm:
     def d2h_bytes(self):
         return 4 * self.M * self.N
 
+    def _copy_cols(self, dst, src, ld, r0, r1, c0, c1, direction, stream):
+        """Pitched copy of rows r0..r1, columns c0..c1 of an (x, ld) matrix between its host and device copies."""
+        off = (r0 * ld + c0) * 4
+        check(_lib.load().b2_copy_matrix_async(C.c_void_p(dst.data_ptr() + off), ld, C.c_void_p(src.data_ptr() + off), ld,
+                                               r1 - r0, c1 - c0, direction, C.c_void_p(stream.cuda_stream)))
+
     def run(self, alpha, beta, ft=False):
         """hC <- alpha*hA*hB + beta*hC through the device; returns hC (pinned) after everything has landed."""
+        if self.pk < self.K:
+            return self._run_k_panels(alpha, beta, ft)
         compute = torch.cuda.current_stream()
         h2d, d2h = self._h2d, self._d2h
         h2d.wait_stream(compute)          # earlier work on the device buffers is finished
         d2h.wait_stream(compute)
         M, N, K = self.M, self.N, self.K
         rows = [(r0, min(M, r0 + self.pr)) for r0 in range(0, max(M, 1), max(self.pr, 1))]
+        cols = [(c0, min(N, c0 + self.pc)) for c0 in range(0, max(N, 1), max(self.pc, 1))]
+        L = _lib.load()
+        # scratch sized once, outside the pipeline (growing it would synchronise the device)
+        default_handle().reserve(max(L.b2_sgemm_workspace_bytes(self.path, r1 - r0, N, K) for r0, r1 in rows))
+        fn = ft_sgemm if ft else sgemm
+
+        def send_rows(p, with_c):
+            r0, r1 = rows[p]
+            with torch.cuda.stream(h2d):
+                self.dA[r0:r1].copy_(self.hA[r0:r1], non_blocking=True)
+                if with_c and beta != 0.0:
+                    self.dC[r0:r1].copy_(self.hC[r0:r1], non_blocking=True)
+                return h2d.record_event()
+
+        def back(p):
+            r0, r1 = rows[p]
+            ev = compute.record_event()
+            d2h.wait_event(ev)
+            with torch.cuda.stream(d2h):
+                self.hC[r0:r1].copy_(self.dC[r0:r1], non_blocking=True)
+
+        # first row panel: tile by tile behind the column panels of B
+        r0, r1 = rows[0]
+        compute.wait_event(send_rows(0, with_c=False))
+        for c0, c1 in cols:
+            self._copy_cols(self.dB, self.hB, N, 0, K, c0, c1, 1, h2d)
+            if beta != 0.0:
+                self._copy_cols(self.dC, self.hC, N, r0, r1, c0, c1, 1, h2d)
+            compute.wait_event(h2d.record_event())
+            fn(r1 - r0, c1 - c0, K, alpha, self.dA[r0:r1], self.dB[:, c0:c1], beta, self.dC[r0:r1, c0:c1], path=self.path,
+               lda=K, ldb=N, ldc=N)
+        back(0)
+        # the other row panels: one full-width GEMM each
+        for p in range(1, len(rows)):
+            r0, r1 = rows[p]
+            compute.wait_event(send_rows(p, with_c=True))
+            fn(r1 - r0, N, K, alpha, self.dA[r0:r1], self.dB, beta, self.dC[r0:r1], path=self.path, lda=K, ldb=N, ldc=N)
+            back(p)
+        compute.wait_stream(d2h)
+        compute.synchronize()
+        return self.hC
+
+    def _run_k_panels(self, alpha, beta, ft=False):
+        compute = torch.cuda.current_stream()
+        h2d, d2h = self._h2d, self._d2h
+        h2d.wait_stream(compute)
+        d2h.wait_stream(compute)
+        M, N, K = self.M, self.N, self.K
+        rows = [(r0, min(M, r0 + self.pr)) for r0 in range(0, max(M, 1), max(self.pr, 1))]
         kps = [(k0, min(K, k0 + self.pk)) for k0 in range(0, max(K, 1), max(self.pk, 1))]
-        if self.path == PATH_3XTF32:      # sized once, outside the pipeline
-            default_handle().reserve(_lib.load().b2_sgemm_workspace_bytes(self.path, self.pr, N, self.pk))
+        default_handle().reserve(_lib.load().b2_sgemm_workspace_bytes(self.path, self.pr, N, self.pk))
         fn = ft_sgemm if ft else sgemm
         row_ev, k_ev = {}, {}
         blocks_done = {p: 0 for p in range(len(rows))}   # K panels already folded into row panel p, in order

@@ -379,6 +379,19 @@ int b2_fill_uniform_host(float *host, int64_t n, uint64_t seed) {
   return B2_OK;
 }
 
+int b2_copy_matrix_async(float *dst, int64_t ld_dst, const float *src, int64_t ld_src, int64_t rows, int64_t cols,
+                         int direction, void *stream) {
+  B2_REQUIRE(rows >= 0 && cols >= 0 && ld_dst >= cols && ld_src >= cols, B2_ERR_INVALID_ARG,
+             "b2_copy_matrix_async: bad shape (rows=%lld cols=%lld ld_dst=%lld ld_src=%lld)", (long long)rows, (long long)cols,
+             (long long)ld_dst, (long long)ld_src);
+  B2_REQUIRE(direction == 1 || direction == 2, B2_ERR_INVALID_ARG, "b2_copy_matrix_async: direction %d is not 1 or 2", direction);
+  if (rows == 0 || cols == 0) return B2_OK;
+  B2_REQUIRE(dst != nullptr && src != nullptr, B2_ERR_INVALID_ARG, "b2_copy_matrix_async: null pointer");
+  B2_CUDA(cudaMemcpy2DAsync(dst, (size_t)ld_dst * sizeof(float), src, (size_t)ld_src * sizeof(float), (size_t)cols * sizeof(float),
+                            (size_t)rows, direction == 1 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return B2_OK;
+}
+
 int b2_fill_const(float *dev, int64_t n, float value, void *stream) {
   B2_REQUIRE(n >= 0 && (n == 0 || dev != nullptr), B2_ERR_INVALID_ARG, "b2_fill_const: bad arguments");
   if (n == 0) return B2_OK;

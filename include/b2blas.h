@@ -191,6 +191,13 @@ int b2_fill_uniform(float *dev, int64_t n, uint64_t seed, void *stream);
 int b2_fill_uniform_host(float *host, int64_t n, uint64_t seed);
 /* fill_vector (utils/utils.cu:15-19) on the device. */
 int b2_fill_const(float *dev, int64_t n, float value, void *stream);
+/* copy_matrix (utils/utils.cu:46-54) between host and device for a rectangular piece of a pitched matrix:
+ * `rows` rows of `cols` floats, source pitch `ld_src` and destination pitch `ld_dst` in floats.
+ * direction: 1 host -> device, 2 device -> host.  Asynchronous on `stream` when the host side is pinned.
+ * The drivers copy whole matrices with cudaMemcpy (kernel/sgemm/sgemm.cu:60-63); the host-buffer pipeline
+ * needs column panels. */
+int b2_copy_matrix_async(float *dst, int64_t ld_dst, const float *src, int64_t ld_src, int64_t rows, int64_t cols,
+                         int direction, void *stream);
 
 /* verify_matrix (utils/utils.cu:75-91): first element with |ref-got| > abs_tol fails.
  * Device-side compare; returns 0 if all pass, 1 if any fail, <0 on error, and writes the

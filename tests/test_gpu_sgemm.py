@@ -346,6 +346,31 @@ def test_host_buffer_api(cuda, shape, panel, panel_k, beta):
     assert np.array_equal(out2, out)
 
 
+@pytest.mark.parametrize("shape,panel,panel_cols", [((300, 520, 96), 128, 128), ((1600, 700, 64), 512, 256), ((130, 2100, 40), 128, 1024),
+                                                    ((256, 300, 72), 1536, 1536)])
+@pytest.mark.parametrize("beta", [0.5, 0.0])
+@pytest.mark.parametrize("path", [0, 1])
+def test_host_buffer_api_column_panels(cuda, shape, panel, panel_cols, beta, path):
+    """The default schedule of the host-buffer pipeline: the first row panel is computed in column tiles behind the
+    pitched copies of B's column panels, the others full width.  Every output still sums all of K in one call, so the
+    FFMA result is bit-identical to the oracle's single call whatever the panel sizes."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    hs = b2.HostSgemm(M, N, K, path=path, panel_rows=panel, panel_cols=panel_cols)
+    hs.hA.copy_(torch.from_numpy(a)); hs.hB.copy_(torch.from_numpy(b)); hs.hC.copy_(torch.from_numpy(c))
+    out = hs.run(-1.5, beta).numpy().copy()
+    c64, den = oracle.sgemm_f64(-1.5, a, b, beta, c)
+    if path == 0:
+        assert np.array_equal(out, oracle.sgemm_fma(-1.5, a, b, beta, c))
+        assert oracle.gemm_error(out, c64, den) <= TOL_FFMA
+    else:
+        assert oracle.gemm_error(out, c64, den) <= TOL_3XTF32
+    hs.hC.copy_(torch.from_numpy(c))
+    out2 = hs.run(-1.5, beta).numpy()                                 # the buffers are reusable
+    assert np.array_equal(out2, out)
+
+
 def test_bounded_wait_times_out_and_context_survives(cuda):
     """A device-side wait that nothing satisfies gives up after its limit, the host reads B2_ERR_TIMEOUT, and the
     next launches run normally (no trap, no hang, no lost context)."""
