@@ -552,6 +552,18 @@ def run_multi(args):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dot = float(t.item())
 
+    # the same with the cross-GPU sum inside the kernel (peer stores over NVLink, no collective call)
+    ms_fused, fused_error = None, None
+    try:
+        fused = b2dist.FusedSdot(torch.device("cuda", local))
+        ms_fused_local = timed(lambda: fused(nloc, x, y), max(5, args.steps), 3, dist_barrier=barrier)
+        b2.check_status()
+        t = torch.tensor([ms_fused_local], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_fused = float(t.item())
+    except Exception as e:   # reported below, never hidden
+        fused_error = f"{type(e).__name__}: {e}"
+
     if rank == 0:
         ffma_peak = b2.ffma_peak_tflops()
         peaks = load_peaks()
@@ -575,7 +587,10 @@ def run_multi(args):
             "clocks": clk.summary(),
             "abft_report": (b2.read_report(report) if args.abft else None),
             "extra": {"sdot_sharded": {"n_total": nloc * world, "ms": ms_dot, "value": 8.0 * nloc * world / (ms_dot * 1e-3) / 1e9,
-                                       "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_dot * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
+                                       "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_dot * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+                      "sdot_sharded_fused": ({"n_total": nloc * world, "ms": ms_fused, "value": 8.0 * nloc * world / (ms_fused * 1e-3) / 1e9,
+                                              "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_fused * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+                                             if ms_fused else {"error": fused_error})},
         }
         print(json.dumps(line))
     dist.barrier()

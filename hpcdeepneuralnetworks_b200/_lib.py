@@ -84,6 +84,7 @@ def load() -> C.CDLL:
     L.b2_fill_uniform.argtypes = [vp, i64, u64, vp]
     L.b2_fill_uniform_host.argtypes = [vp, i64, u64]
     L.b2_fill_const.argtypes = [vp, i64, f32, vp]
+    L.b2_sdot_fused.argtypes = [vp, i64, vp, vp, vp, vp, C.POINTER(vp), i32, i32, u64, vp]
     L.b2_copy_matrix_async.argtypes = [vp, i64, vp, i64, i64, i64, i32, vp]
     L.b2_verify_matrix.argtypes = [vp, vp, i64, i64, i64, f32, C.POINTER(f32), vp]
     L.b2_timer_create.argtypes = [C.POINTER(vp)]

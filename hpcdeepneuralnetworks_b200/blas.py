@@ -176,6 +176,19 @@ def sdot(n, x, y, out=None, handle=None):
     return out
 
 
+def sdot_fused(n, x, y, mailboxes, rank, world, seq, out=None, sum64=None, handle=None):
+    """x . y summed over all ranks inside the kernel (``b2_sdot_fused``).  ``mailboxes``: list of the ``world`` device
+    addresses (ints) of the ranks' 512-byte mailboxes.  Returns (float32 result tensor, float64 sum tensor)."""
+    h = handle or default_handle()
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    if sum64 is None:
+        sum64 = torch.empty(1, dtype=torch.float64, device=x.device)
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in mailboxes])
+    check(_lib.load().b2_sdot_fused(h.raw, n, _ptr(x), _ptr(y), _ptr(out), _ptr(sum64), arr, rank, world, seq, _stream()))
+    return out, sum64
+
+
 def sdot_static(n, x, y, out):
     """out[0] <- x . y through the entry point that allocates nothing (``b2_sdot_static``): no handle, scratch in
     the library's own static device array, n <= 2**30.  ``out`` must be an existing 1-element device tensor."""

@@ -85,8 +85,65 @@ __device__ __forceinline__ double warp_sum(double v) {
   return v;
 }
 
+// ---- SDOT fused with its cross-GPU sum ---------------------------------------------------
+// One process per GPU; every rank owns a 512-byte mailbox that all ranks can address (peer
+// memory over NVLink): double data[2][16] (two epochs x one slot per rank) and, 256 bytes in,
+// unsigned long long flag[16].  The last block of rank r stores its partial sum into slot r of
+// every rank's mailbox, then the call's sequence number into flag r of every rank; it then waits
+// (bounded) until its own flags of all ranks have reached that number and adds the slots in rank
+// order, so every rank ends with the same bits.  Two epochs are enough: a rank can run at most one
+// call ahead of the slowest one, because finishing a call needs everybody's flag of that call.
+constexpr int kSdotMaxRanks = 16;
+struct SdotPeers {
+  unsigned char *buf[kSdotMaxRanks];
+  int rank, world;
+  unsigned long long seq;
+  int *status;
+};
+__device__ __forceinline__ void st_relaxed_sys_f64(double *p, double v) {
+  asm volatile("st.relaxed.sys.global.f64 [%0], %1;" ::"l"(p), "d"(v) : "memory");
+}
+__device__ __forceinline__ double ld_relaxed_sys_f64(const double *p) {
+  double v;
+  asm volatile("ld.relaxed.sys.global.f64 %0, [%1];" : "=d"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The exchange itself, run by one thread: returns the sum over all ranks (this rank's own sum and a TIMEOUT
+// status if a peer does not show up within a second).
+__device__ __forceinline__ double sdot_exchange(double mine, const SdotPeers &pr) {
+  const int slot = (int)(pr.seq & 1ull);
+  for (int p = 0; p < pr.world; ++p)
+    st_relaxed_sys_f64(reinterpret_cast<double *>(pr.buf[p]) + slot * kSdotMaxRanks + pr.rank, mine);
+  __threadfence_system();
+  for (int p = 0; p < pr.world; ++p)
+    st_release_sys_u64(reinterpret_cast<unsigned long long *>(pr.buf[p] + 256) + pr.rank, pr.seq);
+  const unsigned long long *flags = reinterpret_cast<const unsigned long long *>(pr.buf[pr.rank] + 256);
+  const double *data = reinterpret_cast<const double *>(pr.buf[pr.rank]) + slot * kSdotMaxRanks;
+  const uint64_t t0 = global_timer_ns();
+  double total = 0.0;
+  for (int p = 0; p < pr.world; ++p) {
+    while (ld_acquire_sys_u64(flags + p) < pr.seq) {
+      if (global_timer_ns() - t0 > 1000000000ull) {
+        atomicExch(pr.status, (int)B2_ERR_TIMEOUT);
+        return mine;
+      }
+    }
+    total += ld_relaxed_sys_f64(data + p);
+  }
+  return total;
+}
+
 __device__ __forceinline__ void sdot_finish(double thread_sum, double *partials, unsigned int *ticket,
-                                            float *result, double *result64) {
+                                            float *result, double *result64, const SdotPeers *peers = nullptr) {
   __shared__ double warp_part[kVecThreads / 32];
   __shared__ bool is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -114,6 +171,7 @@ __device__ __forceinline__ void sdot_finish(double thread_sum, double *partials,
       double tot = 0.0;
 #pragma unroll
       for (int i = 0; i < kVecThreads / 32; ++i) tot += warp_part[i];
+      if (peers) tot = sdot_exchange(tot, *peers);   // the sum over all GPUs instead of this one's
       *result = (float)tot;
       if (result64) *result64 = tot;
       *ticket = 0u;  // re-arm for the next launch on this scratch
@@ -170,6 +228,14 @@ __global__ void __launch_bounds__(kVecThreads) sdot_kernel(int64_t n, const floa
                                                            const float *__restrict__ y, double *partials,
                                                            unsigned int *ticket, float *result, double *result64) {
   sdot_finish(sdot_thread_sum<ALIGNED>(n, x, y), partials, ticket, result, result64);
+}
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(kVecThreads) sdot_fused_kernel(int64_t n, const float *__restrict__ x,
+                                                                 const float *__restrict__ y, double *partials,
+                                                                 unsigned int *ticket, float *result, double *result64,
+                                                                 const SdotPeers peers) {
+  sdot_finish(sdot_thread_sum<ALIGNED>(n, x, y), partials, ticket, result, result64, &peers);
 }
 
 // ---- SDOT without any allocation ---------------------------------------------------------
@@ -314,6 +380,38 @@ int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, floa
 
 int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, void *stream) {
   return b2_sdot_partial(h, n, x, y, result_dev, nullptr, stream);
+}
+
+int b2_sdot_fused(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, double *sum_dev,
+                  void *const *mailboxes, int rank, int world, uint64_t seq, void *stream) {
+  Context *ctx = h ? (Context *)h : default_context();
+  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_sdot_fused: no context (%s)", b2_last_error());
+  B2_REQUIRE(n >= 0 && result_dev != nullptr, B2_ERR_INVALID_ARG, "b2_sdot_fused: bad arguments");
+  B2_REQUIRE(n == 0 || (x != nullptr && y != nullptr), B2_ERR_INVALID_ARG, "b2_sdot_fused: null vector");
+  B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_sdot_fused: vectors must be 4-byte aligned");
+  B2_REQUIRE(world >= 1 && world <= kSdotMaxRanks && rank >= 0 && rank < world, B2_ERR_INVALID_ARG,
+             "b2_sdot_fused: rank %d of %d (at most %d ranks)", rank, world, kSdotMaxRanks);
+  B2_REQUIRE(seq >= 1 && mailboxes != nullptr, B2_ERR_INVALID_ARG, "b2_sdot_fused: the sequence number starts at 1; mailboxes is NULL");
+  SdotPeers pr;
+  for (int p = 0; p < kSdotMaxRanks; ++p) pr.buf[p] = nullptr;
+  for (int p = 0; p < world; ++p) {
+    B2_REQUIRE(mailboxes[p] != nullptr && ((uintptr_t)mailboxes[p] & 255) == 0, B2_ERR_INVALID_ARG,
+               "b2_sdot_fused: mailbox %d is NULL or not 256-byte aligned", p);
+    pr.buf[p] = (unsigned char *)mailboxes[p];
+  }
+  pr.rank = rank;
+  pr.world = world;
+  pr.seq = (unsigned long long)seq;
+  pr.status = (int *)((char *)ctx->fixed + kFixedStatus);
+  double *partials = (double *)((char *)ctx->fixed + kFixedSdotPartials);
+  unsigned int *ticket = (unsigned int *)((char *)ctx->fixed + kFixedSdotTicket);
+  const bool al = (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+  int grid = vec_grid(ctx, (n >> 2) > 0 ? (n >> 2) : 1, kVecThreads * kVecUnroll);
+  if (grid > (int)kSdotMaxBlocks) grid = (int)kSdotMaxBlocks;
+  if (al) sdot_fused_kernel<true><<<grid, kVecThreads, 0, (cudaStream_t)stream>>>(n, x, y, partials, ticket, result_dev, sum_dev, pr);
+  else sdot_fused_kernel<false><<<grid, kVecThreads, 0, (cudaStream_t)stream>>>(n, x, y, partials, ticket, result_dev, sum_dev, pr);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
 }
 
 int b2_sdot_static(int64_t n, const float *x, const float *y, float *result_dev, void *stream) {

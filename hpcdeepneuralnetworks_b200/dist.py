@@ -105,3 +105,40 @@ def sharded_sdot(n_local: int, x_local: torch.Tensor, y_local: torch.Tensor, *, 
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(part, op=dist.ReduceOp.SUM, group=group)
     return part
+
+
+class FusedSdot:
+    """Sharded SDOT whose cross-GPU sum happens inside the kernel: the last block of every rank's SDOT kernel stores its
+    partial into all ranks' mailboxes (peer stores over NVLink) and adds the others' in rank order after a bounded
+    wait -- no collective call.  The mailboxes live in torch's symmetric memory (one 512-byte buffer per rank mapped
+    into every process); construction is collective and raises if symmetric memory cannot be set up, in which case
+    ``sharded_sdot`` (NCCL all-reduce of the double partials) is the way."""
+
+    def __init__(self, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > 16:
+            raise RuntimeError("FusedSdot supports at most 16 ranks")
+        self.buf = symm.empty(64, dtype=torch.float64, device=device)      # 512 bytes
+        self.buf.zero_()
+        try:
+            self.hdl = symm.rendezvous(self.buf, self.group)
+        except TypeError:
+            self.hdl = symm.rendezvous(self.buf, self.group.group_name)
+        self.mailboxes = [int(p) for p in self.hdl.buffer_ptrs]
+        if len(self.mailboxes) != self.world or any(p % 256 for p in self.mailboxes):
+            raise RuntimeError("symmetric memory gave unusable mailbox addresses")
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)        # every mailbox is zeroed before anyone's first call
+        self.seq = 0
+        self.out = torch.empty(1, dtype=torch.float32, device=device)
+        self.sum64 = torch.empty(1, dtype=torch.float64, device=device)
+
+    def __call__(self, n_local: int, x_local: torch.Tensor, y_local: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks of x_local . y_local as a 1-element float64 device tensor (same bits on every rank)."""
+        from . import blas
+        self.seq += 1
+        blas.sdot_fused(n_local, x_local, y_local, self.mailboxes, self.rank, self.world, self.seq, out=self.out,
+                        sum64=self.sum64)
+        return self.sum64

@@ -164,6 +164,17 @@ int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *resul
 int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev,
                     double *partial_dev, void *stream);
 
+/* SDOT fused with its sum over GPUs (one process per GPU; no library collective).  Every rank owns a
+ * 512-byte, 256-byte aligned, zero-initialised mailbox that every rank can address (peer memory over
+ * NVLink, e.g. symmetric memory); `mailboxes` is this rank's host array of the `world` device addresses.
+ * The kernel's last block stores this GPU's partial sum into every mailbox, flags it with `seq`, waits
+ * (at most one second: then B2_ERR_TIMEOUT is recorded for b2_check_status and the local sum is returned)
+ * for the other ranks' flags and adds the slots in rank order: *result_dev and *sum_dev (double, may be
+ * NULL) hold the same bits on every rank.  All ranks call it the same number of times with seq = 1, 2, 3...
+ * Stands in for the reference's single-GPU _sdot (kernel/sdot/sdot.cu:9) at world > 1; world <= 16. */
+int b2_sdot_fused(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, double *sum_dev,
+                  void *const *mailboxes, int rank, int world, uint64_t seq, void *stream);
+
 /* SDOT for callers that must not allocate.  This entry point has no counterpart in the
  * reference.  It is meant for code that cannot call cudaMalloc at the point where it needs a dot
  * product: a plugin running under a host framework that has already handed all device memory to its

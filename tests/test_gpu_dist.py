@@ -45,6 +45,41 @@ def test_sharded_sdot_single_gpu(cuda):
     assert abs(float(tot.item()) - want) <= 1e-6 * scale
 
 
+def test_fused_sdot_exchange_with_itself(cuda):
+    """World of one: the kernel's exchange runs against its own mailbox (flag, bounded wait, slot sum) and must give
+    b2_sdot's bits, call after call (the two epochs of the mailbox alternate)."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = (1 << 20) + 5
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    box = torch.zeros(64 + 32, dtype=torch.float64, device="cuda")
+    addr = (box.data_ptr() + 255) & ~255
+    want = b2.sdot(n, dx, dy).item()
+    for seq in range(1, 6):
+        out, s64 = b2.sdot_fused(n, dx, dy, [addr], 0, 1, seq)
+        b2.check_status()
+        assert out.item() == want
+    ref, scale = oracle.sdot(x, y)
+    assert abs(float(s64.item()) - ref) <= 1e-6 * scale
+
+
+def test_fused_sdot_missing_peer_times_out(cuda):
+    """A peer that never writes its flag: the bounded wait gives up after a second, the status word says TIMEOUT, the
+    local sum is returned and the context stays usable (the second mailbox is plain local memory nobody writes)."""
+    import hpcdeepneuralnetworks_b200 as b2
+    n = 1 << 16
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    box = torch.zeros(2 * 64 + 32, dtype=torch.float64, device="cuda")
+    a0 = (box.data_ptr() + 255) & ~255
+    out, _ = b2.sdot_fused(n, dx, dy, [a0, a0 + 512], 0, 2, 1)
+    with pytest.raises(b2.B2Error) as e:
+        b2.check_status()
+    assert e.value.status == -4
+    assert out.item() == b2.sdot(n, dx, dy).item()
+    b2.check_status()
+
+
 _RANK_SCRIPT = r"""
 import os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["B2_ROOT"])
@@ -72,6 +107,19 @@ s0, cnt = b2dist.row_block(n, rank, world)
 tot = b2dist.sharded_sdot(cnt, torch.from_numpy(x[s0:s0 + cnt].copy()).cuda(), torch.from_numpy(y[s0:s0 + cnt].copy()).cuda())
 ref, scale = oracle.sdot(x, y)
 assert abs(float(tot.item()) - ref) <= 1e-6 * scale
+# the same sum formed inside the kernels over peer memory (no collective): same bits on both ranks, several calls
+fused = b2dist.FusedSdot(torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+xs, ys = torch.from_numpy(x[s0:s0 + cnt].copy()).cuda(), torch.from_numpy(y[s0:s0 + cnt].copy()).cuda()
+vals = []
+for it in range(5):
+    vals.append(float(fused(cnt, xs, ys).item()))
+b2.check_status()
+assert all(v == vals[0] for v in vals), vals
+assert abs(vals[0] - ref) <= 1e-6 * scale
+both = torch.tensor([vals[0]], dtype=torch.float64, device="cuda")
+gathered = [torch.empty_like(both) for _ in range(world)]
+dist.all_gather(gathered, both)
+assert all(float(g.item()) == vals[0] for g in gathered), "ranks disagree on the fused sum"
 dist.barrier(); dist.destroy_process_group()
 print("rank", rank, "ok")
 """
