@@ -554,8 +554,16 @@ def run_multi(args):
 
     # the same with the cross-GPU sum inside the kernel (peer stores over NVLink, no collective call)
     ms_fused, fused_error = None, None
+    fused = None
     try:
         fused = b2dist.FusedSdot(torch.device("cuda", local))
+    except Exception as e:
+        fused_error = f"{type(e).__name__}: {e}"
+    agree = torch.tensor([1 if fused is not None else 0], device="cuda", dtype=torch.int32)
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)      # every rank runs the fused leg, or none does
+    try:
+        if int(agree.item()) == 0:
+            raise RuntimeError(fused_error or "symmetric memory could not be set up on another rank")
         ms_fused_local = timed(lambda: fused(nloc, x, y), max(5, args.steps), 3, dist_barrier=barrier)
         b2.check_status()
         t = torch.tensor([ms_fused_local], device="cuda", dtype=torch.float64)
