@@ -4,9 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--path ffma|3xtf32]
 
 One JSON line on stdout (rank 0).  A "step" is one SGEMM of the workload:
-  N = 1  : row-major SGEMM M=N=K=6144, alpha=1, beta=0.5 (BASELINE config 2's largest point, the
+  N = 1  : row-major SGEMM M=N=K=6144, alpha=1, beta=0.5 (the largest point of benchmark configuration 2, the
            size the metric "SGEMM TFLOPS @6144^3 fp32" is quoted on); inputs resident in HBM.
-  N > 1  : SGEMM M=N=K=32768, alpha=1, beta=0 (BASELINE config 5), A and C split by row blocks over
+  N > 1  : SGEMM M=N=K=32768, alpha=1, beta=0 (benchmark configuration 5), A and C split by row blocks over
            the ranks, B broadcast once per GEMM from rank 0 with NCCL in K-panels overlapped with
            the compute -- strong scaling; the broadcast is inside the timed step.
 `value` is whole-job TFLOP/s (2*M*N*K per step) on the device clock (CUDA events, max over ranks).
@@ -269,7 +269,7 @@ def cublas_abft_baseline_ms(torch, A, B, Cm, steps, warmup):
 
 
 def run_vec_sweep(args):
-    """BASELINE config 4: SAXPY and SDOT at n = 2^20, 2^24, 2^28, 2^30 (alpha = 2).  The two small sizes fit in the
+    """Benchmark configuration 4: SAXPY and SDOT at n = 2^20, 2^24, 2^28, 2^30 (alpha = 2).  The two small sizes fit in the
     126 MB L2; they are timed twice: back to back on the same vectors (L2-resident) and rotating through enough
     distinct vector pairs to exceed L2 (the reference's own trick, kernel/saxpy/saxpy.cu:79-80,126)."""
     import torch
@@ -331,7 +331,7 @@ def run_series(args):
 
 
 def run_sweep(args):
-    """BASELINE config 2: square row-major SGEMM, N = 256 .. 6144 step 256, alpha=1, beta=0.5, both math paths.
+    """Benchmark configuration 2: square row-major SGEMM, N = 256 .. 6144 step 256, alpha=1, beta=0.5, both math paths.
     Prints one JSON object with a row per size (not the headline line)."""
     import torch
     import hpcdeepneuralnetworks_b200 as b2

@@ -234,7 +234,7 @@ def abft_tile_checksums(a: np.ndarray, b: np.ndarray, tile_m: int, tile_n: int):
 
 
 def make_fault_plan(M: int, N: int, K: int, seed: int, tiles_per_fault: int = 64, bit_lo: int = 20, bit_hi: int = 30):
-    """Seeded plan of BASELINE config 3: one bit flip (random bit bit_lo..bit_hi of a random
+    """Seeded plan of benchmark configuration 3: one bit flip (random bit bit_lo..bit_hi of a random
     accumulator, random K-slab) per `tiles_per_fault` output tiles of 128x128, at most one per tile.
     Returns an int32 array of shape (n, 6): tile_m, tile_n, row, col, k_step, bit."""
     tm, tn = (M + 127) // 128, (N + 127) // 128

@@ -24,7 +24,7 @@
 /* ------------------------------------------------------------------------------------
  * Seeded input generator shared bit-for-bit with the device fill kernel.
  * Replaces generate_random_vector / generate_random_matrix (utils/utils.cu:28-44), which
- * draw from libc rand() and cannot be reproduced on a GPU.  BASELINE configs ask for
+ * draw from libc rand() and cannot be reproduced on a GPU.  The benchmark configurations ask for
  * i.i.d. uniform[-1,1] from a seed.
  * ---------------------------------------------------------------------------------- */
 static inline uint64_t o_mix64(uint64_t z) {

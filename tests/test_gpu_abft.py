@@ -103,7 +103,7 @@ def test_single_fault_each_bit(cuda, bit, k_step):
 
 @pytest.mark.parametrize("seed", [6, 7, 8])
 def test_config3_1024_plan(cuda, seed):
-    """BASELINE config 3 at 1024^3: one flip (bit 20..30) per 64 tiles -- here also a denser plan, one per 2 tiles."""
+    """Benchmark configuration 3 at 1024^3: one flip (bit 20..30) per 64 tiles -- here also a denser plan, one per 2 tiles."""
     import hpcdeepneuralnetworks_b200 as b2
     n = 1024
     a, b, c = mats(n, n, n)
@@ -170,7 +170,7 @@ def test_unsupported_operands_are_refused(cuda):
 
 @pytest.mark.parametrize("n", [4096, 8192])
 def test_config3_large_sizes(cuda, n):
-    """BASELINE config 3 at 4096^3 and 8192^3: seeded plan (one flip per 64 tiles) and a clean run; checked
+    """Benchmark configuration 3 at 4096^3 and 8192^3: seeded plan (one flip per 64 tiles) and a clean run; checked
     against the plain kernel on the device and against the exact CPU walk of each struck accumulator."""
     import hpcdeepneuralnetworks_b200 as b2
     A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)

@@ -129,7 +129,7 @@ def test_single_fault_each_bit(cuda, bit):
 
 @pytest.mark.parametrize("seed", [6, 7, 8])
 def test_config3_1024_plan(cuda, seed):
-    """BASELINE config 3 at 1024^3 on the tensor-core path: one flip (bit 20..30) per 64 tiles of 128 x 128, and a
+    """Benchmark configuration 3 at 1024^3 on the tensor-core path: one flip (bit 20..30) per 64 tiles of 128 x 128, and a
     denser plan of one per 2 tiles."""
     import hpcdeepneuralnetworks_b200 as b2
     n = 1024
@@ -249,7 +249,7 @@ def test_degenerate_products_take_the_scaling_route(cuda):
 
 @pytest.mark.parametrize("n", [4096, 8192])
 def test_config3_large_sizes(cuda, n):
-    """BASELINE config 3 at 4096^3 and 8192^3: a clean run and the seeded plan (one flip per 64 tiles), checked
+    """Benchmark configuration 3 at 4096^3 and 8192^3: a clean run and the seeded plan (one flip per 64 tiles), checked
     against the plain 3xTF32 kernel on the device."""
     import hpcdeepneuralnetworks_b200 as b2
     A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)

@@ -39,7 +39,7 @@ def run_gpu(path, a, b, c, alpha, beta):
 
 
 def test_config1_256_against_reference_cpu_gemm(cuda):
-    """BASELINE config 1: 256^3, alpha=1, beta=0, C zero-initialised, checked against the reference's
+    """Benchmark configuration 1: 256^3, alpha=1, beta=0, C zero-initialised, checked against the reference's
     CPU row-major GEMM arithmetic (utils/utils.cu:93-103) with the reference's own verify_matrix rule
     and with the north-star metric."""
     a, b, c = mats(256, 256, 256, beta=0.0)
@@ -279,7 +279,7 @@ def test_3xtf32_leading_dimensions(cuda):
 
 
 def test_sweep_sizes_both_paths(cuda):
-    """BASELINE config 2 (alpha=1, beta=0.5) at a few sweep sizes, inputs generated on the device; checked on
+    """Benchmark configuration 2 (alpha=1, beta=0.5) at a few sweep sizes, inputs generated on the device; checked on
     sampled rows against the double reference."""
     import hpcdeepneuralnetworks_b200 as b2
     for n in (768, 2048):
