@@ -1,0 +1,74 @@
+// Test infrastructure, not product code: runs the REFERENCE's own GPU kernel sgemm_11
+// (kernel/sgemm/include/kernel_11.cuh:15, launch geometry of kernel/sgemm/sgemm.cu:120-123),
+// included unmodified from the reference tree at build time, on the seeded inputs the tests use,
+// and writes C to a file.  The parity tests compare the library's output with it bit for bit:
+// both sum the products of an output in ascending k with one FMA each.
+//
+//   ref_kernel_dump <N (multiple of 128)> <alpha> <beta> <out.bin>
+//
+// Only kernel 11 is used: it reads exactly the K-slab it computes (kernels 12-14 of the reference
+// prefetch one slab past the end of A and B).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <vector>
+
+// the seeded input hash of the checker (oracle.c o_uniform_at): multiples of 2^-23 in [-1, 1)
+static uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+static void fill(std::vector<float> &v, uint64_t seed) {
+  const uint64_t ms = mix64(seed);
+  for (size_t i = 0; i < v.size(); ++i) {
+    const uint64_t h = mix64(ms ^ ((uint64_t)i * 0xD1342543DE82EF95ull));
+    v[i] = (float)(uint32_t)(h >> 40) * (1.0f / 8388608.0f) - 1.0f;
+  }
+}
+static int run(int n, float alpha, float beta, const char *path);
+
+int main(int argc, char **argv) {
+  if (argc != 5) {
+    fprintf(stderr, "usage: ref_kernel_dump <N> <alpha> <beta> <out.bin>\n");
+    return 2;
+  }
+  const int n = atoi(argv[1]);
+  if (n <= 0 || n % 128 != 0 || n > 8192) {
+    fprintf(stderr, "N must be a multiple of 128 in 128..8192\n");
+    return 2;
+  }
+  return run(n, (float)atof(argv[2]), (float)atof(argv[3]), argv[4]);
+}
+
+// The reference header defines short macros (m, kk_max, tab, tcab): it comes after everything else.
+#include "kernel_11.cuh"
+
+static int run(int n, float alpha, float beta, const char *path) {
+  const size_t count = (size_t)n * n;
+  std::vector<float> a(count), b(count), c(count);
+  fill(a, 1);
+  fill(b, 2);
+  fill(c, 3);
+  float *da, *db, *dc;
+  if (cudaMalloc(&da, count * 4) != cudaSuccess || cudaMalloc(&db, count * 4) != cudaSuccess ||
+      cudaMalloc(&dc, count * 4) != cudaSuccess)
+    return 3;
+  cudaMemcpy(da, a.data(), count * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(db, b.data(), count * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(dc, c.data(), count * 4, cudaMemcpyHostToDevice);
+  dim3 block(256), grid(n / 128, n / 128);
+  sgemm_11<<<grid, block>>>(n, da, db, dc, alpha, beta);
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    fprintf(stderr, "kernel failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+    return 4;
+  }
+  cudaMemcpy(c.data(), dc, count * 4, cudaMemcpyDeviceToHost);
+  FILE *f = fopen(path, "wb");
+  if (!f || fwrite(c.data(), 4, count, f) != count) return 5;
+  fclose(f);
+  return 0;
+}

@@ -4,6 +4,7 @@ FFMA path and every rung of the series: bit-exact against the fused oracle (one 
 ascending k) and within the north-star tolerance max|C-C_ref|/(|A|.|B|) <= 1e-5 of the double
 reference.  3xTF32 path: <= 2e-5."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -434,3 +435,27 @@ def test_ffma_transposed_a_route_needs_no_workspace(cuda):
     finally:
         L.b2_set_workspace(h, None, 0)
         L.b2_destroy(h)
+
+
+@pytest.mark.parametrize("n", [128, 256, 640])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (1.0, 0.5), (2.0, 0.25)])
+def test_bit_identical_to_the_reference_gpu_kernel(cuda, tmp_path, n, alpha, beta):
+    """The reference's own sgemm_11 kernel (kernel/sgemm/include/kernel_11.cuh:15), compiled unmodified from the
+    reference tree into oracle/_ref/ref_kernel_dump, run here on the same seeded inputs: the FFMA path, the series
+    rung that restates that kernel and the CPU oracle all reproduce its output bit for bit.  (alpha and beta are
+    powers of two, so that alpha*t + beta*c rounds once whichever product the compiler fuses.)"""
+    import subprocess
+    import hpcdeepneuralnetworks_b200 as b2
+    exe = os.path.join(os.path.dirname(oracle.__file__), "_ref", "ref_kernel_dump")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/ref_kernel_dump was not built (no reference tree at build time)")
+    out = tmp_path / "c.bin"
+    r = subprocess.run([exe, str(n), repr(alpha), repr(beta), str(out)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = np.fromfile(out, dtype=np.float32).reshape(n, n)
+    a, b, c = mats(n, n, n)
+    assert np.array_equal(run_gpu(0, a, b, c, alpha, beta), ref)
+    assert np.array_equal(oracle.sgemm_fma(alpha, a, b, beta, c), ref)
+    dc = dev(c)
+    b2.sgemm_series(11, n, dev(a), dev(b), dc, alpha, beta)
+    assert np.array_equal(dc.cpu().numpy(), ref)
