@@ -152,3 +152,52 @@ def test_large_vectors_properties(cuda, log2n):
     whole = float(b2.sdot(n, x, ones).item())
     parts = sum(float(b2.sdot(n // 4, x[i * (n // 4):], ones).item()) for i in range(4))
     assert abs(whole - parts) <= 1e-5 * n / 2
+
+
+def _ref_vector_dump():
+    import os
+    exe = os.path.join(os.path.dirname(oracle.__file__), "_ref", "ref_vector_dump")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/ref_vector_dump was not built (no reference tree at build time)")
+    return exe
+
+
+@pytest.mark.parametrize("n", [1024, 4096 + 512, 1 << 20])
+@pytest.mark.parametrize("alpha", [2.0, 0.37, -1.25])
+@pytest.mark.parametrize("kernel", ["saxpy", "saxpy2"])
+def test_saxpy_bit_identical_to_the_reference_gpu_kernels(cuda, tmp_path, n, alpha, kernel):
+    """The reference's own `saxpy` (f128) and `_saxpy` kernels (kernel/saxpy/saxpy.cu:15-48), compiled unmodified from
+    the reference tree and launched with the driver's geometry on the same seeded vectors: b2_saxpy and the CPU oracle
+    reproduce their output bit for bit (one fused multiply-add per element on every side)."""
+    import subprocess
+    import hpcdeepneuralnetworks_b200 as b2
+    exe = _ref_vector_dump()
+    out = tmp_path / "y.bin"
+    r = subprocess.run([exe, kernel, str(n), repr(alpha), "256", str(out)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = np.fromfile(out, dtype=np.float32)
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    dy = dev(y)
+    b2.saxpy(n, alpha, dev(x), dy)
+    assert np.array_equal(dy.cpu().numpy(), ref)
+    assert np.array_equal(oracle.saxpy(alpha, x, y), ref)
+
+
+@pytest.mark.parametrize("n,tpb", [(1024, 256), ((1 << 20) + 77, 1024), (1 << 24, 1024)])
+def test_sdot_against_the_reference_gpu_kernel(cuda, tmp_path, n, tpb):
+    """The reference's `_sdot` (kernel/sdot/sdot.cu:9-35: float partial sums, shared-memory tree, atomicAdd) on the
+    same seeded vectors: b2_sdot agrees with it within the 1e-5 relative tolerance (relative to sum |x_i y_i|); the
+    reference's own float accumulation is the looser side of that comparison."""
+    import subprocess
+    import hpcdeepneuralnetworks_b200 as b2
+    exe = _ref_vector_dump()
+    out = tmp_path / "d.bin"
+    r = subprocess.run([exe, "sdot", str(n), str(tpb), str(out)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = float(np.fromfile(out, dtype=np.float32)[0])
+    x, y = oracle.fill_uniform(n, 4), oracle.fill_uniform(n, 5)
+    got = float(b2.sdot(n, dev(x), dev(y)).item())
+    want, scale = oracle.sdot(x, y)
+    assert abs(got - ref) <= 1e-5 * scale
+    assert abs(ref - want) <= 1e-5 * scale
+    assert abs(got - want) <= 1e-6 * scale
