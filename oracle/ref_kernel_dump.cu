@@ -5,9 +5,14 @@
 // both sum the products of an output in ascending k with one FMA each.
 //
 //   ref_kernel_dump <N (multiple of 128)> <alpha> <beta> <out.bin>
+//   ref_kernel_dump nt <M> <N> <K> <alpha> <beta> <out.bin>      (M, N multiples of 128, K of 8)
 //
-// Only kernel 11 is used: it reads exactly the K-slab it computes (kernels 12-14 of the reference
-// prefetch one slab past the end of A and B).
+// Of the row-major series only kernel 11 is used: it reads exactly the K-slab it computes (kernels
+// 12-14 of the reference prefetch one slab past the end of A and B).  The `nt` form runs the
+// generated column-major kernel sgemm_huge (kernel/ft_sgemm/include_code_gen/sgemm_huge.cuh:11,
+// launched as in kernel/ft_sgemm/sgemm.cu:146-149: C = alpha*A*B^T + beta*C with A MxK, B NxK, C MxN,
+// all column-major); that kernel also prefetches one K-slab past the end on its last iteration, so
+// A and B are allocated one slab (8 columns) larger here and the extra reads stay inside them.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -30,8 +35,17 @@ static void fill(std::vector<float> &v, uint64_t seed) {
   }
 }
 static int run(int n, float alpha, float beta, const char *path);
+static int run_nt(int M, int N, int K, float alpha, float beta, const char *path);
 
 int main(int argc, char **argv) {
+  if (argc == 8 && argv[1][0] == 'n') {
+    const int M = atoi(argv[2]), N = atoi(argv[3]), K = atoi(argv[4]);
+    if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 8 || M > 8192 || N > 8192 || K > 8192) {
+      fprintf(stderr, "M and N must be multiples of 128, K of 8, all at most 8192\n");
+      return 2;
+    }
+    return run_nt(M, N, K, (float)atof(argv[5]), (float)atof(argv[6]), argv[7]);
+  }
   if (argc != 5) {
     fprintf(stderr, "usage: ref_kernel_dump <N> <alpha> <beta> <out.bin>\n");
     return 2;
@@ -69,6 +83,40 @@ static int run(int n, float alpha, float beta, const char *path) {
   cudaMemcpy(c.data(), dc, count * 4, cudaMemcpyDeviceToHost);
   FILE *f = fopen(path, "wb");
   if (!f || fwrite(c.data(), 4, count, f) != count) return 5;
+  fclose(f);
+  return 0;
+}
+
+#undef tab
+#undef tcab
+#undef m
+#undef kk_max
+#include "sgemm_huge.cuh"
+
+static int run_nt(int M, int N, int K, float alpha, float beta, const char *path) {
+  std::vector<float> a((size_t)M * K), b((size_t)N * K), c((size_t)M * N);
+  fill(a, 1);
+  fill(b, 2);
+  fill(c, 3);
+  const size_t pad_a = (size_t)M * 8, pad_b = (size_t)N * 8;   // one K-slab: the kernel's last prefetch lands here
+  float *da, *db, *dc;
+  if (cudaMalloc(&da, (a.size() + pad_a) * 4) != cudaSuccess || cudaMalloc(&db, (b.size() + pad_b) * 4) != cudaSuccess ||
+      cudaMalloc(&dc, c.size() * 4) != cudaSuccess)
+    return 3;
+  cudaMemset(da, 0, (a.size() + pad_a) * 4);
+  cudaMemset(db, 0, (b.size() + pad_b) * 4);
+  cudaMemcpy(da, a.data(), a.size() * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(db, b.data(), b.size() * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(dc, c.data(), c.size() * 4, cudaMemcpyHostToDevice);
+  dim3 block(256), grid(M / 128, N / 128);
+  sgemm_huge<<<grid, block>>>(M, N, K, da, db, dc, alpha, beta);
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    fprintf(stderr, "kernel failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+    return 4;
+  }
+  cudaMemcpy(c.data(), dc, c.size() * 4, cudaMemcpyDeviceToHost);
+  FILE *f = fopen(path, "wb");
+  if (!f || fwrite(c.data(), 4, c.size(), f) != c.size()) return 5;
   fclose(f);
   return 0;
 }

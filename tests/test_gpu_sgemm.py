@@ -459,3 +459,29 @@ def test_bit_identical_to_the_reference_gpu_kernel(cuda, tmp_path, n, alpha, bet
     dc = dev(c)
     b2.sgemm_series(11, n, dev(a), dev(b), dc, alpha, beta)
     assert np.array_equal(dc.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 8), (256, 128, 64), (384, 256, 200)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (1.0, 0.5), (-2.0, 0.25)])
+def test_colmajor_nt_bit_identical_to_the_reference_generated_kernel(cuda, tmp_path, shape, alpha, beta):
+    """The reference's generated column-major kernel sgemm_huge (kernel/ft_sgemm/include_code_gen/sgemm_huge.cuh:11),
+    compiled unmodified and run on the same seeded inputs (its A and B allocated one K-slab larger, because it
+    prefetches one slab past the end): ref_sgemm_colmajor_nt and the CPU oracle reproduce its C bit for bit."""
+    import subprocess
+    import hpcdeepneuralnetworks_b200 as b2
+    exe = os.path.join(os.path.dirname(oracle.__file__), "_ref", "ref_kernel_dump")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/ref_kernel_dump was not built (no reference tree at build time)")
+    M, N, K = shape
+    out = tmp_path / "c.bin"
+    r = subprocess.run([exe, "nt", str(M), str(N), str(K), repr(alpha), repr(beta), str(out)], capture_output=True, text=True,
+                       timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = np.fromfile(out, dtype=np.float32)
+    af = oracle.fill_uniform(M * K, 1)
+    bf = oracle.fill_uniform(N * K, 2)
+    cf = oracle.fill_uniform(M * N, 3)
+    dcf = dev(cf)
+    b2.sgemm_colmajor_nt(M, N, K, dev(af), dev(bf), dcf, alpha, beta)
+    assert np.array_equal(dcf.cpu().numpy().ravel(), ref)
+    assert np.array_equal(np.asarray(oracle.sgemm_colmajor_nt(M, N, K, alpha, af, bf, beta, cf)).ravel(), ref)
