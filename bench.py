@@ -34,7 +34,9 @@ NMULTI = 32768
 CPU_SAMPLE_N = 1152          # reference CPU GEMM sample: 1152^3 = (3/16 * 6144)^3, about 1/152 of the flop
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the committed
 # ncu captures (profiles/), scaled to a full launch; None until a capture exists for that kernel.
-NCU_TRAFFIC = {"sgemm_ffma_6144": 1.479277e9 + 146.472e6, "sgemm_3xtf32_6144": 2.906706e9 + 140.046848e6,
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the bench's own size (profiles/):
+# the K-major FFMA kernel, the CTA-pair 3xTF32 kernel (band-ordered tile walk), SAXPY and SDOT at 2^28 (scaled from 2^26).
+NCU_TRAFFIC = {"sgemm_ffma_6144": 1.342616e9 + 141.759e6, "sgemm_3xtf32_6144": 2.140627e9 + 139.310e6,
                "saxpy_2p28": 4 * (536.936e6 + 221.76e6), "sdot_2p28": 4 * (536.8855e6 + 4.07e6)}
 
 
