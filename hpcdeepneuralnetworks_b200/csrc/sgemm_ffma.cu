@@ -88,6 +88,10 @@ struct FfmaArgs {
 // the fault exactly (the reference subtracts a rounded residual with the location left
 // unfinished, ft_sgemm_huge.cuh:296-371).
 
+// The table of a slab's B sums is read one slab later (phase 2), and the shared-memory ring lets a warp run up to
+// two slabs ahead of the slowest one: with four tables the writer of slab kb + 3 is gated, through the ring's
+// "empty" barrier of slab kb, behind every reader of the table of slab kb - 1 (three tables would leave a window).
+constexpr int kFtTables = 4;
 template <int BM, int NR>
 struct TileCfg {
   static constexpr int BN = 8 * NR;
@@ -95,10 +99,10 @@ struct TileCfg {
   static constexpr int THREADS = 32 * WARPS;
   static constexpr int kStageA = BM * FBK * 4;
   static constexpr int kStageB = FBK * BN * 4;
-  static constexpr int kBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[3]
+  static constexpr int kBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[kFtTables]
   static constexpr int kAwOff = kBarOff + 128;                   // float Asum[WARPS][32]
-  static constexpr int kBgOff = kAwOff + WARPS * 128;            // float Bsum[FSTAGES][8][32]
-  static constexpr int kMiscOff = kBgOff + FSTAGES * 1024;       // int inj[8]; int nflag; int flagged[64]
+  static constexpr int kBgOff = kAwOff + WARPS * 128;            // float Bsum[kFtTables][8][32]
+  static constexpr int kMiscOff = kBgOff + kFtTables * 1024;     // int inj[8]; int nflag; int flagged[64]
   static constexpr int kSmem = 1024 + kMiscOff + 512;
   static constexpr int MIN_BLOCKS = 512 / THREADS;
   static_assert(BM % 16 == 0 && BM >= 32 && BM <= 128, "BM is 32, 64 or 128");
@@ -261,8 +265,9 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int s = 0; s < FSTAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], WARPS);
-      if (FT == 1) mbar_init(&sums_ready[s], WARPS);
     }
+    if (FT == 1)
+      for (int t = 0; t < kFtTables; ++t) mbar_init(&sums_ready[t], WARPS);
     if (FT) *nflag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -401,10 +406,10 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int k = (tid >> 3) + pass * (THREADS / 8);
         // table layout: k = 8r + 4h + e of column set g at h*512 + (r*8 + g)*16 + e*4, so that the 32 lanes
         // (g, r) of a warp read each half as one contiguous 512-byte row in phase 2
-        *reinterpret_cast<float *>(sBg + s * 1024 + ((k >> 2) & 1) * 512 + ((k >> 3) * 8 + (tid & 7)) * 16 + (k & 3) * 4) = lo + hi;
+        *reinterpret_cast<float *>(sBg + (kb & (kFtTables - 1)) * 1024 + ((k >> 2) & 1) * 512 + ((k >> 3) * 8 + (tid & 7)) * 16 + (k & 3) * 4) = lo + hi;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sums_ready[s]);
+      if (lane == 0) mbar_arrive(&sums_ready[kb & (kFtTables - 1)]);
     };
     auto phase2 = [&](int ps, uint32_t pparity) -> bool {
       if (!mbar_wait(&sums_ready[ps], pparity)) return false;
@@ -420,8 +425,8 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       chk2[1] = ffma2(a23.y, g23.y, chk2[1]);
       return true;
     };
-    const int sprev = (kb + FSTAGES - 1) % FSTAGES;
-    const uint32_t pprev = (uint32_t)((kb - 1) / FSTAGES) & 1u;
+    const int sprev = (kb - 1) & (kFtTables - 1);                           // table and barrier of the previous slab
+    const uint32_t pprev = (uint32_t)((kb - 1) / kFtTables) & 1u;
     const unsigned char *As = Ast + a_thread;
     const unsigned char *Bs = Bst + b_thread;
     if (TRANS_A) {
@@ -495,8 +500,8 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   if (FT == 1 && ok && nkb > 0) {
     // the last slab's sums have not been folded yet
-    const int ps = (nkb - 1) % FSTAGES;
-    if (mbar_wait(&sums_ready[ps], (uint32_t)((nkb - 1) / FSTAGES) & 1u)) {
+    const int ps = (nkb - 1) & (kFtTables - 1);
+    if (mbar_wait(&sums_ready[ps], (uint32_t)((nkb - 1) / kFtTables) & 1u)) {
       const unsigned char *pw = sAw + warp * 128 + lm * 32;
       const unsigned char *pg = sBg + ps * 1024 + (lm * 8 + ln) * 16;
       const ulonglong2 a01 = *reinterpret_cast<const ulonglong2 *>(pw);
