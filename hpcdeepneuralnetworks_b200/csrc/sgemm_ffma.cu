@@ -777,7 +777,9 @@ static int g_ft_level = 1;   // ABFT encode granularity of the FFMA path: 1 bloc
 static int g_ffma_transpose_a = 1;
 size_t ffma_workspace_bytes(int M, int N, int K) {
   if (!g_ffma_transpose_a || N < 2048 || M < 128 || K < 32) return 0;
-  return (size_t)K * (((size_t)M + 3) & ~(size_t)3) * sizeof(float) + 2048;
+  const size_t bytes = (size_t)K * (((size_t)M + 3) & ~(size_t)3) * sizeof(float) + 2048;
+  // an optional speed-up does not take gigabytes: beyond 1 GiB (a 16384 x 16384 A) the row-major kernel runs
+  return bytes <= ((size_t)1 << 30) + 2048 ? bytes : 0;
 }
 
 // trans_a = 0: A is M x K row-major (lda >= K).  trans_a = 1: A is given as K x M row-major

@@ -58,7 +58,7 @@ int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
 /* Bytes of workspace an MxNxK problem uses.  path = B2_PATH_3XTF32: required (hi/lo planes of A and B).
  * path = B2_PATH_FFMA: optional; when that much scratch is there (or the handle may grow its own) a
  * row-major A is transposed into it first, which makes large products about 3 % faster; 0 when the
- * pass would not pay.  Results are bit-identical either way. */
+ * pass would not pay or would need more than 1 GiB.  Results are bit-identical either way. */
 size_t b2_sgemm_workspace_bytes(int path, int M, int N, int K);
 
 /* ---- SGEMM: row-major C = alpha*A*B + beta*C --------------------------------------- */
