@@ -465,6 +465,11 @@ def set_tf32_pair(on: int):
     check(_lib.load().b2_set_tf32_pair(on))
 
 
+def set_tf32_persistent(on: int):
+    """1 (default): the plain CTA-pair 3xTF32 kernel is persistent; 0: one cluster per tile."""
+    check(_lib.load().b2_set_tf32_persistent(on))
+
+
 def set_tf32_abft_mode(mode: int):
     """Where the 3xTF32 ABFT checksums are formed: 2 CUDA cores (default), 1 tensor cores."""
     check(_lib.load().b2_set_tf32_abft_mode(mode))

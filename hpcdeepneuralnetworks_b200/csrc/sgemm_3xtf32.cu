@@ -749,9 +749,179 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
 }
 
+// ---- persistent CTA-pair form (plain SGEMM only) -------------------------------------------------
+// As many clusters as the device holds at once; cluster c computes tiles c, c + clusters, ... of the
+// same band-ordered walk.  The accumulator is double-buffered in TMEM (2 x 256 columns): while the
+// epilogue warps drain tile i, the MMA issuer is already accumulating tile i + 1 into the other
+// buffer and the TMA producer runs ahead through the same 3-stage ring, so the per-tile prologue
+// (barrier set-up, TMEM allocation, first loads in flight) is paid once and the epilogue (about
+// 10 us a tile, a third of it waiting for C when beta != 0) hides behind the next tile's MMAs.
+// Barriers beyond the ring: acc_full[b] in both CTAs (the leader's commit after a tile's last MMA),
+// acc_empty[b] in the leader only (one arrival per epilogue warp of either CTA, CTA 1's by a relaxed
+// remote arrive) which the MMA issuer waits on before it reuses buffer b.
+__device__ __forceinline__ void pair_tile_origin(const Tf32Args &p, int t, uint32_t rank, int &m0, int &n0) {
+  const int tiles_n = (p.N + 255) / 256, tiles_m = (p.M + 255) / 256;
+  const int band = t / (kPairBand * tiles_n), within = t % (kPairBand * tiles_n);
+  const int band_rows = min(kPairBand, tiles_m - band * kPairBand);
+  m0 = (band * kPairBand + within % band_rows) * 256 + (int)rank * 128;
+  n0 = (within / band_rows) * 256;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                                    const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                                    const Tf32Args p, int n_tiles) {
+  using PC = PairCfg<0>;
+  constexpr int S = PC::kStages, kTA = PC::kTA, kTB = PC::kTB, kStage = PC::kStage;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + S * kStage);
+  uint64_t *empty = full + S;
+  uint64_t *acc_full = empty + S;       // [2]
+  uint64_t *acc_empty = acc_full + 2;   // [2], used in the leader
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int nkb = (p.K + 31) / 32;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);   // four epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmAh);
+    tma_prefetch_desc(&tmAl);
+    tma_prefetch_desc(&tmBh);
+    tma_prefetch_desc(&tmBl);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (one per CTA): one slab counter across all of this cluster's tiles ------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+        int m0, n0;
+        pair_tile_origin(p, t, rank, m0, n0);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(&empty[s], ((it / S) & 1u) ^ 1u)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          unsigned char *st = smem + s * kStage;
+          const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * kStage);
+          tma_load_2d_pair(st, &tmAh, leader_full, kb * 32, m0);
+          tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
+          tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
+          tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the leader CTA only ------------------------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
+      uint32_t it = 0, n_done = 0;
+      bool ok = true;
+      for (int t = cluster; t < n_tiles && ok; t += n_clusters, ++n_done) {
+        const uint32_t buf = n_done & 1u;
+        // the epilogue warps of both CTAs have drained this buffer (two tiles ago)
+        if (!mbar_wait(&acc_empty[buf], ((n_done >> 1) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + buf * 256u;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(&full[s], (it / S) & 1u)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + s * kStage);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
+            const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
+            const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
+            const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
+            umma_tf32_pair(acc, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+            umma_tf32_pair(acc, a_hi, b_lo, idesc, 1u);
+            umma_tf32_pair(acc, a_hi, b_hi, idesc, 1u);
+          }
+          umma_commit_pair(&empty[s], (uint16_t)3);
+        }
+        if (ok) umma_commit_pair(&acc_full[buf], (uint16_t)3);
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5 of each CTA ------------------------------------------------------
+    const int q = warp & 3;
+    const FtInj inj;
+    uint32_t n_done = 0;
+    const uint32_t leader_empty0 = mapa_u32(smem_u32(&acc_empty[0]), 0), leader_empty1 = mapa_u32(smem_u32(&acc_empty[1]), 0);
+    for (int t = cluster; t < n_tiles; t += n_clusters, ++n_done) {
+      const uint32_t buf = n_done & 1u;
+      int m0, n0;
+      pair_tile_origin(p, t, rank, m0, n0);
+      bool done = false;
+      const uint64_t t0 = global_timer_ns();
+      for (int itw = 0; itw < (1 << 14) && !done; ++itw) {
+        done = mbar_wait(&acc_full[buf], (n_done >> 1) & 1u, 1u << 10);
+        if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+      }
+      const bool ok = __all_sync(0xffffffffu, done);
+      if (!ok) {
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      tf32_epilogue<256, 0>(p, tmem_base + buf * 256u, q, lane, m0, n0, true, nkb, inj, nullptr);
+      // this warp's reads of the buffer are complete (every chunk waited for its tcgen05.ld): hand it back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(&acc_empty[buf]);
+        else mbar_arrive_remote(buf ? leader_empty1 : leader_empty0);
+      }
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+  if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+}
+
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
 static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 static int g_tf32_abft = kFtCuda;  // where the ABFT checksums are formed: 1 tensor cores, 2 CUDA cores
+static int g_tf32_persistent = 1;  // 1: the plain CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
 static int g_tf32_pair = 1;    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
@@ -894,6 +1064,17 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
       B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtCuda>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtCuda>::kSmem));
       pair_configured = true;
     }
+    if (ftm == 0 && g_tf32_persistent) {
+      static bool persistent_configured = false;
+      if (!persistent_configured) {
+        B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<0>::kSmem));
+        persistent_configured = true;
+      }
+      const int clusters = pairs < slots ? pairs : (slots > 0 ? slots : pairs);
+      sgemm_3xtf32_pair_persistent_kernel<<<2 * clusters, 192, PairCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], pa, pairs);
+      B2_CUDA(cudaGetLastError());
+      return B2_OK;
+    }
     if (ftm == kFtTensor) sgemm_3xtf32_pair_kernel<kFtTensor><<<2 * pairs, 192, PairCfg<kFtTensor>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     else if (ftm == kFtCuda) sgemm_3xtf32_pair_kernel<kFtCuda><<<2 * pairs, 192, PairCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     else sgemm_3xtf32_pair_kernel<0><<<2 * pairs, 192, PairCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
@@ -959,6 +1140,12 @@ int b2_set_tf32_pair(int on) {
 int b2_set_tf32_abft_mode(int mode) {
   B2_REQUIRE(mode == 1 || mode == 2, B2_ERR_INVALID_ARG, "b2_set_tf32_abft_mode: %d is not 1 or 2", mode);
   b2::g_tf32_abft = mode;
+  return B2_OK;
+}
+// 1 (default): the plain CTA-pair SGEMM is the persistent kernel; 0: one cluster per tile.
+int b2_set_tf32_persistent(int on) {
+  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_tf32_persistent: %d is not 0 or 1", on);
+  b2::g_tf32_persistent = on;
   return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.

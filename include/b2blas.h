@@ -256,6 +256,10 @@ int b2_set_tf32_slab_k(int k);
  * against 128x128 single-CTA tiles by whole waves (default), 2 always.  A width pinned with b2_set_tf32_tile_n
  * selects the single-CTA kernel of that width. */
 int b2_set_tf32_pair(int on);
+/* 1 (default): the plain CTA-pair kernel is persistent (as many clusters as the device holds, each walking several
+ * tiles, accumulator double-buffered in tensor memory so that a tile's epilogue overlaps the next tile's MMAs);
+ * 0: one cluster per tile. */
+int b2_set_tf32_persistent(int on);
 /* Where b2_ft_sgemm(path = B2_PATH_3XTF32) forms its checksums: 2 (default) on the CUDA cores beside the MMAs
  * (few percent overhead, default tau 2.6e-5*K), 1 on the tensor cores as two extra small MMAs per K-step
  * (about +20 %, default tau 1e-5*K: such checksums follow the accumulators' truncation more closely). */

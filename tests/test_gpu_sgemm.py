@@ -224,7 +224,8 @@ def test_3xtf32_both_tile_widths(cuda, tile_n, slab_k):
 @pytest.mark.parametrize("shape", [(256, 256, 32), (128, 256, 64), (256, 512, 256), (1024, 1024, 1024), (130, 300, 70),
                                    (17, 13, 5), (384, 128, 1000), (200, 520, 36), (257, 255, 33), (1, 1, 1)])
 @pytest.mark.parametrize("alpha,beta", [(1.0, 0.5), (-1.5, 0.0)])
-def test_3xtf32_cta_pair_kernel_matches_single_cta(cuda, shape, alpha, beta):
+@pytest.mark.parametrize("persistent", [1, 0])
+def test_3xtf32_cta_pair_kernel_matches_single_cta(cuda, shape, alpha, beta, persistent):
     """The cta_group::2 kernel (256 x 256 tiles on two CTAs) accumulates every output in the same order as the
     single-CTA kernel, so the two agree bit for bit; both meet the tolerance against the double reference."""
     import hpcdeepneuralnetworks_b200 as b2
@@ -232,14 +233,42 @@ def test_3xtf32_cta_pair_kernel_matches_single_cta(cuda, shape, alpha, beta):
     a, b, c = mats(M, N, K)
     try:
         b2.set_tf32_pair(2)
+        b2.set_tf32_persistent(persistent)     # persistent clusters with a double-buffered accumulator, or one cluster per tile
         pair = run_gpu(1, a, b, c, alpha, beta)
         b2.set_tf32_pair(0)
         single = run_gpu(1, a, b, c, alpha, beta)
     finally:
         b2.set_tf32_pair(1)
+        b2.set_tf32_persistent(1)
     assert np.array_equal(pair, single)
     c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
     assert oracle.gemm_error(pair, c64, den) <= TOL_3XTF32
+
+
+def test_3xtf32_persistent_many_tiles_per_cluster(cuda):
+    """More tiles than resident clusters (13 x 9 = 117 pair tiles on 74 slots, partial tiles on both edges, K not a
+    multiple of the slab): every cluster walks two tiles through both accumulator buffers."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 3200, 2200, 330
+    A = b2.fill_uniform(torch.empty((M, K), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((K, N), device="cuda"), 2)
+    C0 = b2.fill_uniform(torch.empty((M, N), device="cuda"), 3)
+    out = {}
+    try:
+        b2.set_tf32_pair(2)
+        for pers in (1, 0):
+            b2.set_tf32_persistent(pers)
+            Cm = C0.clone()
+            b2.sgemm(M, N, K, 1.5, A, B, 0.5, Cm, path=1)
+            b2.check_status()
+            out[pers] = Cm
+    finally:
+        b2.set_tf32_pair(1)
+        b2.set_tf32_persistent(1)
+    assert torch.equal(out[1], out[0])
+    rows = np.array([0, 127, 128, 1599, 3199])
+    c64, den = oracle.sgemm_f64(1.5, A.cpu().numpy()[rows], B.cpu().numpy(), 0.5, C0.cpu().numpy()[rows])
+    assert oracle.gemm_error(out[1].cpu().numpy()[rows], c64, den) <= TOL_3XTF32
 
 
 def test_3xtf32_cta_pair_large_and_strided(cuda):
