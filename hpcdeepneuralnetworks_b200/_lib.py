@@ -107,6 +107,7 @@ def load() -> C.CDLL:
     L.b2_set_ft_level.argtypes = [i32]
     L.b2_set_ffma_transpose_a.argtypes = [i32]
     L.b2_set_tf32_abft_mode.argtypes = [i32]
+    L.b2_set_tf32_abft_bias.argtypes = [f32]
     _lib = L
     return L
 

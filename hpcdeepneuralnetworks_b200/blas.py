@@ -475,6 +475,11 @@ def set_tf32_abft_mode(mode: int):
     check(_lib.load().b2_set_tf32_abft_mode(mode))
 
 
+def set_tf32_abft_bias(bias: float):
+    """Loss per K-slab that the 3xTF32 ABFT check expects of an accumulator (fraction of its value; < 0: built-in)."""
+    check(_lib.load().b2_set_tf32_abft_bias(bias))
+
+
 def set_tf32_slab_k(k: int):
     """K-slab depth of the 3xTF32 kernel (16 or 32)."""
     check(_lib.load().b2_set_tf32_slab_k(k))

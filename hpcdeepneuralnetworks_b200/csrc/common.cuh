@@ -39,8 +39,23 @@ struct Context {
   size_t ws_bytes = 0;
   bool ws_owned = false;
   int sm_count = 0;
+  int max_pairs = -1;         // CTA pairs of the 3xTF32 kernels this device holds at once (-1: not asked yet)
+  unsigned int launch_seq = 0;  // number of the last SGEMM launch made on this handle (see next_launch_seq)
 };
 Context *default_context();           // process-wide, created on first use for the current device
+// The context behind a handle (NULL: the current device's default handle), or nullptr with the error text set when
+// there is none or when the handle belongs to another device than the current one.
+Context *resolve_context(b2_handle h, const char *who);
+// cudaFuncSetAttribute acts on the current device only: sets the dynamic shared-memory limit (and, when
+// carveout >= 0, the preferred carve-out) of `func` once per device.
+int ensure_func_attributes(const void *func, int device, int dynamic_smem_bytes, int carveout = -1);
+// Every SGEMM launch on a handle gets a number.  A CTA whose bounded wait runs out stores that number in the
+// handle's abort word (and B2_ERR_TIMEOUT in the sticky status word); CTAs of the same launch that start later
+// see their own number there and leave at once, launches made afterwards carry another number and run normally.
+unsigned int next_launch_seq(Context *ctx);
+#define B2_CONTEXT(ctx, h, who)                                   \
+  ::b2::Context *ctx = ::b2::resolve_context((h), (who));         \
+  if (!ctx) return (h) ? B2_ERR_INVALID_ARG : B2_ERR_CUDA
 int ensure_workspace(Context *ctx, size_t bytes, cudaStream_t s);
 // Enqueues the reduction that leaves 3 * rms(X1) * rms(X2) in the context's scratch (1 for operands uniform in
 // [-1, 1)) and returns the device address of that float: the factor by which rounding noise, and so an ABFT
@@ -52,7 +67,7 @@ int ft_data_scale(Context *ctx, const float *X1, int rows1, int cols1, int ld1, 
 constexpr size_t kSdotMaxBlocks = 4096;
 constexpr size_t kFixedSdotPartials = 0;                                  // double[kSdotMaxBlocks]
 constexpr size_t kFixedSdotTicket = kSdotMaxBlocks * sizeof(double);      // unsigned int
-constexpr size_t kFixedStatus = kFixedSdotTicket + 256;                   // int status word of bounded waits
+constexpr size_t kFixedStatus = kFixedSdotTicket + 256;                   // int status word of bounded waits (sticky), then the abort word
 constexpr size_t kFixedVerify = kFixedStatus + 256;                       // verify_matrix result {uint fails, uint maxbits}
 constexpr size_t kFixedFtReport = kFixedVerify + 256;                     // b2_ft_report scratch
 constexpr size_t kFixedFtScale = kFixedFtReport + 256;                    // double ssA, ssB; float scale (ABFT threshold scaling)
@@ -136,6 +151,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32
   return false;
 }
 
+// A bounded wait ran out in the launch numbered `seq`: record it (status[0] sticky for b2_check_status, status[1]
+// the number of the launch, which lets the launch's remaining CTAs leave at once).
+__device__ __forceinline__ void record_timeout(int *status, unsigned int seq) {
+  atomicExch(status, (int)B2_ERR_TIMEOUT);
+  atomicExch(reinterpret_cast<unsigned int *>(status) + 1, seq);
+}
+__device__ __forceinline__ bool launch_aborted(const int *status, unsigned int seq) {
+  return *(reinterpret_cast<const volatile unsigned int *>(status) + 1) == seq;
+}
+
 // ---- device: TMA -----------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)m) : "memory");
@@ -195,6 +220,11 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t cta_addr, uint32_t rank) {
 // a releasing arrive from the MMA-issuing thread stalled it for about a microsecond per K-slab)
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
 }
 // every thread of both CTAs arrives and waits (release/acquire)
 __device__ __forceinline__ void cluster_sync_all() {

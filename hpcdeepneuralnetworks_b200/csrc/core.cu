@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -51,6 +52,48 @@ Context *default_context() {
     g_default[dev] = c;
   }
   return g_default[dev];
+}
+
+Context *resolve_context(b2_handle h, const char *who) {
+  if (!h) {
+    Context *c = default_context();
+    if (!c) {
+      char why[512];
+      snprintf(why, sizeof(why), "%s", g_err);
+      set_error("%s: no context (%s)", who, why);
+    }
+    return c;
+  }
+  Context *c = reinterpret_cast<Context *>(h);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != c->device) {
+    set_error("%s: the handle belongs to device %d but device %d is current", who, c->device, dev);
+    return nullptr;
+  }
+  return c;
+}
+
+unsigned int next_launch_seq(Context *ctx) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  ctx->launch_seq += 1;
+  if (ctx->launch_seq == 0) ctx->launch_seq = 1;   // 0 is what a cleared abort word holds
+  return ctx->launch_seq;
+}
+
+struct FuncOnDevice {
+  const void *func;
+  int device;
+};
+static std::vector<FuncOnDevice> g_configured;
+
+int ensure_func_attributes(const void *func, int device, int dynamic_smem_bytes, int carveout) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (const FuncOnDevice &f : g_configured)
+    if (f.func == func && f.device == device) return B2_OK;
+  B2_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_smem_bytes));
+  if (carveout >= 0) B2_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout, carveout));
+  g_configured.push_back({func, device});
+  return B2_OK;
 }
 
 int ensure_workspace(Context *ctx, size_t bytes, cudaStream_t s) {
@@ -166,8 +209,7 @@ int b2_destroy(b2_handle h) {
 }
 
 int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes) {
-  Context *c = h ? h : default_context();
-  B2_REQUIRE(c != nullptr, B2_ERR_CUDA, "no context");
+  B2_CONTEXT(c, h, "b2_set_workspace");
   B2_REQUIRE(((uintptr_t)dev_ptr & 1023) == 0, B2_ERR_INVALID_ARG, "workspace must be 1024-byte aligned");
   if (c->ws && c->ws_owned) {
     B2_CUDA(cudaDeviceSynchronize());
@@ -214,8 +256,7 @@ int b2_timer_elapsed_ms(b2_timer t, float *ms_out) {
 }
 
 int b2_selftest_wait_timeout(b2_handle h, int timeout_us, void *stream) {
-  Context *c = h ? (Context *)h : default_context();
-  B2_REQUIRE(c != nullptr, B2_ERR_CUDA, "b2_selftest_wait_timeout: no context");
+  B2_CONTEXT(c, h, "b2_selftest_wait_timeout");
   B2_REQUIRE(timeout_us >= 1 && timeout_us <= 100000, B2_ERR_INVALID_ARG, "b2_selftest_wait_timeout: %d us not in 1..100000", timeout_us);
   wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((uint64_t)timeout_us * 1000ull,
                                                                     (int *)((char *)c->fixed + kFixedStatus));

@@ -21,8 +21,11 @@
 //                            stages half of the A rows and half of the B columns (64 KB per slab, 3
 //                            stages), the leader issues MMAs of M = 256 over both CTAs' tiles.  The
 //                            form chosen for large problems; same warp roles, same epilogue.
-// Both GEMM kernels have ABFT forms (template FT: checksums on the tensor cores or on the CUDA
-// cores, verification and repair in the shared epilogue).
+//   sgemm_3xtf32_pair_persistent_kernel  the default for large problems: as many clusters as the device
+//                            holds, each walking several 256 x 256 tiles with the accumulator double-buffered
+//                            in tensor memory; plain and ABFT (CUDA-core checksums) forms.
+// The one-tile kernels have ABFT forms with the checksums on the tensor cores or on the CUDA cores
+// (template FT); verification and repair sit in the shared epilogue.
 // Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
 #include <math.h>
 #include <stdlib.h>
@@ -55,11 +58,18 @@ constexpr int TBM = 128;
 // cores instead: S is then 8 rows of plain FP32 sums s_g[k] per 256-column tile, and the four
 // epilogue warps, idle during the mainloop, read each stage next to the MMAs (their own row of
 // A_hi and A_lo, all of S) and keep chk_g += (a_hi + a_lo) * s_g[k] for the 8 groups in registers.
-// No extra MMA, so the cost is a few percent instead of ~20 %, but an exact checksum does not
-// follow the truncation of the tensor cores' accumulators: the clean residual is 2.6x larger and
-// so is the default threshold.
+// No extra MMA, so the cost is a few percent instead of ~20 %.  An exact checksum does not follow
+// the truncation of the tensor cores' accumulators, whose sum over a group falls short of it by a
+// fraction of what the group held during the K loop; the checksum warps therefore also keep the sum
+// over the slabs of each running checksum, and the epilogue expects the shortfall (tf32_epilogue).
+// That brings the clean residual from 5.9e-6*K down to 4e-7*K at K = 8192 and lets the default
+// threshold sit at half the path's accuracy bound.
 constexpr int kFtRows = 32;                          // rows of S per 256-column tile (FT = 1; FT = 2 uses the first 8)
 constexpr int kFtTensor = 1, kFtCuda = 2;
+// Measured on B200: every 32-deep K-slab (twelve MMAs) costs an accumulator about 4e-7 of its value (the hardware
+// adds an MMA's products to the accumulator with truncation); the best fit is the same for uniform and normal
+// operands of any scale and any K from 256 to 8192.
+constexpr float kFtBiasPerSlab = 4e-7f;
 template <int TBN, int TBK, int FT = 0>
 struct Tf32Cfg {
   static constexpr int kTA = TBM * TBK * 4;          // bytes per A plane tile
@@ -67,7 +77,7 @@ struct Tf32Cfg {
   static constexpr int kTS = FT == kFtTensor ? kFtRows * TBK * 4 : FT == kFtCuda ? 8 * TBK * 4 : 0;  // bytes per checksum tile
   static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;
   static constexpr int kStages = ((FT ? 208 : 192) * 1024) / kStage;
-  static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 4096 : 0);   // + checksum table
+  static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 8192 : 0);   // + checksum table
   // FP32 accumulator: one TMEM column per output column; FT = 1: 16 more, rounded to a power of two
   static constexpr int kTmemCols = FT == kFtTensor ? 2 * TBN : TBN;
   static constexpr uint32_t kSwizzle = (TBK == 32) ? 2u : 4u;   // descriptor layout type: 128-byte / 64-byte swizzle
@@ -174,9 +184,11 @@ struct Tf32Args {
   int M, N, K, ldc;
   float alpha, beta;
   int vec_c;
-  int *status;
+  int *status;      // [0] sticky status word, [1] number of the launch that aborted (see record_timeout)
+  unsigned int seq; // number of this launch on its handle
   FtArgs ft;        // used by the FT instantiations only
   float tau_elem;   // an output further than this from its recomputed value is replaced
+  float ft_bias;    // FT = 2: expected loss of an accumulator per K-slab, as a fraction of its value (see tf32_epilogue)
 };
 
 // FP32 dot product of row `row` of A with column col0 + lane of B, from global memory (two
@@ -224,17 +236,27 @@ __device__ __forceinline__ FtInj ft_scan_plan(const Tf32Args &p, int my_row, int
 // reads every A row once (8 lanes x 16 bytes = one 128-byte row, conflict-free) and S once per
 // lane octet, and keeps 8 rows x 8 groups of partial sums in registers for the whole K loop.
 // The tiles are K-major under the 128-byte swizzle: chunk j of row x sits at chunk j ^ (x & 7).
+template <int RPL = 8>
 struct FtCudaAcc {
-  float v[8][8];   // [row i][group g]
+  float v[RPL][8];   // [row i][group g]: running checksum
+  float r[RPL][8];   // sum over the K-slabs so far of the running checksum (see tf32_epilogue: bias model)
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i)
+#pragma unroll
+      for (int g = 0; g < 8; ++g) v[i][g] = r[i][g] = 0.f;
+  }
 };
+// One K-slab: a warp covers 4 * RPL tile rows from row0 on; lane (rb, kc) takes rows row0 + rb + 4i, i < RPL.
+template <int RPL>
 __device__ __forceinline__ void ft_cuda_slab(const unsigned char *a_hi, const unsigned char *a_lo, const unsigned char *sg,
-                                             int row0, int lane, FtCudaAcc &acc) {
+                                             int row0, int lane, FtCudaAcc<RPL> &acc) {
   const int rb = lane >> 3, kc = lane & 7;
   float4 s4[8];
 #pragma unroll
   for (int g = 0; g < 8; ++g) s4[g] = *reinterpret_cast<const float4 *>(sg + g * 128 + ((kc ^ g) << 4));
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < RPL; ++i) {
     const int r = row0 + rb + 4 * i;
     const int off = r * 128 + ((kc ^ (r & 7)) << 4);
     const float4 h = *reinterpret_cast<const float4 *>(a_hi + off);
@@ -246,23 +268,33 @@ __device__ __forceinline__ void ft_cuda_slab(const unsigned char *a_hi, const un
       t = __fmaf_rn(a0, s4[g].x, t);
       t = __fmaf_rn(a1, s4[g].y, t);
       t = __fmaf_rn(a2, s4[g].z, t);
-      acc.v[i][g] = __fmaf_rn(a3, s4[g].w, t);
+      t = __fmaf_rn(a3, s4[g].w, t);
+      acc.v[i][g] = t;
+      acc.r[i][g] += t;
     }
   }
 }
-// End of the K loop: fold the eight k-chunk lanes of each row and leave chk[row][g] in the warp's
-// rows of the shared table (float [128][8]); the epilogue thread of a row reads its own entries.
-__device__ __forceinline__ void ft_cuda_finish(FtCudaAcc &acc, float *table, int row0, int lane) {
+// End of the K loop: fold the eight k-chunk lanes of each row and leave, per tile row, the 8 checksums and the 8
+// slab sums (less half the checksum: the checksum's mean over the slabs' MMAs) in the warp's rows of the shared
+// table (float [128][16]); the epilogue thread of a row reads its own entries.
+template <int RPL>
+__device__ __forceinline__ void ft_cuda_finish(FtCudaAcc<RPL> &acc, float *table, int row0, int lane) {
   const int rb = lane >> 3, kc = lane & 7;
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < RPL; ++i)
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
-      float t = acc.v[i][g];
+      float t = acc.v[i][g], u = acc.r[i][g];
       t += __shfl_xor_sync(0xffffffffu, t, 1);
+      u += __shfl_xor_sync(0xffffffffu, u, 1);
       t += __shfl_xor_sync(0xffffffffu, t, 2);
+      u += __shfl_xor_sync(0xffffffffu, u, 2);
       t += __shfl_xor_sync(0xffffffffu, t, 4);
-      if (kc == g) table[(row0 + rb + 4 * i) * 8 + g] = t;
+      u += __shfl_xor_sync(0xffffffffu, u, 4);
+      if (kc == g) {
+        table[(row0 + rb + 4 * i) * 16 + g] = t;
+        table[(row0 + rb + 4 * i) * 16 + 8 + g] = u - 0.5f * t;
+      }
     }
   __syncwarp();
 }
@@ -295,7 +327,11 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
         tmem_ld_wait();
         expect = __uint_as_float(e0) + __uint_as_float(e1);
       } else if (FT == kFtCuda) {
-        expect = chk_row[c];   // this row's entry of the shared table
+        // The tensor cores add each MMA's products to the accumulator with truncation, which pulls the
+        // accumulator toward zero by a fraction of its value that is about the same for every MMA; over the
+        // K loop a group of accumulators therefore loses ft_bias times the sum over the slabs of what the
+        // group held at the time, and that sum is what the checksum warps kept beside the checksum.
+        expect = chk_row[c] - p.ft_bias * chk_row[8 + c];
       }
       tmem_ld_wait();
     } else {
@@ -421,7 +457,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   {
     // an earlier CTA of this launch timed out: leave at once (one thread reads, so the whole CTA agrees)
     __shared__ int launch_aborted;
-    if (threadIdx.x == 0) launch_aborted = *reinterpret_cast<volatile int *>(p.status);
+    if (threadIdx.x == 0) launch_aborted = b2::launch_aborted(p.status, p.seq) ? 1 : 0;
     __syncthreads();
     if (launch_aborted != 0) return;
   }
@@ -515,11 +551,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     float *table = reinterpret_cast<float *>(smem + TSTAGES * kTStage + 256);
     if (FT == kFtCuda) {
       // checksums on the CUDA cores: follow the stages next to the MMA issuer
-      FtCudaAcc acc;
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int g = 0; g < 8; ++g) acc.v[i][g] = 0.f;
+      FtCudaAcc<8> acc;
+      acc.zero();
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % TSTAGES;
         if (!mbar_wait(&full[s], (uint32_t)(kb / TSTAGES) & 1u)) {
@@ -546,7 +579,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     ok = __all_sync(0xffffffffu, ok);   // the checksum pass below uses warp collectives
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 8);
+    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16);
   }
 
   tc_fence_before();
@@ -555,7 +588,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+  if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
 }
 
 // ---- CTA-pair form: one 256 x 256 output tile per cluster of two CTAs (tcgen05 cta_group::2) ----
@@ -577,7 +610,7 @@ struct PairCfg {
   static constexpr int kTS = FT == kFtTensor ? 2 * 8 * 32 * 4 : FT == kFtCuda ? 8 * 32 * 4 : 0;   // two 8-row slots / one S tile
   static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;   // 64 KB (+2 KB)
   static constexpr int kStages = 3;
-  static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 4096 : 0);   // + checksum table
+  static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 8192 : 0);   // + checksum table
   static constexpr int kTmemCols = FT == kFtTensor ? 512 : 256;
 };
 
@@ -596,6 +629,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   uint64_t *landed = acc_ready + 1;     // FT = 2, CTA 1: the leader's word that stage s is complete in both CTAs
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(landed + S);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *gate = abort_flag + 1;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
@@ -617,6 +651,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     }
     mbar_init(acc_ready, 1);
     *abort_flag = 0;
+    *gate = (rank == 0 && launch_aborted(p.status, p.seq)) ? 1 : 0;   // the leader decides for the pair
     mbar_fence_init();
     tma_prefetch_desc(&tmAh);
     tma_prefetch_desc(&tmAl);
@@ -632,8 +667,11 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   cluster_sync_all();      // barriers of both CTAs are initialised before anything remote signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // an earlier CTA of this launch timed out: both CTAs of the pair skip the work (tensor memory is still freed below)
+  const bool aborted = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(gate)), 0)) != 0;
 
-  if (warp == 0) {
+  if (aborted) {
+  } else if (warp == 0) {
     // ---- TMA producer (one per CTA) ------------------------------------------------------
     if (lane == 0) {
       for (int kb = 0; kb < nkb; ++kb) {
@@ -706,11 +744,8 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       // checksums on the CUDA cores: the leader's warps watch its "full" barrier, CTA 1's the word the
       // leader forwards once the stage is complete in both CTAs
       uint64_t *data_bar = (rank == 0) ? full : landed;
-      FtCudaAcc acc;
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int g = 0; g < 8; ++g) acc.v[i][g] = 0.f;
+      FtCudaAcc<8> acc;
+      acc.zero();
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % S;
         if (!mbar_wait(&data_bar[s], (uint32_t)(kb / S) & 1u)) {
@@ -736,7 +771,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 8);
+    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16);
   }
 
   // neither CTA leaves (or frees tensor memory) while the other may still be read by an MMA
@@ -746,7 +781,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, PC::kTmemCols);
   }
-  if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+  if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
 }
 
 // ---- persistent CTA-pair form (plain SGEMM only) -------------------------------------------------
@@ -767,11 +802,25 @@ __device__ __forceinline__ void pair_tile_origin(const Tf32Args &p, int t, uint3
   n0 = (within / band_rows) * 256;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+// FT = kFtCuda adds the ABFT form: eight more warps (6..13, 16 tile rows each) form the checksums of the tile being accumulated on the
+// CUDA cores, beside the MMAs, exactly as in the one-tile kernel, and leave them in one of two shared tables
+// (tab_full / tab_empty barriers, local to each CTA); the epilogue warps verify and repair the tile they drain
+// against the table of the same parity.  Checksum warps and epilogue warps are different warps here, so the
+// epilogue of tile i still overlaps the mainloop (MMAs and checksums) of tile i + 1.
+template <int FT>
+struct PersistCfg {
+  static constexpr int kThreads = FT ? 448 : 192;     // FT: 8 checksum warps of 16 tile rows each
+  static constexpr int kTable = FT ? 128 * 16 * 4 : 0;     // bytes per checksum table
+  static constexpr int kSmem = 1024 + PairCfg<FT>::kStages * PairCfg<FT>::kStage + 256 + 2 * kTable;
+};
+
+template <int FT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PersistCfg<FT>::kThreads, 1)
 sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
-                                    const Tf32Args p, int n_tiles) {
-  using PC = PairCfg<0>;
+                                    const __grid_constant__ CUtensorMap tmS, const Tf32Args p, int n_tiles) {
+  static_assert(FT == 0 || FT == kFtCuda, "the persistent form has plain and CUDA-core-checksum variants");
+  using PC = PairCfg<FT>;
   constexpr int S = PC::kStages, kTA = PC::kTA, kTB = PC::kTB, kStage = PC::kStage;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -779,8 +828,13 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
   uint64_t *empty = full + S;
   uint64_t *acc_full = empty + S;       // [2]
   uint64_t *acc_empty = acc_full + 2;   // [2], used in the leader
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  uint64_t *landed = acc_empty + 2;     // [S]  FT, CTA 1: the leader's word that stage s is complete in both CTAs
+  uint64_t *tab_full = landed + S;      // [2]  FT: the checksum warps have written table b
+  uint64_t *tab_empty = tab_full + 2;   // [2]  FT: the epilogue warps have read table b
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tab_empty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *gate = abort_flag + 1;
+  float *tables = reinterpret_cast<float *>(smem + S * kStage + 256);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
@@ -790,18 +844,23 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], FT ? 9 : 1);   // the MMA commit, and the eight checksum warps
+      mbar_init(&landed[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);   // four epilogue warps in each of the two CTAs
+      mbar_init(&tab_full[b], 8);
+      mbar_init(&tab_empty[b], 4);
     }
     *abort_flag = 0;
+    *gate = (rank == 0 && launch_aborted(p.status, p.seq)) ? 1 : 0;   // the leader decides for the pair
     mbar_fence_init();
     tma_prefetch_desc(&tmAh);
     tma_prefetch_desc(&tmAl);
     tma_prefetch_desc(&tmBh);
     tma_prefetch_desc(&tmBl);
+    if (FT) tma_prefetch_desc(&tmS);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -811,8 +870,11 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // an earlier CTA of this launch timed out: both CTAs of the pair skip the work (tensor memory is still freed below)
+  const bool aborted = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(gate)), 0)) != 0;
 
-  if (warp == 0) {
+  if (aborted) {
+  } else if (warp == 0) {
     // ---- TMA producer (one per CTA): one slab counter across all of this cluster's tiles ------
     if (lane == 0) {
       uint32_t it = 0;
@@ -834,6 +896,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
           tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
           tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
           tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
+          if (FT) tma_load_2d_pair(st + 2 * kTA + 2 * kTB, &tmS, leader_full, kb * 32, (n0 >> 8) * 8);
         }
       }
     }
@@ -860,6 +923,9 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
             break;
           }
           tc_fence_after();
+          // CTA 1's checksum warps cannot watch this barrier: forward the word (its tiles were written by its
+          // own TMA loads, whose completion this thread has just observed)
+          if (FT) mbar_arrive_remote(mapa_u32(smem_u32(&landed[s]), 1));
           const uint32_t st = smem_u32(smem + s * kStage);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
@@ -876,36 +942,71 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
         if (ok) umma_commit_pair(&acc_full[buf], (uint16_t)3);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ---- epilogue: warps 2..5 of each CTA ------------------------------------------------------
     const int q = warp & 3;
-    const FtInj inj;
     uint32_t n_done = 0;
     const uint32_t leader_empty0 = mapa_u32(smem_u32(&acc_empty[0]), 0), leader_empty1 = mapa_u32(smem_u32(&acc_empty[1]), 0);
     for (int t = cluster; t < n_tiles; t += n_clusters, ++n_done) {
       const uint32_t buf = n_done & 1u;
       int m0, n0;
       pair_tile_origin(p, t, rank, m0, n0);
+      FtInj inj;
+      if (FT) inj = ft_scan_plan<256>(p, m0 + q * 32 + lane, n0);
       bool done = false;
       const uint64_t t0 = global_timer_ns();
       for (int itw = 0; itw < (1 << 14) && !done; ++itw) {
         done = mbar_wait(&acc_full[buf], (n_done >> 1) & 1u, 1u << 10);
         if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
       }
+      if (FT && done) done = mbar_wait(&tab_full[buf], (n_done >> 1) & 1u);
       const bool ok = __all_sync(0xffffffffu, done);
       if (!ok) {
         *abort_flag = 1;
         break;
       }
       tc_fence_after();
-      tf32_epilogue<256, 0>(p, tmem_base + buf * 256u, q, lane, m0, n0, true, nkb, inj, nullptr);
+      tf32_epilogue<256, FT>(p, tmem_base + buf * 256u, q, lane, m0, n0, true, nkb, inj,
+                             tables + buf * (PersistCfg<FT>::kTable / 4) + (q * 32 + lane) * 16);
       // this warp's reads of the buffer are complete (every chunk waited for its tcgen05.ld): hand it back
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         if (rank == 0) mbar_arrive(&acc_empty[buf]);
         else mbar_arrive_remote(buf ? leader_empty1 : leader_empty0);
+        if (FT) mbar_arrive(&tab_empty[buf]);
       }
+    }
+  } else if (FT) {
+    // ---- checksum warps 6..13, 16 tile rows each: follow the stages beside the MMA issuer --------
+    const int row0 = (warp - 6) * 16;
+    uint64_t *data_bar = (rank == 0) ? full : landed;
+    uint32_t it = 0, n_done = 0;
+    bool ok = true;
+    for (int t = cluster; t < n_tiles && ok; t += n_clusters, ++n_done) {
+      FtCudaAcc<4> acc;
+      acc.zero();
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % S;
+        if (!mbar_wait(&data_bar[s], (it / S) & 1u)) {
+          ok = false;
+          break;
+        }
+        const unsigned char *st = smem + s * kStage;
+        ft_cuda_slab(st, st + kTA, st + 2 * kTA + 2 * kTB, row0, lane, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      const uint32_t buf = n_done & 1u;
+      // the epilogue warps have read this table (two tiles ago)
+      if (ok && !mbar_wait(&tab_empty[buf], ((n_done >> 1) & 1u) ^ 1u)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        *abort_flag = 1;
+        break;
+      }
+      ft_cuda_finish(acc, tables + buf * (PersistCfg<FT>::kTable / 4), row0, lane);
+      if (lane == 0) mbar_arrive(&tab_full[buf]);
     }
   }
 
@@ -915,13 +1016,14 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, 512);
   }
-  if (tid == 0 && *abort_flag) atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+  if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
 }
 
 static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
 static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 static int g_tf32_abft = kFtCuda;  // where the ABFT checksums are formed: 1 tensor cores, 2 CUDA cores
-static int g_tf32_persistent = 1;  // 1: the plain CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
+static int g_tf32_persistent = 1;  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
+static float g_tf32_ft_bias = -1.f;  // < 0: default
 static int g_tf32_pair = 1;    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
@@ -933,13 +1035,9 @@ size_t tf32_workspace_bytes(int M, int N, int K) {
 }
 
 template <int TBN, int TBK, int FT>
-static int launch_tf32(const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_kernel<TBN, TBK, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Tf32Cfg<TBN, TBK, FT>::kSmem));
-    configured = true;
-  }
+static int launch_tf32(const Context *ctx, const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
+  int st = ensure_func_attributes((const void *)sgemm_3xtf32_kernel<TBN, TBK, FT>, ctx->device, Tf32Cfg<TBN, TBK, FT>::kSmem);
+  if (st != B2_OK) return st;
   sgemm_3xtf32_kernel<TBN, TBK, FT><<<grid, 192, Tf32Cfg<TBN, TBK, FT>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3],
                                                                                       maps[4], args);
   B2_CUDA(cudaGetLastError());
@@ -951,11 +1049,10 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
 size_t ffma_workspace_bytes(int M, int N, int K);
 
 // How many CTA pairs the device runs at once (one CTA per SM; a pair needs two SMs of one cluster
-// domain).  Asked of the occupancy API once per process; 0 (pairs are then not chosen automatically)
+// domain).  Asked of the occupancy API once per device and handle; 0 (pairs are then not chosen automatically)
 // if it will not say, e.g. on a partition that cannot schedule clusters.
 static int max_resident_pairs(Context *ctx) {
-  static int cached = -1;
-  if (cached >= 0) return cached;
+  if (ctx->max_pairs >= 0) return ctx->max_pairs;
   int n = 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -969,13 +1066,13 @@ static int max_resident_pairs(Context *ctx) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtTensor>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtTensor>::kSmem) != cudaSuccess ||
+  if (ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtTensor>, ctx->device, PairCfg<kFtTensor>::kSmem) != B2_OK ||
       cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<kFtTensor>, &cfg) != cudaSuccess || n <= 0) {
     (void)cudaGetLastError();
     n = 0;
   }
-  cached = n;
-  return cached;
+  ctx->max_pairs = n;
+  return n;
 }
 
 // ft == NULL: plain 3xTF32 SGEMM; otherwise the ABFT form (checksum operand, verification and
@@ -990,11 +1087,12 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   const int ftm = ft ? g_tf32_abft : 0;
   FtArgs ftl;
   if (ft) {
-    // Default thresholds for operands of unit scale, each about 4.5x the largest residual of a clean
-    // 8192^3 product (more at smaller K): checksums accumulated by the tensor cores follow their
-    // truncation (residual 2.2e-6*K), exact checksums from the CUDA cores do not (5.8e-6*K).
+    // Default thresholds for operands of unit scale.  Checksums on the CUDA cores, corrected for the tensor
+    // cores' truncation (ft_bias, see tf32_epilogue), leave a clean residual of at most 4.7e-7*K (K = 256 .. 8192,
+    // uniform and normal data): 2.5e-6*K is five times that and half the path's tolerance of 2e-5*sum|a||b|
+    // (5e-6*K for operands uniform in [-1, 1)).  Checksums accumulated by the tensor cores: residual 2.2e-6*K.
     ftl = *ft;
-    if (!(ftl.tau > 0.f)) ftl.tau = fmaxf((ftm == kFtTensor ? 1e-5f : 2.6e-5f) * (float)K, 2e-4f);
+    if (!(ftl.tau > 0.f)) ftl.tau = ftm == kFtTensor ? fmaxf(1e-5f * (float)K, 2e-4f) : fmaxf(2.5e-6f * (float)K, 6e-5f);
     ft = &ftl;
   }
   const int kp = (K + 3) & ~3;
@@ -1053,28 +1151,28 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     pa.C = C; pa.M = M; pa.N = N; pa.K = K; pa.ldc = ldc; pa.alpha = alpha; pa.beta = beta;
     pa.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
     pa.status = (int *)((char *)ctx->fixed + kFixedStatus);
+    pa.seq = next_launch_seq(ctx);
     if (ft) {
       pa.ft = *ft;
-      pa.tau_elem = 0.5f * ft->tau;
+      pa.tau_elem = (ftm == kFtCuda ? 0.75f : 0.5f) * ft->tau;
+      pa.ft_bias = g_tf32_ft_bias >= 0.f ? g_tf32_ft_bias : kFtBiasPerSlab;
     }
-    static bool pair_configured = false;
-    if (!pair_configured) {
-      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<0>::kSmem));
-      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtTensor>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtTensor>::kSmem));
-      B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_kernel<kFtCuda>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<kFtCuda>::kSmem));
-      pair_configured = true;
-    }
-    if (ftm == 0 && g_tf32_persistent) {
-      static bool persistent_configured = false;
-      if (!persistent_configured) {
-        B2_CUDA(cudaFuncSetAttribute(sgemm_3xtf32_pair_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<0>::kSmem));
-        persistent_configured = true;
-      }
+    if ((ftm == 0 || ftm == kFtCuda) && g_tf32_persistent) {
+      const void *fn = ftm ? (const void *)sgemm_3xtf32_pair_persistent_kernel<kFtCuda> : (const void *)sgemm_3xtf32_pair_persistent_kernel<0>;
+      st = ensure_func_attributes(fn, ctx->device, ftm ? PersistCfg<kFtCuda>::kSmem : PersistCfg<0>::kSmem);
+      if (st != B2_OK) return st;
       const int clusters = pairs < slots ? pairs : (slots > 0 ? slots : pairs);
-      sgemm_3xtf32_pair_persistent_kernel<<<2 * clusters, 192, PairCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], pa, pairs);
+      if (ftm == kFtCuda)
+        sgemm_3xtf32_pair_persistent_kernel<kFtCuda><<<2 * clusters, PersistCfg<kFtCuda>::kThreads, PersistCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa, pairs);
+      else
+        sgemm_3xtf32_pair_persistent_kernel<0><<<2 * clusters, PersistCfg<0>::kThreads, PersistCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa, pairs);
       B2_CUDA(cudaGetLastError());
       return B2_OK;
     }
+    st = ftm == kFtTensor ? ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtTensor>, ctx->device, PairCfg<kFtTensor>::kSmem)
+         : ftm == kFtCuda ? ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtCuda>, ctx->device, PairCfg<kFtCuda>::kSmem)
+                          : ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<0>, ctx->device, PairCfg<0>::kSmem);
+    if (st != B2_OK) return st;
     if (ftm == kFtTensor) sgemm_3xtf32_pair_kernel<kFtTensor><<<2 * pairs, 192, PairCfg<kFtTensor>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     else if (ftm == kFtCuda) sgemm_3xtf32_pair_kernel<kFtCuda><<<2 * pairs, 192, PairCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     else sgemm_3xtf32_pair_kernel<0><<<2 * pairs, 192, PairCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
@@ -1101,14 +1199,16 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
+  args.seq = next_launch_seq(ctx);
   const int grid = ((M + TBM - 1) / TBM) * ((N + tbn - 1) / tbn);
   if (ft) {
     args.ft = *ft;
-    args.tau_elem = 0.5f * ft->tau;
-    return ftm == kFtTensor ? launch_tf32<256, 32, kFtTensor>(maps, args, grid, s) : launch_tf32<256, 32, kFtCuda>(maps, args, grid, s);
+    args.tau_elem = (ftm == kFtCuda ? 0.75f : 0.5f) * ft->tau;
+    args.ft_bias = g_tf32_ft_bias >= 0.f ? g_tf32_ft_bias : kFtBiasPerSlab;
+    return ftm == kFtTensor ? launch_tf32<256, 32, kFtTensor>(ctx, maps, args, grid, s) : launch_tf32<256, 32, kFtCuda>(ctx, maps, args, grid, s);
   }
-  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, 0>(maps, args, grid, s) : launch_tf32<256, 32, 0>(maps, args, grid, s);
-  return tbn == 128 ? launch_tf32<128, 16, 0>(maps, args, grid, s) : launch_tf32<256, 16, 0>(maps, args, grid, s);
+  if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 32, 0>(ctx, maps, args, grid, s);
+  return tbn == 128 ? launch_tf32<128, 16, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 16, 0>(ctx, maps, args, grid, s);
 }
 
 }  // namespace b2
@@ -1146,6 +1246,13 @@ int b2_set_tf32_abft_mode(int mode) {
 int b2_set_tf32_persistent(int on) {
   B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_tf32_persistent: %d is not 0 or 1", on);
   b2::g_tf32_persistent = on;
+  return B2_OK;
+}
+// Fraction of its value that an accumulator is taken to lose per 32-deep K-slab to the tensor cores' truncating
+// adds (CUDA-core checksums only); negative restores the built-in figure measured on B200.
+int b2_set_tf32_abft_bias(float bias) {
+  B2_REQUIRE(bias < 1e-3f, B2_ERR_INVALID_ARG, "b2_set_tf32_abft_bias: %g is not a plausible loss per K-slab", (double)bias);
+  b2::g_tf32_ft_bias = bias;
   return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.

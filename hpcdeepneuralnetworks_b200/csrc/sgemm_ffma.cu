@@ -62,7 +62,9 @@ struct FfmaArgs {
   int M, N, K, ldc;
   float alpha, beta;
   int vec_c;    // C rows are 16-byte aligned: 128-bit epilogue
-  int *status;  // device status word: set to B2_ERR_TIMEOUT if a bounded wait runs out
+  int *status;  // device status words: [0] set to B2_ERR_TIMEOUT if a bounded wait runs out, [1] the number of that launch
+  unsigned int seq;   // number of this launch on its handle
+  int device;         // host side only: the device the launch goes to
 };
 
 // ABFT arguments.  Checksum algebra of kernel/ft_sgemm/README.md:4-14 at the granularity the
@@ -256,7 +258,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   {
     // an earlier CTA of this launch timed out: leave at once (one thread reads, so the whole CTA agrees)
     __shared__ int launch_aborted;
-    if (threadIdx.x == 0) launch_aborted = *reinterpret_cast<volatile int *>(p.status);
+    if (threadIdx.x == 0) launch_aborted = b2::launch_aborted(p.status, p.seq) ? 1 : 0;
     __syncthreads();
     if (launch_aborted != 0) return;
   }
@@ -517,7 +519,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
   if (!ok) {
-    atomicExch(p.status, (int)B2_ERR_TIMEOUT);
+    record_timeout(p.status, p.seq);
     return;
   }
 
@@ -692,12 +694,8 @@ template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
 static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s,
                        const FtArgs &ft) {
   using Cfg = TileCfg<BM, NR>;
-  static bool configured = false;
-  if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-    B2_CUDA(cudaFuncSetAttribute(sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    configured = true;
-  }
+  int st = ensure_func_attributes((const void *)sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, args.device, Cfg::kSmem, 100);
+  if (st != B2_OK) return st;
   sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
@@ -843,6 +841,8 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
+  args.seq = next_launch_seq(ctx);
+  args.device = ctx->device;
   const int grid = ((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
   FtArgs none = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, 0, 0};
   const int packed = (ft != nullptr || ffma_variant() != 0) ? 1 : 0;
@@ -915,8 +915,7 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
     B2_REQUIRE(lda >= K, B2_ERR_INVALID_ARG, "b2_ft_sgemm: lda = %d < K = %d", lda, K);
     B2_REQUIRE(ldb >= N, B2_ERR_INVALID_ARG, "b2_ft_sgemm: ldb = %d < N = %d", ldb, N);
   }
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ft_sgemm: no context (%s)", b2_last_error());
+  B2_CONTEXT(ctx, h, "b2_ft_sgemm");
   FtArgs ft;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
@@ -952,8 +951,7 @@ int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const
   B2_REQUIRE(n_faults >= 0 && (n_faults == 0 || plan_dev != nullptr), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: bad fault plan");
   if (M == 0 || N == 0) return B2_OK;
   B2_REQUIRE(C != nullptr && (K == 0 || (A != nullptr && B != nullptr)), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: null matrix");
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_ft_sgemm_colmajor_nt: no context (%s)", b2_last_error());
+  B2_CONTEXT(ctx, h, "b2_ft_sgemm_colmajor_nt");
   FtArgs ft;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
@@ -1021,14 +1019,13 @@ int b2_set_ffma_tile(int i) {
 
 // Reads and clears the device status word that bounded waits set; synchronises the stream.
 int b2_check_status(b2_handle h, void *stream) {
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_check_status: no context");
+  B2_CONTEXT(ctx, h, "b2_check_status");
   int v = 0;
   int *dev = (int *)((char *)ctx->fixed + kFixedStatus);
   B2_CUDA(cudaMemcpyAsync(&v, dev, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   B2_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (v != 0) {
-    B2_CUDA(cudaMemsetAsync(dev, 0, 4, (cudaStream_t)stream));
+    B2_CUDA(cudaMemsetAsync(dev, 0, 8, (cudaStream_t)stream));   // the status word and the aborted launch's number
     set_error("a kernel reported status %d (%s)", v, b2_status_string(v));
   }
   return v;
@@ -1047,8 +1044,7 @@ int b2_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const floa
     B2_REQUIRE(ldb >= N, B2_ERR_INVALID_ARG, "b2_sgemm: ldb = %d < N = %d", ldb, N);
   }
   B2_REQUIRE(((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C)) & 3) == 0, B2_ERR_INVALID_ARG, "b2_sgemm: matrices must be 4-byte aligned");
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_sgemm: no context (%s)", b2_last_error());
+  B2_CONTEXT(ctx, h, "b2_sgemm");
   if (path == B2_PATH_3XTF32)
     return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, nullptr, (cudaStream_t)stream);
   return sgemm_ffma_dispatch(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, (cudaStream_t)stream);

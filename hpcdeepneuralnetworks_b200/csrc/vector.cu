@@ -345,8 +345,7 @@ int b2_saxpy(b2_handle h, int64_t n, float alpha, const float *x, float *y, void
   if (n == 0) return B2_OK;
   B2_REQUIRE(x != nullptr && y != nullptr, B2_ERR_INVALID_ARG, "b2_saxpy: null vector");
   B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_saxpy: vectors must be 4-byte aligned");
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_saxpy: no context (%s)", b2_last_error());
+  B2_CONTEXT(ctx, h, "b2_saxpy");
   int64_t head = ((16 - ((uintptr_t)y & 15)) & 15) >> 2;
   if (head > n) head = n;
   const int64_t n4 = (n - head) >> 2;
@@ -364,8 +363,7 @@ int b2_sdot_partial(b2_handle h, int64_t n, const float *x, const float *y, floa
   B2_REQUIRE(result_dev != nullptr, B2_ERR_INVALID_ARG, "b2_sdot: result pointer is NULL");
   B2_REQUIRE(n == 0 || (x != nullptr && y != nullptr), B2_ERR_INVALID_ARG, "b2_sdot: null vector");
   B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_sdot: vectors must be 4-byte aligned");
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_sdot: no context (%s)", b2_last_error());
+  B2_CONTEXT(ctx, h, "b2_sdot");
   char *fixed = (char *)ctx->fixed;
   double *partials = (double *)(fixed + kFixedSdotPartials);
   unsigned int *ticket = (unsigned int *)(fixed + kFixedSdotTicket);
@@ -384,8 +382,7 @@ int b2_sdot(b2_handle h, int64_t n, const float *x, const float *y, float *resul
 
 int b2_sdot_fused(b2_handle h, int64_t n, const float *x, const float *y, float *result_dev, double *sum_dev,
                   void *const *mailboxes, int rank, int world, uint64_t seq, void *stream) {
-  Context *ctx = h ? (Context *)h : default_context();
-  B2_REQUIRE(ctx != nullptr, B2_ERR_CUDA, "b2_sdot_fused: no context (%s)", b2_last_error());
+  B2_CONTEXT(ctx, h, "b2_sdot_fused");
   B2_REQUIRE(n >= 0 && result_dev != nullptr, B2_ERR_INVALID_ARG, "b2_sdot_fused: bad arguments");
   B2_REQUIRE(n == 0 || (x != nullptr && y != nullptr), B2_ERR_INVALID_ARG, "b2_sdot_fused: null vector");
   B2_REQUIRE(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0, B2_ERR_INVALID_ARG, "b2_sdot_fused: vectors must be 4-byte aligned");

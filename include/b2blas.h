@@ -51,7 +51,8 @@ int b2_version(void);
  * or supplied by the caller with b2_set_workspace (no allocation inside the library).
  * The scratch is shared by every call made on the handle: calls on one handle must be ordered
  * on one stream (or otherwise serialised); work on several streams takes one handle per stream.
- * A NULL handle means a default handle per device, with the same rule. */
+ * A NULL handle means a default handle per device, with the same rule.  A handle belongs to the device that was
+ * current in b2_create; calls that pass it while another device is current return B2_ERR_INVALID_ARG. */
 int b2_create(b2_handle *out);
 int b2_destroy(b2_handle h);
 int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
@@ -127,11 +128,14 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
  * 3*rms(A)*rms(B), measured by one extra pass over A and B, for operands of any scale.  The
  * reference uses a fixed 0.1 (kernel/ft_sgemm/include/ft_sgemm_huge.cuh:30).
  * `report_dev`: optional device b2_ft_report that this call ADDS to (caller zeroes it).
- * path = B2_PATH_3XTF32: one checksum per output row and group of 32 columns, formed during the
- * mainloop; a group out of tolerance is recomputed in FP32 from A and B and every output
- * further than tau/2 from its recomputed value is replaced.  Default tau there is 2.6e-5*K (1e-5*K
- * with b2_set_tf32_abft_mode(1)): the tensor cores' truncating accumulation leaves a residual of up
- * to 5.8e-6*K (2.2e-6*K) on clean data of unit scale.
+ * path = B2_PATH_3XTF32: one checksum per output row and group of 32 columns, formed on the CUDA cores beside
+ * the MMAs and corrected for what the tensor cores' truncating accumulation takes from a group over the K loop
+ * (see b2_set_tf32_abft_bias); a group out of tolerance is recomputed in FP32 from A and B and every output further
+ * than 0.75*tau from its recomputed value is replaced.  Default tau there is 2.5e-6*K: five times the largest
+ * residual of clean products (4.7e-7*K for K = 256..8192) and half the path's accuracy bound of
+ * 2e-5*sum_k|a||b| (5e-6*K for operands uniform in [-1, 1)), so a fault that would break that bound is always
+ * found and repaired.  Operands that are all of one sign make the tensor cores' loss coherent (the plain 3xTF32
+ * product itself then drifts to 1e-4 at K = 8192): use the FFMA path for such data.
  * Needs the workspace of b2_sgemm_workspace_bytes(B2_PATH_3XTF32, ...). */
 int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda,
                 const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
@@ -256,16 +260,24 @@ int b2_set_tf32_slab_k(int k);
  * against 128x128 single-CTA tiles by whole waves (default), 2 always.  A width pinned with b2_set_tf32_tile_n
  * selects the single-CTA kernel of that width. */
 int b2_set_tf32_pair(int on);
-/* 1 (default): the plain CTA-pair kernel is persistent (as many clusters as the device holds, each walking several
- * tiles, accumulator double-buffered in tensor memory so that a tile's epilogue overlaps the next tile's MMAs);
- * 0: one cluster per tile. */
+/* 1 (default): the CTA-pair kernels, plain and ABFT with CUDA-core checksums, are persistent (as many clusters as
+ * the device holds, each walking several tiles, accumulator double-buffered in tensor memory so that a tile's
+ * epilogue overlaps the next tile's MMAs); 0: one cluster per tile. */
 int b2_set_tf32_persistent(int on);
 /* Where b2_ft_sgemm(path = B2_PATH_3XTF32) forms its checksums: 2 (default) on the CUDA cores beside the MMAs
- * (few percent overhead, default tau 2.6e-5*K), 1 on the tensor cores as two extra small MMAs per K-step
- * (about +20 %, default tau 1e-5*K: such checksums follow the accumulators' truncation more closely). */
+ * (few percent overhead, default tau 2.5e-6*K), 1 on the tensor cores as two extra small MMAs per K-step
+ * (about +20 %, default tau 1e-5*K, which is above the path's accuracy bound: kept for comparison only). */
 int b2_set_tf32_abft_mode(int mode);
+/* The tensor cores add each MMA's products to the accumulator with truncation, which costs an accumulator a
+ * fraction of its value per K-slab of 32 (about 4e-7 on B200, the built-in figure; the same for uniform and normal
+ * operands of any scale).  The CUDA-core checksums keep, beside each checksum, its sum over the K-slabs, and the
+ * verification expects the group sum to fall short of the checksum by `bias` times that sum.  bias < 0 restores the
+ * built-in figure; 0 switches the correction off (the clean residual is then 15 times larger). */
+int b2_set_tf32_abft_bias(float bias);
 /* Reads and clears the device status word that bounded waits set; synchronises the stream.
- * Returns 0 or the recorded negative status. */
+ * Returns 0 or the recorded negative status.  The word is sticky until it is read here, but it does not stop later
+ * work: a wait that runs out ends only the launch it happened in (that launch's output is then incomplete), and
+ * launches made afterwards on the handle run normally. */
 int b2_check_status(b2_handle h, void *stream);
 
 /* Self-test of the bounded-wait path: one block waits `timeout_us` (1..100000) on a barrier that

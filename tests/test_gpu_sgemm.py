@@ -420,6 +420,40 @@ def test_bounded_wait_times_out_and_context_survives(cuda):
     assert L.b2_selftest_wait_timeout(h.raw, 0, None) == -1
 
 
+def test_unchecked_timeout_does_not_stop_later_launches(cuda):
+    """A timeout that nobody has read yet (the status word is sticky until b2_check_status) must not turn later SGEMMs
+    into no-ops: every kernel form still computes, and the recorded status is still there to be read afterwards."""
+    import hpcdeepneuralnetworks_b200 as b2
+    from hpcdeepneuralnetworks_b200 import _lib
+    L = _lib.load()
+    h = b2.default_handle()
+    assert L.b2_selftest_wait_timeout(h.raw, 2000, None) == 0
+    torch.cuda.synchronize()
+    a, b, c = mats(256, 512, 96)
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+
+    def run(path):                       # run_gpu without its status check
+        dc = dev(c)
+        b2.sgemm(256, 512, 96, 1.0, dev(a), dev(b), 0.5, dc, path=path)
+        return dc.cpu().numpy()
+    assert np.array_equal(run(0), oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    try:
+        for pair, persistent in ((0, 0), (2, 0), (2, 1)):
+            b2.set_tf32_pair(pair)
+            b2.set_tf32_persistent(persistent)
+            assert oracle.gemm_error(run(1), c64, den) <= TOL_3XTF32
+            da, db, dc = dev(a), dev(b), dev(c)
+            b2.ft_sgemm(256, 512, 96, 1.0, da, db, 0.5, dc, path=1)
+            assert oracle.gemm_error(dc.cpu().numpy(), c64, den) <= TOL_3XTF32
+    finally:
+        b2.set_tf32_pair(1)
+        b2.set_tf32_persistent(1)
+    with pytest.raises(b2.B2Error) as e:
+        b2.check_status()
+    assert e.value.status == -4
+    b2.check_status()
+
+
 @pytest.mark.parametrize("shape", [(128, 2048, 32), (130, 2052, 70), (257, 2304, 129), (1024, 3072, 512)])
 def test_ffma_transposed_a_route_is_bit_identical(cuda, shape):
     """With scratch available the FFMA path first transposes a row-major A (K-major A tiles are faster); every output
