@@ -32,12 +32,21 @@ METRIC = "SGEMM TFLOPS @6144^3 fp32"
 N1 = 6144
 NMULTI = 32768
 CPU_SAMPLE_N = 1152          # reference CPU GEMM sample: 1152^3 = (3/16 * 6144)^3, about 1/152 of the flop
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the committed
-# ncu captures (profiles/), scaled to a full launch; None until a capture exists for that kernel.
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the bench's own size (profiles/):
-# the K-major FFMA kernel, the CTA-pair 3xTF32 kernel (band-ordered tile walk), SAXPY and SDOT at 2^28 (scaled from 2^26).
-NCU_TRAFFIC = {"sgemm_ffma_6144": 1.342616e9 + 141.759e6, "sgemm_3xtf32_6144": 2.140627e9 + 139.310e6,
-               "saxpy_2p28": 4 * (536.936e6 + 221.76e6), "sdot_2p28": 4 * (536.8855e6 + 4.07e6)}
+
+
+def ncu_traffic(key):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the table of ncu captures
+    kept in profiles/dram_traffic.md (one row per kernel and size: | key | read bytes | write bytes | capture |);
+    None when no capture of that kernel at that size has been recorded."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    try:
+        for line in open(path):
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) >= 3 and cells[0] == key:
+                return float(cells[1]) + float(cells[2])
+    except (OSError, ValueError):
+        pass
+    return None
 
 
 def load_peaks():
@@ -56,7 +65,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.samples, self.stop_flag, self.thread = index, [], False, None
+        self.index, self.samples, self.stop_flag, self.thread, self.label = index, [], False, None, None
 
     def _nvml_handle(self):
         """NVML handle of this process's CUDA device `index` (by PCI bus id, so that CUDA_VISIBLE_DEVICES does not
@@ -87,7 +96,7 @@ class ClockSampler:
                         rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
                     except Exception:
                         rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                    self.samples.append([str(mhz), str(mx)] + [("Active" if rs & b else "Not Active") for _, b in bits])
+                    self.samples.append([str(mhz), str(mx)] + [("Active" if rs & b else "Not Active") for _, b in bits] + [self.label])
                     time.sleep(0.004)
                 return
             except Exception:
@@ -97,7 +106,7 @@ class ClockSampler:
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
                                      capture_output=True, text=True, timeout=5).stdout.strip()
                 if out:
-                    self.samples.append([v.strip() for v in out.split(",")])
+                    self.samples.append([v.strip() for v in out.split(",")][:6] + [self.label])
             except Exception:
                 pass
             time.sleep(0.1)
@@ -111,9 +120,12 @@ class ClockSampler:
         self.stop_flag = True
         self.thread.join(timeout=10)
 
-    def summary(self):
+    def summary(self, label=None):
+        """All samples, or those taken while `label` was set (the interleaved legs)."""
         mhz, mx, reasons = [], 0, set()
         for s in self.samples:
+            if label is not None and (len(s) < 7 or s[6] != label):
+                continue
             try:
                 mhz.append(int(float(s[0])))
                 mx = max(mx, int(float(s[1])))
@@ -145,6 +157,96 @@ def timed(fn, steps, warmup, dist_barrier=None):
     if dist_barrier:
         dist_barrier()
     return beg.elapsed_time(end) / steps
+
+
+def timed_interleaved(legs, rounds=8, reps=5, clk=None):
+    """Times several alternatives under the same conditions: A, B, A, B, ... for `rounds` rounds, each turn a block of
+    `reps` back-to-back calls between its own event pair, followed by a synchronize.  `clk` (a running ClockSampler)
+    is told which leg is on, so that every leg gets its own clock record.  Returns {leg: {"ms": median over the
+    blocks, "ms_min", "ms_all", "clocks": {...}, "ms_x_ghz": median ms times median SM GHz}}."""
+    import torch
+    for fn in legs.values():
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    out = {k: [] for k in legs}
+    for _ in range(rounds):
+        for k, fn in legs.items():
+            if clk is not None:
+                clk.label = k
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if clk is not None:
+                clk.label = None
+            out[k].append(e0.elapsed_time(e1) / reps)
+    res = {}
+    for k, v in out.items():
+        sv = sorted(v)
+        med = sv[len(sv) // 2]
+        c = clk.summary(k) if clk is not None else None
+        res[k] = {"ms": med, "ms_min": sv[0], "ms_all": v, "clocks": c,
+                  "ms_x_ghz": (med * c["sm_mhz"] / 1e3) if c and c.get("sm_mhz") else None}
+    return res
+
+
+def sampled_rows_error(torch, A_rows, B, C_rows, chunk=4096):
+    """max |C - C_ref| / (|A| |B|) over a few rows of a product C = A B (alpha = 1, beta = 0): the reference rows are
+    double-precision dot products formed on the device in column chunks (checker only; nothing of the library runs)."""
+    worst = 0.0
+    a64 = A_rows.double()
+    for c0 in range(0, B.shape[1], chunk):
+        b64 = B[:, c0:c0 + chunk].double()
+        ref = a64 @ b64
+        den = a64.abs() @ b64.abs()
+        err = ((C_rows[:, c0:c0 + chunk].double() - ref).abs() / den.clamp_min(1e-30)).max().item()
+        worst = max(worst, float(err))
+        del b64, ref, den
+    return worst
+
+
+def abft_fault_report(b2, torch, n, path):
+    """Benchmark configuration 3 at one size and math path: a clean run (false alarms, output identical to the plain
+    kernel) and the seeded plan of one bit flip (bit 20..30 of a random accumulator) per 64 output tiles."""
+    tol = 1e-5 if path == 0 else 2e-5
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    plain = torch.zeros((n, n), device="cuda")
+    b2.sgemm(n, n, n, 1.0, A, B, 0.0, plain, path=path)
+    out = torch.zeros((n, n), device="cuda")
+    rep = b2.new_report()
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, path=path, report=rep)
+    clean = b2.read_report(rep)
+    clean_same = bool(torch.equal(out, plain)) if path == 0 else bool(((out - plain).abs().max() == 0).item())
+    plan = b2.seeded_fault_plan(n, n, n, seed=6)
+    rep = b2.new_report()
+    out.zero_()
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, path=path, plan=b2.make_plan(plan), report=rep)
+    b2.check_status()
+    r = b2.read_report(rep)
+    left = (out != plain)
+    n_left = int(left.sum().item())
+    worst = 0.0
+    if n_left:
+        old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            idx = left.nonzero()
+            rows = idx[:, 0].unique()
+            den = (A[rows].abs() @ B.abs())
+            dev = (out[rows] - plain[rows]).abs() / den
+            worst = float(dev.max().item())
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = old
+    return {"n": n, "planned": int(len(plan)), "injected": r["injected"], "detected": r["detected"], "corrected": r["corrected"],
+            "false_alarms": r["false_alarms"], "clean_run": {"false_alarms": clean["false_alarms"], "detected": clean["detected"],
+                                                            "identical_to_plain_kernel": clean_same},
+            "outputs_differing_from_plain_kernel": n_left,
+            "largest_remaining_deviation_over_abs_a_abs_b": worst, "tolerance": tol,
+            "every_fault_beyond_tolerance_corrected": bool(worst <= tol)}
 
 
 def cpu_reference_gemm_tflops(n, reps):
@@ -232,13 +334,13 @@ def bench_vectors(b2, torch, peaks, steps, warmup, log2n=28):
     gbs = 12.0 * n / (ms * 1e-3) / 1e9
     out["saxpy"] = {"n": n, "ms": ms, "value": gbs, "unit": "GB/s",
                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                 "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["saxpy_2p28"],
+                                 "frac": gbs / peaks["hbm_gbs"], "traffic": ncu_traffic("saxpy_2p28"),
                                  "algorithmic_bytes": 12 * n, "peak_source": peaks["source"], "frac_of_8TBs_spec": gbs / 8000.0}}
     ms = timed(lambda: b2.sdot(n, x, y, res), steps, warmup)
     gbs = 8.0 * n / (ms * 1e-3) / 1e9
     out["sdot"] = {"n": n, "ms": ms, "value": gbs, "unit": "GB/s",
                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["sdot_2p28"],
+                                "frac": gbs / peaks["hbm_gbs"], "traffic": ncu_traffic("sdot_2p28"),
                                 "algorithmic_bytes": 8 * n, "peak_source": peaks["source"], "frac_of_8TBs_spec": gbs / 8000.0}}
     return out
 
@@ -375,6 +477,43 @@ def run_sweep(args):
     return 0
 
 
+def single_gpu_anchors(b2, torch, peaks, ffma_peak, n=NMULTI, panel=4096):
+    """The workloads of the multi-GPU lines on ONE GPU, through the same entry points (b2_mg_sgemm with a world of one:
+    the K-panel schedule without a broadcast; b2_mg_sdot), so that N-GPU values can be divided by a 1-GPU value of the
+    same workload: SGEMM 32768^3 (alpha = 1, beta = 0) and SDOT over 2^30 elements."""
+    from hpcdeepneuralnetworks_b200 import dist as b2dist
+    out = {}
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1000)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    Cm = torch.zeros((n, n), device="cuda")
+    ms = timed(lambda: b2dist.sharded_sgemm(n, n, n, 1.0, A, B, 0.0, Cm, panel=panel, path=0), 2, 1)
+    b2.check_status()
+    rows = torch.tensor([0, n // 2 + 77, n - 1], device="cuda")
+    err = sampled_rows_error(torch, A[rows], B, Cm[rows])
+    tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
+    out["sgemm_32768_1gpu"] = {"n": n, "ms": ms, "value": tf, "unit": "TFLOP/s", "path": "ffma", "panel_k": panel, "steps": 2,
+                               "frac_of_fp32_peak": tf / ffma_peak,
+                               "checked": {"rows": [int(r) for r in rows.tolist()], "max_err_over_abs_a_abs_b": err, "tolerance": 1e-5,
+                                           "ok": bool(err <= 1e-5)}}
+    del A, B, Cm
+    torch.cuda.empty_cache()
+    m = 1 << 30
+    x = b2.fill_uniform(torch.empty(m, device="cuda"), 4)
+    y = b2.fill_uniform(torch.empty(m, device="cuda"), 5)
+    ms = timed(lambda: b2dist.sharded_sdot(m, x, y), 5, 3)
+    got = float(b2dist.sharded_sdot(m, x, y).item())
+    ref, scale = 0.0, 0.0
+    for c0 in range(0, m, 1 << 26):
+        xd, yd = x[c0:c0 + (1 << 26)].double(), y[c0:c0 + (1 << 26)].double()
+        ref += float((xd * yd).sum().item())
+        scale += float((xd * yd).abs().sum().item())
+    gbs = 8.0 * m / (ms * 1e-3) / 1e9
+    out["sdot_2p30_1gpu"] = {"n": m, "ms": ms, "value": gbs, "unit": "GB/s", "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                             "checked": {"rel_err_over_sum_abs": abs(got - ref) / scale, "tolerance": 1e-5,
+                                         "ok": bool(abs(got - ref) <= 1e-5 * scale)}}
+    return out
+
+
 def run_single(args):
     import torch
     import hpcdeepneuralnetworks_b200 as b2
@@ -440,11 +579,11 @@ def run_single(args):
     def roof(p, tf):
         if p == 0:
             return {"bound": "fp32_simt", "achieved": tf, "peak": ffma_peak, "unit": "TFLOP/s", "frac": tf / ffma_peak,
-                    "traffic": NCU_TRAFFIC["sgemm_ffma_6144"], "peak_source": "register-only FFMA probe, same run",
+                    "traffic": ncu_traffic("sgemm_ffma_6144") if n == N1 else None, "peak_source": "register-only FFMA probe, same run",
                     "peak_spec": sm_count * 128 * 2 * 1.965e9 / 1e12, "algorithmic_flop": flop}
         tf32_peak = peaks["bf16_tflops"] / 2.0       # dense TF32 runs at half the bf16 rate
         return {"bound": "tensor", "achieved": 3.0 * tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": 3.0 * tf / tf32_peak,
-                "traffic": NCU_TRAFFIC["sgemm_3xtf32_6144"], "peak_source": f"{peaks['source']} bf16 GEMM / 2",
+                "traffic": ncu_traffic("sgemm_3xtf32_6144") if n == N1 else None, "peak_source": f"{peaks['source']} bf16 GEMM / 2",
                 "useful_tflops": tf, "algorithmic_flop": 3.0 * flop,
                 "cublas_tf32_gemm_tflops_same_run": tf32_lib, "frac_of_cublas_tf32": (3.0 * tf / tf32_lib) if tf32_lib else None}
 
@@ -456,18 +595,30 @@ def run_single(args):
         tf_o = flop / (ms_o * 1e-3) / 1e12
         extras["sgemm_3xtf32" if other == 1 else "sgemm_ffma"] = {"ms": ms_o, "value": tf_o, "unit": "TFLOP/s",
                                                                   "roofline": roof(other, tf_o)}
-        # ABFT overhead: the plain kernel is timed again right before the fault-tolerant one, so that both see the
-        # same clocks (the tensor-core runs above leave the GPU nearer its power cap than the headline run found it)
+        # ABFT overhead: plain and fault-tolerant kernels timed interleaved (A, B, A, B, ... blocks of 5 calls, 8 rounds
+        # each), so that both legs see the same power and clock state; every leg carries its own clock record
         for key, pth in (("abft_ffma", 0), ("abft_3xtf32", 1)):
             try:
-                reps = max(3, args.steps // 2)
-                ms_plain_adj = timed(lambda: step(pth), reps, 3)
-                ms_ft = timed(lambda: b2.ft_sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=pth), reps, 3)
+                with ClockSampler(0) as clk2:
+                    legs = timed_interleaved({"plain": lambda: step(pth),
+                                              "abft": lambda: b2.ft_sgemm(n, n, n, 1.0, A, B, 0.5, Cm, path=pth)}, clk=clk2)
                 b2.check_status()
+                ms_ft, ms_pl = legs["abft"]["ms"], legs["plain"]["ms"]
                 extras[key] = {"ms": ms_ft, "value": flop / (ms_ft * 1e-3) / 1e12, "unit": "TFLOP/s",
-                               "plain_ms_adjacent": ms_plain_adj, "overhead_pct": 100.0 * (ms_ft / ms_plain_adj - 1.0)}
+                               "plain_ms_interleaved": ms_pl, "overhead_pct": 100.0 * (ms_ft / ms_pl - 1.0),
+                               "overhead_pct_at_equal_clock": (100.0 * (legs["abft"]["ms_x_ghz"] / legs["plain"]["ms_x_ghz"] - 1.0)
+                                                               if legs["abft"]["ms_x_ghz"] and legs["plain"]["ms_x_ghz"] else None),
+                               "method": "interleaved blocks of 5 calls, 8 rounds per leg, median block",
+                               "clocks_plain": legs["plain"]["clocks"], "clocks_abft": legs["abft"]["clocks"],
+                               "ms_blocks_plain": legs["plain"]["ms_all"], "ms_blocks_abft": legs["abft"]["ms_all"]}
             except Exception as e:  # reported, not hidden
                 extras[key] = {"error": str(e)}
+        # benchmark configuration 3: clean run and seeded single-bit faults at 1024, 4096, 8192 on both paths
+        try:
+            extras["abft_config3"] = {("ffma" if pth == 0 else "3xtf32"): [abft_fault_report(b2, torch, m, pth) for m in (1024, 4096, 8192)]
+                                      for pth in (0, 1)}
+        except Exception as e:
+            extras["abft_config3"] = {"error": str(e)}
         try:
             ms_cb = cublas_abft_baseline_ms(torch, A, B, Cm, 3, 1)
             extras["abft_cublas_nonfused_baseline"] = {"ms": ms_cb, "value": flop / (ms_cb * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -475,6 +626,15 @@ def run_single(args):
         except Exception as e:
             extras["abft_cublas_nonfused_baseline"] = {"error": str(e)}
         extras.update(bench_vectors(b2, torch, peaks, max(5, args.steps), 3))
+        del A, B, Cm
+        torch.cuda.empty_cache()
+        try:
+            extras.update(single_gpu_anchors(b2, torch, peaks, ffma_peak))
+        except Exception as e:
+            extras["sgemm_32768_1gpu"] = {"error": str(e)}
+        A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+        B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+        Cm = b2.fill_uniform(torch.empty((n, n), device="cuda"), 3)
 
     # end to end through the host-buffer API: pinned host A, B, C -> device -> SGEMM -> host C
     hs = b2.HostSgemm(n, n, n, path=path)
@@ -517,6 +677,7 @@ def run_multi(args):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     n = args.size or NMULTI
     path = 1 if args.path == "3xtf32" else 0
+    tol = 1e-5 if path == 0 else 2e-5
     start, rows = b2dist.row_block(n, rank, world)
     A = torch.empty((rows, n), device="cuda")
     # every rank fills its own row block of A from its own seeded stream; B comes from rank 0 only
@@ -524,35 +685,81 @@ def run_multi(args):
     B = torch.empty((n, n), device="cuda")
     if rank == 0:
         b2.fill_uniform(B, 2)
+    else:
+        B.fill_(float("nan"))        # a rank that computed before its panel landed would show
     Cm = torch.zeros((rows, n), device="cuda")
-    comm = torch.cuda.Stream()
+    mg = b2dist.default_mg()         # the library's own communicator (collective), made outside the timed region
     report = b2.new_report() if args.abft else None
 
-    def step():
-        b2dist.sharded_sgemm(n, n, n, 1.0, A, B, 0.0, Cm, src=0, panel=args.panel, path=path, comm_stream=comm,
-                             abft=args.abft, report=report)
+    def step(abft=args.abft, rep=report):
+        b2dist.sharded_sgemm(n, n, n, 1.0, A, B, 0.0, Cm, src=0, panel=args.panel, path=path, abft=abft, report=rep, mg=mg)
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(v):
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     with ClockSampler(local) as clk:
         ms_local = timed(step, args.steps, args.warmup, dist_barrier=barrier)
     b2.check_status()
-    t = torch.tensor([ms_local], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    ms = max_over_ranks(ms_local)
     flop = 2.0 * n ** 3
     tflops = flop / (ms * 1e-3) / 1e12
 
-    # sharded SDOT: 2^30 elements in total, one scalar all-reduce
+    # ---- the result is checked, outside the timed region: three rows of every rank's block of C against double dot
+    # products of the same rows of A with the B this rank received
+    checked = {}
+    pick = torch.tensor(sorted({0, rows // 2, rows - 1}), device="cuda") if rows else torch.empty(0, dtype=torch.long, device="cuda")
+    err = sampled_rows_error(torch, A[pick], B, Cm[pick]) if rows else 0.0
+    err = max_over_ranks(err if err == err else float("inf"))
+    checked["sgemm"] = {"rows_per_rank": int(pick.numel()), "max_err_over_abs_a_abs_b": err, "tolerance": tol, "ok": bool(err <= tol)}
+
+    # ---- the same product with the fault-tolerant kernels: overhead, and the fault report summed over the ranks
+    abft_extra = None
+    if not args.abft:
+        rep2 = b2.new_report()
+        ms_ft = max_over_ranks(timed(lambda: step(True, rep2), max(1, min(args.steps, 2)), 1, dist_barrier=barrier))
+        b2.check_status()
+        rsum = rep2.clone().to(torch.int64)
+        dist.all_reduce(rsum, op=dist.ReduceOp.SUM)
+        v = rsum.cpu().tolist()
+        err_ft = sampled_rows_error(torch, A[pick], B, Cm[pick]) if rows else 0.0
+        err_ft = max_over_ranks(err_ft if err_ft == err_ft else float("inf"))
+        abft_extra = {"ms": ms_ft, "value": flop / (ms_ft * 1e-3) / 1e12, "unit": "TFLOP/s", "overhead_pct": 100.0 * (ms_ft / ms - 1.0),
+                      "report_summed_over_ranks": {"tiles": v[0], "injected": v[1], "detected": v[2], "corrected": v[3],
+                                                   "uncorrectable": v[4], "false_alarms": v[5]},
+                      "max_err_over_abs_a_abs_b": err_ft}
+        checked["abft"] = {"false_alarms": v[5], "detected": v[2], "max_err_over_abs_a_abs_b": err_ft,
+                           "ok": bool(v[5] == 0 and v[2] == 0 and err_ft <= tol)}
+
+    # sharded SDOT: 2^30 elements in total, one scalar all-reduce (b2_mg_sdot)
     nloc = (1 << 30) // world
     x = b2.fill_uniform(torch.empty(nloc, device="cuda"), 4 + 10 * rank)
     y = b2.fill_uniform(torch.empty(nloc, device="cuda"), 5 + 10 * rank)
-    ms_dot_local = timed(lambda: b2dist.sharded_sdot(nloc, x, y), max(5, args.steps), 3, dist_barrier=barrier)
-    t = torch.tensor([ms_dot_local], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dot = float(t.item())
+    ms_dot = max_over_ranks(timed(lambda: b2dist.sharded_sdot(nloc, x, y, mg=mg), max(5, args.steps), 3, dist_barrier=barrier))
+    dot_nccl = b2dist.sharded_sdot(nloc, x, y, mg=mg).clone()
+    # an independent sum for the check: double products summed by torch, all-reduced
+    ind = torch.zeros(2, dtype=torch.float64, device="cuda")
+    for c0 in range(0, nloc, 1 << 26):
+        pr = x[c0:c0 + (1 << 26)].double() * y[c0:c0 + (1 << 26)].double()
+        ind[0] += pr.sum()
+        ind[1] += pr.abs().sum()
+    dist.all_reduce(ind, op=dist.ReduceOp.SUM)
+    ref, scale = float(ind[0].item()), float(ind[1].item())
+
+    def same_bits_everywhere(t64):
+        g = [torch.empty_like(t64) for _ in range(world)]
+        dist.all_gather(g, t64.contiguous())
+        return all(bool((gi.view(torch.int64) == t64.view(torch.int64)).all().item()) for gi in g)
+
+    nccl_same = same_bits_everywhere(dot_nccl)
+    checked["sdot"] = {"rel_err_over_sum_abs": abs(float(dot_nccl.item()) - ref) / scale, "tolerance": 1e-5,
+                       "same_bits_on_every_rank": nccl_same,
+                       "ok": bool(nccl_same and abs(float(dot_nccl.item()) - ref) <= 1e-5 * scale)}
 
     # the same with the cross-GPU sum inside the kernel (peer stores over NVLink, no collective call)
     ms_fused, fused_error = None, None
@@ -566,25 +773,33 @@ def run_multi(args):
     try:
         if int(agree.item()) == 0:
             raise RuntimeError(fused_error or "symmetric memory could not be set up on another rank")
-        ms_fused_local = timed(lambda: fused(nloc, x, y), max(5, args.steps), 3, dist_barrier=barrier)
+        ms_fused = max_over_ranks(timed(lambda: fused(nloc, x, y), max(5, args.steps), 3, dist_barrier=barrier))
+        dot_fused = fused(nloc, x, y).clone()
         b2.check_status()
-        t = torch.tensor([ms_fused_local], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_fused = float(t.item())
+        fused_same = same_bits_everywhere(dot_fused)
+        gap = abs(float(dot_fused.item()) - float(dot_nccl.item()))
+        checked["sdot_fused"] = {"rel_err_over_sum_abs": abs(float(dot_fused.item()) - ref) / scale, "tolerance": 1e-5,
+                                 "same_bits_on_every_rank": fused_same,
+                                 "gap_to_allreduce_form_over_sum_abs": gap / scale,
+                                 "same_bits_as_allreduce_form": bool(gap == 0.0),
+                                 "ok": bool(fused_same and abs(float(dot_fused.item()) - ref) <= 1e-5 * scale and gap <= 1e-12 * scale)}
     except Exception as e:   # reported below, never hidden
         fused_error = f"{type(e).__name__}: {e}"
 
+    all_ok = all(c["ok"] for c in checked.values())
     if rank == 0:
         ffma_peak = b2.ffma_peak_tflops()
         peaks = load_peaks()
         per_gpu = tflops / world
+        launches_per_panel = 2 if path == 0 else 3     # the GEMM kernel, plus the transpose of the A panel (FFMA) or the two split kernels
         line = {
             "metric": METRIC.replace("6144", str(n)), "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"sgemm_rowmajor_{n}^3_rowblock_sharded" + ("_abft" if args.abft else ""), "path": args.path, "alpha": 1.0, "beta": 0.0,
-                       "parallelism": f"A,C row blocks over {world} GPUs; B broadcast from rank 0 per GEMM in K-panels of {args.panel} (NCCL)",
-                       "l2": "operands are GBs per GPU, far larger than L2"},
+                       "parallelism": f"A,C row blocks over {world} GPUs; B broadcast from rank 0 per GEMM in K-panels of {args.panel} (NCCL) inside b2_mg_sgemm",
+                       "l2": "operands are GBs per GPU, far larger than L2",
+                       "one_gpu_value_of_this_workload": "extra.sgemm_32768_1gpu of the --gpus 1 line"},
             "roofline": {"bound": "fp32_simt" if path == 0 else "tensor", "achieved": per_gpu if path == 0 else 3 * per_gpu,
                          "peak": ffma_peak if path == 0 else peaks["bf16_tflops"] / 2, "unit": "TFLOP/s",
                          "frac": (per_gpu / ffma_peak) if path == 0 else (3 * per_gpu / (peaks["bf16_tflops"] / 2)),
@@ -592,11 +807,12 @@ def run_multi(args):
             "cpu_baseline": None,
             "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "operands of 32768^3 are generated on the device; no host copy is part of this workload"},
-            # per K-panel: the GEMM kernel, plus the transpose of the A panel (FFMA) or the two split kernels (3xTF32)
-            "gpu_launches": args.steps * len(b2dist.k_panels(n, args.panel)) * (2 if path == 0 else 3),
+            "gpu_launches": args.steps * len(b2dist.k_panels(n, args.panel)) * launches_per_panel,
             "clocks": clk.summary(),
+            "checked": dict(checked, all_ok=all_ok),
             "abft_report": (b2.read_report(report) if args.abft else None),
-            "extra": {"sdot_sharded": {"n_total": nloc * world, "ms": ms_dot, "value": 8.0 * nloc * world / (ms_dot * 1e-3) / 1e9,
+            "extra": {"abft": abft_extra,
+                      "sdot_sharded": {"n_total": nloc * world, "ms": ms_dot, "value": 8.0 * nloc * world / (ms_dot * 1e-3) / 1e9,
                                        "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_dot * 1e-3) / 1e9 / peaks["hbm_gbs"]},
                       "sdot_sharded_fused": ({"n_total": nloc * world, "ms": ms_fused, "value": 8.0 * nloc * world / (ms_fused * 1e-3) / 1e9,
                                               "unit": "GB/s", "per_gpu_frac_of_hbm_peak": 8.0 * nloc / (ms_fused * 1e-3) / 1e9 / peaks["hbm_gbs"]}
@@ -604,8 +820,9 @@ def run_multi(args):
         }
         print(json.dumps(line))
     dist.barrier()
+    mg.close()
     dist.destroy_process_group()
-    return 0
+    return 0 if all_ok else 1
 
 
 def main():

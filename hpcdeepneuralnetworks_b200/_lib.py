@@ -108,6 +108,18 @@ def load() -> C.CDLL:
     L.b2_set_ffma_transpose_a.argtypes = [i32]
     L.b2_set_tf32_abft_mode.argtypes = [i32]
     L.b2_set_tf32_abft_bias.argtypes = [f32]
+    L.b2_host_plan_create.argtypes = [C.POINTER(vp), vp, i32, i32, i32, i32, i32, i32, i32]
+    L.b2_host_plan_destroy.argtypes = [vp]
+    L.b2_sgemm_host.argtypes = [vp, f32, vp, i32, vp, i32, f32, vp, i32, i32, vp]
+    L.b2_host_alloc.argtypes = [C.POINTER(vp), C.c_size_t]
+    L.b2_host_free.argtypes = [vp]
+    L.b2_mg_unique_id.argtypes = [vp]
+    L.b2_mg_create.argtypes = [C.POINTER(vp), vp, i32, i32, vp]
+    L.b2_mg_destroy.argtypes = [vp]
+    L.b2_mg_row_block.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
+    L.b2_mg_k_panel.argtypes = [i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]
+    L.b2_mg_sgemm.argtypes = [vp, i32, i32, i32, i32, i32, f32, vp, i32, vp, i32, f32, vp, i32, i32, i32, vp, vp]
+    L.b2_mg_sdot.argtypes = [vp, i64, vp, vp, vp, vp, vp]
     _lib = L
     return L
 

@@ -125,6 +125,22 @@ def make_plan(plan) -> torch.Tensor | None:
     return torch.from_numpy(arr).cuda()
 
 
+def seeded_fault_plan(M, N, K, seed, tiles_per_fault=64, bit_lo=20, bit_hi=30) -> np.ndarray:
+    """The injection plan of benchmark configuration 3: one bit flip (a random bit bit_lo..bit_hi of a random
+    accumulator, after a random K-slab) per ``tiles_per_fault`` output tiles of 128 x 128, at most one per tile, drawn
+    from ``seed``.  Returns an int32 array (n, 6) of (tile_m, tile_n, row, col, k_step, bit) for ``make_plan``."""
+    tm, tn = (M + 127) // 128, (N + 127) // 128
+    rng = np.random.Generator(np.random.PCG64(seed))
+    struck = np.sort(rng.choice(tm * tn, size=max(1, (tm * tn) // tiles_per_fault), replace=False))
+    slabs = max(1, (K + 31) // 32)
+    plan = np.zeros((len(struck), 6), dtype=np.int32)
+    for q, t in enumerate(struck):
+        i, j = divmod(int(t), tn)
+        plan[q] = (i, j, rng.integers(0, min(128, M - i * 128)), rng.integers(0, min(128, N - j * 128)),
+                   rng.integers(0, slabs), rng.integers(bit_lo, bit_hi + 1))
+    return plan
+
+
 def ft_sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, plan=None, tau=0.0, report=None, lda=None, ldb=None,
              ldc=None, handle=None):
     """ABFT SGEMM.  ``plan``: device int32 tensor (n,6) from ``make_plan`` or None.  ``report``: device
@@ -205,33 +221,34 @@ def sdot_partial(n, x, y, out, partial64, handle=None):
 # ---- host-buffer forms: what a caller holding host arrays (the reference drivers' situation
 # before their cudaMemcpy calls, kernel/sgemm/sgemm.cu:50-58) would use -------------------------
 class HostSgemm:
-    """Row-major SGEMM on HOST arrays: pinned staging buffers, device buffers and a three-stream pipeline.
+    """Row-major SGEMM on HOST arrays through ``b2_sgemm_host``: pinned host buffers ``hA``, ``hB``, ``hC`` (torch
+    tensors used as page-locked memory) and a host plan of the library that owns the device copies, three streams
+    and the pipeline schedule.
 
-    Default schedule (one K panel, bit-identical to a single call): C is cut into row panels; B has to be on the
-    device before any full-width row panel can be computed, so the FIRST row panel is cut further into column
-    panels and computed tile by tile while the column panels of B (and of C) arrive -- pitched copies through
-    ``b2_copy_matrix_async`` -- and the following row panels are one full-width GEMM each, issued as soon as their
-    rows of A and C have landed; a row panel of C travels back on a third stream when it is done.  Transfers in
-    both directions overlap the kernels.  ``panel_rows`` defaults to 1536: a 1536 x 6144 panel is 576 tiles of
-    128 x 128, 1.95 waves of the 296 resident CTAs, where 1024 rows would leave the second wave a third full.
+    Default schedule (one K panel, bit-identical to a single device call): C is cut into row panels of
+    ``panel_rows``; the first row panel is computed in column tiles of ``panel_cols`` behind the pitched copies of
+    B's column panels, the others as one full-width GEMM each as their rows land, and each row panel of C travels
+    back as soon as it is done.  With ``panel_k > 0`` the second cut is along K instead and block (p, q) accumulates
+    into C_p with beta on the first K panel and 1 afterwards (same tolerance, different rounding)."""
 
-    With ``panel_k > 0`` the second cut is along K instead (rows of B, contiguous): row panels and K panels are sent
-    alternately and block (p, q) accumulates into C_p with beta on the first K panel and 1 afterwards; each output
-    is then a sum of per-panel partial sums (same tolerance, different rounding)."""
-
-    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=1536, panel_k=0, panel_cols=1536):
+    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=1536, panel_k=0, panel_cols=1536, handle=None):
         self.M, self.N, self.K, self.path = M, N, K, path
+        self._L = _lib.load()
+        self._handle = handle or default_handle()
         self.pr = M if M < 128 else max(128, (min(panel_rows, M) + 127) // 128 * 128)
         self.pk = K if (K < 128 or panel_k <= 0) else max(128, (min(panel_k, K) + 127) // 128 * 128)
         self.pc = N if N < 256 else max(128, (min(panel_cols, N) + 127) // 128 * 128)
         self.hA = torch.empty((M, K), dtype=torch.float32).pin_memory()
         self.hB = torch.empty((K, N), dtype=torch.float32).pin_memory()
         self.hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
-        self.dA = torch.empty((M, K), dtype=torch.float32, device="cuda")
-        self.dB = torch.empty((K, N), dtype=torch.float32, device="cuda")
-        self.dC = torch.empty((M, N), dtype=torch.float32, device="cuda")
-        self._h2d = torch.cuda.Stream()
-        self._d2h = torch.cuda.Stream()
+        # scratch for the largest panel product, handed to the library before the plan is made
+        rows_max, k_max = min(self.pr, M), min(self.pk, K)
+        if M > 0 and N > 0 and K > 0:
+            self._handle.reserve(max(self._L.b2_sgemm_workspace_bytes(path, rows_max, N, k_max),
+                                     self._L.b2_sgemm_workspace_bytes(path, rows_max, min(self.pc, N), k_max)))
+        self._plan = C.c_void_p()
+        check(self._L.b2_host_plan_create(C.byref(self._plan), self._handle.raw, path, M, N, K, panel_rows, panel_cols,
+                                          max(panel_k, 0)))
 
     def h2d_bytes(self):
         return 4 * (self.M * self.K + self.K * self.N + self.M * self.N)
@@ -239,118 +256,23 @@ class HostSgemm:
     def d2h_bytes(self):
         return 4 * self.M * self.N
 
-    def _copy_cols(self, dst, src, ld, r0, r1, c0, c1, direction, stream):
-        """Pitched copy of rows r0..r1, columns c0..c1 of an (x, ld) matrix between its host and device copies."""
-        off = (r0 * ld + c0) * 4
-        check(_lib.load().b2_copy_matrix_async(C.c_void_p(dst.data_ptr() + off), ld, C.c_void_p(src.data_ptr() + off), ld,
-                                               r1 - r0, c1 - c0, direction, C.c_void_p(stream.cuda_stream)))
-
     def run(self, alpha, beta, ft=False):
         """hC <- alpha*hA*hB + beta*hC through the device; returns hC (pinned) after everything has landed."""
-        if self.pk < self.K:
-            return self._run_k_panels(alpha, beta, ft)
-        compute = torch.cuda.current_stream()
-        h2d, d2h = self._h2d, self._d2h
-        h2d.wait_stream(compute)          # earlier work on the device buffers is finished
-        d2h.wait_stream(compute)
-        M, N, K = self.M, self.N, self.K
-        rows = [(r0, min(M, r0 + self.pr)) for r0 in range(0, max(M, 1), max(self.pr, 1))]
-        cols = [(c0, min(N, c0 + self.pc)) for c0 in range(0, max(N, 1), max(self.pc, 1))]
-        L = _lib.load()
-        # scratch sized once, outside the pipeline (growing it would synchronise the device)
-        default_handle().reserve(max(L.b2_sgemm_workspace_bytes(self.path, r1 - r0, N, K) for r0, r1 in rows))
-        fn = ft_sgemm if ft else sgemm
-
-        def send_rows(p, with_c):
-            r0, r1 = rows[p]
-            with torch.cuda.stream(h2d):
-                self.dA[r0:r1].copy_(self.hA[r0:r1], non_blocking=True)
-                if with_c and beta != 0.0:
-                    self.dC[r0:r1].copy_(self.hC[r0:r1], non_blocking=True)
-                return h2d.record_event()
-
-        def back(p):
-            r0, r1 = rows[p]
-            ev = compute.record_event()
-            d2h.wait_event(ev)
-            with torch.cuda.stream(d2h):
-                self.hC[r0:r1].copy_(self.dC[r0:r1], non_blocking=True)
-
-        # first row panel: tile by tile behind the column panels of B
-        r0, r1 = rows[0]
-        compute.wait_event(send_rows(0, with_c=False))
-        for c0, c1 in cols:
-            self._copy_cols(self.dB, self.hB, N, 0, K, c0, c1, 1, h2d)
-            if beta != 0.0:
-                self._copy_cols(self.dC, self.hC, N, r0, r1, c0, c1, 1, h2d)
-            compute.wait_event(h2d.record_event())
-            fn(r1 - r0, c1 - c0, K, alpha, self.dA[r0:r1], self.dB[:, c0:c1], beta, self.dC[r0:r1, c0:c1], path=self.path,
-               lda=K, ldb=N, ldc=N)
-        back(0)
-        # the other row panels: one full-width GEMM each
-        for p in range(1, len(rows)):
-            r0, r1 = rows[p]
-            compute.wait_event(send_rows(p, with_c=True))
-            fn(r1 - r0, N, K, alpha, self.dA[r0:r1], self.dB, beta, self.dC[r0:r1], path=self.path, lda=K, ldb=N, ldc=N)
-            back(p)
-        compute.wait_stream(d2h)
-        compute.synchronize()
+        torch.cuda.current_stream().synchronize()      # earlier work of the caller on the handle's scratch
+        check(self._L.b2_sgemm_host(self._plan, alpha, C.c_void_p(self.hA.data_ptr()), self.K, C.c_void_p(self.hB.data_ptr()),
+                                    self.N, beta, C.c_void_p(self.hC.data_ptr()), self.N, 1 if ft else 0, None))
         return self.hC
 
-    def _run_k_panels(self, alpha, beta, ft=False):
-        compute = torch.cuda.current_stream()
-        h2d, d2h = self._h2d, self._d2h
-        h2d.wait_stream(compute)
-        d2h.wait_stream(compute)
-        M, N, K = self.M, self.N, self.K
-        rows = [(r0, min(M, r0 + self.pr)) for r0 in range(0, max(M, 1), max(self.pr, 1))]
-        kps = [(k0, min(K, k0 + self.pk)) for k0 in range(0, max(K, 1), max(self.pk, 1))]
-        default_handle().reserve(_lib.load().b2_sgemm_workspace_bytes(self.path, self.pr, N, self.pk))
-        fn = ft_sgemm if ft else sgemm
-        row_ev, k_ev = {}, {}
-        blocks_done = {p: 0 for p in range(len(rows))}   # K panels already folded into row panel p, in order
+    def close(self):
+        if self._plan:
+            self._L.b2_host_plan_destroy(self._plan)
+            self._plan = C.c_void_p()
 
-        def send_row(p):
-            r0, r1 = rows[p]
-            with torch.cuda.stream(h2d):
-                self.dA[r0:r1].copy_(self.hA[r0:r1], non_blocking=True)
-                if beta != 0.0:
-                    self.dC[r0:r1].copy_(self.hC[r0:r1], non_blocking=True)
-                row_ev[p] = h2d.record_event()
-
-        def send_k(q):
-            k0, k1 = kps[q]
-            with torch.cuda.stream(h2d):
-                self.dB[k0:k1].copy_(self.hB[k0:k1], non_blocking=True)
-                k_ev[q] = h2d.record_event()
-
-        def compute_ready():
-            for p in sorted(row_ev):
-                r0, r1 = rows[p]
-                while blocks_done[p] < len(kps) and blocks_done[p] in k_ev:
-                    q = blocks_done[p]
-                    k0, k1 = kps[q]
-                    compute.wait_event(row_ev[p])
-                    compute.wait_event(k_ev[q])
-                    fn(r1 - r0, N, k1 - k0, alpha, self.dA[r0:r1, k0:k1], self.dB[k0:k1], beta if q == 0 else 1.0,
-                       self.dC[r0:r1], path=self.path, lda=K, ldb=N, ldc=N)
-                    blocks_done[p] = q + 1
-                    if q + 1 == len(kps):
-                        ev = compute.record_event()
-                        d2h.wait_event(ev)
-                        with torch.cuda.stream(d2h):
-                            self.hC[r0:r1].copy_(self.dC[r0:r1], non_blocking=True)
-
-        for i in range(max(len(rows), len(kps))):
-            if i < len(rows):
-                send_row(i)
-                compute_ready()
-            if i < len(kps):
-                send_k(i)
-                compute_ready()
-        compute.wait_stream(d2h)
-        compute.synchronize()
-        return self.hC
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 # ---- harness ---------------------------------------------------------------------------------

@@ -64,7 +64,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
                     sys.stderr.write(out)
     if jobs or force or _stale(LIB, objs):
         cmd = [nvcc(), "-shared", "-cudart", "shared", "-o", LIB] + objs + \
-              ["-Xlinker", "-rpath,/usr/local/cuda/lib64"]
+              ["-Xlinker", "-rpath,/usr/local/cuda/lib64", "-ldl"]
         run(cmd)
     build_driver()
     return LIB

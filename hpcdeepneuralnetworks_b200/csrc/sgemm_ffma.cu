@@ -859,139 +859,13 @@ using namespace b2;
 namespace b2 {
 int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
                           float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
-
-// Sum of squares of a rows x cols matrix (pitch ld) added to *out: one block per row stripe.
-__global__ void __launch_bounds__(256) sumsq_kernel(const float *__restrict__ X, int rows, int cols, int ld, double *out) {
-  float acc = 0.f;
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float *row = X + (size_t)r * ld;
-    for (int c = threadIdx.x; c < cols; c += 256) acc = __fmaf_rn(row[c], row[c], acc);
-  }
-  double d = (double)acc;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-  __shared__ double part[8];
-  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = d;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    double t = 0.0;
-    for (int w = 0; w < 8; ++w) t += part[w];
-    atomicAdd(out, t);
-  }
-}
-__global__ void ft_scale_kernel(double *ss, double n1, double n2, float *scale) {
-  const double r1 = sqrt(ss[0] / n1), r2 = sqrt(ss[1] / n2);
-  *scale = (float)(3.0 * r1 * r2);   // uniform [-1, 1) has mean square 1/3
-}
-
-int ft_data_scale(Context *ctx, const float *X1, int rows1, int cols1, int ld1, const float *X2, int rows2, int cols2,
-                  int ld2, cudaStream_t s, const float **scale_dev) {
-  double *ss = (double *)((char *)ctx->fixed + kFixedFtScale);
-  float *scale = (float *)(ss + 2);
-  B2_CUDA(cudaMemsetAsync(ss, 0, 2 * sizeof(double), s));
-  const int g1 = rows1 < 1184 ? rows1 : 1184, g2 = rows2 < 1184 ? rows2 : 1184;
-  sumsq_kernel<<<g1, 256, 0, s>>>(X1, rows1, cols1, ld1, ss);
-  sumsq_kernel<<<g2, 256, 0, s>>>(X2, rows2, cols2, ld2, ss + 1);
-  ft_scale_kernel<<<1, 1, 0, s>>>(ss, (double)rows1 * cols1, (double)rows2 * cols2, scale);
-  B2_CUDA(cudaGetLastError());
-  *scale_dev = scale;
-  return B2_OK;
-}
+// knobs of the FFMA path that other translation units set
+void set_ft_level_knob(int level) { g_ft_level = level; }
+void set_ffma_transpose_a_knob(int on) { g_ffma_transpose_a = on; }
 }
 
 extern "C" {
 
-int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
-                float beta, float *C, int ldc, const b2_fault *plan_dev, int n_faults, float tau, b2_ft_report *report_dev,
-                void *stream) {
-  B2_REQUIRE(path == B2_PATH_FFMA || path == B2_PATH_3XTF32, B2_ERR_INVALID_ARG, "b2_ft_sgemm: unknown path %d", path);
-  B2_REQUIRE(M >= 0 && N >= 0 && K >= 0, B2_ERR_INVALID_ARG, "b2_ft_sgemm: negative dimension (M=%d N=%d K=%d)", M, N, K);
-  B2_REQUIRE(n_faults >= 0 && (n_faults == 0 || plan_dev != nullptr), B2_ERR_INVALID_ARG, "b2_ft_sgemm: bad fault plan");
-  if (M == 0 || N == 0) return B2_OK;
-  B2_REQUIRE(C != nullptr, B2_ERR_INVALID_ARG, "b2_ft_sgemm: C is NULL");
-  B2_REQUIRE(ldc >= N, B2_ERR_INVALID_ARG, "b2_ft_sgemm: ldc = %d < N = %d", ldc, N);
-  if (K > 0) {
-    B2_REQUIRE(A != nullptr && B != nullptr, B2_ERR_INVALID_ARG, "b2_ft_sgemm: A or B is NULL");
-    B2_REQUIRE(lda >= K, B2_ERR_INVALID_ARG, "b2_ft_sgemm: lda = %d < K = %d", lda, K);
-    B2_REQUIRE(ldb >= N, B2_ERR_INVALID_ARG, "b2_ft_sgemm: ldb = %d < N = %d", ldb, N);
-  }
-  B2_CONTEXT(ctx, h, "b2_ft_sgemm");
-  FtArgs ft;
-  ft.plan = plan_dev;
-  ft.n_faults = n_faults;
-  ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
-  ft.A = A;
-  ft.B = B;
-  ft.lda = lda;
-  ft.ldb = ldb;
-  ft.tau_scale = nullptr;
-  if (tau < 0.f && K > 0) {
-    // scale-aware default: one pass over A and B for their root mean squares
-    int st = ft_data_scale(ctx, A, M, K, lda, B, K, N, ldb, (cudaStream_t)stream, &ft.tau_scale);
-    if (st != B2_OK) return st;
-  }
-  if (path == B2_PATH_3XTF32) {
-    ft.tau = tau > 0.f ? tau : 0.f;   // 0: the path's own default, which depends on where the checksums are formed
-    return sgemm_3xtf32_dispatch(ctx, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
-  }
-  // default threshold: 2e-6 per unit of K for operands of unit scale, about 16 sigma of the
-  // rounding noise between the two ways a block's sum is formed
-  ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
-  return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, &ft, (cudaStream_t)stream);
-}
-
-// Column-major NT form of the ABFT SGEMM (the layout of the reference's ft_sgemm_* kernels):
-// A is M x K (lda = M), B is stored N x K (ldb = N), C is M x N (ldc = M), C = alpha*A*B^T + beta*C.
-// Computed as the row-major product C^T = B * A^T with the transposed-A tile, so a fault planned
-// at (row, col) of a 128 x 128 tile addresses C^T: row runs along N, col along M.
-int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const float *A, const float *B, float beta,
-                            float *C, const b2_fault *plan_dev, int n_faults, float tau, b2_ft_report *report_dev,
-                            void *stream) {
-  B2_REQUIRE(M >= 0 && N >= 0 && K >= 0, B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: negative dimension");
-  B2_REQUIRE(n_faults >= 0 && (n_faults == 0 || plan_dev != nullptr), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: bad fault plan");
-  if (M == 0 || N == 0) return B2_OK;
-  B2_REQUIRE(C != nullptr && (K == 0 || (A != nullptr && B != nullptr)), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: null matrix");
-  B2_CONTEXT(ctx, h, "b2_ft_sgemm_colmajor_nt");
-  FtArgs ft;
-  ft.plan = plan_dev;
-  ft.n_faults = n_faults;
-  ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
-  ft.tau_scale = nullptr;
-  if (tau < 0.f && K > 0) {
-    int st = ft_data_scale(ctx, A, K, M, M, B, K, N, N, (cudaStream_t)stream, &ft.tau_scale);
-    if (st != B2_OK) return st;
-  }
-  ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
-  ft.A = B;   // left operand of C^T = B * A^T, held K x N in memory
-  ft.B = A;   // right operand, held K x M in memory
-  ft.lda = N;
-  ft.ldb = M;
-  return sgemm_ffma_dispatch_ft(ctx, 1, N, M, K, alpha, B, N, A, M, beta, C, M, &ft, (cudaStream_t)stream);
-}
-
-// Reference-shaped shim: ft_sgemm_<tile>(M, N, K, A, B, C, alpha, beta) of kernel/ft_sgemm
-// (include/ft_sgemm_huge.cuh:21), default stream, no injection.
-int ref_ft_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, float alpha, float beta) {
-  return b2_ft_sgemm_colmajor_nt(nullptr, M, N, K, alpha, A, B, beta, C, nullptr, 0, 0.f, nullptr, nullptr);
-}
-
-int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C) {
-  return b2_ft_sgemm(nullptr, B2_PATH_FFMA, M, N, K, alpha, A, K, B, N, beta, C, N, nullptr, 0, 0.f, nullptr, nullptr);
-}
-
-// ABFT encode granularity of the FFMA path: 1 block-level through shared memory (default), 2 thread-level in
-// registers (128 x 128 tile only; other tiles keep the block-level encoder).
-int b2_set_ft_level(int level) {
-  B2_REQUIRE(level == 1 || level == 2, B2_ERR_INVALID_ARG, "b2_set_ft_level: %d is not 1 or 2", level);
-  b2::g_ft_level = level;
-  return B2_OK;
-}
-// 1 (default): a row-major A is transposed into the workspace first when that pays; 0: never.
-int b2_set_ffma_transpose_a(int on) {
-  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_ffma_transpose_a: %d is not 0 or 1", on);
-  b2::g_ffma_transpose_a = on;
-  return B2_OK;
-}
 // Selects the inner-loop variant of the FFMA kernel (0 scalar FFMA, 1 packed f32x2).  For
 // benchmarking; results are bit-identical.
 int b2_set_ffma_variant(int v) {

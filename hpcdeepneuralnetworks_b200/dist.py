@@ -9,9 +9,11 @@
   all-reduce(sum) of that scalar.
 
 The reference is single-GPU (no NCCL/MPI call anywhere in it); this file has no counterpart
-there.  The arithmetic is always the CUDA library's; ``gemm_fn``/``dot_fn`` exist so that the
-host-side orchestration (partitioning, panel schedule, collectives) can be exercised by CPU
-ranks over gloo in the tests.
+there.  On CUDA tensors both forms are one call into the library (``b2_mg_sgemm``, ``b2_mg_sdot``:
+schedule, streams, events and NCCL calls live in C++ behind the C ABI); this module adds the
+collective construction of the library's communicator over ``torch.distributed``.  ``gemm_fn`` /
+``dot_fn`` exist so that the same partition (``b2_mg_row_block``, ``b2_mg_k_panel``) and panel
+schedule can be exercised by CPU ranks over gloo in the tests.
 """
 from __future__ import annotations
 
@@ -22,19 +24,78 @@ import torch.distributed as dist
 
 
 def row_block(M: int, rank: int, world: int) -> Tuple[int, int]:
-    """(first row, row count) of rank's block: contiguous, sizes differ by at most one row."""
-    base, rem = divmod(M, world)
-    rows = base + (1 if rank < rem else 0)
-    start = rank * base + min(rank, rem)
-    return start, rows
+    """(first row, row count) of rank's block: contiguous, sizes differ by at most one row (``b2_mg_row_block``)."""
+    import ctypes as C
+    from . import _lib
+    start, rows = C.c_int64(), C.c_int64()
+    _lib.check(_lib.load().b2_mg_row_block(M, rank, world, C.byref(start), C.byref(rows)))
+    return start.value, rows.value
 
 
 def k_panels(K: int, panel: int) -> List[Tuple[int, int]]:
-    """[(k0, width)] covering [0, K) in order; widths are `panel` except possibly the last."""
+    """[(k0, width)] covering [0, K) in order; widths are `panel` except possibly the last (``b2_mg_k_panel``)."""
+    import ctypes as C
+    from . import _lib
+    L = _lib.load()
     if K <= 0:
         return []
-    panel = max(1, panel)
-    return [(k0, min(panel, K - k0)) for k0 in range(0, K, panel)]
+    out, k0, kw = [], C.c_int(), C.c_int()
+    count = _lib.check(L.b2_mg_k_panel(K, panel, 0, C.byref(k0), C.byref(kw)))
+    for i in range(count):
+        L.b2_mg_k_panel(K, panel, i, C.byref(k0), C.byref(kw))
+        out.append((k0.value, kw.value))
+    return out
+
+
+class MgHandle:
+    """``b2_mg_handle``: this rank's membership of the library's own NCCL communicator.  Construction is collective:
+    rank 0 draws the communicator id (``b2_mg_unique_id``) and ``torch.distributed`` carries it to the other ranks;
+    with a world of one no communicator is made."""
+
+    def __init__(self, group=None, handle=None):
+        import ctypes as C
+        from . import _lib, blas
+        self._L = _lib.load()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._handle = handle or blas.default_handle()
+        ident = None
+        if self.world > 1:
+            buf = (C.c_char * 128)()
+            if self.rank == 0:
+                _lib.check(self._L.b2_mg_unique_id(buf))
+            box = [bytes(buf)]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            ident = C.create_string_buffer(box[0], 128)
+        self._mg = C.c_void_p()
+        _lib.check(self._L.b2_mg_create(C.byref(self._mg), self._handle.raw, self.rank, self.world, ident))
+
+    @property
+    def raw(self):
+        return self._mg
+
+    def close(self):
+        if self._mg:
+            torch.cuda.synchronize()
+            self._L.b2_mg_destroy(self._mg)
+            self._mg = type(self._mg)()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_mg_default = {}
+
+
+def default_mg(group=None) -> MgHandle:
+    """One ``MgHandle`` per process group and device, made on first use (collectively)."""
+    key = (id(group), torch.cuda.current_device())
+    if key not in _mg_default:
+        _mg_default[key] = MgHandle(group)
+    return _mg_default[key]
 
 
 def _cuda_gemm(path: int, abft: bool, report):
@@ -50,12 +111,13 @@ def _cuda_gemm(path: int, abft: bool, report):
 
 def sharded_sgemm(M: int, N: int, K: int, alpha: float, A_local: torch.Tensor, B: torch.Tensor, beta: float,
                   C_local: torch.Tensor, *, src: int = 0, panel: int = 4096, path: int = 0, abft: bool = False,
-                  report=None, group=None, gemm_fn: Callable | None = None, comm_stream=None) -> torch.Tensor:
+                  report=None, group=None, gemm_fn: Callable | None = None, mg: MgHandle | None = None) -> torch.Tensor:
     """Row-block-sharded row-major SGEMM.
 
     ``A_local`` (rows_r x K) and ``C_local`` (rows_r x N) are this rank's blocks (``row_block``);
     ``B`` is a K x N buffer on every rank whose contents are only valid on ``src`` at entry and on
-    every rank at exit.  Returns ``C_local``.
+    every rank at exit.  On CUDA tensors the whole schedule runs inside ``b2_mg_sgemm`` (the library's own NCCL
+    communicator, ``mg`` or the default one of the group).  Returns ``C_local``.
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -69,8 +131,8 @@ def sharded_sgemm(M: int, N: int, K: int, alpha: float, A_local: torch.Tensor, B
             fn(rows, N, 0, alpha, A_local, max(K, 1), B, N, beta, C_local, N)
         return C_local
 
-    if world == 1 or not on_gpu:
-        # CPU ranks (tests) and the single-GPU case: same schedule, no stream overlap.
+    if not on_gpu or gemm_fn is not None:
+        # CPU ranks (tests): the same schedule, ranks and panels as b2_mg_sgemm, arithmetic injected.
         for i, (k0, kw) in enumerate(panels):
             if world > 1:
                 dist.broadcast(B[k0:k0 + kw], src=src, group=group)
@@ -78,30 +140,31 @@ def sharded_sgemm(M: int, N: int, K: int, alpha: float, A_local: torch.Tensor, B
                 fn(rows, N, kw, alpha, A_local[:, k0:], K, B[k0:], N, beta if i == 0 else 1.0, C_local, N)
         return C_local
 
-    compute = torch.cuda.current_stream()
-    comm = comm_stream or torch.cuda.Stream()
-    comm.wait_stream(compute)            # B may still be being written by earlier work
-    works = []
-    with torch.cuda.stream(comm):
-        for (k0, kw) in panels:
-            works.append(dist.broadcast(B[k0:k0 + kw], src=src, group=group, async_op=True))
-    for i, (k0, kw) in enumerate(panels):
-        works[i].wait()                  # the compute stream waits for panel i only
-        if rows:
-            fn(rows, N, kw, alpha, A_local[:, k0:], K, B[k0:], N, beta if i == 0 else 1.0, C_local, N)
+    import ctypes as C
+    from . import _lib, blas
+    mg = mg or default_mg(group)
+    need = blas.sgemm_workspace_bytes(path, rows, N, min(panel, K)) if rows else 0
+    blas.default_handle().reserve(need)
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    _lib.check(_lib.load().b2_mg_sgemm(mg.raw, path, 1 if abft else 0, M, N, K, alpha, vp(A_local), K, vp(B), N, beta, vp(C_local), N,
+                                       src, panel, vp(report) if report is not None else None,
+                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return C_local
 
 
 def sharded_sdot(n_local: int, x_local: torch.Tensor, y_local: torch.Tensor, *, group=None,
-                 dot_fn: Callable | None = None) -> torch.Tensor:
-    """Sum over ranks of x_local . y_local.  Returns a 1-element float64 tensor (same on every rank)."""
+                 dot_fn: Callable | None = None, mg: MgHandle | None = None) -> torch.Tensor:
+    """Sum over ranks of x_local . y_local.  Returns a 1-element float64 tensor (same on every rank).  On CUDA tensors
+    this is ``b2_mg_sdot``: the SDOT kernel's double partial, then one all-reduce of that scalar."""
     if dot_fn is None:
-        from . import blas
-        out = torch.empty(1, dtype=torch.float32, device=x_local.device)
+        import ctypes as C
+        from . import _lib
+        mg = mg or default_mg(group)
         part = torch.zeros(1, dtype=torch.float64, device=x_local.device)
-        blas.sdot_partial(n_local, x_local, y_local, out, part)
-    else:
-        part = dot_fn(n_local, x_local, y_local)
+        _lib.check(_lib.load().b2_mg_sdot(mg.raw, n_local, C.c_void_p(x_local.data_ptr()), C.c_void_p(y_local.data_ptr()), None,
+                                          C.c_void_p(part.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return part
+    part = dot_fn(n_local, x_local, y_local)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(part, op=dist.ReduceOp.SUM, group=group)
     return part

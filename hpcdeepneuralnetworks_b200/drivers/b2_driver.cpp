@@ -5,6 +5,10 @@
 //   b2_driver ft_sgemm <start> <end> <gap>                        kernel/ft_sgemm/sgemm.cu:14-20,186-196
 //   b2_driver saxpy                                                kernel/saxpy/saxpy.cu:57-135
 //   b2_driver sdot                                                 kernel/sdot/sdot.cu:78-99,156-165
+//   b2_driver sgemm_host <n> [path]        host arrays in, host array out (the drivers' malloc + cudaMemcpy + launch +
+//                                          cudaMemcpy of kernel/sgemm/sgemm.cu:50-63 as one pipelined call)
+//   b2_driver mg <rank> <world> <id file> <n> [panel_k]   one process per GPU: row-block sharded SGEMM and sharded SDOT;
+//                                          rank 0 writes the communicator id to <id file>, the others wait for it
 //
 // Like the reference drivers it verifies one launch per size and then prints a GFLOPS row; unlike
 // them it checks against the library's own naive kernel (rung 1) instead of cuBLAS, times with the
@@ -14,6 +18,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <unistd.h>
+
+#include <string>
 #include <vector>
 
 #include "b2blas.h"
@@ -168,14 +175,151 @@ static int run_vectors(bool dot) {
   return 0;
 }
 
+static int run_sgemm_host(int n, int path) {
+  const float alpha = 1.0f, beta = 0.5f;
+  const size_t n2 = (size_t)n * n;
+  float *hA, *hB, *hC, *hRef;
+  CK(b2_host_alloc((void **)&hA, n2 * 4)); CK(b2_host_alloc((void **)&hB, n2 * 4));
+  CK(b2_host_alloc((void **)&hC, n2 * 4)); CK(b2_host_alloc((void **)&hRef, n2 * 4));
+  CK(b2_fill_uniform_host(hA, (int64_t)n2, 1)); CK(b2_fill_uniform_host(hB, (int64_t)n2, 2)); CK(b2_fill_uniform_host(hC, (int64_t)n2, 3));
+  // the reference drivers' way: blocking copies around one launch
+  float *dA, *dB, *dC;
+  CU(cudaMalloc(&dA, n2 * 4)); CU(cudaMalloc(&dB, n2 * 4)); CU(cudaMalloc(&dC, n2 * 4));
+  CU(cudaMemcpy(dA, hA, n2 * 4, cudaMemcpyHostToDevice)); CU(cudaMemcpy(dB, hB, n2 * 4, cudaMemcpyHostToDevice));
+  CU(cudaMemcpy(dC, hC, n2 * 4, cudaMemcpyHostToDevice));
+  b2_handle h;
+  CK(b2_create(&h));
+  CK(b2_sgemm(h, path, n, n, n, alpha, dA, n, dB, n, beta, dC, n, nullptr));
+  CU(cudaMemcpy(hRef, dC, n2 * 4, cudaMemcpyDeviceToHost));
+  b2_host_plan plan;
+  CK(b2_host_plan_create(&plan, h, path, n, n, n, 0, 0, 0));
+  CK(b2_sgemm_host(plan, alpha, hA, n, hB, n, beta, hC, n, 0, nullptr));
+  if (path == B2_PATH_FFMA && memcmp(hC, hRef, n2 * 4) != 0) {
+    printf("sgemm_host: the pipelined result differs from the single device call at n = %d\n", n);
+    return 5;
+  }
+  double worst = 0.0;
+  for (size_t i = 0; i < n2; ++i) {
+    const double d = (double)hC[i] - (double)hRef[i];
+    if (d > worst) worst = d;
+    if (-d > worst) worst = -d;
+  }
+  if (!(worst <= 1e-3 * n)) { printf("sgemm_host: result off by %g at n = %d\n", worst, n); return 5; }
+  const int iters = 5;
+  cudaEvent_t e0, e1;
+  CU(cudaEventCreate(&e0)); CU(cudaEventCreate(&e1));
+  CU(cudaEventRecord(e0, nullptr));
+  for (int it = 0; it < iters; ++it) CK(b2_sgemm_host(plan, alpha, hA, n, hB, n, beta, hC, n, 0, nullptr));
+  CU(cudaEventRecord(e1, nullptr));
+  CU(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  CU(cudaEventElapsedTime(&ms, e0, e1));
+  printf("sgemm_host n = %5d  path %d  %9.1f GFLOPS end to end (%.3f ms per call, host copies included; max |diff| vs device call %.2e)\n",
+         n, path, 2.0 * iters * (double)n * n * n / 1e9 / (ms / 1e3), ms / iters, worst);
+  CK(b2_host_plan_destroy(plan));
+  CK(b2_check_status(h, nullptr));
+  CK(b2_destroy(h));
+  return 0;
+}
+
+// One process per GPU.  Rank 0 draws the communicator id and publishes it through a file (written under another
+// name and renamed, so that a reader never sees half of it).
+static int run_mg(int rank, int world, const char *id_file, int n, int panel) {
+  int ndev = 0;
+  CU(cudaGetDeviceCount(&ndev));
+  CU(cudaSetDevice(rank % (ndev > 0 ? ndev : 1)));
+  unsigned char id[B2_MG_ID_BYTES];
+  memset(id, 0, sizeof id);
+  if (world > 1) {
+    if (rank == 0) {
+      CK(b2_mg_unique_id(id));
+      std::string tmp = std::string(id_file) + ".tmp";
+      FILE *f = fopen(tmp.c_str(), "wb");
+      if (!f || fwrite(id, 1, sizeof id, f) != sizeof id) { fprintf(stderr, "cannot write %s\n", tmp.c_str()); return 6; }
+      fclose(f);
+      if (rename(tmp.c_str(), id_file) != 0) { fprintf(stderr, "cannot publish %s\n", id_file); return 6; }
+    } else {
+      FILE *f = nullptr;
+      for (int tries = 0; tries < 600 && !(f = fopen(id_file, "rb")); ++tries) usleep(100000);
+      if (!f || fread(id, 1, sizeof id, f) != sizeof id) { fprintf(stderr, "rank %d: no communicator id in %s after 60 s\n", rank, id_file); return 6; }
+      fclose(f);
+    }
+  }
+  b2_mg_handle mg;
+  CK(b2_mg_create(&mg, nullptr, rank, world, world > 1 ? id : nullptr));
+  int64_t start = 0, rows = 0;
+  CK(b2_mg_row_block(n, rank, world, &start, &rows));
+  const size_t n2 = (size_t)n * n, blk = (size_t)rows * n;
+  float *dA, *dB, *dC, *dRef;
+  CU(cudaMalloc(&dA, (blk ? blk : 1) * 4)); CU(cudaMalloc(&dB, n2 * 4)); CU(cudaMalloc(&dC, (blk ? blk : 1) * 4)); CU(cudaMalloc(&dRef, (blk ? blk : 1) * 4));
+  CK(b2_fill_uniform(dA, (int64_t)blk, 1000 + rank, nullptr));
+  CK(b2_fill_uniform(dC, (int64_t)blk, 3000 + rank, nullptr));
+  CU(cudaMemcpy(dRef, dC, blk * 4, cudaMemcpyDeviceToDevice));
+  if (rank == 0) CK(b2_fill_uniform(dB, (int64_t)n2, 2, nullptr));
+  else CU(cudaMemset(dB, 0xff, n2 * 4));     // NaN pattern: a panel used before it landed would show
+  const float alpha = 1.0f, beta = 0.5f;
+  CK(b2_mg_sgemm(mg, B2_PATH_FFMA, 0, n, n, n, alpha, dA, n, dB, n, beta, dC, n, 0, panel, nullptr, nullptr));
+  CU(cudaDeviceSynchronize());
+  // B is now everywhere: the same K-panel schedule, locally, must give the same bits
+  const int count = b2_mg_k_panel(n, panel, 0, nullptr, nullptr);
+  for (int i = 0; i < count && rows > 0; ++i) {
+    int k0 = 0, kw = 0;
+    b2_mg_k_panel(n, panel, i, &k0, &kw);
+    CK(b2_sgemm(nullptr, B2_PATH_FFMA, (int)rows, n, kw, alpha, dA + k0, n, dB + (size_t)k0 * n, n, i == 0 ? beta : 1.0f, dRef, n, nullptr));
+  }
+  float max_abs = 0.f;
+  if (rows > 0 && b2_verify_matrix(dRef, dC, rows, n, n, 0.0f, &max_abs, nullptr) != 0) {
+    printf("rank %d: sharded SGEMM differs from the local panel schedule (max |diff| %g)\n", rank, max_abs);
+    return 5;
+  }
+  b2_timer timer;
+  CK(b2_timer_create(&timer));
+  CK(b2_timer_start(timer, nullptr));
+  const int iters = 3;
+  for (int it = 0; it < iters; ++it)
+    CK(b2_mg_sgemm(mg, B2_PATH_FFMA, 0, n, n, n, alpha, dA, n, dB, n, 0.0f, dC, n, 0, panel, nullptr, nullptr));
+  CK(b2_timer_stop(timer, nullptr));
+  float ms = 0.f;
+  CK(time_ms(timer, &ms));
+  // sharded SDOT: every rank can rebuild every slice, so the expected sum is formed locally
+  const int64_t nloc = (int64_t)1 << 22;
+  float *dx, *dy, *dres;
+  double *dsum, *dpart;
+  CU(cudaMalloc(&dx, nloc * 4)); CU(cudaMalloc(&dy, nloc * 4)); CU(cudaMalloc(&dres, 4)); CU(cudaMalloc(&dsum, 8)); CU(cudaMalloc(&dpart, 8));
+  double expect = 0.0;
+  for (int r = 0; r < world; ++r) {
+    CK(b2_fill_uniform(dx, nloc, 40 + r, nullptr));
+    CK(b2_fill_uniform(dy, nloc, 50 + r, nullptr));
+    CK(b2_sdot_partial(nullptr, nloc, dx, dy, dres, dpart, nullptr));
+    double part = 0.0;
+    CU(cudaMemcpy(&part, dpart, 8, cudaMemcpyDeviceToHost));
+    expect += part;
+  }
+  CK(b2_fill_uniform(dx, nloc, 40 + rank, nullptr));
+  CK(b2_fill_uniform(dy, nloc, 50 + rank, nullptr));
+  CK(b2_mg_sdot(mg, nloc, dx, dy, dres, dsum, nullptr));
+  double got = 0.0;
+  CU(cudaMemcpy(&got, dsum, 8, cudaMemcpyDeviceToHost));
+  const double tol = 1e-12 * (double)nloc * world;
+  if (!(got - expect <= tol && expect - got <= tol)) { printf("rank %d: sharded SDOT %.17g, expected %.17g\n", rank, got, expect); return 5; }
+  printf("rank %d of %d: mg sgemm n = %d rows %lld  %9.1f GFLOPS for the whole product (%.3f ms per call), bit-identical to the local panel schedule; mg sdot ok\n",
+         rank, world, n, (long long)rows, 2.0 * iters * (double)n * n * n / 1e9 / (ms / 1e3), ms / iters);
+  CK(b2_check_status(nullptr, nullptr));
+  CK(b2_mg_destroy(mg));
+  return 0;
+}
+
 int main(int argc, char **argv) {
   if (argc < 2) {
-    printf("usage: %s sgemm <kernel_id 1..14> <start> <end> [threads_x] | ft_sgemm <start> <end> <gap> | saxpy | sdot\n", argv[0]);
+    printf("usage: %s sgemm <kernel_id 1..14> <start> <end> [threads_x] | ft_sgemm <start> <end> <gap> | saxpy | sdot | "
+           "sgemm_host <n> [path] | mg <rank> <world> <id file> <n> [panel_k]\n", argv[0]);
     return 1;
   }
   if (!strcmp(argv[1], "sgemm") && argc >= 5)
     return run_sgemm(atoi(argv[2]), atoi(argv[3]), atoi(argv[4]), argc > 5 ? atoi(argv[5]) : 32);
   if (!strcmp(argv[1], "ft_sgemm") && argc >= 5) return run_ft_sgemm(atoi(argv[2]), atoi(argv[3]), atoi(argv[4]));
+  if (!strcmp(argv[1], "sgemm_host") && argc >= 3) return run_sgemm_host(atoi(argv[2]), argc > 3 ? atoi(argv[3]) : 0);
+  if (!strcmp(argv[1], "mg") && argc >= 6) return run_mg(atoi(argv[2]), atoi(argv[3]), argv[4], atoi(argv[5]), argc > 6 ? atoi(argv[6]) : 0);
   if (!strcmp(argv[1], "saxpy")) return run_vectors(false);
   if (!strcmp(argv[1], "sdot")) return run_vectors(true);
   printf("bad arguments\n");

@@ -196,6 +196,64 @@ int b2_sdot_fused(b2_handle h, int64_t n, const float *x, const float *y, float 
  *    (different streams, no dependency) race with each other; serialise them. */
 int b2_sdot_static(int64_t n, const float *x, const float *y, float *result_dev, void *stream);
 
+/* ---- SGEMM on host arrays --------------------------------------------------------------- */
+
+/* The reference drivers hold their matrices on the host and move them with blocking cudaMemcpy calls around the
+ * launch (kernel/sgemm/sgemm.cu:50-63, kernel/ft_sgemm/sgemm.cu:60-66).  A host plan does the same for one problem
+ * shape with the transfers overlapped with the kernels: it owns device copies of A (M x K), B (K x N) and C (M x N),
+ * three streams and their events.  panel_rows / panel_cols / panel_k = 0 select the defaults (1536 / 1536 / all of
+ * K); they are rounded to multiples of 128.  The plan computes on its own stream with the handle's scratch: do not
+ * use the handle elsewhere while b2_sgemm_host runs. */
+typedef struct b2_host_plan_s *b2_host_plan;
+int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, int K, int panel_rows, int panel_cols,
+                        int panel_k);
+int b2_host_plan_destroy(b2_host_plan p);
+/* C <- alpha*A*B + beta*C on HOST arrays (row-major, leading dimensions in floats); returns when C is complete on
+ * the host.  With one K panel (the default) every output sums all of K inside one kernel, so the FFMA result is
+ * bit-identical to b2_sgemm on device copies; with panel_k < K block (p, q) accumulates into C with beta on the
+ * first K panel and 1 afterwards.  Host memory from b2_host_alloc (or registered with cudaHostRegister) lets the
+ * copies run asynchronously; pageable memory works but serialises them.  abft != 0 runs the fault-tolerant kernels
+ * (default threshold, no injection) and, if report_host is not NULL, leaves the summed report there. */
+int b2_sgemm_host(b2_host_plan p, float alpha, const float *A, int lda, const float *B, int ldb, float beta, float *C,
+                  int ldc, int abft, b2_ft_report *report_host);
+/* Page-locked host memory for the arrays above (cudaMallocHost / cudaFreeHost). */
+int b2_host_alloc(void **out, size_t bytes);
+int b2_host_free(void *p);
+
+/* ---- multi-GPU: one process (or host thread) per GPU --------------------------------------- */
+
+/* The reference is single-GPU.  Large products are sharded the way its row-major layout suggests: A and C by
+ * contiguous row blocks, one per rank; B lives on `root` and is broadcast once per product in K panels (contiguous
+ * row blocks of the row-major B) on a communication stream while the compute stream consumes the panels that have
+ * landed: C_r = beta*C_r + alpha * sum_p A_r[:, panel p] * B[panel p, :].  There is no result exchange.  SDOT: every
+ * rank reduces its slice to a double, then one all-reduce of that scalar.  The collectives are NCCL's, looked up at
+ * run time in libnccl.so.2 (the copy already loaded in the process, else the system's): the library has no
+ * link-time dependency on NCCL, and world = 1 needs none at all. */
+typedef struct b2_mg_context *b2_mg_handle;
+#define B2_MG_ID_BYTES 128
+/* Rank 0 calls this and hands the 128 bytes to every rank by its own means (a file, MPI, a key-value store). */
+int b2_mg_unique_id(void *id_out);
+/* Collective over all ranks, each with its own GPU current: joins the communicator.  `h` is the handle whose
+ * scratch the rank's kernels use (NULL: the device's default handle).  world = 1: `id` may be NULL. */
+int b2_mg_create(b2_mg_handle *out, b2_handle h, int rank, int world, const void *id);
+int b2_mg_destroy(b2_mg_handle mg);
+/* Partition helpers (host only, no device needed): rank's contiguous block of M rows (block sizes differ by at most
+ * one), and K panel `index` of width `panel` (the last may be narrower); b2_mg_k_panel returns the number of panels. */
+int b2_mg_row_block(int64_t M, int rank, int world, int64_t *start, int64_t *rows);
+int b2_mg_k_panel(int K, int panel, int index, int *k0, int *width);
+/* Sharded row-major SGEMM (abft != 0: the fault-tolerant kernels; report_dev as in b2_ft_sgemm, may be NULL).
+ * A_local (rows_r x K, lda) and C_local (rows_r x N, ldc) are this rank's row blocks of b2_mg_row_block(M, ...);
+ * B (K x N, ldb) is a device buffer on every rank whose contents are valid on `root` at entry and on every rank once
+ * the call's work has completed.  panel_k = 0 selects 4096.  Work is enqueued on `stream` and on the handle's own
+ * communication stream; every rank must make the same sequence of b2_mg_* calls. */
+int b2_mg_sgemm(b2_mg_handle mg, int path, int abft, int M, int N, int K, float alpha, const float *A_local, int lda,
+                float *B, int ldb, float beta, float *C_local, int ldc, int root, int panel_k, b2_ft_report *report_dev,
+                void *stream);
+/* Sum over all ranks of x_local . y_local: *sum_dev (double) and *result_dev (float, may be NULL) hold the same value
+ * on every rank once the stream has completed.  b2_sdot_fused is the form without any collective call. */
+int b2_mg_sdot(b2_mg_handle mg, int64_t n_local, const float *x_local, const float *y_local, float *result_dev,
+               double *sum_dev, void *stream);
+
 /* ---- harness (rebuild of utils/utils.cu around CUDA events) ----------------------- */
 
 /* Element i of the stream `seed` is a counter-based hash of (seed, i) mapped to a

@@ -548,3 +548,86 @@ def test_colmajor_nt_bit_identical_to_the_reference_generated_kernel(cuda, tmp_p
     b2.sgemm_colmajor_nt(M, N, K, dev(af), dev(bf), dcf, alpha, beta)
     assert np.array_equal(dcf.cpu().numpy().ravel(), ref)
     assert np.array_equal(np.asarray(oracle.sgemm_colmajor_nt(M, N, K, alpha, af, bf, beta, cf)).ravel(), ref)
+
+
+def test_two_devices_in_one_process(cuda):
+    """One process that drives two GPUs: the kernels' shared-memory opt-in and the resident-pair count are per
+    device, and a handle is refused while another device than its own is current."""
+    import hpcdeepneuralnetworks_b200 as b2
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    a, b, c = mats(512, 768, 256)
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+    want = oracle.sgemm_fma(1.0, a, b, 0.5, c)
+    try:
+        for d in (0, 1, 0):
+            with torch.cuda.device(d):
+                da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+                dc = torch.from_numpy(c).cuda()
+                b2.sgemm(512, 768, 256, 1.0, da, db, 0.5, dc, path=0)
+                assert np.array_equal(dc.cpu().numpy(), want)
+                for pair in (0, 2):
+                    b2.set_tf32_pair(pair)
+                    dc = torch.from_numpy(c).cuda()
+                    b2.sgemm(512, 768, 256, 1.0, da, db, 0.5, dc, path=1)
+                    assert oracle.gemm_error(dc.cpu().numpy(), c64, den) <= TOL_3XTF32
+                    dc = torch.from_numpy(c).cuda()
+                    b2.ft_sgemm(512, 768, 256, 1.0, da, db, 0.5, dc, path=1)
+                    assert oracle.gemm_error(dc.cpu().numpy(), c64, den) <= TOL_3XTF32
+                b2.check_status()
+        with torch.cuda.device(0):
+            h0 = b2.Handle()
+        with torch.cuda.device(1):
+            da, db, dc = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), torch.from_numpy(c).cuda()
+            with pytest.raises(b2.B2Error) as e:
+                b2.sgemm(512, 768, 256, 1.0, da, db, 0.5, dc, handle=h0)
+            assert e.value.status == -1 and "device" in str(e.value)
+        with torch.cuda.device(0):
+            h0.close()
+    finally:
+        b2.set_tf32_pair(1)
+        torch.cuda.set_device(0)
+
+
+def test_two_host_threads_one_handle_each(cuda):
+    """Two host threads on one GPU, each with its own handle and stream, launching both math paths at the same time:
+    every result is the oracle's (the library keeps no per-call state outside the handle)."""
+    import threading
+    import hpcdeepneuralnetworks_b200 as b2
+    shapes = [(384, 512, 160), (256, 2304, 96)]
+    cases = []
+    for M, N, K in shapes:
+        a, b, c = mats(M, N, K)
+        cases.append((M, N, K, a, b, c, oracle.sgemm_fma(1.0, a, b, 0.5, c), oracle.sgemm_f64(1.0, a, b, 0.5, c)))
+    errors = []
+
+    def work(i):
+        try:
+            torch.cuda.set_device(0)
+            h = b2.Handle()
+            stream = torch.cuda.Stream()
+            M, N, K, a, b, c, want, (c64, den) = cases[i]
+            with torch.cuda.stream(stream):
+                da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+                for it in range(20):
+                    dc = torch.from_numpy(c).cuda()
+                    b2.sgemm(M, N, K, 1.0, da, db, 0.5, dc, path=0, handle=h)
+                    stream.synchronize()
+                    if not np.array_equal(dc.cpu().numpy(), want):
+                        errors.append(f"thread {i} iteration {it}: FFMA result differs")
+                    dc = torch.from_numpy(c).cuda()
+                    b2.sgemm(M, N, K, 1.0, da, db, 0.5, dc, path=1, handle=h)
+                    stream.synchronize()
+                    if oracle.gemm_error(dc.cpu().numpy(), c64, den) > TOL_3XTF32:
+                        errors.append(f"thread {i} iteration {it}: 3xTF32 result out of tolerance")
+                b2.check_status(h)
+            h.close()
+        except Exception as e:       # a failed assertion in a thread would otherwise be lost
+            errors.append(f"thread {i}: {type(e).__name__}: {e}")
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert errors == []
