@@ -66,6 +66,8 @@ def load() -> C.CDLL:
     L.b2_set_workspace.argtypes = [vp, vp, C.c_size_t]
     L.b2_sgemm_workspace_bytes.restype = C.c_size_t
     L.b2_sgemm_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    L.b2_ft_sgemm_workspace_bytes.restype = C.c_size_t
+    L.b2_ft_sgemm_workspace_bytes.argtypes = [i32, i32, i32, i32]
     L.sgemm.argtypes = [i32, i32, i32, f32, vp, vp, f32, vp]
     L.ft_sgemm.argtypes = [i32, i32, i32, f32, vp, vp, f32, vp]
     L.b2_sgemm.argtypes = [vp, i32, i32, i32, i32, f32, vp, i32, vp, i32, f32, vp, i32, vp]

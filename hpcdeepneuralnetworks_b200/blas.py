@@ -148,7 +148,7 @@ def ft_sgemm(M, N, K, alpha, A, B, beta, Cm, *, path=PATH_FFMA, plan=None, tau=0
     0 the default for operands of unit scale, < 0 that default scaled by 3*rms(A)*rms(B).  Returns ``Cm``."""
     L = _lib.load()
     h = handle or default_handle()
-    h.reserve(L.b2_sgemm_workspace_bytes(path, M, N, K))
+    h.reserve(L.b2_ft_sgemm_workspace_bytes(path, M, N, K))
     nf = 0 if plan is None else int(plan.shape[0])
     check(L.b2_ft_sgemm(h.raw, path, M, N, K, alpha, _ptr(A), lda or K, _ptr(B), ldb or N, beta, _ptr(Cm), ldc or N,
                         _ptr(plan), nf, tau, _ptr(report), _stream()))
@@ -159,6 +159,7 @@ def ft_sgemm_colmajor_nt(M, N, K, A, B, Cm, alpha, beta, *, plan=None, tau=0.0, 
     """ABFT SGEMM in the kernel/ft_sgemm layout (column-major A MxK, B NxK, C MxN; C = alpha*A*B^T + beta*C).
     A planned fault's (row, col) address C^T."""
     h = handle or default_handle()
+    h.reserve(_lib.load().b2_ft_sgemm_workspace_bytes(PATH_FFMA, N, M, K))
     nf = 0 if plan is None else int(plan.shape[0])
     check(_lib.load().b2_ft_sgemm_colmajor_nt(h.raw, M, N, K, alpha, _ptr(A), _ptr(B), beta, _ptr(Cm), _ptr(plan), nf, tau,
                                               _ptr(report), _stream()))
@@ -244,8 +245,8 @@ class HostSgemm:
         # scratch for the largest panel product, handed to the library before the plan is made
         rows_max, k_max = min(self.pr, M), min(self.pk, K)
         if M > 0 and N > 0 and K > 0:
-            self._handle.reserve(max(self._L.b2_sgemm_workspace_bytes(path, rows_max, N, k_max),
-                                     self._L.b2_sgemm_workspace_bytes(path, rows_max, min(self.pc, N), k_max)))
+            self._handle.reserve(max(self._L.b2_ft_sgemm_workspace_bytes(path, rows_max, N, k_max),
+                                     self._L.b2_ft_sgemm_workspace_bytes(path, rows_max, min(self.pc, N), k_max)))
         self._plan = C.c_void_p()
         check(self._L.b2_host_plan_create(C.byref(self._plan), self._handle.raw, path, M, N, K, panel_rows, panel_cols,
                                           max(panel_k, 0)))

@@ -105,6 +105,8 @@ struct FtArgs {
   int *report;  // b2_ft_report as ints: tiles, injected, detected, corrected, uncorrectable, false alarms, max residual bits
   const float *A, *B;
   int lda, ldb;
+  int nbands_pad;   // FFMA path: 16-row bands of A per K-slab in the table of A's band checksums
+  size_t ws_used;   // FFMA path, host side: bytes at the front of the workspace that hold the transposed A
 };
 
 #ifdef __CUDACC__

@@ -14,6 +14,9 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
 int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
                           float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
 void set_ft_level_knob(int level);
+size_t ffma_workspace_bytes(int M, int N, int K);
+size_t ft_tables_bytes(int M, int N, int K);
+size_t tf32_workspace_bytes(int M, int N, int K);
 void set_ffma_transpose_a_knob(int on);
 
 // Sum of squares of a rows x cols matrix (pitch ld) added to *out: one block per row stripe.
@@ -59,6 +62,8 @@ int ft_sgemm_on(Context *ctx, int path, int M, int N, int K, float alpha, const 
                 float beta, float *C, int ldc, const b2_fault *plan_dev, int n_faults, float tau, b2_ft_report *report_dev,
                 cudaStream_t s) {
   FtArgs ft;
+  ft.nbands_pad = 0;
+  ft.ws_used = 0;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
   ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
@@ -136,6 +141,8 @@ int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const
   B2_REQUIRE(C != nullptr && (K == 0 || (A != nullptr && B != nullptr)), B2_ERR_INVALID_ARG, "b2_ft_sgemm_colmajor_nt: null matrix");
   B2_CONTEXT(ctx, h, "b2_ft_sgemm_colmajor_nt");
   FtArgs ft;
+  ft.nbands_pad = 0;
+  ft.ws_used = 0;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
   ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);
@@ -156,6 +163,14 @@ int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const
 // (include/ft_sgemm_huge.cuh:21), default stream, no injection.
 int ref_ft_sgemm_colmajor_nt(int M, int N, int K, float *A, float *B, float *C, float alpha, float beta) {
   return b2_ft_sgemm_colmajor_nt(nullptr, M, N, K, alpha, A, B, beta, C, nullptr, 0, 0.f, nullptr, nullptr);
+}
+
+// Workspace of the fault-tolerant SGEMM: the plain product's, plus on the FFMA path the two operand-checksum tables.
+size_t b2_ft_sgemm_workspace_bytes(int path, int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (path == B2_PATH_3XTF32) return tf32_workspace_bytes(M, N, K);
+  if (path != B2_PATH_FFMA) return 0;
+  return ffma_workspace_bytes(M, N, K) + ft_tables_bytes(M, N, K);
 }
 
 int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C) {

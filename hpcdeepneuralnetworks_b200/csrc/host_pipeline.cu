@@ -133,8 +133,8 @@ int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, 
   size_t ws = 0;
   const int rows_max = p->pr < M ? p->pr : M, k_max = p->pk < K ? p->pk : K;
   if (M > 0 && N > 0 && K > 0) {
-    ws = b2_sgemm_workspace_bytes(path, rows_max, N, k_max);
-    const size_t ws_first = b2_sgemm_workspace_bytes(path, rows_max, p->pc < N ? p->pc : N, k_max);
+    ws = b2_ft_sgemm_workspace_bytes(path, rows_max, N, k_max);
+    const size_t ws_first = b2_ft_sgemm_workspace_bytes(path, rows_max, p->pc < N ? p->pc : N, k_max);
     if (ws_first > ws) ws = ws_first;
   }
   if (ws > ctx->ws_bytes && (ctx->ws == nullptr || ctx->ws_owned)) {

@@ -189,7 +189,7 @@ int b2_mg_sgemm(b2_mg_handle mg, int path, int abft, int M, int N, int K, float 
     return sgemm_dispatch(mg->ctx, path, abft != 0, rows, N, 0, alpha, A_local, lda > 0 ? lda : 1, B, ldb, beta, C_local, ldc, report_dev, s);
   // scratch for the largest panel product up front: growing it between panels would synchronise the device
   if (rows > 0 && (mg->ctx->ws == nullptr || mg->ctx->ws_owned)) {
-    const size_t need = b2_sgemm_workspace_bytes(path, rows, N, panel < K ? panel : K);
+    const size_t need = b2_ft_sgemm_workspace_bytes(path, rows, N, panel < K ? panel : K);
     if (need > mg->ctx->ws_bytes) {
       int st = ensure_workspace(mg->ctx, need, s);
       if (st != B2_OK && path == B2_PATH_3XTF32) return st;

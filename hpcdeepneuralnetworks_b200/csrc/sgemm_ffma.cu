@@ -67,33 +67,26 @@ struct FfmaArgs {
   int device;         // host side only: the device the launch goes to
 };
 
-// ABFT arguments.  Checksum algebra of kernel/ft_sgemm/README.md:4-14 at the granularity the
-// accumulators are held: block (w, g) = the 16 rows of warp w x the NR columns of lane column g
-// (64 blocks of 16 x 16 in a 128 x 128 tile).  With Asum_w[k] = sum of A over the 16 rows of w
-// (a column checksum e^T A of that row band) and Bsum_g[k] = sum of B[k][.] over the columns
-// of g (a row checksum B e of that column set),
+// ABFT.  Checksum algebra of kernel/ft_sgemm/README.md:4-14 at the granularity the accumulators are held:
+// block (w, g) = the 16 rows of warp w x the NR columns of lane column g (64 blocks of 16 x 16 in a 128 x 128
+// tile).  With Asum_w[k] = sum of A over the 16 rows of w (a column checksum e^T A of that row band) and
+// Bsum_g[k] = sum of B[k][.] over the columns of g (a row checksum B e of that column set),
 //     sum of the block's outputs = sum_k Asum_w[k] * Bsum_g[k].
-// Both sums are formed slab by slab in the mainloop from the shared-memory stage that the FMAs
-// consume (the reference encodes from the registers it prefetched,
-// kernel/ft_sgemm/include/ft_sgemm_tall.cuh:178-267):
-//   phase 1 (before the slab's FMAs): each warp sums its own 16 rows of the A slab (4 loads,
-//           packed adds, a 3-shuffle transpose-reduce) and keeps the 32 sums in a private
-//           shared row; thread (k, g) sums the NR columns of g in row k of the B slab into a
-//           per-stage shared table, announced on a split-phase mbarrier;
-//   phase 2 (after the FMAs, when all warps' sums have long arrived): lane (g, r) adds
-//           sum_{8 k of r} Asum_w[k] * Bsum_g[k] to its running checksum (4 packed FMAs).
-// The epilogue folds the 4 k-ranges and the 4 x NR accumulators of the 4 lanes that share a
-// block with two shuffles each and compares them in registers (the reference compares every
-// 256 of K through shared memory, ft_sgemm_huge.cuh:143-271).  A block out of tolerance is
-// recomputed element by element from A and B in global memory with the kernel's own
-// arithmetic; every accumulator that differs is replaced, which both locates and corrects
-// the fault exactly (the reference subtracts a rounded residual with the location left
-// unfinished, ft_sgemm_huge.cuh:296-371).
-
-// The table of a slab's B sums is read one slab later (phase 2), and the shared-memory ring lets a warp run up to
-// two slabs ahead of the slowest one: with four tables the writer of slab kb + 3 is gated, through the ring's
-// "empty" barrier of slab kb, behind every reader of the table of slab kb - 1 (three tables would leave a window).
-constexpr int kFtTables = 4;
+// The reference encodes both operand checksums inside every CTA from the registers it prefetched
+// (kernel/ft_sgemm/include/ft_sgemm_tall.cuh:178-267), so every CTA of a tile row re-encodes the same band of A
+// and every CTA of a tile column the same panel of B.  Here (FT = 1) the operand checksums are encoded ONCE per
+// product by two small pre-pass kernels (ft_encode_a_kernel, ft_encode_b_kernel: one more read of A and B, 1/16
+// of their size written) into per-slab tables, and travel with each K-slab through the same TMA ring as the
+// operand tiles (1 KB + 128 B per warp and stage); in the mainloop lane (g, r) adds
+// sum_{8 k of r} Asum_w[k] * Bsum_g[k] to its running checksum: 4 shared loads and 4 packed FMAs per slab beside
+// the 1024 packed FMAs of the product.  A corrupted operand tile in shared memory now disagrees with its checksum
+// (with in-CTA encoding both would be wrong together).
+// The epilogue folds the 4 k-ranges and the 4 x NR accumulators of the 4 lanes that share a block with two
+// shuffles each and compares them in registers (the reference compares every 256 of K through shared memory,
+// ft_sgemm_huge.cuh:143-271).  A block out of tolerance is recomputed element by element from A and B in global
+// memory with the kernel's own arithmetic; every accumulator that differs is replaced, which both locates and
+// corrects the fault exactly (the reference subtracts a rounded residual with the location left unfinished,
+// ft_sgemm_huge.cuh:296-371).
 template <int BM, int NR>
 struct TileCfg {
   static constexpr int BN = 8 * NR;
@@ -101,10 +94,10 @@ struct TileCfg {
   static constexpr int THREADS = 32 * WARPS;
   static constexpr int kStageA = BM * FBK * 4;
   static constexpr int kStageB = FBK * BN * 4;
-  static constexpr int kBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3], sums_ready[kFtTables]
-  static constexpr int kAwOff = kBarOff + 128;                   // float Asum[WARPS][32]
-  static constexpr int kBgOff = kAwOff + WARPS * 128;            // float Bsum[kFtTables][8][32]
-  static constexpr int kMiscOff = kBgOff + kFtTables * 1024;     // int inj[8]; int nflag; int flagged[64]
+  static constexpr int kBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3]
+  static constexpr int kCsOff = kBarOff + 128;                   // per stage: float Asum[WARPS][32], float Bsum[256]
+  static constexpr int kStageCs = WARPS * 128 + 1024;
+  static constexpr int kMiscOff = kCsOff + FSTAGES * kStageCs;   // int inj[8]; int nflag; int flagged[64]
   static constexpr int kSmem = 1024 + kMiscOff + 512;
   static constexpr int MIN_BLOCKS = 512 / THREADS;
   static_assert(BM % 16 == 0 && BM >= 32 && BM <= 128, "BM is 32, 64 or 128");
@@ -228,7 +221,8 @@ __device__ __forceinline__ float thread_checksum_step(const float (&a)[4], const
 
 template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
 __global__ void __launch_bounds__(TileCfg<BM, NR>::THREADS, TileCfg<BM, NR>::MIN_BLOCKS)
-sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FfmaArgs p,
+sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const FfmaArgs p,
                   const FtArgs ft) {
   using Cfg = TileCfg<BM, NR>;
   constexpr int BN = Cfg::BN, WARPS = Cfg::WARPS, THREADS = Cfg::THREADS;
@@ -240,9 +234,9 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   unsigned char *sB = smem + FSTAGES * kStageA;
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + Cfg::kBarOff);
   uint64_t *empty = full + FSTAGES;
-  uint64_t *sums_ready = empty + FSTAGES;
-  unsigned char *sAw = smem + Cfg::kAwOff;   // [warp][32] sums of the warp's 16 rows of the A slab
-  unsigned char *sBg = smem + Cfg::kBgOff;   // [stage] 1 KB table of the sums of column set g of the B slab per k
+  unsigned char *sCs = smem + Cfg::kCsOff;   // per stage: the slab's operand checksums, Asum[warp][32] then Bsum (1 KB)
+  constexpr int kStageCs = Cfg::kStageCs;
+  constexpr uint32_t kStageBytes = kStageA + kStageB + (FT == 1 ? kStageCs : 0);
   int *inj = reinterpret_cast<int *>(smem + Cfg::kMiscOff);
   int *nflag = inj + 8;
   int *flagged = inj + 9;
@@ -268,12 +262,14 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], WARPS);
     }
-    if (FT == 1)
-      for (int t = 0; t < kFtTables; ++t) mbar_init(&sums_ready[t], WARPS);
     if (FT) *nflag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (FT == 1) {
+      tma_prefetch_desc(&tmSA);
+      tma_prefetch_desc(&tmSB);
+    }
   }
   if (FT && warp == WARPS - 1) {
     // first planned fault that names this tile (a plan holds at most one per tile; tiles are
@@ -299,10 +295,14 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __syncthreads();
   if (tid == 0) {
     for (int s = 0; s < FSTAGES && s < nkb; ++s) {
-      mbar_expect_tx(&full[s], kStageA + kStageB);
+      mbar_expect_tx(&full[s], kStageBytes);
       if (TRANS_A) tma_load_2d(sA + s * kStageA, &tmA, &full[s], m0, s * FBK);
       else tma_load_2d(sA + s * kStageA, &tmA, &full[s], s * FBK, m0);
       tma_load_2d(sB + s * kStageB, &tmB, &full[s], n0, s * FBK);
+      if (FT == 1) {
+        tma_load_2d(sCs + s * kStageCs, &tmSA, &full[s], 0, s * ft.nbands_pad + tile_m * WARPS);
+        tma_load_2d(sCs + s * kStageCs + WARPS * 128, &tmSB, &full[s], 0, s * tiles_n + tile_n);
+      }
     }
   }
 
@@ -323,11 +323,6 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t a_thread = TRANS_A ? (uint32_t)(warp * 16 + lm * 4) * 4u : (uint32_t)(warp * 16 + lm) * 128u;
   const uint32_t a_swz = (uint32_t)lm << 4;
   const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;
-  // ABFT encoder offsets: this lane's part of the warp's 16 A rows, and its (k, g) cells of B
-  const uint32_t e_a_off = TRANS_A ? (uint32_t)(lane >> 2) * (BM * 4) + (uint32_t)warp * 64u + (uint32_t)(lane & 3) * 16u
-                                   : (uint32_t)(warp * 16 + lm) * 128u + (uint32_t)((ln ^ lm) << 4);
-  const int ta_k = 8 * (2 * (lane & 1) + ((lane >> 1) & 1)) + (lane >> 2);   // the k whose A sum this lane ends up with
-  const uint32_t e_b_off = (uint32_t)(tid >> 3) * BROW + (uint32_t)(tid & 7) * 16u;
   uint64_t chk2[2] = {0ull, 0ull};  // running checksum of block (warp, ln) over this lane's k-range, packed
   float tchk = 0.f;                 // FT = 2: running checksum of this thread's own 4 x NR outputs
   bool ok = true;
@@ -341,82 +336,13 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     const unsigned char *Ast = sA + s * kStageA;
     const unsigned char *Bst = sB + s * kStageB;
-    // ---- ABFT phase 1 (slab sums) and phase 2 (fold the PREVIOUS slab's sums into the running
-    // checksum) are issued from inside the unrolled FMA stream below, so that their load ->
-    // add -> shuffle -> store chains overlap with FMAs instead of idling the warp.
-    auto phase1 = [&]() {
-      // ---- phase 1: slab sums ----
-      float aw;  // this lane's entry of the warp's 32 A sums: k = 4*ln + lm, or k = ta_k for transposed A
-      if (TRANS_A) {
-        // [k][BM] stage: the warp's 16 columns are 64 bytes of each 512-byte row, always the same 16
-        // banks.  Lane (ksub, c4) = (lane >> 2, lane & 3) reads chunk c4 of rows 8j + ksub (8 rows per
-        // load instead of 32: a quarter of the bank conflicts), then the four chunk lanes fold.
-        const unsigned char *pa = Ast + e_a_off;
-        float p[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(pa + j * 8 * (BM * 4));
-          float lo, hi;
-          unpack2(fadd2(v.x, v.y), lo, hi);
-          p[j] = lo + hi;
-        }
-        const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
-        float k0 = b0 ? p[2] : p[0], k1 = b0 ? p[3] : p[1];
-        k0 += __shfl_xor_sync(0xffffffffu, b0 ? p[0] : p[2], 1);
-        k1 += __shfl_xor_sync(0xffffffffu, b0 ? p[1] : p[3], 1);
-        aw = b1 ? k1 : k0;
-        aw += __shfl_xor_sync(0xffffffffu, b1 ? k0 : k1, 2);
-      } else {
-        // rows warp*16 + lm + 4e (e = 0..3), k-chunk ln; rows with (r & 7) >= 4, i.e. odd e, sit in
-        // the 16-byte chunk with bit 2 flipped (128-byte swizzle)
-        const ulonglong2 w0 = *reinterpret_cast<const ulonglong2 *>(Ast + e_a_off);
-        const ulonglong2 w1 = *reinterpret_cast<const ulonglong2 *>(Ast + ((e_a_off ^ 64u) + 512));
-        const ulonglong2 w2 = *reinterpret_cast<const ulonglong2 *>(Ast + (e_a_off + 1024));
-        const ulonglong2 w3 = *reinterpret_cast<const ulonglong2 *>(Ast + ((e_a_off ^ 64u) + 1536));
-        const uint64_t pxy = fadd2(fadd2(w0.x, w1.x), fadd2(w2.x, w3.x));
-        const uint64_t pzw = fadd2(fadd2(w0.y, w1.y), fadd2(w2.y, w3.y));
-        float px, py, pz, pw;
-        unpack2(pxy, px, py);
-        unpack2(pzw, pz, pw);
-        // 4 components x 4 lanes (lm) -> one total per lane: halve the live components per fold
-        const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
-        float k0 = h16 ? pz : px, k1 = h16 ? pw : py;
-        k0 += __shfl_xor_sync(0xffffffffu, h16 ? px : pz, 16);
-        k1 += __shfl_xor_sync(0xffffffffu, h16 ? py : pw, 16);
-        aw = h8 ? k1 : k0;
-        aw += __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
-      }
-      __syncwarp();  // the previous slab's phase-2 reads of this warp's row are done
-      *reinterpret_cast<float *>(sAw + warp * 128 + (TRANS_A ? ta_k : (4 * ln + lm)) * 4) = aw;
-      // B: cell (k, g) = sum of the NR columns of column set g in row k; THREADS cells per pass
-#pragma unroll
-      for (int pass = 0; pass < 256 / THREADS; ++pass) {
-        const unsigned char *pb = Bst + e_b_off + pass * (THREADS / 8) * BROW;
-        uint64_t sb2;
-        {
-          const ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(pb);
-          const ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(pb + 128);
-          sb2 = fadd2(fadd2(v0.x, v0.y), fadd2(v1.x, v1.y));
-          if (NR == 16) {
-            const ulonglong2 v2 = *reinterpret_cast<const ulonglong2 *>(pb + 256);
-            const ulonglong2 v3 = *reinterpret_cast<const ulonglong2 *>(pb + 384);
-            sb2 = fadd2(sb2, fadd2(fadd2(v2.x, v2.y), fadd2(v3.x, v3.y)));
-          }
-        }
-        float lo, hi;
-        unpack2(sb2, lo, hi);
-        const int k = (tid >> 3) + pass * (THREADS / 8);
-        // table layout: k = 8r + 4h + e of column set g at h*512 + (r*8 + g)*16 + e*4, so that the 32 lanes
-        // (g, r) of a warp read each half as one contiguous 512-byte row in phase 2
-        *reinterpret_cast<float *>(sBg + (kb & (kFtTables - 1)) * 1024 + ((k >> 2) & 1) * 512 + ((k >> 3) * 8 + (tid & 7)) * 16 + (k & 3) * 4) = lo + hi;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sums_ready[kb & (kFtTables - 1)]);
-    };
-    auto phase2 = [&](int ps, uint32_t pparity) -> bool {
-      if (!mbar_wait(&sums_ready[ps], pparity)) return false;
-      const unsigned char *pw = sAw + warp * 128 + lm * 32;
-      const unsigned char *pg = sBg + ps * 1024 + (lm * 8 + ln) * 16;
+    // ---- ABFT (FT = 1): the slab's operand checksums came in with the stage; lane (g, r) = (ln, lm) folds
+    // sum_{8 k of r} Asum_w[k] * Bsum_g[k] into its running checksum, issued from inside the unrolled FMA stream.
+    // Bsum table: k = 8r + 4h + e of column set g at h*512 + (r*8 + g)*16 + e*4, so that the 32 lanes of a warp
+    // read each half as one contiguous 512-byte row.
+    auto fold = [&]() {
+      const unsigned char *pw = sCs + s * kStageCs + warp * 128 + lm * 32;
+      const unsigned char *pg = sCs + s * kStageCs + WARPS * 128 + (lm * 8 + ln) * 16;
       const ulonglong2 a01 = *reinterpret_cast<const ulonglong2 *>(pw);
       const ulonglong2 a23 = *reinterpret_cast<const ulonglong2 *>(pw + 16);
       const ulonglong2 g01 = *reinterpret_cast<const ulonglong2 *>(pg);
@@ -425,17 +351,13 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       chk2[1] = ffma2(a01.y, g01.y, chk2[1]);
       chk2[0] = ffma2(a23.x, g23.x, chk2[0]);
       chk2[1] = ffma2(a23.y, g23.y, chk2[1]);
-      return true;
     };
-    const int sprev = (kb - 1) & (kFtTables - 1);                           // table and barrier of the previous slab
-    const uint32_t pprev = (uint32_t)((kb - 1) / kFtTables) & 1u;
     const unsigned char *As = Ast + a_thread;
     const unsigned char *Bs = Bst + b_thread;
     if (TRANS_A) {
 #pragma unroll
       for (int k = 0; k < FBK; ++k) {
-        if (FT == 1 && k == 4 && kb > 0 && !phase2(sprev, pprev)) ok = false;
-        if (FT == 1 && k == 8) phase1();
+        if (FT == 1 && k == 8) fold();
         const float4 a4 = *reinterpret_cast<const float4 *>(As + k * (BM * 4));
         float4 b[NR / 4];
 #pragma unroll
@@ -447,8 +369,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else {
 #pragma unroll
       for (int kc = 0; kc < FBK / 4; ++kc) {
-        if (FT == 1 && kc == 1 && kb > 0 && !phase2(sprev, pprev)) ok = false;
-        if (FT == 1 && kc == 2) phase1();
+        if (FT == 1 && kc == 2) fold();
         const uint32_t y0 = ((uint32_t)kc << 4) ^ a_swz, y1 = y0 ^ 64u;
         float4 a4[4];
 #pragma unroll
@@ -468,7 +389,6 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
     if (FT) {
-      if (!ok) break;
       // ---- simulated soft error: flip one bit of one accumulator after this slab ----
       if (kb == inj_kb) {
         const int inj_i = TRANS_A ? (inj[1] & 3) : ((inj[1] & 15) >> 2), inj_j = (inj[2] >> 5) * 4 + (inj[2] & 3);
@@ -493,29 +413,15 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           ok = false;
           break;
         }
-        mbar_expect_tx(&full[sp], kStageA + kStageB);
+        mbar_expect_tx(&full[sp], kStageBytes);
         if (TRANS_A) tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], m0, knext * FBK);
         else tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], knext * FBK, m0);
         tma_load_2d(sB + sp * kStageB, &tmB, &full[sp], n0, knext * FBK);
+        if (FT == 1) {
+          tma_load_2d(sCs + sp * kStageCs, &tmSA, &full[sp], 0, knext * ft.nbands_pad + tile_m * WARPS);
+          tma_load_2d(sCs + sp * kStageCs + WARPS * 128, &tmSB, &full[sp], 0, knext * tiles_n + tile_n);
+        }
       }
-    }
-  }
-  if (FT == 1 && ok && nkb > 0) {
-    // the last slab's sums have not been folded yet
-    const int ps = (nkb - 1) & (kFtTables - 1);
-    if (mbar_wait(&sums_ready[ps], (uint32_t)((nkb - 1) / kFtTables) & 1u)) {
-      const unsigned char *pw = sAw + warp * 128 + lm * 32;
-      const unsigned char *pg = sBg + ps * 1024 + (lm * 8 + ln) * 16;
-      const ulonglong2 a01 = *reinterpret_cast<const ulonglong2 *>(pw);
-      const ulonglong2 a23 = *reinterpret_cast<const ulonglong2 *>(pw + 16);
-      const ulonglong2 g01 = *reinterpret_cast<const ulonglong2 *>(pg);
-      const ulonglong2 g23 = *reinterpret_cast<const ulonglong2 *>(pg + 512);
-      chk2[0] = ffma2(a01.x, g01.x, chk2[0]);
-      chk2[1] = ffma2(a01.y, g01.y, chk2[1]);
-      chk2[0] = ffma2(a23.x, g23.x, chk2[0]);
-      chk2[1] = ffma2(a23.y, g23.y, chk2[1]);
-    } else {
-      ok = false;
     }
   }
   if (!ok) {
@@ -690,19 +596,93 @@ static int ffma_variant() {
   return g_ffma_variant;
 }
 
+// ---- ABFT pre-pass: the operand checksums of one product, one table entry per K-slab -------------------------
+// Band checksums of A: out[(slab * nbands_pad + band) * 32 + k % 32] = sum over the 16 rows of `band` of A(m, k)
+// (rows past M, k past K and bands past the matrix count as zero).  trans = 0: A is M x K row-major; trans = 1:
+// A is held K x M (the column-major operand of the kernel/ft_sgemm family, or the transposed copy in the
+// workspace).  One block per (slab, 8 bands).
+__global__ void __launch_bounds__(256) ft_encode_a_kernel(const float *__restrict__ A, int M, int K, int lda, int trans,
+                                                          float *__restrict__ out, int nbands_pad) {
+  const int slab = blockIdx.x, tid = threadIdx.x;
+  float sum = 0.f;
+  int kk, band;
+  if (!trans) {
+    kk = tid & 31;
+    band = blockIdx.y * 8 + (tid >> 5);                  // a warp reads 32 consecutive k of one row at a time
+    const int k = slab * FBK + kk;
+    if (k < K) {
+      const float *col = A + k;
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int m = band * 16 + i;
+        if (m < M) sum += __ldg(col + (size_t)m * lda);
+      }
+    }
+  } else {
+    kk = tid >> 3;
+    band = blockIdx.y * 8 + (tid & 7);                   // 8 lanes read 128 consecutive m of one k
+    const int k = slab * FBK + kk, m0 = band * 16;
+    if (k < K && m0 < M) {
+      const float *row = A + (size_t)k * lda + m0;
+      if (m0 + 15 < M && (((uintptr_t)row) & 15) == 0) {
+        const float4 v0 = __ldg(reinterpret_cast<const float4 *>(row)), v1 = __ldg(reinterpret_cast<const float4 *>(row) + 1);
+        const float4 v2 = __ldg(reinterpret_cast<const float4 *>(row) + 2), v3 = __ldg(reinterpret_cast<const float4 *>(row) + 3);
+        sum = ((v0.x + v0.y) + (v0.z + v0.w)) + ((v1.x + v1.y) + (v1.z + v1.w)) + ((v2.x + v2.y) + (v2.z + v2.w)) +
+              ((v3.x + v3.y) + (v3.z + v3.w));
+      } else {
+        for (int i = 0; i < 16 && m0 + i < M; ++i) sum += __ldg(row + i);
+      }
+    }
+  }
+  if (band < nbands_pad) out[((size_t)slab * nbands_pad + band) * FBK + kk] = sum;
+}
+
+// Column-set checksums of B for tiles of BN = 8 * NR columns: per (slab, tile_n) a 1 KB block in which the entry of
+// k (0..31) and column set g (0..7: tile columns g*4 + 32q + e, q < NR/4, e < 4) sits at float offset
+// ((k >> 2) & 1) * 128 + ((k >> 3) * 8 + g) * 4 + (k & 3), the order in which the mainloop reads it.
+template <int NR>
+__global__ void __launch_bounds__(256) ft_encode_b_kernel(const float *__restrict__ B, int K, int N, int ldb,
+                                                          float *__restrict__ out, int tiles_n) {
+  const int slab = blockIdx.x, tile_n = blockIdx.y, tid = threadIdx.x;
+  const int k = tid >> 3, g = tid & 7, row = slab * FBK + k;
+  float sum = 0.f;
+  if (row < K) {
+    const float *r = B + (size_t)row * ldb;
+#pragma unroll
+    for (int q = 0; q < NR / 4; ++q) {
+      const int col = tile_n * (8 * NR) + g * 4 + 32 * q;
+      if (col + 3 < N && (((uintptr_t)(r + col)) & 15) == 0) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(r + col));
+        sum += (v.x + v.y) + (v.z + v.w);
+      } else {
+        for (int e = 0; e < 4; ++e)
+          if (col + e < N) sum += __ldg(r + col + e);
+      }
+    }
+  }
+  out[((size_t)slab * tiles_n + tile_n) * 256 + ((k >> 2) & 1) * 128 + ((k >> 3) * 8 + g) * 4 + (k & 3)] = sum;
+}
+
+// Upper bound, for any tile of the family, of the bytes the two tables of an M x N x K product take.
+size_t ft_tables_bytes(int M, int N, int K) {
+  const size_t slabs = ((size_t)K + FBK - 1) / FBK;
+  return slabs * (((size_t)M / 16 + 9) * 128 + ((size_t)N / 64 + 1) * 1024) + 4096;
+}
+
 template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
-static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const FfmaArgs &args, int grid, cudaStream_t s,
-                       const FtArgs &ft) {
+static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
+                       const FfmaArgs &args, int grid, cudaStream_t s, const FtArgs &ft) {
   using Cfg = TileCfg<BM, NR>;
   int st = ensure_func_attributes((const void *)sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, args.device, Cfg::kSmem, 100);
   if (st != B2_OK) return st;
-  sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, args, ft);
+  sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, tsa, tsb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
 
 // One row per generated tile: the launcher for each (packed?, transposed A?, ABFT?) combination.
-typedef int (*FfmaLauncher)(const CUtensorMap &, const CUtensorMap &, const FfmaArgs &, int, cudaStream_t, const FtArgs &);
+typedef int (*FfmaLauncher)(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const FfmaArgs &, int,
+                            cudaStream_t, const FtArgs &);
 struct FfmaTile {
   const char *name;
   int bm, bn, threads;
@@ -809,10 +789,15 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
     B2_CUDA(cudaGetLastError());
     return B2_OK;
   }
+  // block-level ABFT keeps the two operand-checksum tables of this product in the workspace, behind the transposed
+  // copy of A if there is one
+  const bool tables = ft != nullptr && g_ft_level == 1;
+  size_t ws_front = ft ? ft->ws_used : 0;
   if (!trans_a) {
-    const size_t want = ffma_workspace_bytes(M, N, K);
+    const size_t want_t = ffma_workspace_bytes(M, N, K);
+    const size_t want = want_t + (tables ? ft_tables_bytes(M, N, K) : 0);
     const bool fixed_too_small = ctx->ws != nullptr && !ctx->ws_owned && ctx->ws_bytes < want;
-    if (want != 0 && !fixed_too_small) {
+    if (want_t != 0 && !fixed_too_small) {
       if (ensure_workspace(ctx, want, s) == B2_OK) {
         const int mp = (M + 3) & ~3;
         float *AT = (float *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023);
@@ -823,6 +808,7 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
           FtArgs ft2 = *ft;
           ft2.A = AT;     // the recomputation reads the operand the kernel used
           ft2.lda = mp;
+          ft2.ws_used = (((size_t)K * mp * sizeof(float)) + 2047) & ~(size_t)1023;
           return sgemm_ffma_dispatch_ft(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, &ft2, s);
         }
         return sgemm_ffma_dispatch_ft(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, nullptr, s);
@@ -831,25 +817,54 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
     }
   }
   const FfmaTile &tl = g_tiles[pick_tile(ctx, M, N)];
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tsa, tsb;
   int st = trans_a ? make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, tl.bm, FBK, CU_TENSOR_MAP_SWIZZLE_NONE)
                    : make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, FBK, tl.bm, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != B2_OK) return st;
   st = make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, tl.bn, FBK, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (st != B2_OK) return st;
+  tsa = ta;
+  tsb = tb;
   FfmaArgs args;
   args.C = C; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.alpha = alpha; args.beta = beta;
   args.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
   args.status = (int *)((char *)ctx->fixed + kFixedStatus);
   args.seq = next_launch_seq(ctx);
   args.device = ctx->device;
-  const int grid = ((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
-  FtArgs none = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, 0, 0};
+  const int tiles_m = (M + tl.bm - 1) / tl.bm, tiles_n = (N + tl.bn - 1) / tl.bn;
+  const int grid = tiles_m * tiles_n;
+  FtArgs ftl = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  if (ft) ftl = *ft;
+  const bool thread_level = ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128;   // built for the 128 x 128 tile only
+  if (ft && !thread_level) {
+    // operand checksums of this product, one entry per K-slab, encoded once and brought in by TMA with each slab
+    const int slabs = (K + FBK - 1) / FBK, warps = tl.bm / 16;
+    const int nbands_pad = tiles_m * warps;
+    const size_t bytes_a = (size_t)slabs * nbands_pad * 128, bytes_b = (size_t)slabs * tiles_n * 1024;
+    const size_t need = ws_front + bytes_a + bytes_b + 4096;
+    st = ensure_workspace(ctx, need, s);
+    if (st != B2_OK) {
+      set_error("ft_sgemm: the operand-checksum tables need %zu bytes of workspace (b2_ft_sgemm_workspace_bytes); the handle has %zu",
+                need, ctx->ws_bytes);
+      return B2_ERR_WORKSPACE;
+    }
+    char *base = (char *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023) + ws_front;
+    float *TA = (float *)base, *TB = (float *)(base + ((bytes_a + 1023) & ~(size_t)1023));
+    ft_encode_a_kernel<<<dim3(slabs, (nbands_pad + 7) / 8), 256, 0, s>>>(A, M, K, lda, trans_a ? 1 : 0, TA, nbands_pad);
+    if (tl.bn == 128) ft_encode_b_kernel<16><<<dim3(slabs, tiles_n), 256, 0, s>>>(B, K, N, ldb, TB, tiles_n);
+    else ft_encode_b_kernel<8><<<dim3(slabs, tiles_n), 256, 0, s>>>(B, K, N, ldb, TB, tiles_n);
+    B2_CUDA(cudaGetLastError());
+    st = make_tmap_2d(&tsa, TA, 32, (uint64_t)slabs * nbands_pad, 32, 32, warps, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st != B2_OK) return st;
+    st = make_tmap_2d(&tsb, TB, 256, (uint64_t)slabs * tiles_n, 256, 256, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st != B2_OK) return st;
+    ftl.nbands_pad = nbands_pad;
+  }
   const int packed = (ft != nullptr || ffma_variant() != 0) ? 1 : 0;
-  if (ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128)   // thread-level encode: built for the 128 x 128 tile only
-    return trans_a ? launch_ffma<128, 16, true, true, 2>(ta, tb, args, grid, s, *ft)
-                   : launch_ffma<128, 16, true, false, 2>(ta, tb, args, grid, s, *ft);
-  return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, args, grid, s, ft ? *ft : none);
+  if (thread_level)
+    return trans_a ? launch_ffma<128, 16, true, true, 2>(ta, tb, tsa, tsb, args, grid, s, ftl)
+                   : launch_ffma<128, 16, true, false, 2>(ta, tb, tsa, tsb, args, grid, s, ftl);
+  return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, tsa, tsb, args, grid, s, ftl);
 }
 
 }  // namespace b2

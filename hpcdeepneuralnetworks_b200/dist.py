@@ -143,7 +143,7 @@ def sharded_sgemm(M: int, N: int, K: int, alpha: float, A_local: torch.Tensor, B
     import ctypes as C
     from . import _lib, blas
     mg = mg or default_mg(group)
-    need = blas.sgemm_workspace_bytes(path, rows, N, min(panel, K)) if rows else 0
+    need = int(_lib.load().b2_ft_sgemm_workspace_bytes(path, rows, N, min(panel, K))) if rows else 0
     blas.default_handle().reserve(need)
     vp = lambda t: C.c_void_p(t.data_ptr())
     _lib.check(_lib.load().b2_mg_sgemm(mg.raw, path, 1 if abft else 0, M, N, K, alpha, vp(A_local), K, vp(B), N, beta, vp(C_local), N,

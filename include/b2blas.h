@@ -141,6 +141,12 @@ int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const f
                 const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
                 int n_faults, float tau, b2_ft_report *report_dev, void *stream);
 
+/* Bytes of workspace the fault-tolerant product uses.  path = B2_PATH_FFMA: the operand-checksum tables (one entry
+ * per K-slab of 32: about (M + 2N) * K / 8 bytes) are REQUIRED, the transposed copy of A of b2_sgemm_workspace_bytes
+ * stays optional; a handle that owns its workspace grows it on demand (synchronising), a caller-supplied workspace
+ * that is too small makes b2_ft_sgemm return B2_ERR_WORKSPACE.  path = B2_PATH_3XTF32: as b2_sgemm_workspace_bytes. */
+size_t b2_ft_sgemm_workspace_bytes(int path, int M, int N, int K);
+
 /* The same in the reference's own ABFT layout, column-major NT (A MxK lda=M, B NxK ldb=N, C MxN
  * ldc=M): ft_sgemm_<tile>(M, N, K, A, B, C, alpha, beta) of kernel/ft_sgemm/include/ft_sgemm_huge.cuh:21
  * and include_code_gen/ft_sgemm_wide.cuh:11.  The product is computed as C^T = B * A^T, so a planned
