@@ -87,10 +87,11 @@ struct FfmaArgs {
 // memory with the kernel's own arithmetic; every accumulator that differs is replaced, which both locates and
 // corrects the fault exactly (the reference subtracts a rounded residual with the location left unfinished,
 // ft_sgemm_huge.cuh:296-371).
-template <int BM, int NR>
+template <int BM, int NR, int MR = 4>
 struct TileCfg {
   static constexpr int BN = 8 * NR;
-  static constexpr int WARPS = BM / 16;
+  static constexpr int BAND = 4 * MR;          // rows of a warp: 4 lanes along M x MR rows per thread
+  static constexpr int WARPS = BM / BAND;
   static constexpr int THREADS = 32 * WARPS;
   static constexpr int kStageA = BM * FBK * 4;
   static constexpr int kStageB = FBK * BN * 4;
@@ -99,28 +100,30 @@ struct TileCfg {
   static constexpr int kStageCs = WARPS * 128 + 1024;
   static constexpr int kMiscOff = kCsOff + FSTAGES * kStageCs;   // int inj[8]; int nflag; int flagged[64]
   static constexpr int kSmem = 1024 + kMiscOff + 512;
-  static constexpr int MIN_BLOCKS = 512 / THREADS;
-  static_assert(BM % 16 == 0 && BM >= 32 && BM <= 128, "BM is 32, 64 or 128");
+  // resident CTAs per SM: 16 warps of 4 x NR thread tiles; 8 x NR thread tiles (twice the accumulators) take two CTAs
+  static constexpr int MIN_BLOCKS = MR == 4 ? 512 / THREADS : 2;
+  static_assert(MR == 4 || MR == 8, "MR is 4 or 8 rows per thread");
+  static_assert(BM % BAND == 0 && BM >= 32 && BM <= 128, "BM is 32, 64 or 128 and a multiple of the warp's rows");
   static_assert(NR == 8 || NR == 16, "NR is 8 or 16 columns per thread");
 };
 
-// Accumulators of one thread: 4 rows x NR columns.  Row i is tile row warp*16 + lm + 4*i
-// (row-major A) or warp*16 + lm*4 + i (transposed A); column j is tile column
-// ln*4 + 32*(j/4) + j%4, so one warp spans all BN columns of 16 rows.
-template <bool PACKED, int NR>
+// Accumulators of one thread: MR rows x NR columns.  Row i is tile row warp*4*MR + lm + 4*i
+// (row-major A) or warp*4*MR + lm*MR + i (transposed A); column j is tile column
+// ln*4 + 32*(j/4) + j%4, so one warp spans all BN columns of 4*MR rows.
+template <bool PACKED, int NR, int MR>
 struct Acc;
-template <int NR>
-struct Acc<false, NR> {
-  float v[4][NR];
+template <int NR, int MR>
+struct Acc<false, NR, MR> {
+  float v[MR][NR];
   __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MR; ++i)
 #pragma unroll
       for (int j = 0; j < NR; ++j) v[i][j] = 0.f;
   }
-  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[NR / 4]) {
+  __device__ __forceinline__ void step(const float (&a)[MR], const float4 (&b)[NR / 4]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MR; ++i)
 #pragma unroll
       for (int q = 0; q < NR / 4; ++q) {
         v[i][4 * q + 0] = __fmaf_rn(a[i], b[q].x, v[i][4 * q + 0]);
@@ -134,22 +137,22 @@ struct Acc<false, NR> {
   __device__ __forceinline__ float total() const {
     float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MR; ++i)
 #pragma unroll
-      for (int j = 0; j < NR; ++j) s[i] += v[i][j];
+      for (int j = 0; j < NR; ++j) s[i & 3] += v[i][j];
     return (s[0] + s[1]) + (s[2] + s[3]);
   }
 };
-template <int NR>
-struct Acc<true, NR> {
-  uint64_t v[4][NR / 2];  // pairs of adjacent columns
+template <int NR, int MR>
+struct Acc<true, NR, MR> {
+  uint64_t v[MR][NR / 2];  // pairs of adjacent columns
   __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MR; ++i)
 #pragma unroll
       for (int j = 0; j < NR / 2; ++j) v[i][j] = 0ull;
   }
-  __device__ __forceinline__ void step(const float (&a)[4], const float4 (&b)[NR / 4]) {
+  __device__ __forceinline__ void step(const float (&a)[MR], const float4 (&b)[NR / 4]) {
     uint64_t bp[NR / 2];
 #pragma unroll
     for (int q = 0; q < NR / 4; ++q) {
@@ -157,7 +160,7 @@ struct Acc<true, NR> {
       bp[2 * q + 1] = pack2(b[q].z, b[q].w);
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < MR; ++i) {
       const uint64_t aa = pack2(a[i], a[i]);
 #pragma unroll
       for (int j = 0; j < NR / 2; ++j) v[i][j] = ffma2(aa, bp[j], v[i][j]);
@@ -182,6 +185,10 @@ struct Acc<true, NR> {
 #pragma unroll
       for (int j = 1; j < NR / 2; ++j) s[i] = fadd2(s[i], v[i][j]);
     }
+#pragma unroll
+    for (int i = 4; i < MR; ++i)
+#pragma unroll
+      for (int j = 0; j < NR / 2; ++j) s[i & 3] = fadd2(s[i & 3], v[i][j]);
     float lo, hi;
     unpack2(fadd2(fadd2(s[0], s[1]), fadd2(s[2], s[3])), lo, hi);
     return lo + hi;
@@ -198,9 +205,9 @@ __device__ __forceinline__ void tile_of_block(int bid, int tiles_m, int tiles_n,
 }
 
 // Tile row of accumulator row i of a thread (see Acc) and tile column of accumulator column j.
-template <bool TRANS_A>
+template <bool TRANS_A, int MR>
 __device__ __forceinline__ int acc_row(int warp, int lm, int i) {
-  return TRANS_A ? (warp * 16 + lm * 4 + i) : (warp * 16 + lm + 4 * i);
+  return TRANS_A ? (warp * (4 * MR) + lm * MR + i) : (warp * (4 * MR) + lm + 4 * i);
 }
 __device__ __forceinline__ int acc_col(int ln, int j) { return ln * 4 + 32 * (j >> 2) + (j & 3); }
 
@@ -209,23 +216,25 @@ __device__ __forceinline__ int acc_col(int ln, int j) { return ln * 4 + 32 * (j 
 // chk += (sum of its 4 A values) * (sum of its NR B values) at every k, all in registers -- no
 // shared-memory encoder, no extra barrier, but about 13 more instructions per k beside the 32
 // packed FMAs.  Kept as a measured alternative to the block-level encoder (FT = 1).
-template <int NR>
-__device__ __forceinline__ float thread_checksum_step(const float (&a)[4], const float4 (&b)[NR / 4], float chk) {
+template <int NR, int MR>
+__device__ __forceinline__ float thread_checksum_step(const float (&a)[MR], const float4 (&b)[NR / 4], float chk) {
   uint64_t s2 = fadd2(pack2(b[0].x, b[0].y), pack2(b[0].z, b[0].w));
 #pragma unroll
   for (int q = 1; q < NR / 4; ++q) s2 = fadd2(s2, fadd2(pack2(b[q].x, b[q].y), pack2(b[q].z, b[q].w)));
   float lo, hi;
   unpack2(s2, lo, hi);
-  return __fmaf_rn((a[0] + a[1]) + (a[2] + a[3]), lo + hi, chk);
+  float as = (a[0] + a[1]) + (a[2] + a[3]);
+  if (MR == 8) as += (a[4 % MR] + a[5 % MR]) + (a[6 % MR] + a[7 % MR]);
+  return __fmaf_rn(as, lo + hi, chk);
 }
 
-template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
-__global__ void __launch_bounds__(TileCfg<BM, NR>::THREADS, TileCfg<BM, NR>::MIN_BLOCKS)
+template <int BM, int NR, int MR, bool PACKED, bool TRANS_A, int FT>
+__global__ void __launch_bounds__(TileCfg<BM, NR, MR>::THREADS, TileCfg<BM, NR, MR>::MIN_BLOCKS)
 sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const FfmaArgs p,
                   const FtArgs ft) {
-  using Cfg = TileCfg<BM, NR>;
-  constexpr int BN = Cfg::BN, WARPS = Cfg::WARPS, THREADS = Cfg::THREADS;
+  using Cfg = TileCfg<BM, NR, MR>;
+  constexpr int BN = Cfg::BN, WARPS = Cfg::WARPS, THREADS = Cfg::THREADS, BAND = Cfg::BAND;
   constexpr int kStageA = Cfg::kStageA, kStageB = Cfg::kStageB, BROW = BN * 4;  // bytes per k row of the B stage
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
@@ -310,17 +319,17 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   int inj_kb = -1;
   if (FT && inj[0]) {
     const int r = inj[1], c = inj[2];
-    const bool own = r >= 0 && r < BM && c >= 0 && c < BN && (r >> 4) == warp &&
-                     (TRANS_A ? (((r & 15) >> 2) == lm) : ((r & 3) == lm)) && ((c & 31) >> 2) == ln;
+    const bool own = r >= 0 && r < BM && c >= 0 && c < BN && (r / BAND) == warp &&
+                     (TRANS_A ? (((r % BAND) / MR) == lm) : ((r & 3) == lm)) && ((c & 31) >> 2) == ln;
     if (own) inj_kb = inj[3] < 0 ? 0 : (inj[3] >= nkb ? nkb - 1 : inj[3]);
   }
 
-  Acc<PACKED, NR> acc;
+  Acc<PACKED, NR, MR> acc;
   acc.zero();
   // Byte offsets inside a stage.  A: row r at r*128, 16-byte chunk c of that row at
   // ((c ^ (r & 7)) << 4); rows of this thread are warp*16 + lm + 4*i, so r & 7 is lm for even
   // i and lm + 4 for odd i.  B: row k at k*BROW, column c at c*4.
-  const uint32_t a_thread = TRANS_A ? (uint32_t)(warp * 16 + lm * 4) * 4u : (uint32_t)(warp * 16 + lm) * 128u;
+  const uint32_t a_thread = TRANS_A ? (uint32_t)(warp * BAND + lm * MR) * 4u : (uint32_t)(warp * BAND + lm) * 128u;
   const uint32_t a_swz = (uint32_t)lm << 4;
   const uint32_t b_thread = (uint32_t)(ln * 4) * 4u;
   uint64_t chk2[2] = {0ull, 0ull};  // running checksum of block (warp, ln) over this lane's k-range, packed
@@ -358,43 +367,47 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
       for (int k = 0; k < FBK; ++k) {
         if (FT == 1 && k == 8) fold();
-        const float4 a4 = *reinterpret_cast<const float4 *>(As + k * (BM * 4));
+        float a[MR];
+#pragma unroll
+        for (int h = 0; h < MR / 4; ++h) {
+          const float4 a4 = *reinterpret_cast<const float4 *>(As + k * (BM * 4) + h * 16);
+          a[4 * h + 0] = a4.x; a[4 * h + 1] = a4.y; a[4 * h + 2] = a4.z; a[4 * h + 3] = a4.w;
+        }
         float4 b[NR / 4];
 #pragma unroll
         for (int q = 0; q < NR / 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + k * BROW + q * 128);
-        const float a[4] = {a4.x, a4.y, a4.z, a4.w};
         acc.step(a, b);
-        if (FT == 2) tchk = thread_checksum_step<NR>(a, b, tchk);
+        if (FT == 2) tchk = thread_checksum_step<NR, MR>(a, b, tchk);
       }
     } else {
 #pragma unroll
       for (int kc = 0; kc < FBK / 4; ++kc) {
         if (FT == 1 && kc == 2) fold();
         const uint32_t y0 = ((uint32_t)kc << 4) ^ a_swz, y1 = y0 ^ 64u;
-        float4 a4[4];
+        float4 a4[MR];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < MR; ++i)
           a4[i] = *reinterpret_cast<const float4 *>(As + ((i & 1) ? y1 : y0) + i * 512);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           float4 b[NR / 4];
 #pragma unroll
           for (int q = 0; q < NR / 4; ++q) b[q] = *reinterpret_cast<const float4 *>(Bs + (kc * 4 + kk) * BROW + q * 128);
-          float a[4];
+          float a[MR];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) a[i] = (kk == 0) ? a4[i].x : (kk == 1) ? a4[i].y : (kk == 2) ? a4[i].z : a4[i].w;
+          for (int i = 0; i < MR; ++i) a[i] = (kk == 0) ? a4[i].x : (kk == 1) ? a4[i].y : (kk == 2) ? a4[i].z : a4[i].w;
           acc.step(a, b);
-          if (FT == 2) tchk = thread_checksum_step<NR>(a, b, tchk);
+          if (FT == 2) tchk = thread_checksum_step<NR, MR>(a, b, tchk);
         }
       }
     }
     if (FT) {
       // ---- simulated soft error: flip one bit of one accumulator after this slab ----
       if (kb == inj_kb) {
-        const int inj_i = TRANS_A ? (inj[1] & 3) : ((inj[1] & 15) >> 2), inj_j = (inj[2] >> 5) * 4 + (inj[2] & 3);
+        const int inj_i = TRANS_A ? (inj[1] % MR) : ((inj[1] % BAND) >> 2), inj_j = (inj[2] >> 5) * 4 + (inj[2] & 3);
         const uint32_t inj_mask = 1u << (inj[4] & 31);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < MR; ++i)
 #pragma unroll
           for (int j = 0; j < NR; ++j)
             if (i == inj_i && j == inj_j) acc.set(i, j, __uint_as_float(__float_as_uint(acc.get(i, j)) ^ inj_mask));
@@ -451,12 +464,12 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (bad && lm == 0) flagged[atomicAdd(nflag, 1)] = warp * 8 + ln;
       __syncthreads();
       const int nf = *nflag;
-      float *rec = reinterpret_cast<float *>(sA);  // [16 rows][NR] recomputed outputs of one block
+      float *rec = reinterpret_cast<float *>(sA);  // [BAND rows][NR] recomputed outputs of one block
       for (int f = 0; f < nf; ++f) {
         const int bw = flagged[f] >> 3, bg = flagged[f] & 7;
-        for (int e = tid; e < 16 * NR; e += THREADS) {
+        for (int e = tid; e < BAND * NR; e += THREADS) {
           const int er = e / NR, ec = e % NR;
-          const int row = m0 + bw * 16 + er, col = n0 + acc_col(bg, ec);
+          const int row = m0 + bw * BAND + er, col = n0 + acc_col(bg, ec);
           float v = 0.f;
           if (row < p.M && col < p.N) {
             const float *ap = TRANS_A ? ft.A + row : ft.A + (size_t)row * ft.lda;
@@ -470,10 +483,10 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (warp == bw && ln == bg) {
           int fixed = 0;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
+          for (int i = 0; i < MR; ++i)
 #pragma unroll
             for (int j = 0; j < NR; ++j) {
-              const float want = rec[(acc_row<TRANS_A>(0, lm, i)) * NR + j];
+              const float want = rec[(acc_row<TRANS_A, MR>(0, lm, i)) * NR + j];
               if (__float_as_uint(want) != __float_as_uint(acc.get(i, j))) {
                 acc.set(i, j, want);
                 ++fixed;
@@ -499,8 +512,8 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   // Epilogue straight from registers: per row, 8 lanes x 16 bytes = 128 contiguous bytes per store.
   const bool read_c = (p.beta != 0.f);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = m0 + acc_row<TRANS_A>(warp, lm, i);
+  for (int i = 0; i < MR; ++i) {
+    const int row = m0 + acc_row<TRANS_A, MR>(warp, lm, i);
     if (row >= p.M) continue;
     float *crow = p.C + (size_t)row * p.ldc;
 #pragma unroll
@@ -597,12 +610,12 @@ static int ffma_variant() {
 }
 
 // ---- ABFT pre-pass: the operand checksums of one product, one table entry per K-slab -------------------------
-// Band checksums of A: out[(slab * nbands_pad + band) * 32 + k % 32] = sum over the 16 rows of `band` of A(m, k)
+// Band checksums of A: out[(slab * nbands_pad + band) * 32 + k % 32] = sum over the band_rows rows of `band` of A(m, k)
 // (rows past M, k past K and bands past the matrix count as zero).  trans = 0: A is M x K row-major; trans = 1:
 // A is held K x M (the column-major operand of the kernel/ft_sgemm family, or the transposed copy in the
 // workspace).  One block per (slab, 8 bands).
 __global__ void __launch_bounds__(256) ft_encode_a_kernel(const float *__restrict__ A, int M, int K, int lda, int trans,
-                                                          float *__restrict__ out, int nbands_pad) {
+                                                          float *__restrict__ out, int nbands_pad, int band_rows) {
   const int slab = blockIdx.x, tid = threadIdx.x;
   float sum = 0.f;
   int kk, band;
@@ -613,24 +626,24 @@ __global__ void __launch_bounds__(256) ft_encode_a_kernel(const float *__restric
     if (k < K) {
       const float *col = A + k;
 #pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int m = band * 16 + i;
+      for (int i = 0; i < band_rows; ++i) {
+        const int m = band * band_rows + i;
         if (m < M) sum += __ldg(col + (size_t)m * lda);
       }
     }
   } else {
     kk = tid >> 3;
-    band = blockIdx.y * 8 + (tid & 7);                   // 8 lanes read 128 consecutive m of one k
-    const int k = slab * FBK + kk, m0 = band * 16;
+    band = blockIdx.y * 8 + (tid & 7);                   // 8 lanes read 8 consecutive bands of one k
+    const int k = slab * FBK + kk, m0 = band * band_rows;
     if (k < K && m0 < M) {
       const float *row = A + (size_t)k * lda + m0;
-      if (m0 + 15 < M && (((uintptr_t)row) & 15) == 0) {
-        const float4 v0 = __ldg(reinterpret_cast<const float4 *>(row)), v1 = __ldg(reinterpret_cast<const float4 *>(row) + 1);
-        const float4 v2 = __ldg(reinterpret_cast<const float4 *>(row) + 2), v3 = __ldg(reinterpret_cast<const float4 *>(row) + 3);
-        sum = ((v0.x + v0.y) + (v0.z + v0.w)) + ((v1.x + v1.y) + (v1.z + v1.w)) + ((v2.x + v2.y) + (v2.z + v2.w)) +
-              ((v3.x + v3.y) + (v3.z + v3.w));
+      if (m0 + band_rows - 1 < M && (((uintptr_t)row) & 15) == 0) {
+        for (int q = 0; q < band_rows / 4; ++q) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(row) + q);
+          sum += (v.x + v.y) + (v.z + v.w);
+        }
       } else {
-        for (int i = 0; i < 16 && m0 + i < M; ++i) sum += __ldg(row + i);
+        for (int i = 0; i < band_rows && m0 + i < M; ++i) sum += __ldg(row + i);
       }
     }
   }
@@ -669,13 +682,13 @@ size_t ft_tables_bytes(int M, int N, int K) {
   return slabs * (((size_t)M / 16 + 9) * 128 + ((size_t)N / 64 + 1) * 1024) + 4096;
 }
 
-template <int BM, int NR, bool PACKED, bool TRANS_A, int FT>
+template <int BM, int NR, int MR, bool PACKED, bool TRANS_A, int FT>
 static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
                        const FfmaArgs &args, int grid, cudaStream_t s, const FtArgs &ft) {
-  using Cfg = TileCfg<BM, NR>;
-  int st = ensure_func_attributes((const void *)sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT>, args.device, Cfg::kSmem, 100);
+  using Cfg = TileCfg<BM, NR, MR>;
+  int st = ensure_func_attributes((const void *)sgemm_ffma_kernel<BM, NR, MR, PACKED, TRANS_A, FT>, args.device, Cfg::kSmem, 100);
   if (st != B2_OK) return st;
-  sgemm_ffma_kernel<BM, NR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, tsa, tsb, args, ft);
+  sgemm_ffma_kernel<BM, NR, MR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, tsa, tsb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
@@ -685,24 +698,25 @@ typedef int (*FfmaLauncher)(const CUtensorMap &, const CUtensorMap &, const CUte
                             cudaStream_t, const FtArgs &);
 struct FfmaTile {
   const char *name;
-  int bm, bn, threads;
-  float efficiency;  // measured fraction of the 128x128 tile's throughput, used by the picker
+  int bm, bn, mr, threads, ctas_per_sm;
+  float efficiency;  // measured throughput at large sizes relative to the 128 x 128 tile of 4 x 16 thread tiles, used by the picker
+  int min_waves;     // the picker considers the tile only for problems of at least this many waves of CTAs
   FfmaLauncher fn[2][2][2];  // [packed][trans_a][ft]
 };
 
-#define B2_FFMA_TILE(NAME, BM, NR, EFF)                                                          \
-  {NAME, BM, 8 * NR, 2 * BM, EFF,                                                                \
-   {{{launch_ffma<BM, NR, false, false, false>, launch_ffma<BM, NR, false, false, true>},        \
-     {launch_ffma<BM, NR, false, true, false>, launch_ffma<BM, NR, false, true, true>}},         \
-    {{launch_ffma<BM, NR, true, false, false>, launch_ffma<BM, NR, true, false, true>},          \
-     {launch_ffma<BM, NR, true, true, false>, launch_ffma<BM, NR, true, true, true>}}}},
+#define B2_FFMA_TILE(NAME, BM, NR, MR, EFF, MIN_WAVES)                                                             \
+  {NAME, BM, 8 * NR, MR, TileCfg<BM, NR, MR>::THREADS, TileCfg<BM, NR, MR>::MIN_BLOCKS, EFF, MIN_WAVES,            \
+   {{{launch_ffma<BM, NR, MR, false, false, false>, launch_ffma<BM, NR, MR, false, false, true>},                  \
+     {launch_ffma<BM, NR, MR, false, true, false>, launch_ffma<BM, NR, MR, false, true, true>}},                   \
+    {{launch_ffma<BM, NR, MR, true, false, false>, launch_ffma<BM, NR, MR, true, false, true>},                    \
+     {launch_ffma<BM, NR, MR, true, true, false>, launch_ffma<BM, NR, MR, true, true, true>}}}},
 static const FfmaTile g_tiles[] = {
 #include "ffma_tiles.inc"
 };
 constexpr int kNumTiles = sizeof(g_tiles) / sizeof(g_tiles[0]);
 
 // Picks the tile with the best predicted throughput: its measured efficiency times how well its
-// CTA count fills whole waves of (512 / threads) co-resident CTAs per SM.  The fill term matters
+// CTA count fills whole waves of the CTAs that are co-resident on an SM.  The fill term matters
 // less the more waves there are (the hardware back-fills), hence the 1/waves exponent.
 static int pick_tile(const Context *ctx, int M, int N) {
   if (g_ffma_tile >= 0 && g_ffma_tile < kNumTiles) return g_ffma_tile;
@@ -711,8 +725,9 @@ static int pick_tile(const Context *ctx, int M, int N) {
   for (int t = 0; t < kNumTiles; ++t) {
     const FfmaTile &tl = g_tiles[t];
     const double ctas = (double)((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
-    const double slots = (double)ctx->sm_count * (512 / tl.threads);
+    const double slots = (double)ctx->sm_count * tl.ctas_per_sm;
     const double waves = ceil(ctas / slots);
+    if (ctas / slots < (double)tl.min_waves) continue;
     const double fill = ctas / (waves * slots);
     // padding: work done on rows/columns outside the matrix
     const double useful = ((double)M * N) / (ctas * tl.bm * tl.bn);
@@ -835,10 +850,10 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   const int grid = tiles_m * tiles_n;
   FtArgs ftl = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
   if (ft) ftl = *ft;
-  const bool thread_level = ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128;   // built for the 128 x 128 tile only
+  const bool thread_level = ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128 && tl.mr == 4;   // built for that tile only
   if (ft && !thread_level) {
     // operand checksums of this product, one entry per K-slab, encoded once and brought in by TMA with each slab
-    const int slabs = (K + FBK - 1) / FBK, warps = tl.bm / 16;
+    const int slabs = (K + FBK - 1) / FBK, band_rows = 4 * tl.mr, warps = tl.bm / band_rows;
     const int nbands_pad = tiles_m * warps;
     const size_t bytes_a = (size_t)slabs * nbands_pad * 128, bytes_b = (size_t)slabs * tiles_n * 1024;
     const size_t need = ws_front + bytes_a + bytes_b + 4096;
@@ -850,7 +865,7 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
     }
     char *base = (char *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023) + ws_front;
     float *TA = (float *)base, *TB = (float *)(base + ((bytes_a + 1023) & ~(size_t)1023));
-    ft_encode_a_kernel<<<dim3(slabs, (nbands_pad + 7) / 8), 256, 0, s>>>(A, M, K, lda, trans_a ? 1 : 0, TA, nbands_pad);
+    ft_encode_a_kernel<<<dim3(slabs, (nbands_pad + 7) / 8), 256, 0, s>>>(A, M, K, lda, trans_a ? 1 : 0, TA, nbands_pad, band_rows);
     if (tl.bn == 128) ft_encode_b_kernel<16><<<dim3(slabs, tiles_n), 256, 0, s>>>(B, K, N, ldb, TB, tiles_n);
     else ft_encode_b_kernel<8><<<dim3(slabs, tiles_n), 256, 0, s>>>(B, K, N, ldb, TB, tiles_n);
     B2_CUDA(cudaGetLastError());
@@ -862,8 +877,8 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   }
   const int packed = (ft != nullptr || ffma_variant() != 0) ? 1 : 0;
   if (thread_level)
-    return trans_a ? launch_ffma<128, 16, true, true, 2>(ta, tb, tsa, tsb, args, grid, s, ftl)
-                   : launch_ffma<128, 16, true, false, 2>(ta, tb, tsa, tsb, args, grid, s, ftl);
+    return trans_a ? launch_ffma<128, 16, 4, true, true, 2>(ta, tb, tsa, tsb, args, grid, s, ftl)
+                   : launch_ffma<128, 16, 4, true, false, 2>(ta, tb, tsa, tsb, args, grid, s, ftl);
   return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, tsa, tsb, args, grid, s, ftl);
 }
 

@@ -5,6 +5,10 @@
 //   b2_driver ft_sgemm <start> <end> <gap>                        kernel/ft_sgemm/sgemm.cu:14-20,186-196
 //   b2_driver saxpy                                                kernel/saxpy/saxpy.cu:57-135
 //   b2_driver sdot                                                 kernel/sdot/sdot.cu:78-99,156-165
+//   b2_driver small                        the small cases of the benchmark configurations timed from C++: SGEMM 256..1024
+//                                          on both math paths and SAXPY/SDOT at 2^20 and 2^24, back-to-back launches on
+//                                          rotating buffers (kernel/saxpy/saxpy.cu:79-80,126), so that the figures are the
+//                                          kernels' and not a binding's
 //   b2_driver sgemm_host <n> [path]        host arrays in, host array out (the drivers' malloc + cudaMemcpy + launch +
 //                                          cudaMemcpy of kernel/sgemm/sgemm.cu:50-63 as one pipelined call)
 //   b2_driver mg <rank> <world> <id file> <n> [panel_k]   one process per GPU: row-block sharded SGEMM and sharded SDOT;
@@ -14,6 +18,7 @@
 // them it checks against the library's own naive kernel (rung 1) instead of cuBLAS, times with the
 // CUDA-event timer of the harness, and turns every failure into a non-zero exit code.
 #include <cuda_runtime.h>
+#include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -222,6 +227,71 @@ static int run_sgemm_host(int n, int path) {
   return 0;
 }
 
+// Small cases through the C ABI alone: 200 back-to-back launches per figure, operands rotated through enough
+// distinct buffers to exceed the 126 MB L2.
+static int run_small() {
+  b2_timer timer;
+  CK(b2_timer_create(&timer));
+  b2_handle h;
+  CK(b2_create(&h));
+  const int iters = 200;
+  for (int n = 256; n <= 1024; n += 256) {
+    const size_t n2 = (size_t)n * n;
+    int sets = (int)((size_t)160 * 1024 * 1024 / (3 * n2 * 4)) + 1;
+    if (sets > 64) sets = 64;
+    float *buf;
+    CU(cudaMalloc(&buf, (size_t)sets * 3 * n2 * 4));
+    CK(b2_fill_uniform(buf, (int64_t)sets * 3 * n2, 7, nullptr));
+    void *ws = nullptr;
+    const size_t wsb = b2_sgemm_workspace_bytes(B2_PATH_3XTF32, n, n, n);
+    CU(cudaMalloc(&ws, wsb + 1024));
+    CK(b2_set_workspace(h, (void *)(((uintptr_t)ws + 1023) & ~(uintptr_t)1023), wsb));
+    for (int path = 0; path < 2; ++path) {
+      for (int it = 0; it < 10; ++it) CK(b2_sgemm(h, path, n, n, n, 1.0f, buf, n, buf + n2, n, 0.5f, buf + 2 * n2, n, nullptr));
+      CK(b2_timer_start(timer, nullptr));
+      for (int it = 0; it < iters; ++it) {
+        float *b = buf + (size_t)(it % sets) * 3 * n2;
+        CK(b2_sgemm(h, path, n, n, n, 1.0f, b, n, b + n2, n, 0.5f, b + 2 * n2, n, nullptr));
+      }
+      CK(b2_timer_stop(timer, nullptr));
+      float ms = 0.f;
+      CK(time_ms(timer, &ms));
+      printf("sgemm n = %4d  path %d  %8.2f us per call  %8.2f TFLOPS  (%d buffer sets in rotation)\n", n, path, 1e3 * ms / iters,
+             2.0 * iters * (double)n * n * n / 1e12 / (ms / 1e3), sets);
+    }
+    CK(b2_set_workspace(h, nullptr, 0));
+    CU(cudaFree(ws));
+    CU(cudaFree(buf));
+  }
+  for (int lg = 20; lg <= 24; lg += 4) {
+    const int64_t n = (int64_t)1 << lg;
+    int sets = (int)(((int64_t)512 << 20) / (8 * n));
+    if (sets > 64) sets = 64;
+    if (sets < 1) sets = 1;
+    float *x, *y, *res;
+    CU(cudaMalloc(&x, (size_t)sets * n * 4)); CU(cudaMalloc(&y, (size_t)sets * n * 4)); CU(cudaMalloc(&res, 4));
+    CK(b2_fill_uniform(x, sets * n, 4, nullptr));
+    CK(b2_fill_uniform(y, sets * n, 5, nullptr));
+    for (int which = 0; which < 2; ++which) {
+      CK(b2_timer_start(timer, nullptr));
+      for (int it = 0; it < iters; ++it) {
+        const size_t o = (size_t)(it % sets) * n;
+        if (which == 0) CK(b2_saxpy(h, n, 2.0f, x + o, y + o, nullptr));
+        else CK(b2_sdot(h, n, x + o, y + o, res, nullptr));
+      }
+      CK(b2_timer_stop(timer, nullptr));
+      float ms = 0.f;
+      CK(time_ms(timer, &ms));
+      printf("%s n = 2^%d  %8.2f us per call  %8.1f GB/s  (%d vector pairs in rotation)\n", which == 0 ? "saxpy" : "sdot ", lg,
+             1e3 * ms / iters, (which == 0 ? 12.0 : 8.0) * iters * n / 1e9 / (ms / 1e3), sets);
+    }
+    CU(cudaFree(x)); CU(cudaFree(y)); CU(cudaFree(res));
+  }
+  CK(b2_check_status(h, nullptr));
+  CK(b2_destroy(h));
+  return 0;
+}
+
 // One process per GPU.  Rank 0 draws the communicator id and publishes it through a file (written under another
 // name and renamed, so that a reader never sees half of it).
 static int run_mg(int rank, int world, const char *id_file, int n, int panel) {
@@ -312,7 +382,7 @@ static int run_mg(int rank, int world, const char *id_file, int n, int panel) {
 int main(int argc, char **argv) {
   if (argc < 2) {
     printf("usage: %s sgemm <kernel_id 1..14> <start> <end> [threads_x] | ft_sgemm <start> <end> <gap> | saxpy | sdot | "
-           "sgemm_host <n> [path] | mg <rank> <world> <id file> <n> [panel_k]\n", argv[0]);
+           "small | sgemm_host <n> [path] | mg <rank> <world> <id file> <n> [panel_k]\n", argv[0]);
     return 1;
   }
   if (!strcmp(argv[1], "sgemm") && argc >= 5)
@@ -320,6 +390,7 @@ int main(int argc, char **argv) {
   if (!strcmp(argv[1], "ft_sgemm") && argc >= 5) return run_ft_sgemm(atoi(argv[2]), atoi(argv[3]), atoi(argv[4]));
   if (!strcmp(argv[1], "sgemm_host") && argc >= 3) return run_sgemm_host(atoi(argv[2]), argc > 3 ? atoi(argv[3]) : 0);
   if (!strcmp(argv[1], "mg") && argc >= 6) return run_mg(atoi(argv[2]), atoi(argv[3]), argv[4], atoi(argv[5]), argc > 6 ? atoi(argv[6]) : 0);
+  if (!strcmp(argv[1], "small")) return run_small();
   if (!strcmp(argv[1], "saxpy")) return run_vectors(false);
   if (!strcmp(argv[1], "sdot")) return run_vectors(true);
   printf("bad arguments\n");

@@ -67,9 +67,9 @@ def test_generated_tile_table_is_current_and_exported(L):
     assert gen_ft_sgemm.main(["--check"]) == 0                       # csrc/ffma_tiles.inc matches the generator
     assert L.b2_ffma_tile_count() == len(gen_ft_sgemm.TILES)
     bm, bn, th, name = C.c_int(), C.c_int(), C.c_int(), C.c_char_p()
-    for i, (tname, (param, _)) in enumerate(gen_ft_sgemm.TILES.items()):
+    for i, (tname, (param, _, _)) in enumerate(gen_ft_sgemm.TILES.items()):
         assert L.b2_ffma_tile_info(i, C.byref(bm), C.byref(bn), C.byref(th), C.byref(name)) == 0
-        assert (name.value.decode(), bm.value, bn.value, th.value) == (tname, param[0], param[1], 2 * param[0])
+        assert (name.value.decode(), bm.value, bn.value, th.value) == (tname, param[0], param[1], 8 * param[0] // param[5])
     assert L.b2_ffma_tile_info(99, None, None, None, None) == -1
     assert L.b2_set_ffma_tile(99) == -1 and L.b2_set_ffma_tile(-1) == 0
     import pytest as _pt
