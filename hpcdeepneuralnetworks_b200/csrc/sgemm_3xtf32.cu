@@ -1048,6 +1048,20 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s);
 size_t ffma_workspace_bytes(int M, int N, int K);
 
+// The kernel forms the dispatcher chooses among (generated by gen_ft_sgemm.py from the tile parameters and the
+// measured costs).
+struct Tf32Tile {
+  const char *name;
+  int form;      // 0: one tile per CTA; 1: one 256 x 256 tile per CTA pair
+  int tbn, tbk;
+  double cost;   // time of one tile relative to a single-CTA 128 x 256 tile
+};
+#define B2_TF32_TILE(NAME, FORM, TBN, TBK, COST) {NAME, FORM, TBN, TBK, COST},
+static const Tf32Tile g_tf32_tiles[] = {
+#include "tf32_tiles.inc"
+};
+constexpr int kNumTf32Tiles = sizeof(g_tf32_tiles) / sizeof(g_tf32_tiles[0]);
+
 // How many CTA pairs the device runs at once (one CTA per SM; a pair needs two SMs of one cluster
 // domain).  Asked of the occupancy API once per device and handle; 0 (pairs are then not chosen automatically)
 // if it will not say, e.g. on a partition that cannot schedule clusters.
@@ -1123,18 +1137,34 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[1], Al, (uint64_t)K, (uint64_t)M, (uint64_t)kp, tbk, TBM, swz);
   if (st != B2_OK) return st;
-  // Tile shape by whole waves: a pair tile (256 x 256 on two SMs) costs about 0.9 of a 128 x 256 tile
-  // per SM, a 128 x 128 tile about 0.55; a pinned width selects the single-CTA kernel of that width.
-  const double sms = (double)ctx->sm_count;
-  const double tm = (double)((M + TBM - 1) / TBM);
-  const double t256 = ceil(tm * ((N + 255) / 256) / sms), t128 = 0.55 * ceil(tm * ((N + 127) / 128) / sms);
+  // Kernel form and tile width by whole waves, from the generated table (tf32_tiles.inc: cost = time of one tile
+  // relative to a single-CTA 128 x 256 tile); later rows win ties.  A pinned width selects the single-CTA kernel of that
+  // width; the ABFT form exists for 256-column tiles only.
   const int pairs = ((M + 255) / 256) * ((N + 255) / 256);
   const int slots = max_resident_pairs(ctx);
-  const double tpair = slots > 0 ? 0.9 * ceil((double)pairs / (double)slots) : 1e30;
   const bool pinned = (g_tf32_tile_n == 128 || g_tf32_tile_n == 256);
-  // (the ABFT form has no 128-wide kernel: pairs against 128 x 256 tiles)
-  const bool use_pair = tbk == 32 && !pinned &&
-                        (g_tf32_pair == 2 || (g_tf32_pair == 1 && tpair <= t256 && (ft != nullptr || tpair <= t128)));
+  int chosen = -1;
+  double best_time = 1e300;
+  for (int t = 0; t < kNumTf32Tiles; ++t) {
+    const Tf32Tile &tl = g_tf32_tiles[t];
+    if (tl.tbk != 32) continue;
+    if (ft != nullptr && tl.tbn != 256) continue;
+    double time;
+    if (tl.form == 1) {
+      if (tbk != 32 || pinned || g_tf32_pair == 0 || (g_tf32_pair == 1 && slots <= 0)) continue;
+      time = g_tf32_pair == 2 ? -1.0 : tl.cost * ceil((double)pairs / (double)slots);
+    } else {
+      if (pinned && tl.tbn != g_tf32_tile_n) continue;
+      const double tiles = (double)((M + TBM - 1) / TBM) * ((N + tl.tbn - 1) / tl.tbn);
+      time = tl.cost * ceil(tiles / (double)ctx->sm_count);
+    }
+    if (time <= best_time) {
+      best_time = time;
+      chosen = t;
+    }
+  }
+  B2_REQUIRE(chosen >= 0, B2_ERR_UNSUPPORTED, "3xTF32: no kernel form of the tile table fits this call");
+  const bool use_pair = g_tf32_tiles[chosen].form == 1;
   if (use_pair) {
     st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
     if (st != B2_OK) return st;
@@ -1179,9 +1209,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     B2_CUDA(cudaGetLastError());
     return B2_OK;
   }
-  int tbn = (t128 < t256) ? 128 : 256;
-  if (g_tf32_tile_n == 128 || g_tf32_tile_n == 256) tbn = g_tf32_tile_n;
-  if (ft) tbn = 256;   // the checksum operand is laid out for 256-column tiles
+  const int tbn = g_tf32_tiles[chosen].tbn;
   st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);

@@ -35,7 +35,7 @@
 
 namespace b2 {
 
-constexpr int FBK = 32, FSTAGES = 3;
+constexpr int FBK = 32;
 constexpr int kGroupM = 16;  // tile rasterisation: 16 tile-rows share their B panels in L2
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -87,22 +87,27 @@ struct FfmaArgs {
 // memory with the kernel's own arithmetic; every accumulator that differs is replaced, which both locates and
 // corrects the fault exactly (the reference subtracts a rounded residual with the location left unfinished,
 // ft_sgemm_huge.cuh:296-371).
-template <int BM, int NR, int MR = 4>
+template <int BM, int NR, int MR = 4, int NSTAGES = 3>
 struct TileCfg {
   static constexpr int BN = 8 * NR;
+  static constexpr int STAGES = NSTAGES;        // depth of the TMA ring
   static constexpr int BAND = 4 * MR;          // rows of a warp: 4 lanes along M x MR rows per thread
   static constexpr int WARPS = BM / BAND;
   static constexpr int THREADS = 32 * WARPS;
   static constexpr int kStageA = BM * FBK * 4;
   static constexpr int kStageB = FBK * BN * 4;
-  static constexpr int kBarOff = FSTAGES * (kStageA + kStageB);  // full[3], empty[3]
+  static constexpr int kBarOff = STAGES * (kStageA + kStageB);   // full[STAGES], empty[STAGES]
   static constexpr int kCsOff = kBarOff + 128;                   // per stage: float Asum[WARPS][32], float Bsum[256]
   static constexpr int kStageCs = WARPS * 128 + 1024;
-  static constexpr int kMiscOff = kCsOff + FSTAGES * kStageCs;   // int inj[8]; int nflag; int flagged[64]
+  static constexpr int kMiscOff = kCsOff + STAGES * kStageCs;    // int inj[8]; int nflag; int flagged[64]
   static constexpr int kSmem = 1024 + kMiscOff + 512;
-  // resident CTAs per SM: 16 warps of 4 x NR thread tiles; 8 x NR thread tiles (twice the accumulators) take two CTAs
-  static constexpr int MIN_BLOCKS = MR == 4 ? 512 / THREADS : 2;
+  // resident CTAs per SM: 16 warps of 4 x NR thread tiles or 8 warps of 8 x NR thread tiles (twice the accumulators), as
+  // far as 227 KB of shared memory hold that many rings (each CTA also takes 1 KB of system use)
+  static constexpr int kByWarps = (MR == 4 ? 16 : 8) / WARPS;
+  static constexpr int kBySmem = (227 * 1024) / (kSmem + 1024);
+  static constexpr int MIN_BLOCKS = kByWarps < kBySmem ? kByWarps : (kBySmem > 0 ? kBySmem : 1);
   static_assert(MR == 4 || MR == 8, "MR is 4 or 8 rows per thread");
+  static_assert(STAGES >= 2 && STAGES <= 8, "2 to 8 stages (the barriers share one 128-byte line)");
   static_assert(BM % BAND == 0 && BM >= 32 && BM <= 128, "BM is 32, 64 or 128 and a multiple of the warp's rows");
   static_assert(NR == 8 || NR == 16, "NR is 8 or 16 columns per thread");
 };
@@ -228,13 +233,13 @@ __device__ __forceinline__ float thread_checksum_step(const float (&a)[MR], cons
   return __fmaf_rn(as, lo + hi, chk);
 }
 
-template <int BM, int NR, int MR, bool PACKED, bool TRANS_A, int FT>
-__global__ void __launch_bounds__(TileCfg<BM, NR, MR>::THREADS, TileCfg<BM, NR, MR>::MIN_BLOCKS)
+template <int BM, int NR, int MR, int NSTAGES, bool PACKED, bool TRANS_A, int FT>
+__global__ void __launch_bounds__(TileCfg<BM, NR, MR, NSTAGES>::THREADS, TileCfg<BM, NR, MR, NSTAGES>::MIN_BLOCKS)
 sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const FfmaArgs p,
                   const FtArgs ft) {
-  using Cfg = TileCfg<BM, NR, MR>;
-  constexpr int BN = Cfg::BN, WARPS = Cfg::WARPS, THREADS = Cfg::THREADS, BAND = Cfg::BAND;
+  using Cfg = TileCfg<BM, NR, MR, NSTAGES>;
+  constexpr int BN = Cfg::BN, WARPS = Cfg::WARPS, THREADS = Cfg::THREADS, BAND = Cfg::BAND, FSTAGES = Cfg::STAGES;
   constexpr int kStageA = Cfg::kStageA, kStageB = Cfg::kStageB, BROW = BN * 4;  // bytes per k row of the B stage
   extern __shared__ unsigned char smem_raw[];
   // round the dynamic shared window up to 1024 bytes without leaving the shared address space
@@ -682,13 +687,13 @@ size_t ft_tables_bytes(int M, int N, int K) {
   return slabs * (((size_t)M / 16 + 9) * 128 + ((size_t)N / 64 + 1) * 1024) + 4096;
 }
 
-template <int BM, int NR, int MR, bool PACKED, bool TRANS_A, int FT>
+template <int BM, int NR, int MR, int NSTAGES, bool PACKED, bool TRANS_A, int FT>
 static int launch_ffma(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb,
                        const FfmaArgs &args, int grid, cudaStream_t s, const FtArgs &ft) {
-  using Cfg = TileCfg<BM, NR, MR>;
-  int st = ensure_func_attributes((const void *)sgemm_ffma_kernel<BM, NR, MR, PACKED, TRANS_A, FT>, args.device, Cfg::kSmem, 100);
+  using Cfg = TileCfg<BM, NR, MR, NSTAGES>;
+  int st = ensure_func_attributes((const void *)sgemm_ffma_kernel<BM, NR, MR, NSTAGES, PACKED, TRANS_A, FT>, args.device, Cfg::kSmem, 100);
   if (st != B2_OK) return st;
-  sgemm_ffma_kernel<BM, NR, MR, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, tsa, tsb, args, ft);
+  sgemm_ffma_kernel<BM, NR, MR, NSTAGES, PACKED, TRANS_A, FT><<<grid, Cfg::THREADS, Cfg::kSmem, s>>>(ta, tb, tsa, tsb, args, ft);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
@@ -698,18 +703,18 @@ typedef int (*FfmaLauncher)(const CUtensorMap &, const CUtensorMap &, const CUte
                             cudaStream_t, const FtArgs &);
 struct FfmaTile {
   const char *name;
-  int bm, bn, mr, threads, ctas_per_sm;
+  int bm, bn, mr, stages, threads, ctas_per_sm;
   float efficiency;  // measured throughput at large sizes relative to the 128 x 128 tile of 4 x 16 thread tiles, used by the picker
   int min_waves;     // the picker considers the tile only for problems of at least this many waves of CTAs
   FfmaLauncher fn[2][2][2];  // [packed][trans_a][ft]
 };
 
-#define B2_FFMA_TILE(NAME, BM, NR, MR, EFF, MIN_WAVES)                                                             \
-  {NAME, BM, 8 * NR, MR, TileCfg<BM, NR, MR>::THREADS, TileCfg<BM, NR, MR>::MIN_BLOCKS, EFF, MIN_WAVES,            \
-   {{{launch_ffma<BM, NR, MR, false, false, false>, launch_ffma<BM, NR, MR, false, false, true>},                  \
-     {launch_ffma<BM, NR, MR, false, true, false>, launch_ffma<BM, NR, MR, false, true, true>}},                   \
-    {{launch_ffma<BM, NR, MR, true, false, false>, launch_ffma<BM, NR, MR, true, false, true>},                    \
-     {launch_ffma<BM, NR, MR, true, true, false>, launch_ffma<BM, NR, MR, true, true, true>}}}},
+#define B2_FFMA_TILE(NAME, BM, NR, MR, ST, EFF, MIN_WAVES)                                                         \
+  {NAME, BM, 8 * NR, MR, ST, TileCfg<BM, NR, MR, ST>::THREADS, TileCfg<BM, NR, MR, ST>::MIN_BLOCKS, EFF, MIN_WAVES, \
+   {{{launch_ffma<BM, NR, MR, ST, false, false, false>, launch_ffma<BM, NR, MR, ST, false, false, true>},          \
+     {launch_ffma<BM, NR, MR, ST, false, true, false>, launch_ffma<BM, NR, MR, ST, false, true, true>}},           \
+    {{launch_ffma<BM, NR, MR, ST, true, false, false>, launch_ffma<BM, NR, MR, ST, true, false, true>},            \
+     {launch_ffma<BM, NR, MR, ST, true, true, false>, launch_ffma<BM, NR, MR, ST, true, true, true>}}}},
 static const FfmaTile g_tiles[] = {
 #include "ffma_tiles.inc"
 };
@@ -725,7 +730,9 @@ static int pick_tile(const Context *ctx, int M, int N) {
   for (int t = 0; t < kNumTiles; ++t) {
     const FfmaTile &tl = g_tiles[t];
     const double ctas = (double)((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
-    const double slots = (double)ctx->sm_count * tl.ctas_per_sm;
+    // the wave model counts 16 warps (8 for the 8-row thread tiles) per SM whatever shared memory allows: a CTA that
+    // runs with fewer neighbours than that runs faster, which is what the 1/waves exponent below absorbs
+    const double slots = (double)ctx->sm_count * ((tl.mr == 4 ? 512 : 256) / tl.threads);
     const double waves = ceil(ctas / slots);
     if (ctas / slots < (double)tl.min_waves) continue;
     const double fill = ctas / (waves * slots);
@@ -850,7 +857,7 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   const int grid = tiles_m * tiles_n;
   FtArgs ftl = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
   if (ft) ftl = *ft;
-  const bool thread_level = ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128 && tl.mr == 4;   // built for that tile only
+  const bool thread_level = ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128 && tl.mr == 4 && tl.stages == 3;   // built for that tile only
   if (ft && !thread_level) {
     // operand checksums of this product, one entry per K-slab, encoded once and brought in by TMA with each slab
     const int slabs = (K + FBK - 1) / FBK, band_rows = 4 * tl.mr, warps = tl.bm / band_rows;
@@ -877,8 +884,8 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   }
   const int packed = (ft != nullptr || ffma_variant() != 0) ? 1 : 0;
   if (thread_level)
-    return trans_a ? launch_ffma<128, 16, 4, true, true, 2>(ta, tb, tsa, tsb, args, grid, s, ftl)
-                   : launch_ffma<128, 16, 4, true, false, 2>(ta, tb, tsa, tsb, args, grid, s, ftl);
+    return trans_a ? launch_ffma<128, 16, 4, 3, true, true, 2>(ta, tb, tsa, tsb, args, grid, s, ftl)
+                   : launch_ffma<128, 16, 4, 3, true, false, 2>(ta, tb, tsa, tsb, args, grid, s, ftl);
   return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, tsa, tsb, args, grid, s, ftl);
 }
 

@@ -9,6 +9,8 @@
 //                                          on both math paths and SAXPY/SDOT at 2^20 and 2^24, back-to-back launches on
 //                                          rotating buffers (kernel/saxpy/saxpy.cu:79-80,126), so that the figures are the
 //                                          kernels' and not a binding's
+//   b2_driver tiles <n>                    every tile of the generated FFMA family, pinned, at n^3: the table the generator's
+//                                          tile_measurements.json is filled from (code_gen/main.py:8-16 names the reference's tiles)
 //   b2_driver sgemm_host <n> [path]        host arrays in, host array out (the drivers' malloc + cudaMemcpy + launch +
 //                                          cudaMemcpy of kernel/sgemm/sgemm.cu:50-63 as one pipelined call)
 //   b2_driver mg <rank> <world> <id file> <n> [panel_k]   one process per GPU: row-block sharded SGEMM and sharded SDOT;
@@ -292,6 +294,43 @@ static int run_small() {
   return 0;
 }
 
+// Throughput of every generated FFMA tile at one size (and of the automatic choice), back-to-back launches on rotating buffers.
+static int run_tiles(int n) {
+  b2_timer timer;
+  CK(b2_timer_create(&timer));
+  b2_handle h;
+  CK(b2_create(&h));
+  const size_t n2 = (size_t)n * n;
+  int sets = (int)((size_t)160 * 1024 * 1024 / (3 * n2 * 4)) + 1;
+  if (sets > 64) sets = 64;
+  float *buf;
+  CU(cudaMalloc(&buf, (size_t)sets * 3 * n2 * 4));
+  CK(b2_fill_uniform(buf, (int64_t)sets * 3 * n2, 7, nullptr));
+  const int iters = n <= 1024 ? 200 : (n <= 3072 ? 40 : 8);
+  printf("{\"n\": %d, \"tflops\": {", n);
+  for (int tile = -1; tile < b2_ffma_tile_count(); ++tile) {
+    CK(b2_set_ffma_tile(tile));
+    for (int it = 0; it < 3; ++it) CK(b2_sgemm(h, B2_PATH_FFMA, n, n, n, 1.0f, buf, n, buf + n2, n, 0.5f, buf + 2 * n2, n, nullptr));
+    CK(b2_timer_start(timer, nullptr));
+    for (int it = 0; it < iters; ++it) {
+      float *b = buf + (size_t)(it % sets) * 3 * n2;
+      CK(b2_sgemm(h, B2_PATH_FFMA, n, n, n, 1.0f, b, n, b + n2, n, 0.5f, b + 2 * n2, n, nullptr));
+    }
+    CK(b2_timer_stop(timer, nullptr));
+    float ms = 0.f;
+    CK(time_ms(timer, &ms));
+    const char *name = "automatic";
+    if (tile >= 0) CK(b2_ffma_tile_info(tile, nullptr, nullptr, nullptr, &name));
+    printf("%s\"%s\": %.2f", tile >= 0 ? ", " : "", name, 2.0 * iters * (double)n * n * n / 1e12 / (ms / 1e3));
+  }
+  printf("}}\n");
+  CK(b2_set_ffma_tile(-1));
+  CK(b2_check_status(h, nullptr));
+  CK(b2_destroy(h));
+  CU(cudaFree(buf));
+  return 0;
+}
+
 // One process per GPU.  Rank 0 draws the communicator id and publishes it through a file (written under another
 // name and renamed, so that a reader never sees half of it).
 static int run_mg(int rank, int world, const char *id_file, int n, int panel) {
@@ -382,7 +421,7 @@ static int run_mg(int rank, int world, const char *id_file, int n, int panel) {
 int main(int argc, char **argv) {
   if (argc < 2) {
     printf("usage: %s sgemm <kernel_id 1..14> <start> <end> [threads_x] | ft_sgemm <start> <end> <gap> | saxpy | sdot | "
-           "small | sgemm_host <n> [path] | mg <rank> <world> <id file> <n> [panel_k]\n", argv[0]);
+           "small | tiles <n> | sgemm_host <n> [path] | mg <rank> <world> <id file> <n> [panel_k]\n", argv[0]);
     return 1;
   }
   if (!strcmp(argv[1], "sgemm") && argc >= 5)
@@ -391,6 +430,7 @@ int main(int argc, char **argv) {
   if (!strcmp(argv[1], "sgemm_host") && argc >= 3) return run_sgemm_host(atoi(argv[2]), argc > 3 ? atoi(argv[3]) : 0);
   if (!strcmp(argv[1], "mg") && argc >= 6) return run_mg(atoi(argv[2]), atoi(argv[3]), argv[4], atoi(argv[5]), argc > 6 ? atoi(argv[6]) : 0);
   if (!strcmp(argv[1], "small")) return run_small();
+  if (!strcmp(argv[1], "tiles") && argc >= 3) return run_tiles(atoi(argv[2]));
   if (!strcmp(argv[1], "saxpy")) return run_vectors(false);
   if (!strcmp(argv[1], "sdot")) return run_vectors(true);
   printf("bad arguments\n");

@@ -67,14 +67,21 @@ def test_generated_tile_table_is_current_and_exported(L):
     assert gen_ft_sgemm.main(["--check"]) == 0                       # csrc/ffma_tiles.inc matches the generator
     assert L.b2_ffma_tile_count() == len(gen_ft_sgemm.TILES)
     bm, bn, th, name = C.c_int(), C.c_int(), C.c_int(), C.c_char_p()
-    for i, (tname, (param, _, _)) in enumerate(gen_ft_sgemm.TILES.items()):
+    for i, (tname, t) in enumerate(gen_ft_sgemm.FFMA_TILES.items()):
+        param = t["param"]
         assert L.b2_ffma_tile_info(i, C.byref(bm), C.byref(bn), C.byref(th), C.byref(name)) == 0
         assert (name.value.decode(), bm.value, bn.value, th.value) == (tname, param[0], param[1], 8 * param[0] // param[5])
     assert L.b2_ffma_tile_info(99, None, None, None, None) == -1
     assert L.b2_set_ffma_tile(99) == -1 and L.b2_set_ffma_tile(-1) == 0
     import pytest as _pt
-    with _pt.raises(ValueError):
+    with _pt.raises(ValueError, match="ks must be 32"):
         gen_ft_sgemm.validate("small", (16, 16, 16, 8, 16, 2, 2))    # the reference's 16x16x16 tile has no B200 form
+    with _pt.raises(ValueError, match="shared memory"):
+        gen_ft_sgemm.derive_ffma("too_deep", (128, 128, 32, 16, 128, 4, 16), stages=8)
+    with _pt.raises(ValueError, match="tensor-memory|accumulates"):
+        gen_ft_sgemm.derive_tf32("too_wide", (128, 512, 32), "single")
+    d = gen_ft_sgemm.derive_ffma("b200_8x16", *[gen_ft_sgemm.FFMA_TILES["b200_8x16"][k] for k in ("param", "stages")])
+    assert (d["threads"], d["ctas_per_sm"], d["mr"]) == (128, 2, 8) and d["smem_bytes"] <= 113 * 1024
 
 
 def test_workspace_query(L):
