@@ -228,6 +228,14 @@ __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
   asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
   return v;
 }
+// A bounded wait of a CTA pair ran out: raise the abort flag of BOTH CTAs (same shared-memory offset in each), so that
+// the peer's roles leave their polling loops at once instead of sitting out their own limit.  Both CTAs stay resident
+// until the kernel's final cluster barrier, so the remote word exists whenever this runs.
+__device__ __forceinline__ void pair_abort(volatile int *flag) {
+  *flag = 1;
+  const uint32_t peer = mapa_u32(smem_u32(const_cast<const int *>(flag)), cluster_ctarank() ^ 1u);
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"(1) : "memory");
+}
 // every thread of both CTAs arrives and waits (release/acquire)
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -677,7 +677,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % S;
         if (!mbar_wait(&empty[s], ((uint32_t)(kb / S) & 1u) ^ 1u)) {
-          *abort_flag = 1;
+          pair_abort(abort_flag);
           break;
         }
         unsigned char *st = smem + s * kStage;
@@ -704,7 +704,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % S;
         if (!mbar_wait(&full[s], (uint32_t)(kb / S) & 1u)) {
-          *abort_flag = 1;
+          pair_abort(abort_flag);
           ok = false;
           break;
         }
@@ -749,7 +749,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % S;
         if (!mbar_wait(&data_bar[s], (uint32_t)(kb / S) & 1u)) {
-          *abort_flag = 1;
+          pair_abort(abort_flag);
           break;
         }
         const unsigned char *st = smem + s * kStage;
@@ -769,7 +769,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
       ok = done;
     }
     ok = __all_sync(0xffffffffu, ok);
-    if (!ok) *abort_flag = 1;
+    if (!ok) pair_abort(abort_flag);
     tc_fence_after();
     tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16);
   }
@@ -885,7 +885,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(&empty[s], ((it / S) & 1u) ^ 1u)) {
-            *abort_flag = 1;
+            pair_abort(abort_flag);
             ok = false;
             break;
           }
@@ -910,7 +910,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
         const uint32_t buf = n_done & 1u;
         // the epilogue warps of both CTAs have drained this buffer (two tiles ago)
         if (!mbar_wait(&acc_empty[buf], ((n_done >> 1) & 1u) ^ 1u)) {
-          *abort_flag = 1;
+          pair_abort(abort_flag);
           break;
         }
         tc_fence_after();
@@ -918,7 +918,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(&full[s], (it / S) & 1u)) {
-            *abort_flag = 1;
+            pair_abort(abort_flag);
             ok = false;
             break;
           }
@@ -962,7 +962,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
       if (FT && done) done = mbar_wait(&tab_full[buf], (n_done >> 1) & 1u);
       const bool ok = __all_sync(0xffffffffu, done);
       if (!ok) {
-        *abort_flag = 1;
+        pair_abort(abort_flag);
         break;
       }
       tc_fence_after();
@@ -1002,7 +1002,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
       if (ok && !mbar_wait(&tab_empty[buf], ((n_done >> 1) & 1u) ^ 1u)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
-        *abort_flag = 1;
+        pair_abort(abort_flag);
         break;
       }
       ft_cuda_finish(acc, tables + buf * (PersistCfg<FT>::kTable / 4), row0, lane);

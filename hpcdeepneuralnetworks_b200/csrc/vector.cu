@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(kVecThreads) sdot_fused_kernel(int64_t n, cons
 // ---- SDOT without any allocation ---------------------------------------------------------
 // Scratch of b2_sdot_static: one double per block plus the ticket word, held in the module's
 // own device memory (every GPU that loads the library carries these 16.25 KB until exit).
-constexpr int kStaticSdotBlocks = 2048;
+constexpr int kStaticSdotBlocks = 2048;   // the launch uses min(8 blocks per SM, this many): 1184 on a 148-SM B200
 constexpr int64_t kStaticSdotMaxN = (int64_t)1 << 30;
 static __device__ __align__(256) unsigned char g_sdot_static_scratch[kStaticSdotBlocks * sizeof(double) + 256];
 
@@ -325,6 +325,19 @@ __global__ void __launch_bounds__(256) ffma2_probe_kernel(int64_t iters, float a
     s += lo + hi;
   }
   if (s == 123.456f) *sink = s;
+}
+
+// SM count of the current device for the harness entry points that take no handle (asked of the runtime once per device).
+static int current_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
 
 static int vec_grid(Context *ctx, int64_t work_items, int per_block) {
@@ -461,7 +474,7 @@ int b2_fill_uniform(float *dev, int64_t n, uint64_t seed, void *stream) {
   B2_REQUIRE(n >= 0 && (n == 0 || dev != nullptr), B2_ERR_INVALID_ARG, "b2_fill_uniform: bad arguments");
   if (n == 0) return B2_OK;
   int64_t blocks = (n + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (int64_t)current_sm_count() * 32) blocks = (int64_t)current_sm_count() * 32;
   fill_uniform_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(dev, n, mix64(seed));
   B2_CUDA(cudaGetLastError());
   return B2_OK;
@@ -491,7 +504,7 @@ int b2_fill_const(float *dev, int64_t n, float value, void *stream) {
   B2_REQUIRE(n >= 0 && (n == 0 || dev != nullptr), B2_ERR_INVALID_ARG, "b2_fill_const: bad arguments");
   if (n == 0) return B2_OK;
   int64_t blocks = (n + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (int64_t)current_sm_count() * 32) blocks = (int64_t)current_sm_count() * 32;
   fill_const_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(dev, n, value);
   B2_CUDA(cudaGetLastError());
   return B2_OK;
@@ -508,7 +521,7 @@ int b2_verify_matrix(const float *ref_dev, const float *got_dev, int64_t rows, i
   B2_CUDA(cudaMemsetAsync(out, 0, 8, s));
   if (rows * cols > 0) {
     int64_t blocks = (rows * cols + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
     verify_kernel<<<(int)blocks, 256, 0, s>>>(ref_dev, got_dev, rows, cols, ld, abs_tol, out);
     B2_CUDA(cudaGetLastError());
   }

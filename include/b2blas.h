@@ -280,7 +280,9 @@ int b2_copy_matrix_async(float *dst, int64_t ld_dst, const float *src, int64_t l
 
 /* verify_matrix (utils/utils.cu:75-91): first element with |ref-got| > abs_tol fails.
  * Device-side compare; returns 0 if all pass, 1 if any fail, <0 on error, and writes the
- * max |ref-got| to *max_abs_host when non-NULL.  Synchronises the stream. */
+ * max |ref-got| to *max_abs_host when non-NULL.  Synchronises the stream.  Like the FFMA peak probes below it takes
+ * no handle and keeps its two result words in the scratch of the device's default handle: calls on one device must
+ * not overlap (different streams without ordering), nor overlap other work on the default handle. */
 int b2_verify_matrix(const float *ref_dev, const float *got_dev, int64_t rows, int64_t cols,
                      int64_t ld, float abs_tol, float *max_abs_host, void *stream);
 

@@ -34,14 +34,23 @@ class Fault(C.Structure):
                 ("col", C.c_int32), ("k_step", C.c_int32), ("bit", C.c_int32)]
 
 
+def reference_tree():
+    """The reference project's source tree, or None: the directory named by B2_REFERENCE_TREE, else a directory
+    called ``reference`` beside this repository.  It exists where the checker is built, not where the GPU tests run
+    (they use the prebuilt files under oracle/_ref)."""
+    cand = os.environ.get("B2_REFERENCE_TREE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isfile(os.path.join(cand, "utils", "utils.cu")) else None
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (and oracle/_ref when the reference tree is present)."""
     so = os.path.join(_HERE, "liboracle.so")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
         subprocess.check_call(["make", "-C", _HERE, "--no-print-directory", os.path.join(_HERE, "liboracle.so")],
                               stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference/utils") and (force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_utils.so"))):
-        subprocess.call(["make", "-C", _HERE, "--no-print-directory", "ref"], stdout=subprocess.DEVNULL,
+    ref = reference_tree()
+    if ref and (force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_utils.so"))):
+        subprocess.call(["make", "-C", _HERE, "--no-print-directory", "ref", "REFERENCE=" + ref], stdout=subprocess.DEVNULL,
                         stderr=subprocess.DEVNULL)
 
 

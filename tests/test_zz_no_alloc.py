@@ -60,3 +60,46 @@ def test_static_sdot_rejects_sizes_beyond_its_limit(cuda):
     assert _call_static(L, (1 << 30) + 1, t, t, out) == -2      # B2_ERR_UNSUPPORTED, nothing launched
     assert b"exceeds the limit" in L.b2_last_error()
     assert _call_static(L, -1, t, t, out) == -1
+
+
+_FRESH = r"""
+import ctypes as C, os, sys
+sys.path.insert(0, os.environ["B2_ROOT"])
+import torch
+from hpcdeepneuralnetworks_b200 import _lib
+L = _lib.load()
+torch.cuda.set_device(0)
+n = (1 << 20) + 3
+x = torch.rand(n, device="cuda") - 0.5
+y = torch.rand(n, device="cuda") - 0.5
+out = torch.zeros(1, device="cuda")
+torch.cuda.synchronize()
+def call():
+    st = L.b2_sdot_static(n, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), C.c_void_p(out.data_ptr()), None)
+    assert st == 0, st
+    torch.cuda.synchronize()
+call()                                   # first call on the device: looks up the scratch symbol's address
+free0, _ = torch.cuda.mem_get_info()
+for _ in range(50):
+    call()
+free1, _ = torch.cuda.mem_get_info()
+want = float((x.double() * y.double()).sum().item())
+scale = float((x.double() * y.double()).abs().sum().item())
+assert abs(float(out.item()) - want) <= 1e-5 * scale
+assert free1 == free0, (free0, free1)
+print("free bytes unchanged over 50 calls:", free0)
+"""
+
+
+def test_static_sdot_allocates_nothing_in_a_fresh_process(cuda, tmp_path):
+    """The point of the entry point: in a process that never creates a library handle, the free device memory the
+    driver reports does not move across fifty calls (any cudaMalloc inside would show, whole pages at a time)."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "fresh.py"
+    script.write_text(_FRESH)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, str(script)], env=dict(os.environ, B2_ROOT=root), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "free bytes unchanged" in r.stdout
