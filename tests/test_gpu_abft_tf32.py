@@ -371,3 +371,30 @@ def test_clean_runs_raise_no_alarm_at_any_data_scale(cuda, n, scale):
     assert r["detected"] == 0 and r["corrected"] == 0 and r["false_alarms"] == 0, r
     assert r["max_residual"] <= 0.5 * default_tau(n) * scale
     assert torch.equal(out, plain)
+
+
+@pytest.mark.parametrize("K", [1024, 8192])
+def test_truncation_model_shrinks_the_clean_residual(cuda, K):
+    """The check expects a group's sum to fall short of its checksum by the built-in fraction of the group's running sum
+    (the tensor cores' truncating accumulation).  On clean data, with the threshold out of the way, the largest residual
+    with that model is several times smaller than with a plain checksum (coefficient 0), and below a fifth of the
+    default threshold."""
+    import hpcdeepneuralnetworks_b200 as b2
+    if _mode["abft"] != 2:
+        pytest.skip("the model belongs to the CUDA-core checksums")
+    M = N = 2048
+    A = b2.fill_uniform(torch.empty((M, K), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((K, N), device="cuda"), 2)
+    worst = {}
+    try:
+        for bias in (0.0, -1.0):           # 0: plain checksum; negative: the built-in coefficient
+            b2.set_tf32_abft_bias(bias)
+            rep = b2.new_report()
+            out = torch.zeros((M, N), device="cuda")
+            b2.ft_sgemm(M, N, K, 1.0, A, B, 0.0, out, path=b2.PATH_3XTF32, tau=1e30, report=rep)
+            b2.check_status()
+            worst[bias] = b2.read_report(rep)["max_residual"]
+    finally:
+        b2.set_tf32_abft_bias(-1.0)
+    assert worst[-1.0] <= 0.2 * default_tau(K)
+    assert worst[0.0] >= 4.0 * worst[-1.0], worst
