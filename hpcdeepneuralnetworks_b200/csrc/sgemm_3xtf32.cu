@@ -31,6 +31,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b2 {
@@ -1019,12 +1021,12 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
   if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
 }
 
-static int g_tf32_tile_n = 0;  // 0: automatic; 128 or 256 pins the tile width
-static int g_tf32_slab_k = 32; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
-static int g_tf32_abft = kFtCuda;  // where the ABFT checksums are formed: 1 tensor cores, 2 CUDA cores
-static int g_tf32_persistent = 1;  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
-static float g_tf32_ft_bias = -1.f;  // < 0: default
-static int g_tf32_pair = 1;    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
+static std::atomic<int> g_tf32_tile_n{0};  // 0: automatic; 128 or 256 pins the tile width
+static std::atomic<int> g_tf32_slab_k{32}; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
+static std::atomic<int> g_tf32_abft{kFtCuda};  // where the ABFT checksums are formed: 1 tensor cores, 2 CUDA cores
+static std::atomic<int> g_tf32_persistent{1};  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
+static std::atomic<float> g_tf32_ft_bias{-1.f};  // < 0: default
+static std::atomic<int> g_tf32_pair{1};    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
 // (24 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
@@ -1098,7 +1100,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s);
   int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
   if (st != B2_OK) return st;
-  const int ftm = ft ? g_tf32_abft : 0;
+  const int ftm = ft ? g_tf32_abft.load() : 0;
   FtArgs ftl;
   if (ft) {
     // Default thresholds for operands of unit scale.  Checksums on the CUDA cores, corrected for the tensor
@@ -1185,7 +1187,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     if (ft) {
       pa.ft = *ft;
       pa.tau_elem = (ftm == kFtCuda ? 0.75f : 0.5f) * ft->tau;
-      pa.ft_bias = g_tf32_ft_bias >= 0.f ? g_tf32_ft_bias : kFtBiasPerSlab;
+      pa.ft_bias = g_tf32_ft_bias.load() >= 0.f ? g_tf32_ft_bias.load() : kFtBiasPerSlab;
     }
     if ((ftm == 0 || ftm == kFtCuda) && g_tf32_persistent) {
       const void *fn = ftm ? (const void *)sgemm_3xtf32_pair_persistent_kernel<kFtCuda> : (const void *)sgemm_3xtf32_pair_persistent_kernel<0>;
@@ -1232,7 +1234,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (ft) {
     args.ft = *ft;
     args.tau_elem = (ftm == kFtCuda ? 0.75f : 0.5f) * ft->tau;
-    args.ft_bias = g_tf32_ft_bias >= 0.f ? g_tf32_ft_bias : kFtBiasPerSlab;
+    args.ft_bias = g_tf32_ft_bias.load() >= 0.f ? g_tf32_ft_bias.load() : kFtBiasPerSlab;
     return ftm == kFtTensor ? launch_tf32<256, 32, kFtTensor>(ctx, maps, args, grid, s) : launch_tf32<256, 32, kFtCuda>(ctx, maps, args, grid, s);
   }
   if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 32, 0>(ctx, maps, args, grid, s);

@@ -31,6 +31,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b2 {
@@ -602,8 +604,8 @@ __global__ void scale_c_kernel(int M, int N, float beta, float *C, int ldc) {
   }
 }
 
-static int g_ffma_variant = -1;  // -1: pick from B2_FFMA_VARIANT (default packed)
-static int g_ffma_tile = -1;     // -1: automatic; otherwise an index into the tile table
+static std::atomic<int> g_ffma_variant{-1};  // -1: pick from B2_FFMA_VARIANT (default packed)
+static std::atomic<int> g_ffma_tile{-1};     // -1: automatic; otherwise an index into the tile table
 
 static int ffma_variant() {
   if (g_ffma_variant < 0) {
@@ -773,8 +775,8 @@ __global__ void __launch_bounds__(256) transpose_kernel(const float *__restrict_
 // fetches four rows of one k instead of four k of one row, which frees the inner loop of the
 // component selects).  A row-major A is therefore transposed into the workspace first when the
 // pass pays for itself (it moves 8*M*K bytes; the gain grows with N) and scratch can be had.
-static int g_ft_level = 1;   // ABFT encode granularity of the FFMA path: 1 block (16 x NR per warp slice), 2 thread
-static int g_ffma_transpose_a = 1;
+static std::atomic<int> g_ft_level{1};   // ABFT encode granularity of the FFMA path: 1 block (16 x NR per warp slice), 2 thread
+static std::atomic<int> g_ffma_transpose_a{1};
 size_t ffma_workspace_bytes(int M, int N, int K) {
   if (!g_ffma_transpose_a || N < 2048 || M < 128 || K < 32) return 0;
   const size_t bytes = (size_t)K * (((size_t)M + 3) & ~(size_t)3) * sizeof(float) + 2048;
