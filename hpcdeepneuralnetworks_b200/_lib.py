@@ -110,7 +110,7 @@ def load() -> C.CDLL:
     L.b2_set_ffma_transpose_a.argtypes = [i32]
     L.b2_set_tf32_abft_mode.argtypes = [i32]
     L.b2_set_tf32_abft_bias.argtypes = [f32]
-    L.b2_host_plan_create.argtypes = [C.POINTER(vp), vp, i32, i32, i32, i32, i32, i32, i32]
+    L.b2_host_plan_create.argtypes = [C.POINTER(vp), vp, i32, i32, i32, i32, i32, i32, i32, i32]
     L.b2_host_plan_destroy.argtypes = [vp]
     L.b2_sgemm_host.argtypes = [vp, f32, vp, i32, vp, i32, f32, vp, i32, i32, vp]
     L.b2_host_alloc.argtypes = [C.POINTER(vp), C.c_size_t]

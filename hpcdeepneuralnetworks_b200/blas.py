@@ -226,30 +226,33 @@ class HostSgemm:
     tensors used as page-locked memory) and a host plan of the library that owns the device copies, three streams
     and the pipeline schedule.
 
-    Default schedule (one K panel, bit-identical to a single device call): C is cut into row panels of
-    ``panel_rows``; the first row panel is computed in column tiles of ``panel_cols`` behind the pitched copies of
-    B's column panels, the others as one full-width GEMM each as their rows land, and each row panel of C travels
-    back as soon as it is done.  With ``panel_k > 0`` the second cut is along K instead and block (p, q) accumulates
+    Default schedule (one K panel, bit-identical to a single device call): the first ``first_panel_rows`` rows of C
+    (default: half) are computed in column tiles of ``panel_cols`` behind the pitched copies of B's column panels, the
+    other rows in panels of ``panel_rows`` as one full-width GEMM each as their rows land, and each row panel of C
+    travels back as soon as it is done.  With ``panel_k > 0`` the second cut is along K instead and block (p, q) accumulates
     into C_p with beta on the first K panel and 1 afterwards (same tolerance, different rounding)."""
 
-    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=1536, panel_k=0, panel_cols=1536, handle=None):
+    def __init__(self, M, N, K, path=PATH_FFMA, panel_rows=0, panel_k=0, panel_cols=0, first_panel_rows=0, handle=None):
         self.M, self.N, self.K, self.path = M, N, K, path
         self._L = _lib.load()
         self._handle = handle or default_handle()
-        self.pr = M if M < 128 else max(128, (min(panel_rows, M) + 127) // 128 * 128)
-        self.pk = K if (K < 128 or panel_k <= 0) else max(128, (min(panel_k, K) + 127) // 128 * 128)
-        self.pc = N if N < 256 else max(128, (min(panel_cols, N) + 127) // 128 * 128)
+        def _round(want, extent, floor_at):
+            return extent if extent < floor_at else max(128, (min(want, extent) + 127) // 128 * 128)
+        self.pr0 = _round(first_panel_rows or (M + 1) // 2, M, 128)      # the library's own defaults and rounding
+        self.pr = _round(panel_rows or min(1536, max(128, 128 * (296 // max(1, (N + 127) // 128)))), M, 128)
+        self.pc = _round(panel_cols or 768, N, 256)
+        self.pk = K if (K < 128 or panel_k <= 0) else _round(panel_k, K, 128)
         self.hA = torch.empty((M, K), dtype=torch.float32).pin_memory()
         self.hB = torch.empty((K, N), dtype=torch.float32).pin_memory()
         self.hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
         # scratch for the largest panel product, handed to the library before the plan is made
-        rows_max, k_max = min(self.pr, M), min(self.pk, K)
+        rows_max, k_max = min(max(self.pr, self.pr0), M), min(self.pk, K)
         if M > 0 and N > 0 and K > 0:
             self._handle.reserve(max(self._L.b2_ft_sgemm_workspace_bytes(path, rows_max, N, k_max),
                                      self._L.b2_ft_sgemm_workspace_bytes(path, rows_max, min(self.pc, N), k_max)))
         self._plan = C.c_void_p()
-        check(self._L.b2_host_plan_create(C.byref(self._plan), self._handle.raw, path, M, N, K, panel_rows, panel_cols,
-                                          max(panel_k, 0)))
+        check(self._L.b2_host_plan_create(C.byref(self._plan), self._handle.raw, path, M, N, K, first_panel_rows, panel_rows,
+                                          panel_cols, max(panel_k, 0)))
 
     def h2d_bytes(self):
         return 4 * (self.M * self.K + self.K * self.N + self.M * self.N)

@@ -23,7 +23,7 @@ using namespace b2;
 struct b2_host_plan_s {
   Context *ctx = nullptr;
   int path = 0, M = 0, N = 0, K = 0;
-  int pr = 0, pc = 0, pk = 0;       // panel sizes: rows of C, columns of the first row panel, K (== K: one panel)
+  int pr0 = 0, pr = 0, pc = 0, pk = 0;   // panel sizes: rows of the first row panel, of the others, columns of the first panel's tiles, K (== K: one panel)
   float *dA = nullptr, *dB = nullptr, *dC = nullptr;
   b2_ft_report *report = nullptr;   // device
   cudaStream_t compute = nullptr, h2d = nullptr, d2h = nullptr;
@@ -100,21 +100,29 @@ int b2_host_plan_destroy(b2_host_plan p) {
   return B2_OK;
 }
 
-int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, int K, int panel_rows, int panel_cols,
-                        int panel_k) {
+int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, int K, int first_panel_rows, int panel_rows,
+                        int panel_cols, int panel_k) {
   B2_REQUIRE(out != nullptr, B2_ERR_INVALID_ARG, "b2_host_plan_create: out is NULL");
   B2_REQUIRE(path == B2_PATH_FFMA || path == B2_PATH_3XTF32, B2_ERR_INVALID_ARG, "b2_host_plan_create: unknown path %d", path);
   B2_REQUIRE(M >= 0 && N >= 0 && K >= 0, B2_ERR_INVALID_ARG, "b2_host_plan_create: negative dimension (M=%d N=%d K=%d)", M, N, K);
-  B2_REQUIRE(panel_rows >= 0 && panel_cols >= 0 && panel_k >= 0, B2_ERR_INVALID_ARG, "b2_host_plan_create: negative panel size");
+  B2_REQUIRE(first_panel_rows >= 0 && panel_rows >= 0 && panel_cols >= 0 && panel_k >= 0, B2_ERR_INVALID_ARG,
+             "b2_host_plan_create: negative panel size");
   B2_CONTEXT(ctx, h, "b2_host_plan_create");
   b2_host_plan_s *p = new b2_host_plan_s();
   p->ctx = ctx;
   p->path = path;
   p->M = M; p->N = N; p->K = K;
-  // 1536 rows: a 1536 x 6144 panel is 576 tiles of 128 x 128, 1.95 waves of the 296 CTAs a B200 holds, where 1024
-  // rows would leave the second wave a third full
-  p->pr = round_panel(panel_rows > 0 ? panel_rows : 1536, M, 128);
-  p->pc = round_panel(panel_cols > 0 ? panel_cols : 1536, N, 256);
+  // Defaults.  The first row panel is half of C, computed in column tiles of 768 behind the column panels of B: a
+  // 3072 x 768 tile of a 6144^3 product takes about as long as its share of B and C takes to arrive, so the kernels keep
+  // pace with the link while B streams in.  The other half follows in row panels that are one wave of 128 x 128 tiles
+  // each (768 rows at N = 6144: 288 tiles for the 296 CTAs a B200 holds), short enough that the last kernel and the last
+  // copy back add little after the last byte has gone in.  Measured at 6144^3: 12.5 ms with four panels of 1536, 11.05 ms so.
+  int wave_rows = 128 * ((2 * ctx->sm_count) / ((N + 127) / 128 > 0 ? (N + 127) / 128 : 1));
+  if (wave_rows < 128) wave_rows = 128;
+  if (wave_rows > 1536) wave_rows = 1536;
+  p->pr0 = round_panel(first_panel_rows > 0 ? first_panel_rows : (M + 1) / 2, M, 128);
+  p->pr = round_panel(panel_rows > 0 ? panel_rows : wave_rows, M, 128);
+  p->pc = round_panel(panel_cols > 0 ? panel_cols : 768, N, 256);
   p->pk = panel_k > 0 ? round_panel(panel_k, K, 128) : K;
   auto fail = [&](int st) {
     b2_host_plan_destroy(p);
@@ -131,7 +139,8 @@ int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, 
     return fail(cuda_fail(cudaGetLastError(), "b2_host_plan_create (device buffers and streams)", __FILE__, __LINE__));
   // scratch sized once, outside the pipeline (growing it later would synchronise the device)
   size_t ws = 0;
-  const int rows_max = p->pr < M ? p->pr : M, k_max = p->pk < K ? p->pk : K;
+  const int rows_big = p->pr0 > p->pr ? p->pr0 : p->pr;
+  const int rows_max = rows_big < M ? rows_big : M, k_max = p->pk < K ? p->pk : K;
   if (M > 0 && N > 0 && K > 0) {
     ws = b2_ft_sgemm_workspace_bytes(path, rows_max, N, k_max);
     const size_t ws_first = b2_ft_sgemm_workspace_bytes(path, rows_max, p->pc < N ? p->pc : N, k_max);
@@ -162,7 +171,12 @@ int b2_sgemm_host(b2_host_plan p, float alpha, const float *A, int lda, const fl
   const bool use_c = beta != 0.f;
   struct Span { int a, b; };
   std::vector<Span> rows, cols, kps;
-  for (int r0 = 0; r0 < M; r0 += p->pr) rows.push_back({r0, r0 + p->pr < M ? r0 + p->pr : M});
+  for (int r0 = 0; r0 < M;) {
+    // with several K panels every row panel has the regular height
+    const int h = (r0 == 0 && p->pk >= K) ? p->pr0 : p->pr;
+    rows.push_back({r0, r0 + h < M ? r0 + h : M});
+    r0 += h;
+  }
   for (int c0 = 0; c0 < N; c0 += p->pc) cols.push_back({c0, c0 + p->pc < N ? c0 + p->pc : N});
   for (int k0 = 0; k0 < K; k0 += (p->pk > 0 ? p->pk : 1)) kps.push_back({k0, k0 + p->pk < K ? k0 + p->pk : K});
   auto gemm = [&](int m, int n, int k, const float *a, const float *b, float bt, float *c) {

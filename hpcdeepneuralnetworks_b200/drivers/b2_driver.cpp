@@ -199,7 +199,7 @@ static int run_sgemm_host(int n, int path) {
   CK(b2_sgemm(h, path, n, n, n, alpha, dA, n, dB, n, beta, dC, n, nullptr));
   CU(cudaMemcpy(hRef, dC, n2 * 4, cudaMemcpyDeviceToHost));
   b2_host_plan plan;
-  CK(b2_host_plan_create(&plan, h, path, n, n, n, 0, 0, 0));
+  CK(b2_host_plan_create(&plan, h, path, n, n, n, 0, 0, 0, 0));
   CK(b2_sgemm_host(plan, alpha, hA, n, hB, n, beta, hC, n, 0, nullptr));
   if (path == B2_PATH_FFMA && memcmp(hC, hRef, n2 * 4) != 0) {
     printf("sgemm_host: the pipelined result differs from the single device call at n = %d\n", n);

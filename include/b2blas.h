@@ -207,12 +207,14 @@ int b2_sdot_static(int64_t n, const float *x, const float *y, float *result_dev,
 /* The reference drivers hold their matrices on the host and move them with blocking cudaMemcpy calls around the
  * launch (kernel/sgemm/sgemm.cu:50-63, kernel/ft_sgemm/sgemm.cu:60-66).  A host plan does the same for one problem
  * shape with the transfers overlapped with the kernels: it owns device copies of A (M x K), B (K x N) and C (M x N),
- * three streams and their events.  panel_rows / panel_cols / panel_k = 0 select the defaults (1536 / 1536 / all of
- * K); they are rounded to multiples of 128.  The plan computes on its own stream with the handle's scratch: do not
- * use the handle elsewhere while b2_sgemm_host runs. */
+ * three streams and their events.  first_panel_rows / panel_rows / panel_cols / panel_k = 0 select the defaults (half of
+ * M / one wave of 128 x 128 tiles, 768 rows at N = 6144 / 768 / all of K); they are rounded to multiples of 128.  The first row panel of C is computed in column tiles
+ * of panel_cols while the column panels of B arrive, the following row panels of panel_rows full width as their rows of A
+ * and C land.  The plan computes on its own stream with the handle's scratch: do not use the handle elsewhere while
+ * b2_sgemm_host runs. */
 typedef struct b2_host_plan_s *b2_host_plan;
-int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, int K, int panel_rows, int panel_cols,
-                        int panel_k);
+int b2_host_plan_create(b2_host_plan *out, b2_handle h, int path, int M, int N, int K, int first_panel_rows, int panel_rows,
+                        int panel_cols, int panel_k);
 int b2_host_plan_destroy(b2_host_plan p);
 /* C <- alpha*A*B + beta*C on HOST arrays (row-major, leading dimensions in floats); returns when C is complete on
  * the host.  With one K panel (the default) every output sums all of K inside one kernel, so the FFMA result is
