@@ -102,6 +102,7 @@ def load() -> C.CDLL:
     L.b2_set_ffma_variant.argtypes = [i32]
     L.b2_ffma_tile_info.argtypes = [i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_char_p)]
     L.b2_set_ffma_tile.argtypes = [i32]
+    L.b2_set_ffma_split_k.argtypes = [i32]
     L.b2_set_tf32_tile_n.argtypes = [i32]
     L.b2_set_tf32_slab_k.argtypes = [i32]
     L.b2_set_tf32_pair.argtypes = [i32]

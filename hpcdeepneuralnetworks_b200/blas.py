@@ -366,6 +366,11 @@ def set_ffma_tile(index: int):
 
 
 
+def set_ffma_split_k(ways: int):
+    """Split-K of the plain FFMA SGEMM: 0 never (default), 2..8 that many ways, -1 automatic."""
+    check(_lib.load().b2_set_ffma_split_k(ways))
+
+
 def set_tf32_tile_n(n: int):
     """Pin the 3xTF32 tile width (128 or 256; 0 = automatic)."""
     check(_lib.load().b2_set_tf32_tile_n(n))

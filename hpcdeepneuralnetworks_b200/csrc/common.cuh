@@ -106,7 +106,6 @@ struct FtArgs {
   const float *A, *B;
   int lda, ldb;
   int nbands_pad;   // FFMA path: 16-row bands of A per K-slab in the table of A's band checksums
-  size_t ws_used;   // FFMA path, host side: bytes at the front of the workspace that hold the transposed A
 };
 
 #ifdef __CUDACC__

@@ -63,7 +63,6 @@ int ft_sgemm_on(Context *ctx, int path, int M, int N, int K, float alpha, const 
                 cudaStream_t s) {
   FtArgs ft;
   ft.nbands_pad = 0;
-  ft.ws_used = 0;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
   ft.report = report_dev ? (int *)report_dev : (int *)((char *)ctx->fixed + kFixedFtReport);
@@ -142,7 +141,6 @@ int b2_ft_sgemm_colmajor_nt(b2_handle h, int M, int N, int K, float alpha, const
   B2_CONTEXT(ctx, h, "b2_ft_sgemm_colmajor_nt");
   FtArgs ft;
   ft.nbands_pad = 0;
-  ft.ws_used = 0;
   ft.plan = plan_dev;
   ft.n_faults = n_faults;
   ft.tau = tau > 0.f ? tau : fmaxf(2e-6f * (float)K, 4e-5f);

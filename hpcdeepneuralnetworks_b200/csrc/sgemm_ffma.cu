@@ -67,6 +67,10 @@ struct FfmaArgs {
   int *status;  // device status words: [0] set to B2_ERR_TIMEOUT if a bounded wait runs out, [1] the number of that launch
   unsigned int seq;   // number of this launch on its handle
   int device;         // host side only: the device the launch goes to
+  // split-K (plain SGEMM only): CTA (split s, tile t) sums K-slabs [s * slabs_per_split, (s + 1) * slabs_per_split) and
+  // writes its raw sums to partial[s] (M x ldp); splitk_reduce_kernel adds the parts in ascending s and applies alpha/beta
+  int k_splits, slabs_per_split, ldp;
+  float *partial;
 };
 
 // ABFT.  Checksum algebra of kernel/ft_sgemm/README.md:4-14 at the granularity the accumulators are held:
@@ -261,9 +265,13 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int lm = lane >> 3, ln = lane & 7;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   int tile_m, tile_n;
-  tile_of_block(blockIdx.x, tiles_m, tiles_n, tile_m, tile_n);
+  const int split = p.k_splits > 1 ? (int)blockIdx.x / (tiles_m * tiles_n) : 0;
+  tile_of_block((int)blockIdx.x - split * tiles_m * tiles_n, tiles_m, tiles_n, tile_m, tile_n);
   const int m0 = tile_m * BM, n0 = tile_n * BN;
-  const int nkb = (p.K + FBK - 1) / FBK;
+  // this CTA's K-slabs: all of them, or one share of a split-K launch (possibly empty: it then writes zeros)
+  const int kb0 = split * p.slabs_per_split;
+  const int nkb_all = (p.K + FBK - 1) / FBK;
+  const int nkb = p.k_splits > 1 ? max(0, min(p.slabs_per_split, nkb_all - kb0)) : nkb_all;
 
   {
     // an earlier CTA of this launch timed out: leave at once (one thread reads, so the whole CTA agrees)
@@ -312,12 +320,12 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (tid == 0) {
     for (int s = 0; s < FSTAGES && s < nkb; ++s) {
       mbar_expect_tx(&full[s], kStageBytes);
-      if (TRANS_A) tma_load_2d(sA + s * kStageA, &tmA, &full[s], m0, s * FBK);
-      else tma_load_2d(sA + s * kStageA, &tmA, &full[s], s * FBK, m0);
-      tma_load_2d(sB + s * kStageB, &tmB, &full[s], n0, s * FBK);
+      if (TRANS_A) tma_load_2d(sA + s * kStageA, &tmA, &full[s], m0, (kb0 + s) * FBK);
+      else tma_load_2d(sA + s * kStageA, &tmA, &full[s], (kb0 + s) * FBK, m0);
+      tma_load_2d(sB + s * kStageB, &tmB, &full[s], n0, (kb0 + s) * FBK);
       if (FT == 1) {
-        tma_load_2d(sCs + s * kStageCs, &tmSA, &full[s], 0, s * ft.nbands_pad + tile_m * WARPS);
-        tma_load_2d(sCs + s * kStageCs + WARPS * 128, &tmSB, &full[s], 0, s * tiles_n + tile_n);
+        tma_load_2d(sCs + s * kStageCs, &tmSA, &full[s], 0, (kb0 + s) * ft.nbands_pad + tile_m * WARPS);
+        tma_load_2d(sCs + s * kStageCs + WARPS * 128, &tmSB, &full[s], 0, (kb0 + s) * tiles_n + tile_n);
       }
     }
   }
@@ -434,12 +442,12 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           break;
         }
         mbar_expect_tx(&full[sp], kStageBytes);
-        if (TRANS_A) tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], m0, knext * FBK);
-        else tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], knext * FBK, m0);
-        tma_load_2d(sB + sp * kStageB, &tmB, &full[sp], n0, knext * FBK);
+        if (TRANS_A) tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], m0, (kb0 + knext) * FBK);
+        else tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], (kb0 + knext) * FBK, m0);
+        tma_load_2d(sB + sp * kStageB, &tmB, &full[sp], n0, (kb0 + knext) * FBK);
         if (FT == 1) {
-          tma_load_2d(sCs + sp * kStageCs, &tmSA, &full[sp], 0, knext * ft.nbands_pad + tile_m * WARPS);
-          tma_load_2d(sCs + sp * kStageCs + WARPS * 128, &tmSB, &full[sp], 0, knext * tiles_n + tile_n);
+          tma_load_2d(sCs + sp * kStageCs, &tmSA, &full[sp], 0, (kb0 + knext) * ft.nbands_pad + tile_m * WARPS);
+          tma_load_2d(sCs + sp * kStageCs + WARPS * 128, &tmSB, &full[sp], 0, (kb0 + knext) * tiles_n + tile_n);
         }
       }
     }
@@ -517,28 +525,34 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 
   // Epilogue straight from registers: per row, 8 lanes x 16 bytes = 128 contiguous bytes per store.
-  const bool read_c = (p.beta != 0.f);
+  // (a split-K share goes to its own partial matrix unscaled: alpha = 1 is exact)
+  const bool parts = p.k_splits > 1;
+  float *const out_base = parts ? p.partial + (size_t)split * p.M * p.ldp : p.C;
+  const int out_ld = parts ? p.ldp : p.ldc;
+  const float alpha = parts ? 1.f : p.alpha, beta = parts ? 0.f : p.beta;
+  const int vec_out = parts ? 1 : p.vec_c;
+  const bool read_c = (beta != 0.f);
 #pragma unroll
   for (int i = 0; i < MR; ++i) {
     const int row = m0 + acc_row<TRANS_A, MR>(warp, lm, i);
     if (row >= p.M) continue;
-    float *crow = p.C + (size_t)row * p.ldc;
+    float *crow = out_base + (size_t)row * out_ld;
 #pragma unroll
     for (int h = 0; h < NR / 4; ++h) {
       const int col = n0 + ln * 4 + 32 * h;
-      if (p.vec_c && col + 3 < p.N) {
+      if (vec_out && col + 3 < p.N) {
         float4 o;
         if (read_c) {
           const float4 c = *reinterpret_cast<const float4 *>(crow + col);
-          o.x = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 0), __fmul_rn(p.beta, c.x));
-          o.y = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 1), __fmul_rn(p.beta, c.y));
-          o.z = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 2), __fmul_rn(p.beta, c.z));
-          o.w = __fmaf_rn(p.alpha, acc.get(i, 4 * h + 3), __fmul_rn(p.beta, c.w));
+          o.x = __fmaf_rn(alpha, acc.get(i, 4 * h + 0), __fmul_rn(beta, c.x));
+          o.y = __fmaf_rn(alpha, acc.get(i, 4 * h + 1), __fmul_rn(beta, c.y));
+          o.z = __fmaf_rn(alpha, acc.get(i, 4 * h + 2), __fmul_rn(beta, c.z));
+          o.w = __fmaf_rn(alpha, acc.get(i, 4 * h + 3), __fmul_rn(beta, c.w));
         } else {
-          o.x = __fmul_rn(p.alpha, acc.get(i, 4 * h + 0));
-          o.y = __fmul_rn(p.alpha, acc.get(i, 4 * h + 1));
-          o.z = __fmul_rn(p.alpha, acc.get(i, 4 * h + 2));
-          o.w = __fmul_rn(p.alpha, acc.get(i, 4 * h + 3));
+          o.x = __fmul_rn(alpha, acc.get(i, 4 * h + 0));
+          o.y = __fmul_rn(alpha, acc.get(i, 4 * h + 1));
+          o.z = __fmul_rn(alpha, acc.get(i, 4 * h + 2));
+          o.w = __fmul_rn(alpha, acc.get(i, 4 * h + 3));
         }
         *reinterpret_cast<float4 *>(crow + col) = o;
       } else {
@@ -546,7 +560,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int e = 0; e < 4; ++e) {
           if (col + e < p.N) {
             const float a = acc.get(i, 4 * h + e);
-            crow[col + e] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col + e])) : __fmul_rn(p.alpha, a);
+            crow[col + e] = read_c ? __fmaf_rn(alpha, a, __fmul_rn(beta, crow[col + e])) : __fmul_rn(alpha, a);
           }
         }
       }
@@ -606,6 +620,41 @@ __global__ void scale_c_kernel(int M, int N, float beta, float *C, int ldc) {
 
 static std::atomic<int> g_ffma_variant{-1};  // -1: pick from B2_FFMA_VARIANT (default packed)
 static std::atomic<int> g_ffma_tile{-1};     // -1: automatic; otherwise an index into the tile table
+
+// Sum of the split-K parts in ascending order of the split, then the usual epilogue: deterministic, one rounding per
+// added part.  One thread per 4 consecutive columns.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ P, int S, int M, int N, int ldp, float alpha,
+                                                            float beta, float *__restrict__ C, int ldc, int vec_c) {
+  const int quads = (N + 3) / 4;
+  const int64_t total = (int64_t)M * quads;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / quads), c = (int)(i - (int64_t)r * quads) * 4;
+    const float *p0 = P + (size_t)r * ldp + c;
+    float4 sum = *reinterpret_cast<const float4 *>(p0);
+    for (int s = 1; s < S; ++s) {
+      const float4 v = *reinterpret_cast<const float4 *>(p0 + (size_t)s * M * ldp);
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    float *cp = C + (size_t)r * ldc + c;
+    const float in[4] = {sum.x, sum.y, sum.z, sum.w};
+    if (vec_c && c + 3 < N) {
+      float4 o;
+      if (beta != 0.f) {
+        const float4 cc = *reinterpret_cast<const float4 *>(cp);
+        o.x = __fmaf_rn(alpha, sum.x, __fmul_rn(beta, cc.x)); o.y = __fmaf_rn(alpha, sum.y, __fmul_rn(beta, cc.y));
+        o.z = __fmaf_rn(alpha, sum.z, __fmul_rn(beta, cc.z)); o.w = __fmaf_rn(alpha, sum.w, __fmul_rn(beta, cc.w));
+      } else {
+        o.x = __fmul_rn(alpha, sum.x); o.y = __fmul_rn(alpha, sum.y); o.z = __fmul_rn(alpha, sum.z); o.w = __fmul_rn(alpha, sum.w);
+      }
+      *reinterpret_cast<float4 *>(cp) = o;
+    } else {
+      for (int e = 0; e < 4 && c + e < N; ++e)
+        cp[e] = beta != 0.f ? __fmaf_rn(alpha, in[e], __fmul_rn(beta, cp[e])) : __fmul_rn(alpha, in[e]);
+    }
+  }
+}
+
+static std::atomic<int> g_ffma_split_k{0};  // 0: never (every output is one FMA chain over all of K); n > 1: n ways; -1: automatic
 
 static int ffma_variant() {
   if (g_ffma_variant < 0) {
@@ -793,8 +842,17 @@ int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float al
 
 // ft == nullptr: plain SGEMM.  Otherwise the ABFT kernel (operands must be describable to TMA,
 // i.e. 16-byte aligned with leading dimensions that are multiples of 4).
+static int ffma_dispatch_impl(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda, const float *B,
+                              int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s, size_t ws_front);
+
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s) {
+  return ffma_dispatch_impl(ctx, trans_a, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s, 0);
+}
+
+// ws_front: bytes at the front of the workspace that are in use (the transposed copy of A).
+static int ffma_dispatch_impl(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda, const float *B,
+                              int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s, size_t ws_front) {
   if (M == 0 || N == 0) return B2_OK;
   if (K == 0 || alpha == 0.f) {
     if (beta == 1.f) return B2_OK;
@@ -816,7 +874,6 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   // block-level ABFT keeps the two operand-checksum tables of this product in the workspace, behind the transposed
   // copy of A if there is one
   const bool tables = ft != nullptr && g_ft_level == 1;
-  size_t ws_front = ft ? ft->ws_used : 0;
   if (!trans_a) {
     const size_t want_t = ffma_workspace_bytes(M, N, K);
     const size_t want = want_t + (tables ? ft_tables_bytes(M, N, K) : 0);
@@ -828,14 +885,14 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
         dim3 g((K + 63) / 64, (M + 63) / 64);
         transpose_kernel<<<g, 256, 0, s>>>(A, M, K, lda, AT, mp);
         B2_CUDA(cudaGetLastError());
+        const size_t used = (((size_t)K * mp * sizeof(float)) + 2047) & ~(size_t)1023;
         if (ft) {
           FtArgs ft2 = *ft;
           ft2.A = AT;     // the recomputation reads the operand the kernel used
           ft2.lda = mp;
-          ft2.ws_used = (((size_t)K * mp * sizeof(float)) + 2047) & ~(size_t)1023;
-          return sgemm_ffma_dispatch_ft(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, &ft2, s);
+          return ffma_dispatch_impl(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, &ft2, s, used);
         }
-        return sgemm_ffma_dispatch_ft(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, nullptr, s);
+        return ffma_dispatch_impl(ctx, 1, M, N, K, alpha, AT, mp, B, ldb, beta, C, ldc, nullptr, s, used);
       }
       set_error("");   // no scratch to be had: the row-major kernel needs none
     }
@@ -856,8 +913,36 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   args.seq = next_launch_seq(ctx);
   args.device = ctx->device;
   const int tiles_m = (M + tl.bm - 1) / tl.bm, tiles_n = (N + tl.bn - 1) / tl.bn;
-  const int grid = tiles_m * tiles_n;
-  FtArgs ftl = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  int grid = tiles_m * tiles_n;
+  args.k_splits = 1;
+  args.slabs_per_split = 0;
+  args.ldp = 0;
+  args.partial = nullptr;
+  // Split-K, opt-in (b2_set_ffma_split_k) and for the plain product only: with fewer CTAs than the GPU holds, the K loop of
+  // every tile is cut into `ways` shares computed side by side and summed by a second kernel.  Each output is then a sum
+  // of `ways` FMA chains instead of one, so the result differs in the last bits from the default's.
+  if (!ft) {
+    const int knob = g_ffma_split_k, slabs = (K + FBK - 1) / FBK;
+    int ways = 1;
+    if (knob > 1) ways = knob;
+    else if (knob < 0) ways = (int)((double)ctx->sm_count * tl.ctas_per_sm / (double)grid);
+    if (ways > 8) ways = 8;
+    if (ways > slabs / 2) ways = slabs / 2;          // at least two K-slabs per share
+    if (ways > 1) {
+      const int ldp = (N + 3) & ~3;
+      const size_t need = ws_front + (size_t)ways * M * ldp * sizeof(float) + 2048;
+      if (ensure_workspace(ctx, need, s) == B2_OK) {
+        args.k_splits = ways;
+        args.slabs_per_split = (slabs + ways - 1) / ways;
+        args.ldp = ldp;
+        args.partial = (float *)((char *)(((uintptr_t)ctx->ws + 1023) & ~(uintptr_t)1023) + ws_front);
+        grid *= ways;
+      } else {
+        set_error("");   // no scratch for the parts: one chain per output, as by default
+      }
+    }
+  }
+  FtArgs ftl = {nullptr, 0, 0.f, nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
   if (ft) ftl = *ft;
   const bool thread_level = ft && g_ft_level == 2 && tl.bm == 128 && tl.bn == 128 && tl.mr == 4 && tl.stages == 3;   // built for that tile only
   if (ft && !thread_level) {
@@ -888,7 +973,14 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
   if (thread_level)
     return trans_a ? launch_ffma<128, 16, 4, 3, true, true, 2>(ta, tb, tsa, tsb, args, grid, s, ftl)
                    : launch_ffma<128, 16, 4, 3, true, false, 2>(ta, tb, tsa, tsb, args, grid, s, ftl);
-  return tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, tsa, tsb, args, grid, s, ftl);
+  st = tl.fn[packed][trans_a ? 1 : 0][ft ? 1 : 0](ta, tb, tsa, tsb, args, grid, s, ftl);
+  if (st != B2_OK || args.k_splits <= 1) return st;
+  const int64_t quads = (int64_t)M * ((N + 3) / 4);
+  int64_t blocks = (quads + 255) / 256;
+  if (blocks > (int64_t)ctx->sm_count * 8) blocks = (int64_t)ctx->sm_count * 8;
+  splitk_reduce_kernel<<<(int)blocks, 256, 0, s>>>(args.partial, args.k_splits, M, N, args.ldp, alpha, beta, C, ldc, args.vec_c);
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
 }
 
 }  // namespace b2
@@ -910,6 +1002,14 @@ extern "C" {
 int b2_set_ffma_variant(int v) {
   B2_REQUIRE(v >= 0 && v <= 1, B2_ERR_INVALID_ARG, "b2_set_ffma_variant: %d not in 0..1", v);
   b2::g_ffma_variant = v;
+  return B2_OK;
+}
+
+// Split-K of the plain FFMA SGEMM: 0 never (default), n > 1 n ways (at most 8, at least two K-slabs each), -1 as many
+// ways as fill the GPU.
+int b2_set_ffma_split_k(int ways) {
+  B2_REQUIRE(ways >= -1 && ways != 1 && ways <= 8, B2_ERR_INVALID_ARG, "b2_set_ffma_split_k: %d is not -1, 0 or 2..8", ways);
+  b2::g_ffma_split_k = ways;
   return B2_OK;
 }
 

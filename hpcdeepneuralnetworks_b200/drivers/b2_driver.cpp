@@ -245,10 +245,13 @@ static int run_small() {
     CU(cudaMalloc(&buf, (size_t)sets * 3 * n2 * 4));
     CK(b2_fill_uniform(buf, (int64_t)sets * 3 * n2, 7, nullptr));
     void *ws = nullptr;
-    const size_t wsb = b2_sgemm_workspace_bytes(B2_PATH_3XTF32, n, n, n);
+    size_t wsb = b2_sgemm_workspace_bytes(B2_PATH_3XTF32, n, n, n);
+    if (wsb < 8 * n2 * 4 + 4096) wsb = 8 * n2 * 4 + 4096;      // room for the parts of an 8-way split-K as well
     CU(cudaMalloc(&ws, wsb + 1024));
     CK(b2_set_workspace(h, (void *)(((uintptr_t)ws + 1023) & ~(uintptr_t)1023), wsb));
-    for (int path = 0; path < 2; ++path) {
+    for (int leg = 0; leg < 3; ++leg) {                 // FFMA, 3xTF32, FFMA with automatic split-K
+      const int path = leg == 1 ? B2_PATH_3XTF32 : B2_PATH_FFMA;
+      CK(b2_set_ffma_split_k(leg == 2 ? -1 : 0));
       for (int it = 0; it < 10; ++it) CK(b2_sgemm(h, path, n, n, n, 1.0f, buf, n, buf + n2, n, 0.5f, buf + 2 * n2, n, nullptr));
       CK(b2_timer_start(timer, nullptr));
       for (int it = 0; it < iters; ++it) {
@@ -258,9 +261,11 @@ static int run_small() {
       CK(b2_timer_stop(timer, nullptr));
       float ms = 0.f;
       CK(time_ms(timer, &ms));
-      printf("sgemm n = %4d  path %d  %8.2f us per call  %8.2f TFLOPS  (%d buffer sets in rotation)\n", n, path, 1e3 * ms / iters,
+      printf("sgemm n = %4d  %-22s %8.2f us per call  %8.2f TFLOPS  (%d buffer sets in rotation)\n", n,
+             leg == 0 ? "FFMA" : leg == 1 ? "3xTF32" : "FFMA, split-K automatic", 1e3 * ms / iters,
              2.0 * iters * (double)n * n * n / 1e12 / (ms / 1e3), sets);
     }
+    CK(b2_set_ffma_split_k(0));
     CK(b2_set_workspace(h, nullptr, 0));
     CU(cudaFree(ws));
     CU(cudaFree(buf));

@@ -315,6 +315,12 @@ int b2_set_ft_level(int level);
 /* 1 (default): the FFMA path may transpose a row-major A into the workspace first (see
  * b2_sgemm_workspace_bytes); 0: never. */
 int b2_set_ffma_transpose_a(int on);
+/* Split-K of the plain FFMA SGEMM, for products with fewer tiles than the GPU holds CTAs: 0 (default) never -- every
+ * output is one FMA chain over all of K, the arithmetic the path is pinned on bit for bit; n = 2..8: the K loop of every
+ * tile is cut into n shares computed side by side (partial sums in the handle's workspace, grown on demand) and added in
+ * ascending order by a second kernel, deterministic but different in the last bits; -1: as many ways as fill the GPU.
+ * The role of the reference generator's small tiles (kernel/ft_sgemm/code_gen/main.py:8-9) on a 148-SM GPU. */
+int b2_set_ffma_split_k(int ways);
 /* FFMA tile family (generated table): count, description of tile i, and a pin for the automatic
  * picker (-1 = automatic).  Stands in for the positional kernel ids of kernel/ft_sgemm/sgemm.cu:114-157. */
 int b2_ffma_tile_count(void);

@@ -88,3 +88,43 @@ def test_workspace_query(L):
     assert L.b2_sgemm_workspace_bytes(0, 1024, 1024, 1024) == 0
     need = L.b2_sgemm_workspace_bytes(1, 1024, 1024, 1024)
     assert need >= 4 * 1024 * 1024 * 4
+
+
+def test_partition_helpers_need_no_device(L):
+    """b2_mg_row_block / b2_mg_k_panel: contiguous row blocks whose sizes differ by at most one, K panels in order."""
+    start, rows = C.c_int64(), C.c_int64()
+    for M in (0, 1, 7, 128, 1000, 32768):
+        for world in (1, 2, 3, 8):
+            seen = 0
+            sizes = []
+            for r in range(world):
+                assert L.b2_mg_row_block(M, r, world, C.byref(start), C.byref(rows)) == 0
+                assert start.value == seen
+                seen += rows.value
+                sizes.append(rows.value)
+            assert seen == M and max(sizes) - min(sizes) <= 1
+    assert L.b2_mg_row_block(10, 2, 2, C.byref(start), C.byref(rows)) == -1          # rank out of range
+    k0, kw = C.c_int(), C.c_int()
+    assert L.b2_mg_k_panel(0, 4096, 0, C.byref(k0), C.byref(kw)) == 0
+    assert L.b2_mg_k_panel(10, 4, 2, C.byref(k0), C.byref(kw)) == 3 and (k0.value, kw.value) == (8, 2)
+    assert L.b2_mg_k_panel(32768, 4096, 7, C.byref(k0), C.byref(kw)) == 8 and (k0.value, kw.value) == (28672, 4096)
+    assert L.b2_mg_k_panel(5, 0, 4, C.byref(k0), C.byref(kw)) == 5 and (k0.value, kw.value) == (4, 1)   # panel < 1 means 1
+
+
+def test_new_entry_points_validate_before_touching_a_device(L):
+    null = C.c_void_p(None)
+    plan = C.c_void_p()
+    assert L.b2_host_plan_create(None, null, 0, 4, 4, 4, 0, 0, 0, 0) == -1                 # out is NULL
+    assert L.b2_host_plan_create(C.byref(plan), null, 9, 4, 4, 4, 0, 0, 0, 0) == -1        # unknown path
+    assert L.b2_host_plan_create(C.byref(plan), null, 0, -4, 4, 4, 0, 0, 0, 0) == -1       # negative dimension
+    assert L.b2_host_plan_create(C.byref(plan), null, 0, 4, 4, 4, -1, 0, 0, 0) == -1       # negative panel size
+    assert L.b2_sgemm_host(null, 1.0, null, 4, null, 4, 0.0, null, 4, 0, null) == -1       # plan is NULL
+    assert L.b2_host_plan_destroy(null) == 0 and L.b2_mg_destroy(null) == 0
+    mg = C.c_void_p()
+    assert L.b2_mg_create(C.byref(mg), null, 3, 2, null) == -1                             # rank 3 of 2
+    assert L.b2_mg_create(C.byref(mg), null, 0, 2, null) == -1                             # two ranks need an id
+    assert L.b2_mg_sgemm(null, 0, 0, 4, 4, 4, 1.0, null, 4, null, 4, 0.0, null, 4, 0, 0, null, null) == -1
+    assert L.b2_mg_sdot(null, 4, null, null, null, null, null) == -1
+    assert L.b2_ft_sgemm_workspace_bytes(0, 1024, 1024, 1024) > 0                          # the checksum tables
+    assert L.b2_ft_sgemm_workspace_bytes(1, 1024, 1024, 1024) == L.b2_sgemm_workspace_bytes(1, 1024, 1024, 1024)
+    assert L.b2_set_tf32_abft_bias(0.5) == -1

@@ -631,3 +631,36 @@ def test_two_host_threads_one_handle_each(cuda):
     for t in ts:
         t.join()
     assert errors == []
+
+
+@pytest.mark.parametrize("shape,ways", [((256, 256, 256), 4), ((300, 260, 1000), 3), ((64, 64, 2048), 8), ((130, 70, 96), 2),
+                                        ((512, 384, 640), -1)])
+@pytest.mark.parametrize("beta", [0.0, 0.5])
+def test_split_k_is_deterministic_exactly_modelled_and_within_tolerance(cuda, shape, ways, beta):
+    """The opt-in split-K form of the FFMA path: each output is the sum, in ascending order, of `ways` FMA chains over
+    consecutive shares of K.  Deterministic run to run, bit-identical to that model (alpha = 1, beta = 0, where the
+    epilogue adds no rounding of its own), inside the path's tolerance; off again, the default is the single chain."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K, beta)
+    c64, den = oracle.sgemm_f64(1.0, a, b, beta, c)
+    try:
+        b2.set_ffma_split_k(ways)
+        out1 = run_gpu(0, a, b, c, 1.0, beta)
+        out2 = run_gpu(0, a, b, c, 1.0, beta)
+        assert np.array_equal(out1, out2)
+        assert oracle.gemm_error(out1, c64, den) <= TOL_FFMA
+        if beta == 0.0 and ways > 1:
+            slabs = (K + 31) // 32
+            w = min(ways, 8, slabs // 2)
+            per = (slabs + w - 1) // w * 32
+            total = None
+            for k0 in range(0, per * w, per):
+                k1 = min(K, k0 + per)
+                part = (np.zeros((M, N), np.float32) if k0 >= K else
+                        oracle.sgemm_fma(1.0, np.ascontiguousarray(a[:, k0:k1]), np.ascontiguousarray(b[k0:k1]), 0.0, np.zeros((M, N), np.float32)))
+                total = part if total is None else (total + part).astype(np.float32)
+            assert np.array_equal(out1, total)
+    finally:
+        b2.set_ffma_split_k(0)
+    assert np.array_equal(run_gpu(0, a, b, c, 1.0, beta), oracle.sgemm_fma(1.0, a, b, beta, c))
