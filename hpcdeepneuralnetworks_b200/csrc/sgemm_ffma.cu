@@ -774,6 +774,16 @@ constexpr int kNumTiles = sizeof(g_tiles) / sizeof(g_tiles[0]);
 // Picks the tile with the best predicted throughput: its measured efficiency times how well its
 // CTA count fills whole waves of the CTAs that are co-resident on an SM.  The fill term matters
 // less the more waves there are (the hardware back-fills), hence the 1/waves exponent.
+// Ways of an automatic split-K for a tile whose grid has `ctas` CTAs: as many as fill the CTAs the GPU holds, at most 8,
+// at least two K-slabs each.
+static int auto_split_ways(const Context *ctx, const FfmaTile &tl, double ctas, int K) {
+  int ways = (int)((double)ctx->sm_count * tl.ctas_per_sm / ctas);
+  const int slabs = (K + FBK - 1) / FBK;
+  if (ways > 8) ways = 8;
+  if (ways > slabs / 2) ways = slabs / 2;
+  return ways < 1 ? 1 : ways;
+}
+
 static int pick_tile(const Context *ctx, int M, int N) {
   if (g_ffma_tile >= 0 && g_ffma_tile < kNumTiles) return g_ffma_tile;
   int best = 0;
@@ -925,7 +935,7 @@ static int ffma_dispatch_impl(Context *ctx, int trans_a, int M, int N, int K, fl
     const int knob = g_ffma_split_k, slabs = (K + FBK - 1) / FBK;
     int ways = 1;
     if (knob > 1) ways = knob;
-    else if (knob < 0) ways = (int)((double)ctx->sm_count * tl.ctas_per_sm / (double)grid);
+    else if (knob < 0) ways = auto_split_ways(ctx, tl, (double)grid, K);
     if (ways > 8) ways = 8;
     if (ways > slabs / 2) ways = slabs / 2;          // at least two K-slabs per share
     if (ways > 1) {
