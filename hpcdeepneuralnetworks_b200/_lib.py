@@ -109,7 +109,6 @@ def load() -> C.CDLL:
     L.b2_set_tf32_persistent.argtypes = [i32]
     L.b2_set_ft_level.argtypes = [i32]
     L.b2_set_ffma_transpose_a.argtypes = [i32]
-    L.b2_set_tf32_abft_mode.argtypes = [i32]
     L.b2_set_tf32_abft_bias.argtypes = [f32]
     L.b2_host_plan_create.argtypes = [C.POINTER(vp), vp, i32, i32, i32, i32, i32, i32, i32, i32]
     L.b2_host_plan_destroy.argtypes = [vp]

@@ -401,11 +401,6 @@ def set_tf32_persistent(on: int):
     check(_lib.load().b2_set_tf32_persistent(on))
 
 
-def set_tf32_abft_mode(mode: int):
-    """Where the 3xTF32 ABFT checksums are formed: 2 CUDA cores (default), 1 tensor cores."""
-    check(_lib.load().b2_set_tf32_abft_mode(mode))
-
-
 def set_tf32_abft_bias(bias: float):
     """Loss per K-slab that the 3xTF32 ABFT check expects of an accumulator (fraction of its value; < 0: built-in)."""
     check(_lib.load().b2_set_tf32_abft_bias(bias))

@@ -43,31 +43,18 @@ constexpr int TBM = 128;
 // floats = one 64-byte swizzled row; the shallower slab doubles the number of stages that fit
 // (more TMA bytes in flight for the same shared memory).
 //
-// FT adds the ABFT checksum operand.  A checksum covers one row of a group of 32 output columns.
-// With s_g[k] = sum_{j<32} B[k][32g + j] split into hi and lo parts like B itself, the operand is,
-// per 256-column tile and K-slab, a 32 x TBK tile S (K-major like the B planes):
-//     rows 0..7 s_hi of groups 0..7, rows 8..15 s_lo, rows 16..23 s_hi again, rows 24..31 zero.
-// Two more MMAs of N = 16 per K-step multiply it by the A tiles the main MMAs already use, both
-// into the same 16 extra TMEM columns:
-//     A_lo x S[16..31]  -> column TBN + g     += A_lo*s_hi
-//     A_hi x S[0..15]   -> column TBN + g     += A_hi*s_hi,   column TBN + 8 + g += A_hi*s_lo
-// and the expected sum of a row's group g is column TBN + g plus column TBN + 8 + g.  A small-N
-// MMA costs about as much as fetching its A operand again, so two of them rather than three
-// matter; keeping both s_hi terms in one accumulator makes its truncation error follow that of
-// the data accumulators more closely (smaller clean residual) than three separate columns do.
-//
-// FT = 1 is that form (checksums on the tensor cores).  FT = 2 forms the checksums on the CUDA
-// cores instead: S is then 8 rows of plain FP32 sums s_g[k] per 256-column tile, and the four
-// epilogue warps, idle during the mainloop, read each stage next to the MMAs (their own row of
-// A_hi and A_lo, all of S) and keep chk_g += (a_hi + a_lo) * s_g[k] for the 8 groups in registers.
-// No extra MMA, so the cost is a few percent instead of ~20 %.  An exact checksum does not follow
-// the truncation of the tensor cores' accumulators, whose sum over a group falls short of it by a
-// fraction of what the group held during the K loop; the checksum warps therefore also keep the sum
-// over the slabs of each running checksum, and the epilogue expects the shortfall (tf32_epilogue).
-// That brings the clean residual from 5.9e-6*K down to 4e-7*K at K = 8192 and lets the default
-// threshold sit at half the path's accuracy bound.
-constexpr int kFtRows = 32;                          // rows of S per 256-column tile (FT = 1; FT = 2 uses the first 8)
-constexpr int kFtTensor = 1, kFtCuda = 2;
+// FT adds ABFT.  A checksum covers one row of a group of 32 output columns: with s_g[k] = sum_{j<32} B[k][32g + j]
+// (the plane S, 8 rows of plain FP32 sums per 256-column tile, written by the transposing split pre-pass),
+// sum_j C[i][32g + j] = sum_k A[i][k] * s_g[k].  The checksums are formed on the CUDA cores: checksum warps read each
+// stage next to the MMAs (their rows of A_hi and A_lo, all of S) and keep chk_g += (a_hi + a_lo) * s_g[k] for the 8
+// groups in registers -- no extra MMA, a few percent of time.  An exact checksum does not follow the truncation of
+// the tensor cores' accumulators, whose sum over a group falls short of it by a fraction of what the group held
+// during the K loop; the checksum warps therefore also keep the sum over the slabs of each running checksum, and the
+// epilogue expects the shortfall (tf32_epilogue).  That brings the clean residual from 5.9e-6*K down to 4e-7*K at
+// K = 8192 and lets the default threshold sit at half the path's accuracy bound.  (An earlier form multiplied a
+// split copy of S by the A tiles on the tensor cores, two more small MMAs per K-step: +20-30 % time and a residual
+// of 2.2e-6*K, above what the bound allows; it was removed.)
+constexpr int kFtCuda = 2;    // the value of the FT template parameter of the ABFT instantiations (0: plain)
 // Measured on B200: every 32-deep K-slab (twelve MMAs) costs an accumulator about 4e-7 of its value (the hardware
 // adds an MMA's products to the accumulator with truncation); the best fit is the same for uniform and normal
 // operands of any scale and any K from 256 to 8192.
@@ -76,12 +63,11 @@ template <int TBN, int TBK, int FT = 0>
 struct Tf32Cfg {
   static constexpr int kTA = TBM * TBK * 4;          // bytes per A plane tile
   static constexpr int kTB = TBN * TBK * 4;          // bytes per B plane tile
-  static constexpr int kTS = FT == kFtTensor ? kFtRows * TBK * 4 : FT == kFtCuda ? 8 * TBK * 4 : 0;  // bytes per checksum tile
+  static constexpr int kTS = FT ? 8 * TBK * 4 : 0;  // bytes per checksum tile
   static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;
   static constexpr int kStages = ((FT ? 208 : 192) * 1024) / kStage;
   static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 8192 : 0);   // + checksum table
-  // FP32 accumulator: one TMEM column per output column; FT = 1: 16 more, rounded to a power of two
-  static constexpr int kTmemCols = FT == kFtTensor ? 2 * TBN : TBN;
+  static constexpr int kTmemCols = TBN;             // FP32 accumulator: one TMEM column per output column
   static constexpr uint32_t kSwizzle = (TBK == 32) ? 2u : 4u;   // descriptor layout type: 128-byte / 64-byte swizzle
   static constexpr uint32_t kSbo = 8 * TBK * 4;                 // bytes between 8-row groups
 };
@@ -123,15 +109,12 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float *__restri
 // a multiple of 4).  Tiles of 128 rows x 64 columns of X through shared memory: reads run 256
 // bytes along a row of X, writes 512 bytes along a row of the planes (the writes are two thirds of
 // the traffic).
-// With S != NULL it also writes the ABFT checksum plane (pitch ldp): for every row r of X and group
-// g of 32 columns inside 256-column tile t, with sum = sum_{j<32} X[r][256t + 32g + j],
-//   smode 1 (32 rows per tile): S[32t + g][r] = S[32t + 16 + g][r] = hi(sum), S[32t + 8 + g][r] = lo(sum),
-//                               S[32t + 24 + g][r] = 0;
-//   smode 2 (8 rows per tile):  S[8t + g][r] = sum.
+// With S != NULL it also writes the ABFT checksum plane (pitch ldp, 8 rows per 256-column tile): for every row r of
+// X and group g of 32 columns inside tile t, S[8t + g][r] = sum_{j<32} X[r][256t + 32g + j].
 constexpr int kSplitTK = 128, kSplitTN = 64;
 __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__restrict__ X, int rows, int cols, int ld,
                                                              float *__restrict__ hi, float *__restrict__ lo, int ldp,
-                                                             float *__restrict__ S, int smode) {
+                                                             float *__restrict__ S) {
   __shared__ float t[kSplitTK][kSplitTN + 1];
   const int c0 = blockIdx.x * kSplitTN, r0 = blockIdx.y * kSplitTK, tid = threadIdx.x;
 #pragma unroll 8
@@ -167,16 +150,7 @@ __global__ void __launch_bounds__(256) split_planes_t_kernel(const float *__rest
 #pragma unroll
       for (int j = 0; j < 32; ++j) sum += t[rr][32 * gg + j];
       const int g = (c0 % 256) / 32 + gg;
-      if (smode == kFtCuda) {
-        S[((size_t)(c0 / 256) * 8 + g) * ldp + r0 + rr] = sum;
-      } else {
-        const float h = tf32_rna(sum);
-        const size_t o = ((size_t)(c0 / 256) * kFtRows + g) * ldp + r0 + rr;
-        S[o] = h;
-        S[o + (size_t)8 * ldp] = tf32_rna(sum - h);
-        S[o + (size_t)16 * ldp] = h;
-        S[o + (size_t)24 * ldp] = 0.f;
-      }
+      S[((size_t)(c0 / 256) * 8 + g) * ldp + r0 + rr] = sum;
     }
   }
 }
@@ -323,12 +297,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
     float expect = 0.f;
     if (ok && nkb > 0) {
       tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-      if (FT == kFtTensor) {
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(TBN + c);
-        const uint32_t e0 = tmem_ld_32x1(t0), e1 = tmem_ld_32x1(t0 + 8);
-        tmem_ld_wait();
-        expect = __uint_as_float(e0) + __uint_as_float(e1);
-      } else if (FT == kFtCuda) {
+      if (FT) {
         // The tensor cores add each MMA's products to the accumulator with truncation, which pulls the
         // accumulator toward zero by a fraction of its value that is about the same for every MMA; over the
         // K loop a group of accumulators therefore loses ft_bias times the sum over the slabs of what the
@@ -503,7 +472,6 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * TBK, n0);
           tma_load_2d(st + 2 * kTA + kTB, &tmBl, &full[s], kb * TBK, n0);
         }
-        if (FT == kFtTensor) tma_load_2d(st + 2 * kTA + 2 * kTB, &tmS, &full[s], kb * TBK, tile_n * kFtRows);
         if (FT == kFtCuda) tma_load_2d(st + 2 * kTA + 2 * kTB, &tmS, &full[s], kb * TBK, tile_n * 8);
       }
     }
@@ -511,7 +479,6 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     // ---- MMA issuer -------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(TBM, TBN, 0, 0);
-      constexpr uint32_t idesc_s = umma_idesc_tf32(TBM, 16, 0, 0);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % TSTAGES;
@@ -533,12 +500,6 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
           umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
-          if (FT == kFtTensor) {
-            const uint64_t s_lohi = umma_smem_desc(st + 2 * kTA + 2 * kTB + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
-            const uint64_t s_hi0 = umma_smem_desc(st + 2 * kTA + 2 * kTB + 16 * TBK * 4 + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
-            umma_tf32(tmem_base + TBN, a_lo, s_hi0, idesc_s, (kb > 0 || k4 > 0) ? 1u : 0u);
-            umma_tf32(tmem_base + TBN, a_hi, s_lohi, idesc_s, 1u);
-          }
         }
         umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
       }
@@ -599,21 +560,17 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 // of L2 per flop); the leader (r = 0) issues MMAs of M = 256 that read both CTAs' tiles and write
 // 128 accumulator rows into each CTA's TMEM.  Every TMA load is a plain per-CTA load that signals
 // the leader's "full" barrier; the leader's commits free the stage in both CTAs.
-//
-// FT: the checksum operand of an MMA with N = 16 is split between the CTAs like any B operand, 8
-// rows each.  CTA 0 stages rows 0..7 (s_hi) and 16..23 (s_hi) of the tile's 32-row S block, CTA 1
-// rows 8..15 (s_lo) and 24..31 (zero), so the two extra MMAs see [s_hi | s_lo] and [s_hi | 0] as
-// in the single-CTA kernel and the 16 checksum columns mean the same.
+// FT: both CTAs stage the tile's S rows; their checksum warps cover their own 128 accumulator rows.
 constexpr int kPairBand = 8;   // tile rows per band of the pair kernel's tile order
 template <int FT>
 struct PairCfg {
   static constexpr int kTA = TBM * 32 * 4;           // bytes per A plane tile (128 rows)
   static constexpr int kTB = 128 * 32 * 4;           // bytes per B plane half tile (128 columns)
-  static constexpr int kTS = FT == kFtTensor ? 2 * 8 * 32 * 4 : FT == kFtCuda ? 8 * 32 * 4 : 0;   // two 8-row slots / one S tile
-  static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;   // 64 KB (+2 KB)
+  static constexpr int kTS = FT ? 8 * 32 * 4 : 0;    // one S tile
+  static constexpr int kStage = 2 * kTA + 2 * kTB + kTS;   // 64 KB (+1 KB)
   static constexpr int kStages = 3;
   static constexpr int kSmem = 1024 + kStages * kStage + 256 + (FT == kFtCuda ? 8192 : 0);   // + checksum table
-  static constexpr int kTmemCols = FT == kFtTensor ? 512 : 256;
+  static constexpr int kTmemCols = 256;
 };
 
 template <int FT>
@@ -690,18 +647,12 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
         tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
         if (FT == kFtCuda) tma_load_2d_pair(st + 2 * kTA + 2 * kTB, &tmS, leader_full, kb * 32, tile_n * 8);
-        if (FT == kFtTensor) {
-          const int srow = tile_n * kFtRows + 8 * (int)rank;
-          tma_load_2d_pair(st + 2 * kTA + 2 * kTB, &tmS, leader_full, kb * 32, srow);
-          tma_load_2d_pair(st + 2 * kTA + 2 * kTB + 1024, &tmS, leader_full, kb * 32, srow + 16);
-        }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer: the leader CTA only -------------------------------------------------
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
-      constexpr uint32_t idesc_s = umma_idesc_tf32(256, 16, 0, 0);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % S;
@@ -724,12 +675,6 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
           umma_tf32_pair(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
           umma_tf32_pair(tmem_base, a_hi, b_lo, idesc, 1u);
           umma_tf32_pair(tmem_base, a_hi, b_hi, idesc, 1u);
-          if (FT == kFtTensor) {
-            const uint64_t w1 = umma_smem_desc(st + 2 * kTA + 2 * kTB + k4 * 32, 16, 1024, 2);
-            const uint64_t w2 = umma_smem_desc(st + 2 * kTA + 2 * kTB + 1024 + k4 * 32, 16, 1024, 2);
-            umma_tf32_pair(tmem_base + 256, a_lo, w2, idesc_s, (kb > 0 || k4 > 0) ? 1u : 0u);
-            umma_tf32_pair(tmem_base + 256, a_hi, w1, idesc_s, 1u);
-          }
         }
         umma_commit_pair(&empty[s], (uint16_t)3);   // frees the stage in both CTAs
       }
@@ -1023,16 +968,15 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
 
 static std::atomic<int> g_tf32_tile_n{0};  // 0: automatic; 128 or 256 pins the tile width
 static std::atomic<int> g_tf32_slab_k{32}; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
-static std::atomic<int> g_tf32_abft{kFtCuda};  // where the ABFT checksums are formed: 1 tensor cores, 2 CUDA cores
 static std::atomic<int> g_tf32_persistent{1};  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
 static std::atomic<float> g_tf32_ft_bias{-1.f};  // < 0: default
 static std::atomic<int> g_tf32_pair{1};    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
-// (24 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
+// (8 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
 size_t tf32_workspace_bytes(int M, int N, int K) {
   const size_t kp = ((size_t)K + 3) & ~(size_t)3;
-  const size_t srows = (((size_t)N + 255) / 256) * kFtRows;
+  const size_t srows = (((size_t)N + 255) / 256) * 8;
   return (2 * (size_t)M * kp + 2 * (size_t)N * kp + srows * kp) * sizeof(float) + 8 * 1024;
 }
 
@@ -1074,7 +1018,7 @@ static int max_resident_pairs(Context *ctx) {
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * ctx->sm_count, 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
-  cfg.dynamicSmemBytes = PairCfg<kFtTensor>::kSmem;
+  cfg.dynamicSmemBytes = PairCfg<kFtCuda>::kSmem;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 2;
@@ -1082,8 +1026,8 @@ static int max_resident_pairs(Context *ctx) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtTensor>, ctx->device, PairCfg<kFtTensor>::kSmem) != B2_OK ||
-      cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<kFtTensor>, &cfg) != cudaSuccess || n <= 0) {
+  if (ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtCuda>, ctx->device, PairCfg<kFtCuda>::kSmem) != B2_OK ||
+      cudaOccupancyMaxActiveClusters(&n, sgemm_3xtf32_pair_kernel<kFtCuda>, &cfg) != cudaSuccess || n <= 0) {
     (void)cudaGetLastError();
     n = 0;
   }
@@ -1100,7 +1044,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s);
   int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
   if (st != B2_OK) return st;
-  const int ftm = ft ? g_tf32_abft.load() : 0;
+  const int ftm = ft ? kFtCuda : 0;
   FtArgs ftl;
   if (ft) {
     // Default thresholds for operands of unit scale.  Checksums on the CUDA cores, corrected for the tensor
@@ -1108,7 +1052,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     // uniform and normal data): 2.5e-6*K is five times that and half the path's tolerance of 2e-5*sum|a||b|
     // (5e-6*K for operands uniform in [-1, 1)).  Checksums accumulated by the tensor cores: residual 2.2e-6*K.
     ftl = *ft;
-    if (!(ftl.tau > 0.f)) ftl.tau = ftm == kFtTensor ? fmaxf(1e-5f * (float)K, 2e-4f) : fmaxf(2.5e-6f * (float)K, 6e-5f);
+    if (!(ftl.tau > 0.f)) ftl.tau = fmaxf(2.5e-6f * (float)K, 6e-5f);
     ft = &ftl;
   }
   const int kp = (K + 3) & ~3;
@@ -1119,7 +1063,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   float *Al = (float *)(w + align1k(a_elems * 4));
   float *Bh = (float *)(w + 2 * align1k(a_elems * 4));
   float *Bl = (float *)(w + 2 * align1k(a_elems * 4) + align1k(b_elems * 4));
-  const int srows = ((N + 255) / 256) * (g_tf32_abft == kFtTensor ? kFtRows : 8);
+  const int srows = ((N + 255) / 256) * 8;
   float *S = (float *)(w + 2 * align1k(a_elems * 4) + 2 * align1k(b_elems * 4));
 
   {
@@ -1128,7 +1072,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     split_planes_kernel<<<g, 256, 0, s>>>(A, M, K, lda, Ah, Al, kp, vec);
     // the ABFT form covers whole 256-column tiles so that every checksum row is written
     dim3 gt(ft ? ((N + 255) / 256) * (256 / kSplitTN) : (N + kSplitTN - 1) / kSplitTN, (kp + kSplitTK - 1) / kSplitTK);
-    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp, ft ? S : nullptr, ftm);
+    split_planes_t_kernel<<<gt, 256, 0, s>>>(B, K, N, ldb, Bh, Bl, kp, ft ? S : nullptr);
   }
   B2_CUDA(cudaGetLastError());
 
@@ -1186,10 +1130,10 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     pa.seq = next_launch_seq(ctx);
     if (ft) {
       pa.ft = *ft;
-      pa.tau_elem = (ftm == kFtCuda ? 0.75f : 0.5f) * ft->tau;
+      pa.tau_elem = 0.75f * ft->tau;
       pa.ft_bias = g_tf32_ft_bias.load() >= 0.f ? g_tf32_ft_bias.load() : kFtBiasPerSlab;
     }
-    if ((ftm == 0 || ftm == kFtCuda) && g_tf32_persistent) {
+    if (g_tf32_persistent) {
       const void *fn = ftm ? (const void *)sgemm_3xtf32_pair_persistent_kernel<kFtCuda> : (const void *)sgemm_3xtf32_pair_persistent_kernel<0>;
       st = ensure_func_attributes(fn, ctx->device, ftm ? PersistCfg<kFtCuda>::kSmem : PersistCfg<0>::kSmem);
       if (st != B2_OK) return st;
@@ -1201,12 +1145,10 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
       B2_CUDA(cudaGetLastError());
       return B2_OK;
     }
-    st = ftm == kFtTensor ? ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtTensor>, ctx->device, PairCfg<kFtTensor>::kSmem)
-         : ftm == kFtCuda ? ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtCuda>, ctx->device, PairCfg<kFtCuda>::kSmem)
-                          : ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<0>, ctx->device, PairCfg<0>::kSmem);
+    st = ftm == kFtCuda ? ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtCuda>, ctx->device, PairCfg<kFtCuda>::kSmem)
+                        : ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<0>, ctx->device, PairCfg<0>::kSmem);
     if (st != B2_OK) return st;
-    if (ftm == kFtTensor) sgemm_3xtf32_pair_kernel<kFtTensor><<<2 * pairs, 192, PairCfg<kFtTensor>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
-    else if (ftm == kFtCuda) sgemm_3xtf32_pair_kernel<kFtCuda><<<2 * pairs, 192, PairCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
+    if (ftm == kFtCuda) sgemm_3xtf32_pair_kernel<kFtCuda><<<2 * pairs, 192, PairCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     else sgemm_3xtf32_pair_kernel<0><<<2 * pairs, 192, PairCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
@@ -1218,7 +1160,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (st != B2_OK) return st;
 
   if (ft) {
-    st = make_tmap_2d(&maps[4], S, (uint64_t)K, (uint64_t)srows, (uint64_t)kp, tbk, ftm == kFtTensor ? kFtRows : 8, swz);
+    st = make_tmap_2d(&maps[4], S, (uint64_t)K, (uint64_t)srows, (uint64_t)kp, tbk, 8, swz);
     if (st != B2_OK) return st;
   } else {
     maps[4] = maps[2];
@@ -1233,9 +1175,9 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   const int grid = ((M + TBM - 1) / TBM) * ((N + tbn - 1) / tbn);
   if (ft) {
     args.ft = *ft;
-    args.tau_elem = (ftm == kFtCuda ? 0.75f : 0.5f) * ft->tau;
+    args.tau_elem = 0.75f * ft->tau;
     args.ft_bias = g_tf32_ft_bias.load() >= 0.f ? g_tf32_ft_bias.load() : kFtBiasPerSlab;
-    return ftm == kFtTensor ? launch_tf32<256, 32, kFtTensor>(ctx, maps, args, grid, s) : launch_tf32<256, 32, kFtCuda>(ctx, maps, args, grid, s);
+    return launch_tf32<256, 32, kFtCuda>(ctx, maps, args, grid, s);
   }
   if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 32, 0>(ctx, maps, args, grid, s);
   return tbn == 128 ? launch_tf32<128, 16, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 16, 0>(ctx, maps, args, grid, s);
@@ -1264,12 +1206,6 @@ int b2_set_tf32_tile_n(int n) {
 int b2_set_tf32_pair(int on) {
   B2_REQUIRE(on >= 0 && on <= 2, B2_ERR_INVALID_ARG, "b2_set_tf32_pair: %d is not 0, 1 or 2", on);
   b2::g_tf32_pair = on;
-  return B2_OK;
-}
-// Where the ABFT checksums of the 3xTF32 path are formed: 1 on the tensor cores, 2 on the CUDA cores (default).
-int b2_set_tf32_abft_mode(int mode) {
-  B2_REQUIRE(mode == 1 || mode == 2, B2_ERR_INVALID_ARG, "b2_set_tf32_abft_mode: %d is not 1 or 2", mode);
-  b2::g_tf32_abft = mode;
   return B2_OK;
 }
 // 1 (default): the plain CTA-pair SGEMM is the persistent kernel; 0: one cluster per tile.

@@ -338,10 +338,6 @@ int b2_set_tf32_pair(int on);
  * the device holds, each walking several tiles, accumulator double-buffered in tensor memory so that a tile's
  * epilogue overlaps the next tile's MMAs); 0: one cluster per tile. */
 int b2_set_tf32_persistent(int on);
-/* Where b2_ft_sgemm(path = B2_PATH_3XTF32) forms its checksums: 2 (default) on the CUDA cores beside the MMAs
- * (few percent overhead, default tau 2.5e-6*K), 1 on the tensor cores as two extra small MMAs per K-step
- * (about +20 %, default tau 1e-5*K, which is above the path's accuracy bound: kept for comparison only). */
-int b2_set_tf32_abft_mode(int mode);
 /* The tensor cores add each MMA's products to the accumulator with truncation, which costs an accumulator a
  * fraction of its value per K-slab of 32 (about 4e-7 on B200, the built-in figure; the same for uniform and normal
  * operands of any scale).  The CUDA-core checksums keep, beside each checksum, its sum over the K-slabs, and the

@@ -14,30 +14,23 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-5          # max|C - C_ref| / (|A| |B|) that the 3xTF32 path has to meet
 
 
-TAU_PER_K = {1: 1e-5, 2: 2.5e-6}     # default thresholds: checksums on the tensor cores / on the CUDA cores
-TAU_FLOOR = {1: 2e-4, 2: 6e-5}
-ELEM = {1: 0.5, 2: 0.75}             # an output further than this fraction of tau from its recomputed value is replaced
-_mode = {"abft": 2}
+TAU_PER_K = 2.5e-6       # default threshold per unit of K: half the accuracy bound of uniform [-1, 1) operands (5e-6 * K)
+TAU_FLOOR = 6e-5
+ELEM = 0.75              # an output further than this fraction of tau from its recomputed value is replaced
 
 
-@pytest.fixture(autouse=True, params=[(2, 2, 1), (2, 2, 0), (0, 2, 0), (0, 1, 0), (2, 1, 0)],
-                ids=["cta_pair_persistent-cuda_checksums", "cta_pair-cuda_checksums", "single_cta-cuda_checksums",
-                     "single_cta-tensor_checksums", "cta_pair-tensor_checksums"])
+@pytest.fixture(autouse=True, params=[(2, 1), (2, 0), (0, 0)],
+                ids=["cta_pair_persistent", "cta_pair_one_tile_per_cluster", "single_cta"])
 def _kernel_form(request, cuda):
-    """Every test runs on the persistent CTA-pair kernel (the default: 256 x 256 tiles, checksums on the CUDA cores),
-    on the one-tile-per-cluster CTA-pair kernel and on the single-CTA kernel (128 x 256 tiles), and with the
-    checksums formed on the tensor cores."""
+    """Every test runs on the persistent CTA-pair kernel (the default for large problems: 256 x 256 tiles), on the
+    one-tile-per-cluster CTA-pair kernel and on the single-CTA kernel (128 x 256 tiles)."""
     import hpcdeepneuralnetworks_b200 as b2
-    pair, abft, persistent = request.param
+    pair, persistent = request.param
     b2.set_tf32_pair(pair)
-    b2.set_tf32_abft_mode(abft)
     b2.set_tf32_persistent(persistent)
-    _mode["abft"] = abft
     yield
     b2.set_tf32_pair(1)
-    b2.set_tf32_abft_mode(2)
     b2.set_tf32_persistent(1)
-    _mode["abft"] = 2
 
 
 def dev(a):
@@ -52,12 +45,12 @@ def mats(M, N, K):
 
 
 def default_tau(K):
-    return max(TAU_PER_K[_mode["abft"]] * K, TAU_FLOOR[_mode["abft"]])
+    return max(TAU_PER_K * K, TAU_FLOOR)
 
 
 def elem_tol(K):
     """How far a repaired output (an FP32 recomputation) may sit from the tensor-core value it replaces."""
-    return ELEM[_mode["abft"]] * default_tau(K)
+    return ELEM * default_tau(K)
 
 
 def flip(x, bit):
@@ -312,8 +305,6 @@ def test_every_flip_beyond_the_path_tolerance_is_repaired(cuda, n):
     every fourth 128 x 128 tile gets the SMALLEST single-bit flip that breaks that bound for it (the flip moves it by
     one to two times the bound): every one of them has to be found and rebuilt, and nothing else may move."""
     import hpcdeepneuralnetworks_b200 as b2
-    if _mode["abft"] != 2:
-        pytest.skip("tensor-core checksums are the coarser, non-default form: their threshold is above this bound")
     A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
     B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
     plain = torch.zeros((n, n), device="cuda")
@@ -380,8 +371,6 @@ def test_truncation_model_shrinks_the_clean_residual(cuda, K):
     with that model is several times smaller than with a plain checksum (coefficient 0), and below a fifth of the
     default threshold."""
     import hpcdeepneuralnetworks_b200 as b2
-    if _mode["abft"] != 2:
-        pytest.skip("the model belongs to the CUDA-core checksums")
     M = N = 2048
     A = b2.fill_uniform(torch.empty((M, K), device="cuda"), 1)
     B = b2.fill_uniform(torch.empty((K, N), device="cuda"), 2)
