@@ -401,6 +401,13 @@ def set_tf32_persistent(on: int):
     check(_lib.load().b2_set_tf32_persistent(on))
 
 
+def set_tf32_chunk(slabs: int):
+    """Plain 3xTF32 SGEMM: K-slabs (of 32) accumulated in tensor memory before they are added to FP32 sums in
+    registers (default 16; applies when K spans more than two chunks); 0: one accumulation over all of K; negative:
+    the default."""
+    check(_lib.load().b2_set_tf32_chunk(slabs))
+
+
 def set_tf32_abft_bias(bias: float):
     """Loss per K-slab that the 3xTF32 ABFT check expects of an accumulator (fraction of its value; < 0: built-in)."""
     check(_lib.load().b2_set_tf32_abft_bias(bias))

@@ -900,12 +900,18 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
       pair_tile_origin(p, t, rank, m0, n0);
       FtInj inj;
       if (FT) inj = ft_scan_plan<256>(p, m0 + q * 32 + lane, n0);
+      // one lane polls (the barrier words share the shared-memory pipe with the MMAs' operand reads); the others
+      // then look once for themselves
       bool done = false;
-      const uint64_t t0 = global_timer_ns();
-      for (int itw = 0; itw < (1 << 14) && !done; ++itw) {
-        done = mbar_wait(&acc_full[buf], (n_done >> 1) & 1u, 1u << 10);
-        if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+      if (lane == 0) {
+        const uint64_t t0 = global_timer_ns();
+        for (int itw = 0; itw < (1 << 14) && !done; ++itw) {
+          done = mbar_wait(&acc_full[buf], (n_done >> 1) & 1u, 1u << 10);
+          if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+        }
       }
+      done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
+      if (done && lane != 0) done = mbar_wait(&acc_full[buf], (n_done >> 1) & 1u, 1u << 10);
       if (FT && done) done = mbar_wait(&tab_full[buf], (n_done >> 1) & 1u);
       const bool ok = __all_sync(0xffffffffu, done);
       if (!ok) {
@@ -966,10 +972,477 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
   if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
 }
 
+// ---- the epilogue side of chunked accumulation, shared by the two kernels below --------------------
+// A warp owns 32 accumulator rows (its TMEM lane quarter) x 128 columns; thread = row, acc[j] = column j.
+
+// Adds (first chunk: copies) the 128 columns at `src` of a finished chunk to the sums.
+__device__ __forceinline__ void chunk_drain(uint32_t src, bool first, float (&acc)[128]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint32_t v[16];
+    tmem_ld_32x16(src + (uint32_t)(c * 16), v);
+    tmem_ld_wait();
+    if (first) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[c * 16 + j] = __uint_as_float(v[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[c * 16 + j] = __fadd_rn(acc[c * 16 + j], __uint_as_float(v[j]));
+    }
+  }
+}
+
+// The tile's last chunk is on its way: fetch the warp's first 32 x 32 block of C meanwhile (one lane).
+__device__ __forceinline__ void chunk_fetch_c(const Tf32Args &p, const CUtensorMap *tmC, unsigned char *stg, uint64_t *cb,
+                                              int row0, int colw) {
+  if (p.beta != 0.f && p.vec_c && row0 < p.M && colw < (p.N & ~3)) {
+    mbar_expect_tx(cb, 4096);
+    tma_load_2d(stg, tmC, cb, colw, row0);
+  }
+}
+
+// C = alpha*acc + beta*C for the warp's 32 x 128 part of the tile.  Registers hold one row per thread.  Each
+// 32 x 32 block goes through the warp's 4 KB of shared memory in the 128-byte-swizzled layout of the tensor map of
+// C: the block of C arrives there by TMA (the first one was asked for by chunk_fetch_c), every thread replaces its
+// own row by the result, and a TMA store takes the block to C, clipped at the matrix edges.  No thread issues a
+// global load or store, and the next block is fetched as soon as the store has read the staging area.  The tensor
+// map ends at the last whole group of four columns (a TMA store writes whole 16-byte pieces, also at the edge);
+// up to three columns beyond it, and everything when C is not 16-byte aligned, go element by element from the
+// registers.  False: a wait ran out.
+__device__ __forceinline__ bool chunk_store(const Tf32Args &p, const CUtensorMap *tmC, unsigned char *stg, uint64_t *cb,
+                                            uint32_t &c_phase, const float (&acc)[128], int row0, int colw, int lane) {
+  const bool read_c = (p.beta != 0.f);
+  const int n4 = p.N & ~3;   // where the tensor map of C ends
+  bool ok = true;
+  if (p.vec_c) {
+    if (row0 >= p.M) return true;
+    if (n4 < p.N && colw <= n4 && n4 < colw + 128 && row0 + lane < p.M) {
+      // the one to three columns after the last whole group of four
+      float *ct = p.C + (size_t)(row0 + lane) * p.ldc + n4;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        if (colw + 4 * k == n4) {
+#pragma unroll
+          for (int e = 0; e < 3; ++e)
+            if (n4 + e < p.N) ct[e] = read_c ? __fmaf_rn(p.alpha, acc[4 * k + e], __fmul_rn(p.beta, ct[e])) : __fmul_rn(p.alpha, acc[4 * k + e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col0 = colw + c * 32;
+      if (col0 >= n4) break;   // uniform over the warp
+      if (read_c) {
+        if (!mbar_wait(cb, c_phase)) ok = false;
+        c_phase ^= 1u;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float4 *slot = reinterpret_cast<float4 *>(stg + lane * 128 + ((k ^ (lane & 7)) << 4));
+        float4 o;
+        if (read_c) {
+          const float4 cc = *slot;
+          o.x = __fmaf_rn(p.alpha, acc[c * 32 + 4 * k + 0], __fmul_rn(p.beta, cc.x));
+          o.y = __fmaf_rn(p.alpha, acc[c * 32 + 4 * k + 1], __fmul_rn(p.beta, cc.y));
+          o.z = __fmaf_rn(p.alpha, acc[c * 32 + 4 * k + 2], __fmul_rn(p.beta, cc.z));
+          o.w = __fmaf_rn(p.alpha, acc[c * 32 + 4 * k + 3], __fmul_rn(p.beta, cc.w));
+        } else {
+          o.x = __fmul_rn(p.alpha, acc[c * 32 + 4 * k + 0]);
+          o.y = __fmul_rn(p.alpha, acc[c * 32 + 4 * k + 1]);
+          o.z = __fmul_rn(p.alpha, acc[c * 32 + 4 * k + 2]);
+          o.w = __fmul_rn(p.alpha, acc[c * 32 + 4 * k + 3]);
+        }
+        *slot = o;
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tmC, stg, col0, row0);
+        bulk_commit_group();
+        bulk_wait_read_all();   // the staging area may be written again
+        if (read_c && c < 3 && col0 + 32 < n4) {
+          mbar_expect_tx(cb, 4096);
+          tma_load_2d(stg, tmC, cb, col0 + 32, row0);
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    const int row = row0 + lane;
+    if (row < p.M) {
+      float *crow = p.C + (size_t)row * p.ldc;
+#pragma unroll
+      for (int j = 0; j < 128; ++j) {
+        if (colw + j < p.N)
+          crow[colw + j] = read_c ? __fmaf_rn(p.alpha, acc[j], __fmul_rn(p.beta, crow[colw + j])) : __fmul_rn(p.alpha, acc[j]);
+      }
+    }
+    __syncwarp();
+  }
+  return ok;
+}
+
+// ---- persistent CTA-pair form with chunked accumulation (plain SGEMM) ------------------------------
+// The tensor cores add every MMA's products to the accumulator with truncation: an accumulator loses a fixed
+// fraction of what it holds per K-slab, so over a long K loop the loss grows with K and, for operands of one sign,
+// adds up coherently.  Here the K loop is cut into chunks of `chunk` slabs.  Each chunk is accumulated from zero
+// into one of the two TMEM buffers; eight epilogue warps per CTA (one 32-row lane quarter x one 128-column half
+// each) add the finished chunk to FP32 sums that they keep in registers while the MMA issuer is already filling
+// the other buffer with the next chunk - of the same tile or of the cluster's next tile.  The loss is then bounded
+// by that of one chunk whatever K is, and the tile's last chunk goes to C straight from the registers, so a
+// buffer is handed back as soon as it has been read and the global-memory part of the epilogue no longer holds
+// tensor memory.  Barriers as in the persistent kernel above, counted in chunks instead of tiles.
+constexpr int kChunkThreads = 320;   // TMA producer, MMA issuer, eight epilogue warps
+constexpr int kChunkSmem = 1024 + PairCfg<0>::kStages * PairCfg<0>::kStage + 8 * 4096 + 256;   // ring, 4 KB of staging per epilogue warp, barriers
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kChunkThreads, 1)
+sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                                 const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                                 const __grid_constant__ CUtensorMap tmC, const Tf32Args p, int n_tiles, int chunk) {
+  using PC = PairCfg<0>;
+  constexpr int S = PC::kStages, kTA = PC::kTA, kTB = PC::kTB, kStage = PC::kStage;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char *staging = smem + S * kStage;   // 4 KB per epilogue warp, each on a 1 KB boundary (128-byte swizzle)
+  uint64_t *full = reinterpret_cast<uint64_t *>(staging + 8 * 4096);
+  uint64_t *empty = full + S;
+  uint64_t *acc_full = empty + S;       // [2]
+  uint64_t *acc_empty = acc_full + 2;   // [2], used in the leader
+  uint64_t *c_bar = acc_empty + 2;      // [8]  one per epilogue warp: its block of C has landed in its staging area
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c_bar + 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *gate = abort_flag + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int nkb = (p.K + 31) / 32;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 16);   // eight epilogue warps in each of the two CTAs
+    }
+    for (int w = 0; w < 8; ++w) mbar_init(&c_bar[w], 1);
+    *abort_flag = 0;
+    *gate = (rank == 0 && launch_aborted(p.status, p.seq)) ? 1 : 0;   // the leader decides for the pair
+    mbar_fence_init();
+    tma_prefetch_desc(&tmAh);
+    tma_prefetch_desc(&tmAl);
+    tma_prefetch_desc(&tmBh);
+    tma_prefetch_desc(&tmBl);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool aborted = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(gate)), 0)) != 0;
+
+  if (aborted) {
+  } else if (warp == 0) {
+    // ---- TMA producer (one per CTA): one slab counter across all of this cluster's tiles ------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+        int m0, n0;
+        pair_tile_origin(p, t, rank, m0, n0);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(&empty[s], ((it / S) & 1u) ^ 1u)) {
+            pair_abort(abort_flag);
+            ok = false;
+            break;
+          }
+          unsigned char *st = smem + s * kStage;
+          const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * kStage);
+          tma_load_2d_pair(st, &tmAh, leader_full, kb * 32, m0);
+          tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
+          tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
+          tma_load_2d_pair(st + 2 * kTA + kTB, &tmBl, leader_full, kb * 32, n0 + (int)rank * 128);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the leader CTA only; one accumulator buffer per chunk -----------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
+      uint32_t it = 0, g = 0;
+      bool ok = true;
+      for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+        for (int kb0 = 0; kb0 < nkb && ok; kb0 += chunk, ++g) {
+          const uint32_t buf = g & 1u;
+          // the epilogue warps of both CTAs have read this buffer (two chunks ago)
+          if (!mbar_wait(&acc_empty[buf], ((g >> 1) & 1u) ^ 1u)) {
+            pair_abort(abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem_base + buf * 256u;
+          const int kend = min(kb0 + chunk, nkb);
+          for (int kb = kb0; kb < kend; ++kb, ++it) {
+            const int s = it % S;
+            if (!mbar_wait(&full[s], (it / S) & 1u)) {
+              pair_abort(abort_flag);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + s * kStage);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
+              const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
+              const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
+              const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
+              umma_tf32_pair(acc, a_lo, b_hi, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+              umma_tf32_pair(acc, a_hi, b_lo, idesc, 1u);
+              umma_tf32_pair(acc, a_hi, b_hi, idesc, 1u);
+            }
+            umma_commit_pair(&empty[s], (uint16_t)3);
+          }
+          if (ok) umma_commit_pair(&acc_full[buf], (uint16_t)3);
+        }
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..9 of each CTA; lane quarter q, column half h -------------------------
+    const int q = warp & 3, h = (warp - 2) >> 2;
+    const uint32_t leader_empty0 = mapa_u32(smem_u32(&acc_empty[0]), 0), leader_empty1 = mapa_u32(smem_u32(&acc_empty[1]), 0);
+    unsigned char *stg = staging + (warp - 2) * 4096;
+    uint64_t *cb = &c_bar[warp - 2];
+    uint32_t g = 0, c_phase = 0;
+    bool ok = true;
+    for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+      int m0, n0;
+      pair_tile_origin(p, t, rank, m0, n0);
+      const int row0 = m0 + q * 32, colw = n0 + h * 128;   // this warp's 32 rows x 128 columns
+      float acc[128];
+      for (int kb0 = 0; kb0 < nkb; kb0 += chunk, ++g) {
+        const uint32_t buf = g & 1u;
+        if (kb0 + chunk >= nkb && lane == 0) chunk_fetch_c(p, &tmC, stg, cb, row0, colw);
+        // one lane polls (the barrier words share the shared-memory pipe with the MMAs' operand reads); the
+        // others then look once for themselves
+        bool done = false;
+        if (lane == 0) {
+          const uint64_t t0 = global_timer_ns();
+          for (int itw = 0; itw < (1 << 14) && !done; ++itw) {
+            done = mbar_wait(&acc_full[buf], (g >> 1) & 1u, 1u << 10);
+            if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+          }
+        }
+        done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
+        if (done && lane != 0) done = mbar_wait(&acc_full[buf], (g >> 1) & 1u, 1u << 10);
+        ok = __all_sync(0xffffffffu, done);
+        if (!ok) {
+          pair_abort(abort_flag);
+          break;
+        }
+        tc_fence_after();
+        chunk_drain(tmem_base + buf * 256u + (uint32_t)(h * 128) + ((uint32_t)(q * 32) << 16), kb0 == 0, acc);
+        // this warp's reads of the buffer are complete: hand it back
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(&acc_empty[buf]);
+          else mbar_arrive_remote(buf ? leader_empty1 : leader_empty0);
+        }
+      }
+      if (!ok) break;
+      if (!chunk_store(p, &tmC, stg, cb, c_phase, acc, row0, colw, lane)) {
+        pair_abort(abort_flag);
+        break;
+      }
+    }
+    if (lane == 0) bulk_wait_all();   // this thread's stores to C are complete before the CTA goes
+  }
+
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+  if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
+}
+
+// ---- single-CTA form with chunked accumulation (plain SGEMM, 128 x 128 tiles) -----------------------
+// One tile per CTA, the same chunks in the same order as the pair kernel above (the two agree bit for bit): the MMA
+// issuer alternates between two 128-column TMEM buffers, the four epilogue warps keep the sums of their 32 rows x
+// 128 columns in registers and store the tile through their staging areas.
+constexpr int kChunk1Smem = 1024 + Tf32Cfg<128, 32, 0>::kStages * Tf32Cfg<128, 32, 0>::kStage + 4 * 4096 + 256;
+__global__ void __launch_bounds__(192, 1)
+sgemm_3xtf32_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                            const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                            const __grid_constant__ CUtensorMap tmC, const Tf32Args p, int chunk) {
+  using Cfg = Tf32Cfg<128, 32, 0>;
+  constexpr int S = Cfg::kStages, kTA = Cfg::kTA, kTB = Cfg::kTB, kStage = Cfg::kStage;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char *staging = smem + S * kStage;
+  uint64_t *full = reinterpret_cast<uint64_t *>(staging + 4 * 4096);
+  uint64_t *empty = full + S;
+  uint64_t *acc_full = empty + S;       // [2]
+  uint64_t *acc_empty = acc_full + 2;   // [2]
+  uint64_t *c_bar = acc_empty + 2;      // [4]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c_bar + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_n = (p.N + 127) / 128;
+  const int m0 = (blockIdx.x / tiles_n) * TBM, n0 = (blockIdx.x % tiles_n) * 128;
+  const int nkb = (p.K + 31) / 32;
+
+  {
+    __shared__ int launch_aborted;
+    if (threadIdx.x == 0) launch_aborted = b2::launch_aborted(p.status, p.seq) ? 1 : 0;
+    __syncthreads();
+    if (launch_aborted != 0) return;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    for (int w = 0; w < 4; ++w) mbar_init(&c_bar[w], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmAh);
+    tma_prefetch_desc(&tmAl);
+    tma_prefetch_desc(&tmBh);
+    tma_prefetch_desc(&tmBl);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S;
+        if (!mbar_wait(&empty[s], ((uint32_t)(kb / S) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        unsigned char *st = smem + s * kStage;
+        mbar_expect_tx(&full[s], kStage);
+        tma_load_2d(st, &tmAh, &full[s], kb * 32, m0);
+        tma_load_2d(st + kTA, &tmAl, &full[s], kb * 32, m0);
+        tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * 32, n0);
+        tma_load_2d(st + 2 * kTA + kTB, &tmBl, &full[s], kb * 32, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(TBM, 128, 0, 0);
+      bool ok = true;
+      uint32_t g = 0;
+      for (int kb0 = 0; kb0 < nkb && ok; kb0 += chunk, ++g) {
+        const uint32_t buf = g & 1u;
+        if (!mbar_wait(&acc_empty[buf], ((g >> 1) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + buf * 128u;
+        const int kend = min(kb0 + chunk, nkb);
+        for (int kb = kb0; kb < kend; ++kb) {
+          const int s = kb % S;
+          if (!mbar_wait(&full[s], (uint32_t)(kb / S) & 1u)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + s * kStage);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+            const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+            const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+            const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, Cfg::kSbo, Cfg::kSwizzle);
+            umma_tf32(acc, a_lo, b_hi, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+            umma_tf32(acc, a_hi, b_lo, idesc, 1u);
+            umma_tf32(acc, a_hi, b_hi, idesc, 1u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    unsigned char *stg = staging + (warp - 2) * 4096;
+    uint64_t *cb = &c_bar[warp - 2];
+    const int row0 = m0 + q * 32, colw = n0;
+    uint32_t g = 0, c_phase = 0;
+    bool ok = true;
+    float acc[128];
+    for (int kb0 = 0; kb0 < nkb; kb0 += chunk, ++g) {
+      const uint32_t buf = g & 1u;
+      if (kb0 + chunk >= nkb && lane == 0) chunk_fetch_c(p, &tmC, stg, cb, row0, colw);
+      bool done = false;
+      if (lane == 0) {
+        const uint64_t t0 = global_timer_ns();
+        for (int itw = 0; itw < (1 << 14) && !done; ++itw) {
+          done = mbar_wait(&acc_full[buf], (g >> 1) & 1u, 1u << 10);
+          if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+        }
+      }
+      done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
+      if (done && lane != 0) done = mbar_wait(&acc_full[buf], (g >> 1) & 1u, 1u << 10);
+      ok = __all_sync(0xffffffffu, done);
+      if (!ok) {
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      chunk_drain(tmem_base + buf * 128u + ((uint32_t)(q * 32) << 16), kb0 == 0, acc);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (ok && !chunk_store(p, &tmC, stg, cb, c_phase, acc, row0, colw, lane)) *abort_flag = 1;
+    if (lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+  if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
+}
+
 static std::atomic<int> g_tf32_tile_n{0};  // 0: automatic; 128 or 256 pins the tile width
 static std::atomic<int> g_tf32_slab_k{32}; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 static std::atomic<int> g_tf32_persistent{1};  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
 static std::atomic<float> g_tf32_ft_bias{-1.f};  // < 0: default
+constexpr int kDefaultChunk = 16;
+static std::atomic<int> g_tf32_chunk{kDefaultChunk};  // plain SGEMM: K-slabs per accumulation chunk (0: one accumulation over all of K)
 static std::atomic<int> g_tf32_pair{1};    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
@@ -1110,7 +1583,21 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     }
   }
   B2_REQUIRE(chosen >= 0, B2_ERR_UNSUPPORTED, "3xTF32: no kernel form of the tile table fits this call");
-  const bool use_pair = g_tf32_tiles[chosen].form == 1;
+  bool use_pair = g_tf32_tiles[chosen].form == 1;
+  // Chunked accumulation (plain calls with more than two chunks of K-slabs, no pinned width): two forms exist, the
+  // persistent CTA-pair kernel and single-CTA 128 x 128 tiles; whole waves decide between them as above.
+  const int chunk = g_tf32_chunk.load();
+  const bool chunked = ft == nullptr && chunk > 0 && (K + 31) / 32 > 2 * chunk && tbk == 32 && !pinned;
+  if (chunked) {
+    const bool pair_ok = g_tf32_pair != 0 && slots > 0 && g_tf32_persistent != 0;
+    double cost_pair = 0.9, cost_single = 0.55;
+    for (int t = 0; t < kNumTf32Tiles; ++t) {
+      if (g_tf32_tiles[t].form == 1) cost_pair = g_tf32_tiles[t].cost;
+      else if (g_tf32_tiles[t].tbn == 128 && g_tf32_tiles[t].tbk == 32) cost_single = g_tf32_tiles[t].cost;
+    }
+    const double tiles128 = (double)((M + 127) / 128) * ((N + 127) / 128);
+    use_pair = pair_ok && (g_tf32_pair == 2 || cost_pair * ceil((double)pairs / (double)slots) <= cost_single * ceil(tiles128 / (double)ctx->sm_count));
+  }
   if (use_pair) {
     st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
     if (st != B2_OK) return st;
@@ -1133,6 +1620,20 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
       pa.tau_elem = 0.75f * ft->tau;
       pa.ft_bias = g_tf32_ft_bias.load() >= 0.f ? g_tf32_ft_bias.load() : kFtBiasPerSlab;
     }
+    if (chunked) {
+      st = ensure_func_attributes((const void *)sgemm_3xtf32_pair_chunked_kernel, ctx->device, kChunkSmem);
+      if (st != B2_OK) return st;
+      const int clusters = pairs < slots ? pairs : (slots > 0 ? slots : pairs);
+      CUtensorMap map_c = maps[0];
+      if (N < 4) pa.vec_c = 0;
+      if (pa.vec_c) {
+        st = make_tmap_2d(&map_c, C, (uint64_t)(N & ~3), (uint64_t)M, (uint64_t)ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != B2_OK) return st;
+      }
+      sgemm_3xtf32_pair_chunked_kernel<<<2 * clusters, kChunkThreads, kChunkSmem, s>>>(maps[0], maps[1], maps[2], maps[3], map_c, pa, pairs, chunk);
+      B2_CUDA(cudaGetLastError());
+      return B2_OK;
+    }
     if (g_tf32_persistent) {
       const void *fn = ftm ? (const void *)sgemm_3xtf32_pair_persistent_kernel<kFtCuda> : (const void *)sgemm_3xtf32_pair_persistent_kernel<0>;
       st = ensure_func_attributes(fn, ctx->device, ftm ? PersistCfg<kFtCuda>::kSmem : PersistCfg<0>::kSmem);
@@ -1153,7 +1654,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     B2_CUDA(cudaGetLastError());
     return B2_OK;
   }
-  const int tbn = g_tf32_tiles[chosen].tbn;
+  const int tbn = chunked ? 128 : g_tf32_tiles[chosen].tbn;
   st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
   if (st != B2_OK) return st;
   st = make_tmap_2d(&maps[3], Bl, (uint64_t)K, (uint64_t)N, (uint64_t)kp, tbk, tbn, swz);
@@ -1178,6 +1679,19 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     args.tau_elem = 0.75f * ft->tau;
     args.ft_bias = g_tf32_ft_bias.load() >= 0.f ? g_tf32_ft_bias.load() : kFtBiasPerSlab;
     return launch_tf32<256, 32, kFtCuda>(ctx, maps, args, grid, s);
+  }
+  if (chunked) {
+    CUtensorMap map_c = maps[0];
+    if (N < 4) args.vec_c = 0;
+    if (args.vec_c) {
+      st = make_tmap_2d(&map_c, C, (uint64_t)(N & ~3), (uint64_t)M, (uint64_t)ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (st != B2_OK) return st;
+    }
+    st = ensure_func_attributes((const void *)sgemm_3xtf32_chunked_kernel, ctx->device, kChunk1Smem);
+    if (st != B2_OK) return st;
+    sgemm_3xtf32_chunked_kernel<<<grid, 192, kChunk1Smem, s>>>(maps[0], maps[1], maps[2], maps[3], map_c, args, chunk);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
   }
   if (tbk == 32) return tbn == 128 ? launch_tf32<128, 32, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 32, 0>(ctx, maps, args, grid, s);
   return tbn == 128 ? launch_tf32<128, 16, 0>(ctx, maps, args, grid, s) : launch_tf32<256, 16, 0>(ctx, maps, args, grid, s);
@@ -1219,6 +1733,14 @@ int b2_set_tf32_persistent(int on) {
 int b2_set_tf32_abft_bias(float bias) {
   B2_REQUIRE(bias < 1e-3f, B2_ERR_INVALID_ARG, "b2_set_tf32_abft_bias: %g is not a plausible loss per K-slab", (double)bias);
   b2::g_tf32_ft_bias = bias;
+  return B2_OK;
+}
+// Chunked accumulation of the plain CTA-pair 3xTF32 SGEMM: every `slabs` K-slabs (of 32) the tensor-memory
+// accumulator is added to FP32 sums in registers and started again from zero, which bounds the tensor cores'
+// truncation loss by that of one chunk.  0: one accumulation over all of K; negative: the default (16).
+int b2_set_tf32_chunk(int slabs) {
+  B2_REQUIRE(slabs <= 4096, B2_ERR_INVALID_ARG, "b2_set_tf32_chunk: %d is not in 0..4096 (or negative for the default)", slabs);
+  b2::g_tf32_chunk = slabs < 0 ? b2::kDefaultChunk : slabs;
   return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.

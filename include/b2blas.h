@@ -338,6 +338,16 @@ int b2_set_tf32_pair(int on);
  * the device holds, each walking several tiles, accumulator double-buffered in tensor memory so that a tile's
  * epilogue overlaps the next tile's MMAs); 0: one cluster per tile. */
 int b2_set_tf32_persistent(int on);
+/* Chunked accumulation of the plain 3xTF32 SGEMM.  The tensor cores add every MMA's products to the accumulator
+ * with truncation, a loss per K-slab of 32 proportional to what the accumulator holds; over a long K loop it grows
+ * with K and, for operands of one sign, adds up coherently (9e-5 of sum|a||b| at K = 8192).  With chunks, every
+ * `slabs` K-slabs the tensor-memory accumulator is added to FP32 sums that the epilogue warps hold in registers and
+ * started again from zero while the MMAs go on in a second buffer: the loss is bounded by that of one chunk whatever
+ * K is (5.6e-6 for operands of one sign at the default 16, 2.5e-7 for signed operands at K = 8192) at no
+ * measurable cost in time.  Applies to plain calls (not ABFT) whose K spans more than two chunks (K > 1024 at the
+ * default) and no pinned tile width; 0: one accumulation over all of K; negative: the default.  No counterpart in
+ * the reference. */
+int b2_set_tf32_chunk(int slabs);
 /* The tensor cores add each MMA's products to the accumulator with truncation, which costs an accumulator a
  * fraction of its value per K-slab of 32 (about 4e-7 on B200, the built-in figure; the same for uniform and normal
  * operands of any scale).  The CUDA-core checksums keep, beside each checksum, its sum over the K-slabs, and the

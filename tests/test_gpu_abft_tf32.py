@@ -23,14 +23,17 @@ ELEM = 0.75              # an output further than this fraction of tau from its 
                 ids=["cta_pair_persistent", "cta_pair_one_tile_per_cluster", "single_cta"])
 def _kernel_form(request, cuda):
     """Every test runs on the persistent CTA-pair kernel (the default for large problems: 256 x 256 tiles), on the
-    one-tile-per-cluster CTA-pair kernel and on the single-CTA kernel (128 x 256 tiles)."""
+    one-tile-per-cluster CTA-pair kernel and on the single-CTA kernel (128 x 256 tiles).  The ABFT kernels accumulate
+    over all of K in one go, so the plain products they are compared with here are made the same way (no chunks)."""
     import hpcdeepneuralnetworks_b200 as b2
     pair, persistent = request.param
     b2.set_tf32_pair(pair)
     b2.set_tf32_persistent(persistent)
+    b2.set_tf32_chunk(0)
     yield
     b2.set_tf32_pair(1)
     b2.set_tf32_persistent(1)
+    b2.set_tf32_chunk(-1)
 
 
 def dev(a):

@@ -308,6 +308,87 @@ def test_3xtf32_leading_dimensions(cuda):
     assert np.array_equal(got[mask], Cb[mask])          # nothing outside the view was touched
 
 
+# ---- chunked accumulation of the 3xTF32 path (K beyond two chunks of 16 K-slabs) --------------------------
+@pytest.mark.parametrize("shape", [(300, 1000, 2100), (256, 256, 1056), (1, 5, 1100), (513, 260, 4096), (130, 36, 1500),
+                                   (2048, 2048, 2048)])
+@pytest.mark.parametrize("alpha,beta", [(1.25, 0.5), (-1.5, 0.0)])
+@pytest.mark.parametrize("chunk", [16, 3])
+def test_3xtf32_chunked_forms_agree_bit_for_bit(cuda, shape, alpha, beta, chunk):
+    """Chunked accumulation: the persistent CTA-pair kernel and the single-CTA 128 x 128 kernel cut K at the same
+    slabs and add the chunks in the same order, so they agree bit for bit (partial tiles on every edge, K not a
+    multiple of the slab, chunks that do not divide the slab count); both meet the tolerance."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    try:
+        b2.set_tf32_chunk(chunk)
+        b2.set_tf32_pair(2)
+        pair = run_gpu(1, a, b, c, alpha, beta)
+        b2.set_tf32_pair(0)
+        single = run_gpu(1, a, b, c, alpha, beta)
+    finally:
+        b2.set_tf32_pair(1)
+        b2.set_tf32_chunk(-1)
+    assert np.array_equal(pair, single)
+    c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
+    assert oracle.gemm_error(pair, c64, den) <= 0.25 * TOL_3XTF32
+
+
+@pytest.mark.parametrize("pair", [2, 0])
+@pytest.mark.parametrize("col_offset", [4, 1])
+@pytest.mark.parametrize("N", [300, 301, 303, 3])
+def test_3xtf32_chunked_strided_c(cuda, pair, col_offset, N):
+    """C as a view inside a larger array: 16-byte aligned (the blocks travel by TMA, clipped at the view's edges; the
+    columns after the last whole group of four go element by element) and not aligned (everything element by
+    element from the registers).  Nothing outside the view moves."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, K, ldc = 200, 1200, 312
+    a, b, _ = mats(M, N, K)
+    Cb = oracle.fill_uniform((M + 3) * ldc, 3).reshape(M + 3, ldc)
+    dC = dev(Cb)
+    try:
+        b2.set_tf32_pair(pair)
+        b2.sgemm(M, N, K, 1.0, dev(a), dev(b), 0.5, dC[2:, col_offset:], path=1, ldc=ldc)
+        b2.check_status()
+    finally:
+        b2.set_tf32_pair(1)
+    got = dC.cpu().numpy()
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, Cb[2:M + 2, col_offset:col_offset + N])
+    assert oracle.gemm_error(np.ascontiguousarray(got[2:M + 2, col_offset:col_offset + N]), c64, den) <= 0.25 * TOL_3XTF32
+    mask = np.ones_like(Cb, dtype=bool)
+    mask[2:M + 2, col_offset:col_offset + N] = False
+    assert np.array_equal(got[mask], Cb[mask])
+
+
+@pytest.mark.parametrize("pair", [2, 0])
+def test_3xtf32_chunks_bound_the_loss_for_operands_of_one_sign(cuda, pair):
+    """Operands of one sign make the tensor cores' truncating accumulation lose coherently: over all of K = 8192 in
+    one go the error passes the path's tolerance; in chunks of 16 slabs it stays below a third of it, and signed
+    operands come out ten times closer than without chunks."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 512, 512, 8192
+    A = b2.fill_uniform(torch.empty((M, K), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((K, N), device="cuda"), 2)
+    err = {}
+    try:
+        b2.set_tf32_pair(pair)
+        for name, (X, Y) in {"signed": (A, B), "positive": (A.abs().contiguous(), B.abs().contiguous())}.items():
+            ref = X.double() @ Y.double()
+            den = X.double().abs() @ Y.double().abs()
+            for chunk in (0, -1):
+                b2.set_tf32_chunk(chunk)
+                Cm = torch.zeros((M, N), device="cuda")
+                b2.sgemm(M, N, K, 1.0, X, Y, 0.0, Cm, path=1)
+                b2.check_status()
+                err[name, chunk] = float(((Cm.double() - ref).abs() / den).max().item())
+    finally:
+        b2.set_tf32_pair(1)
+        b2.set_tf32_chunk(-1)
+    assert err["positive", 0] > TOL_3XTF32, err          # the loss the chunks are there for
+    assert err["positive", -1] <= 7e-6, err
+    assert err["signed", -1] <= 1e-6 and err["signed", -1] < 0.2 * err["signed", 0], err
+
+
 def test_sweep_sizes_both_paths(cuda):
     """Benchmark configuration 2 (alpha=1, beta=0.5) at a few sweep sizes, inputs generated on the device; checked on
     sampled rows against the double reference."""
