@@ -310,7 +310,7 @@ def test_3xtf32_leading_dimensions(cuda):
 
 # ---- chunked accumulation of the 3xTF32 path (K beyond two chunks of 16 K-slabs) --------------------------
 @pytest.mark.parametrize("shape", [(300, 1000, 2100), (256, 256, 1056), (1, 5, 1100), (513, 260, 4096), (130, 36, 1500),
-                                   (2048, 2048, 2048)])
+                                   (2048, 2048, 2048), (3200, 2200, 1100)])     # the last: 117 pair tiles on 74 clusters
 @pytest.mark.parametrize("alpha,beta", [(1.25, 0.5), (-1.5, 0.0)])
 @pytest.mark.parametrize("chunk", [16, 3])
 def test_3xtf32_chunked_forms_agree_bit_for_bit(cuda, shape, alpha, beta, chunk):
