@@ -408,6 +408,12 @@ def set_tf32_chunk(slabs: int):
     check(_lib.load().b2_set_tf32_chunk(slabs))
 
 
+def set_tf32_tail_split(on: int):
+    """1 (default): the last, partial round of tiles of a chunked CTA-pair 3xTF32 call is shared out in chunks over all
+    clusters; 0: every tile on one cluster."""
+    check(_lib.load().b2_set_tf32_tail_split(on))
+
+
 def set_tf32_abft_bias(bias: float):
     """Loss per K-slab that the 3xTF32 ABFT check expects of an accumulator (fraction of its value; < 0: built-in)."""
     check(_lib.load().b2_set_tf32_abft_bias(bias))

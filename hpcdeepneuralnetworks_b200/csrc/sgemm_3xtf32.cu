@@ -1094,12 +1094,113 @@ __device__ __forceinline__ bool chunk_store(const Tf32Args &p, const CUtensorMap
 // by that of one chunk whatever K is, and the tile's last chunk goes to C straight from the registers, so a
 // buffer is handed back as soon as it has been read and the global-memory part of the epilogue no longer holds
 // tensor memory.  Barriers as in the persistent kernel above, counted in chunks instead of tiles.
+//
+// The last round.  n_tiles tiles on n_clusters clusters are whole rounds plus a remainder, and a remainder of R tiles
+// would keep R clusters busy for a whole tile while the others idle (81 tiles on 74 clusters: two rounds for 1.09).
+// When at least 2R clusters exist, the R tiles from first_sk on are therefore each cut along K into
+// parts = n_clusters / R runs of whole chunks: cluster c < parts * R takes run c / R of tile first_sk + c % R, so
+// that at any time the busy clusters read the same K-slabs of neighbouring tiles (shared A and B panels in L2, as
+// in a whole round).  A run's FP32 sums go, unscaled, to slot c of the workspace (256 x 256 floats), from which
+// tf32_tail_fixup_kernel adds a tile's runs in K order and applies alpha and beta.  Deterministic: the cut depends
+// on the shape and the cluster count only.
+constexpr size_t kTailSlotBytes = 256 * 256 * sizeof(float);
+constexpr size_t kTailSlotsMax = 80;   // one per cluster
+struct ChunkWork {
+  int tile, ch0, ch1;   // chunks [ch0, ch1) of this tile
+  int slot;             // < 0: the whole tile, result to C; else the workspace slot of the run
+};
+struct ChunkWorkIter {
+  int t, n_clusters, first_sk, nch, cluster, parts, tail_tiles;
+  bool tail_done;
+  __device__ __forceinline__ ChunkWorkIter(int cluster_, int n_clusters_, int first_sk_, int parts_, int tail_tiles_, int nch_)
+      : t(cluster_), n_clusters(n_clusters_), first_sk(first_sk_), nch(nch_), cluster(cluster_), parts(parts_),
+        tail_tiles(tail_tiles_), tail_done(false) {}
+  __device__ __forceinline__ bool next(ChunkWork &w) {
+    if (t < first_sk) {
+      w.tile = t; w.ch0 = 0; w.ch1 = nch; w.slot = -1;
+      t += n_clusters;
+      return true;
+    }
+    if (!tail_done && parts > 0 && cluster < parts * tail_tiles) {
+      tail_done = true;
+      const int run = cluster / tail_tiles;
+      w.tile = first_sk + cluster % tail_tiles;
+      w.ch0 = (int)((long long)run * nch / parts);
+      w.ch1 = (int)((long long)(run + 1) * nch / parts);
+      w.slot = cluster;
+      return w.ch1 > w.ch0;
+    }
+    return false;
+  }
+};
+
+// The warp's 32 x 128 sums, unscaled, to the workspace tile at (x0, y0) of the tensor map tmW, through its staging area.
+__device__ __forceinline__ void chunk_store_raw(const CUtensorMap *tmW, unsigned char *stg, const float (&acc)[128], int x0,
+                                                int y0, int lane) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      *reinterpret_cast<float4 *>(stg + lane * 128 + ((k ^ (lane & 7)) << 4)) =
+          make_float4(acc[c * 32 + 4 * k], acc[c * 32 + 4 * k + 1], acc[c * 32 + 4 * k + 2], acc[c * 32 + 4 * k + 3]);
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmW, stg, x0 + c * 32, y0);
+      bulk_commit_group();
+      bulk_wait_read_all();
+    }
+    __syncwarp();
+  }
+}
+
+// One thread per four columns of a tail tile: adds the tile's runs in K order, C = alpha*sum + beta*C.
+__global__ void __launch_bounds__(256) tf32_tail_fixup_kernel(const Tf32Args p, const float *__restrict__ ws, int first_sk,
+                                                             int parts, int tail_tiles, int nch) {
+  const int j = blockIdx.y;   // tail tile
+  int m0, n0;
+  pair_tile_origin(p, first_sk + j, 0, m0, n0);
+  const int idx = blockIdx.x * 256 + threadIdx.x;   // 0 .. 256*64-1
+  const int r = idx >> 6, c4 = (idx & 63) * 4;
+  const int row = m0 + r, col = n0 + c4;
+  if (row >= p.M || col >= p.N) return;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  bool first = true;
+  for (int run = 0; run < parts; ++run) {
+    if ((long long)(run + 1) * nch / parts <= (long long)run * nch / parts) continue;   // an empty run
+    const int slot = run * tail_tiles + j;
+    const float4 v = *reinterpret_cast<const float4 *>(ws + ((size_t)slot * 256 + r) * 256 + c4);
+    if (first) sum = v;
+    else { sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y); sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w); }
+    first = false;
+  }
+  float *cp = p.C + (size_t)row * p.ldc + col;
+  const float s4[4] = {sum.x, sum.y, sum.z, sum.w};
+  if (p.vec_c && col + 3 < p.N) {
+    float4 o;
+    if (p.beta != 0.f) {
+      const float4 cc = *reinterpret_cast<const float4 *>(cp);
+      o.x = __fmaf_rn(p.alpha, sum.x, __fmul_rn(p.beta, cc.x));
+      o.y = __fmaf_rn(p.alpha, sum.y, __fmul_rn(p.beta, cc.y));
+      o.z = __fmaf_rn(p.alpha, sum.z, __fmul_rn(p.beta, cc.z));
+      o.w = __fmaf_rn(p.alpha, sum.w, __fmul_rn(p.beta, cc.w));
+    } else {
+      o.x = __fmul_rn(p.alpha, sum.x); o.y = __fmul_rn(p.alpha, sum.y); o.z = __fmul_rn(p.alpha, sum.z); o.w = __fmul_rn(p.alpha, sum.w);
+    }
+    *reinterpret_cast<float4 *>(cp) = o;
+  } else {
+    for (int e = 0; e < 4; ++e)
+      if (col + e < p.N) cp[e] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, s4[e], __fmul_rn(p.beta, cp[e])) : __fmul_rn(p.alpha, s4[e]);
+  }
+}
+
 constexpr int kChunkThreads = 320;   // TMA producer, MMA issuer, eight epilogue warps
 constexpr int kChunkSmem = 1024 + PairCfg<0>::kStages * PairCfg<0>::kStage + 8 * 4096 + 256;   // ring, 4 KB of staging per epilogue warp, barriers
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kChunkThreads, 1)
 sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                  const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
-                                 const __grid_constant__ CUtensorMap tmC, const Tf32Args p, int n_tiles, int chunk) {
+                                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmW,
+                                 const Tf32Args p, int first_sk, int tail_parts, int tail_tiles, int chunk) {
   using PC = PairCfg<0>;
   constexpr int S = PC::kStages, kTA = PC::kTA, kTB = PC::kTB, kStage = PC::kStage;
   extern __shared__ unsigned char smem_raw[];
@@ -1117,7 +1218,7 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
   const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  const int nkb = (p.K + 31) / 32;
+  const int nkb = (p.K + 31) / 32, nch = (nkb + chunk - 1) / chunk;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -1137,6 +1238,7 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
     tma_prefetch_desc(&tmBh);
     tma_prefetch_desc(&tmBl);
     tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmW);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -1154,10 +1256,13 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+      ChunkWorkIter work(cluster, n_clusters, first_sk, tail_parts, tail_tiles, nch);
+      ChunkWork w;
+      while (ok && work.next(w)) {
         int m0, n0;
-        pair_tile_origin(p, t, rank, m0, n0);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        pair_tile_origin(p, w.tile, rank, m0, n0);
+        const int kb_end = min(w.ch1 * chunk, nkb);
+        for (int kb = w.ch0 * chunk; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(&empty[s], ((it / S) & 1u) ^ 1u)) {
             pair_abort(abort_flag);
@@ -1180,8 +1285,10 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
       constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
       uint32_t it = 0, g = 0;
       bool ok = true;
-      for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
-        for (int kb0 = 0; kb0 < nkb && ok; kb0 += chunk, ++g) {
+      ChunkWorkIter work(cluster, n_clusters, first_sk, tail_parts, tail_tiles, nch);
+      ChunkWork w;
+      while (ok && work.next(w)) {
+        for (int kb0 = w.ch0 * chunk; kb0 < min(w.ch1 * chunk, nkb) && ok; kb0 += chunk, ++g) {
           const uint32_t buf = g & 1u;
           // the epilogue warps of both CTAs have read this buffer (two chunks ago)
           if (!mbar_wait(&acc_empty[buf], ((g >> 1) & 1u) ^ 1u)) {
@@ -1225,14 +1332,17 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
     uint64_t *cb = &c_bar[warp - 2];
     uint32_t g = 0, c_phase = 0;
     bool ok = true;
-    for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+    ChunkWorkIter work(cluster, n_clusters, first_sk, tail_parts, tail_tiles, nch);
+    ChunkWork w;
+    while (ok && work.next(w)) {
       int m0, n0;
-      pair_tile_origin(p, t, rank, m0, n0);
+      pair_tile_origin(p, w.tile, rank, m0, n0);
       const int row0 = m0 + q * 32, colw = n0 + h * 128;   // this warp's 32 rows x 128 columns
+      const int kb_first = w.ch0 * chunk, kb_end = min(w.ch1 * chunk, nkb);
       float acc[128];
-      for (int kb0 = 0; kb0 < nkb; kb0 += chunk, ++g) {
+      for (int kb0 = kb_first; kb0 < kb_end; kb0 += chunk, ++g) {
         const uint32_t buf = g & 1u;
-        if (kb0 + chunk >= nkb && lane == 0) chunk_fetch_c(p, &tmC, stg, cb, row0, colw);
+        if (w.slot < 0 && kb0 + chunk >= kb_end && lane == 0) chunk_fetch_c(p, &tmC, stg, cb, row0, colw);
         // one lane polls (the barrier words share the shared-memory pipe with the MMAs' operand reads); the
         // others then look once for themselves
         bool done = false;
@@ -1251,7 +1361,7 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
           break;
         }
         tc_fence_after();
-        chunk_drain(tmem_base + buf * 256u + (uint32_t)(h * 128) + ((uint32_t)(q * 32) << 16), kb0 == 0, acc);
+        chunk_drain(tmem_base + buf * 256u + (uint32_t)(h * 128) + ((uint32_t)(q * 32) << 16), kb0 == kb_first, acc);
         // this warp's reads of the buffer are complete: hand it back
         tc_fence_before();
         __syncwarp();
@@ -1261,7 +1371,9 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
         }
       }
       if (!ok) break;
-      if (!chunk_store(p, &tmC, stg, cb, c_phase, acc, row0, colw, lane)) {
+      if (w.slot >= 0) {
+        chunk_store_raw(&tmW, stg, acc, h * 128, w.slot * 256 + (int)rank * 128 + q * 32, lane);
+      } else if (!chunk_store(p, &tmC, stg, cb, c_phase, acc, row0, colw, lane)) {
         pair_abort(abort_flag);
         break;
       }
@@ -1441,16 +1553,23 @@ static std::atomic<int> g_tf32_tile_n{0};  // 0: automatic; 128 or 256 pins the 
 static std::atomic<int> g_tf32_slab_k{32}; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 static std::atomic<int> g_tf32_persistent{1};  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
 static std::atomic<float> g_tf32_ft_bias{-1.f};  // < 0: default
+static std::atomic<int> g_tf32_tail{1};    // 1: the last round of the chunked CTA-pair kernel is shared out in chunks over all clusters
 constexpr int kDefaultChunk = 16;
 static std::atomic<int> g_tf32_chunk{kDefaultChunk};  // plain SGEMM: K-slabs per accumulation chunk (0: one accumulation over all of K)
 static std::atomic<int> g_tf32_pair{1};    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
 // (8 rows per 256 columns of B, x kp); every plane starts on a 1 KB boundary.
-size_t tf32_workspace_bytes(int M, int N, int K) {
+static size_t tf32_planes_bytes(int M, int N, int K) {
   const size_t kp = ((size_t)K + 3) & ~(size_t)3;
   const size_t srows = (((size_t)N + 255) / 256) * 8;
   return (2 * (size_t)M * kp + 2 * (size_t)N * kp + srows * kp) * sizeof(float) + 8 * 1024;
+}
+// ... plus, for the K that chunked accumulation applies to by default, the slots that the tail tiles' runs go
+// through (one 256 x 256 tile per cluster, 80 clusters at most); a caller-supplied workspace without them is
+// accepted and the last round then runs tile by tile.
+size_t tf32_workspace_bytes(int M, int N, int K) {
+  return tf32_planes_bytes(M, N, K) + (K > 1024 ? kTailSlotsMax * kTailSlotBytes + 1024 : 0);
 }
 
 template <int TBN, int TBK, int FT>
@@ -1515,7 +1634,10 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (M == 0 || N == 0) return B2_OK;
   // nothing for the tensor cores to do: the FFMA path's scaling pass covers it
   if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s);
-  int st = ensure_workspace(ctx, tf32_workspace_bytes(M, N, K), s);
+  // the planes are needed; the slots of the tail tiles only let the last round be shared out
+  bool tail_slots = ft == nullptr && K > 1024;
+  if (tail_slots && ctx->ws && !ctx->ws_owned && ctx->ws_bytes < tf32_workspace_bytes(M, N, K)) tail_slots = false;
+  int st = ensure_workspace(ctx, tail_slots ? tf32_workspace_bytes(M, N, K) : tf32_planes_bytes(M, N, K), s);
   if (st != B2_OK) return st;
   const int ftm = ft ? kFtCuda : 0;
   FtArgs ftl;
@@ -1587,6 +1709,8 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   // Chunked accumulation (plain calls with more than two chunks of K-slabs, no pinned width): two forms exist, the
   // persistent CTA-pair kernel and single-CTA 128 x 128 tiles; whole waves decide between them as above.
   const int chunk = g_tf32_chunk.load();
+  int tail_parts = 0;   // >= 2: each tile from tail_first on is cut along K into that many runs on different clusters
+  int tail_first = pairs;
   const bool chunked = ft == nullptr && chunk > 0 && (K + 31) / 32 > 2 * chunk && tbk == 32 && !pinned;
   if (chunked) {
     const bool pair_ok = g_tf32_pair != 0 && slots > 0 && g_tf32_persistent != 0;
@@ -1596,7 +1720,22 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
       else if (g_tf32_tiles[t].tbn == 128 && g_tf32_tiles[t].tbk == 32) cost_single = g_tf32_tiles[t].cost;
     }
     const double tiles128 = (double)((M + 127) / 128) * ((N + 127) / 128);
-    use_pair = pair_ok && (g_tf32_pair == 2 || cost_pair * ceil((double)pairs / (double)slots) <= cost_single * ceil(tiles128 / (double)ctx->sm_count));
+    double pair_rounds = pair_ok ? ceil((double)pairs / (double)slots) : 0.0;
+    if (pair_ok) {
+      // the last round shared out in chunks (see ChunkWorkIter): worth it when it saves more K-slabs of time than
+      // the parts' trip through the workspace costs
+      const int nkb = (K + 31) / 32, nch = (nkb + chunk - 1) / chunk, rem = pairs % slots;
+      const int parts = rem > 0 ? (slots / rem < nch ? slots / rem : nch) : 0;
+      if (tail_slots && g_tf32_tail.load() != 0 && parts >= 2 && (size_t)slots <= kTailSlotsMax) {
+        const int longest = (nch + parts - 1) / parts;   // chunks of the longest run
+        if ((nch - longest) * chunk >= 32) {
+          tail_parts = parts;
+          tail_first = pairs - rem;
+          pair_rounds = (double)(pairs / slots) + (double)longest / (double)nch;
+        }
+      }
+    }
+    use_pair = pair_ok && (g_tf32_pair == 2 || cost_pair * pair_rounds <= cost_single * ceil(tiles128 / (double)ctx->sm_count));
   }
   if (use_pair) {
     st = make_tmap_2d(&maps[2], Bh, (uint64_t)K, (uint64_t)N, (uint64_t)kp, 32, 128, swz);
@@ -1623,15 +1762,26 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     if (chunked) {
       st = ensure_func_attributes((const void *)sgemm_3xtf32_pair_chunked_kernel, ctx->device, kChunkSmem);
       if (st != B2_OK) return st;
-      const int clusters = pairs < slots ? pairs : (slots > 0 ? slots : pairs);
-      CUtensorMap map_c = maps[0];
+      const int clusters = tail_parts > 0 ? slots : (pairs < slots ? pairs : (slots > 0 ? slots : pairs));
+      CUtensorMap map_c = maps[0], map_w = maps[0];
       if (N < 4) pa.vec_c = 0;
       if (pa.vec_c) {
         st = make_tmap_2d(&map_c, C, (uint64_t)(N & ~3), (uint64_t)M, (uint64_t)ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != B2_OK) return st;
       }
-      sgemm_3xtf32_pair_chunked_kernel<<<2 * clusters, kChunkThreads, kChunkSmem, s>>>(maps[0], maps[1], maps[2], maps[3], map_c, pa, pairs, chunk);
+      float *tail_ws = (float *)(w + 2 * align1k(a_elems * 4) + 2 * align1k(b_elems * 4) + align1k((size_t)srows * kp * 4));
+      if (tail_parts > 0) {
+        st = make_tmap_2d(&map_w, tail_ws, 256, (uint64_t)clusters * 256, 256, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != B2_OK) return st;
+      }
+      sgemm_3xtf32_pair_chunked_kernel<<<2 * clusters, kChunkThreads, kChunkSmem, s>>>(maps[0], maps[1], maps[2], maps[3], map_c, map_w, pa,
+                                                                                       tail_first, tail_parts, pairs - tail_first, chunk);
       B2_CUDA(cudaGetLastError());
+      if (tail_parts > 0) {
+        const int nch = ((K + 31) / 32 + chunk - 1) / chunk;
+        tf32_tail_fixup_kernel<<<dim3(64, pairs - tail_first), 256, 0, s>>>(pa, tail_ws, tail_first, tail_parts, pairs - tail_first, nch);
+        B2_CUDA(cudaGetLastError());
+      }
       return B2_OK;
     }
     if (g_tf32_persistent) {
@@ -1741,6 +1891,13 @@ int b2_set_tf32_abft_bias(float bias) {
 int b2_set_tf32_chunk(int slabs) {
   B2_REQUIRE(slabs <= 4096, B2_ERR_INVALID_ARG, "b2_set_tf32_chunk: %d is not in 0..4096 (or negative for the default)", slabs);
   b2::g_tf32_chunk = slabs < 0 ? b2::kDefaultChunk : slabs;
+  return B2_OK;
+}
+// 1 (default): the last, partial round of the chunked CTA-pair kernel is shared out in chunks over all clusters
+// (parts through the workspace, added in K order); 0: tile by tile.
+int b2_set_tf32_tail_split(int on) {
+  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_tf32_tail_split: %d is not 0 or 1", on);
+  b2::g_tf32_tail = on;
   return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.

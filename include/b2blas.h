@@ -348,6 +348,14 @@ int b2_set_tf32_persistent(int on);
  * default) and no pinned tile width; 0: one accumulation over all of K; negative: the default.  No counterpart in
  * the reference. */
 int b2_set_tf32_chunk(int slabs);
+/* 1 (default): when the tiles of a chunked CTA-pair call leave at least half of the clusters idle in the last round,
+ * each tile of that round is cut along K into runs of whole chunks on different clusters; the runs' sums go through
+ * the workspace and a second kernel adds them in K order and applies alpha and beta (deterministic for a given shape
+ * and device; identical to the uncut result when every run is one chunk, else different in the last bits).  A
+ * caller-supplied workspace smaller than b2_sgemm_workspace_bytes() but large enough for the operand planes is
+ * accepted, and the last round then runs tile by tile.  0: every tile on one cluster.  No counterpart in the
+ * reference. */
+int b2_set_tf32_tail_split(int on);
 /* The tensor cores add each MMA's products to the accumulator with truncation, which costs an accumulator a
  * fraction of its value per K-slab of 32 (about 4e-7 on B200, the built-in figure; the same for uniform and normal
  * operands of any scale).  The CUDA-core checksums keep, beside each checksum, its sum over the K-slabs, and the

@@ -322,6 +322,7 @@ def test_3xtf32_chunked_forms_agree_bit_for_bit(cuda, shape, alpha, beta, chunk)
     a, b, c = mats(M, N, K)
     try:
         b2.set_tf32_chunk(chunk)
+        b2.set_tf32_tail_split(0)      # every tile on one cluster: one chain of chunk sums per output in both forms
         b2.set_tf32_pair(2)
         pair = run_gpu(1, a, b, c, alpha, beta)
         b2.set_tf32_pair(0)
@@ -329,9 +330,37 @@ def test_3xtf32_chunked_forms_agree_bit_for_bit(cuda, shape, alpha, beta, chunk)
     finally:
         b2.set_tf32_pair(1)
         b2.set_tf32_chunk(-1)
+        b2.set_tf32_tail_split(1)
     assert np.array_equal(pair, single)
     c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
     assert oracle.gemm_error(pair, c64, den) <= 0.25 * TOL_3XTF32
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 8192), (2304, 2304, 2304), (256, 300, 4100), (3328, 3300, 2047), (513, 260, 4096),
+                                   (4096, 4096, 1200)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.5), (-1.5, 0.0)])
+def test_3xtf32_last_round_cut_along_k(cuda, shape, alpha, beta):
+    """When the tiles do not fill the last round of clusters, each tile of that round is cut along K into runs of
+    whole chunks on different clusters, whose sums go through the workspace and are added in K order.  Same result as
+    tile by tile up to the order of a few FP32 additions (identical when every run is one chunk), and the same twice."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    out = {}
+    try:
+        b2.set_tf32_pair(2)
+        for tail in (1, 0, 1):
+            b2.set_tf32_tail_split(tail)
+            out.setdefault(tail, []).append(run_gpu(1, a, b, c, alpha, beta))
+    finally:
+        b2.set_tf32_pair(1)
+        b2.set_tf32_tail_split(1)
+    assert np.array_equal(out[1][0], out[1][1])                 # deterministic
+    c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
+    assert oracle.gemm_error(out[1][0], c64, den) <= 0.25 * TOL_3XTF32
+    assert float(np.max(np.abs(out[1][0].astype(np.float64) - out[0][0]) / den)) <= 2e-7
+    if shape == (2304, 2304, 2304):                             # five runs of one chunk each: the same chain of additions
+        assert np.array_equal(out[1][0], out[0][0])
 
 
 @pytest.mark.parametrize("pair", [2, 0])
