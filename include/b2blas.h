@@ -56,7 +56,9 @@ int b2_version(void);
 int b2_create(b2_handle *out);
 int b2_destroy(b2_handle h);
 int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
-/* Bytes of workspace an MxNxK problem uses.  path = B2_PATH_3XTF32: required (hi/lo planes of A and B).
+/* Bytes of workspace an MxNxK problem uses.  path = B2_PATH_3XTF32: the hi/lo planes of A and B are required; for
+ * K > 1024 the figure includes 20 MB of slots that let a partial last round of tiles be cut along K (see
+ * b2_set_tf32_tail_split), and a caller-supplied workspace without them is accepted.
  * path = B2_PATH_FFMA: optional; when that much scratch is there (or the handle may grow its own) a
  * row-major A is transposed into it first, which makes large products about 3 % faster; 0 when the
  * pass would not pay or would need more than 1 GiB.  Results are bit-identical either way. */
@@ -134,8 +136,10 @@ int ft_sgemm(int M, int N, int K, float alpha, const float *A, const float *B, f
  * than 0.75*tau from its recomputed value is replaced.  Default tau there is 2.5e-6*K: five times the largest
  * residual of clean products (4.7e-7*K for K = 256..8192) and half the path's accuracy bound of
  * 2e-5*sum_k|a||b| (5e-6*K for operands uniform in [-1, 1)), so a fault that would break that bound is always
- * found and repaired.  Operands that are all of one sign make the tensor cores' loss coherent (the plain 3xTF32
- * product itself then drifts to 1e-4 at K = 8192): use the FFMA path for such data.
+ * found and repaired.  Operands that are all of one sign make the tensor cores' loss coherent; the plain 3xTF32
+ * product bounds it with chunked accumulation (b2_set_tf32_chunk), this form accumulates over all of K in one go
+ * and raises alarms on such data at K beyond about 2000 (every alarmed group is then recomputed in FP32: correct,
+ * slow): use the FFMA path's ABFT for it.
  * Needs the workspace of b2_sgemm_workspace_bytes(B2_PATH_3XTF32, ...). */
 int b2_ft_sgemm(b2_handle h, int path, int M, int N, int K, float alpha, const float *A, int lda,
                 const float *B, int ldb, float beta, float *C, int ldc, const b2_fault *plan_dev,
