@@ -1572,6 +1572,27 @@ size_t tf32_workspace_bytes(int M, int N, int K) {
   return tf32_planes_bytes(M, N, K) + (K > 1024 ? kTailSlotsMax * kTailSlotBytes + 1024 : 0);
 }
 
+// How the chunked CTA-pair kernel treats `tiles` tiles on `clusters` clusters with `nkb` K-slabs in chunks of `chunk`:
+// whole rounds for the tiles below *first; when the remaining R tiles would leave at least half of the clusters
+// idle and the cut saves 32 K-slabs or more of time, each of them in *parts runs of whole chunks (run r = chunks
+// [r*nch/parts, (r+1)*nch/parts), none empty; the longest has *longest chunks) on clusters r*R + j.  False: no cut.
+bool tf32_tail_plan(int tiles, int clusters, int nkb, int chunk, int *first, int *parts, int *longest) {
+  *first = tiles;
+  *parts = 0;
+  *longest = 0;
+  if (tiles <= 0 || clusters <= 0 || chunk <= 0 || nkb <= 0) return false;
+  const int nch = (nkb + chunk - 1) / chunk, rem = tiles % clusters;
+  if (rem == 0) return false;
+  const int p = clusters / rem < nch ? clusters / rem : nch;
+  if (p < 2) return false;
+  const int lg = (nch + p - 1) / p;
+  if ((nch - lg) * chunk < 32) return false;
+  *first = tiles - rem;
+  *parts = p;
+  *longest = lg;
+  return true;
+}
+
 template <int TBN, int TBK, int FT>
 static int launch_tf32(const Context *ctx, const CUtensorMap *maps, const Tf32Args &args, int grid, cudaStream_t s) {
   int st = ensure_func_attributes((const void *)sgemm_3xtf32_kernel<TBN, TBK, FT>, ctx->device, Tf32Cfg<TBN, TBK, FT>::kSmem);
@@ -1722,17 +1743,13 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     const double tiles128 = (double)((M + 127) / 128) * ((N + 127) / 128);
     double pair_rounds = pair_ok ? ceil((double)pairs / (double)slots) : 0.0;
     if (pair_ok) {
-      // the last round shared out in chunks (see ChunkWorkIter): worth it when it saves more K-slabs of time than
-      // the parts' trip through the workspace costs
-      const int nkb = (K + 31) / 32, nch = (nkb + chunk - 1) / chunk, rem = pairs % slots;
-      const int parts = rem > 0 ? (slots / rem < nch ? slots / rem : nch) : 0;
-      if (tail_slots && g_tf32_tail.load() != 0 && parts >= 2 && (size_t)slots <= kTailSlotsMax) {
-        const int longest = (nch + parts - 1) / parts;   // chunks of the longest run
-        if ((nch - longest) * chunk >= 32) {
-          tail_parts = parts;
-          tail_first = pairs - rem;
-          pair_rounds = (double)(pairs / slots) + (double)longest / (double)nch;
-        }
+      int parts = 0, first = pairs, longest = 0;
+      if (tail_slots && g_tf32_tail.load() != 0 && (size_t)slots <= kTailSlotsMax &&
+          tf32_tail_plan(pairs, slots, (K + 31) / 32, chunk, &first, &parts, &longest)) {
+        tail_parts = parts;
+        tail_first = first;
+        const int nch = ((K + 31) / 32 + chunk - 1) / chunk;
+        pair_rounds = (double)(pairs / slots) + (double)longest / (double)nch;
       }
     }
     use_pair = pair_ok && (g_tf32_pair == 2 || cost_pair * pair_rounds <= cost_single * ceil(tiles128 / (double)ctx->sm_count));
@@ -1899,6 +1916,16 @@ int b2_set_tf32_tail_split(int on) {
   B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_tf32_tail_split: %d is not 0 or 1", on);
   b2::g_tf32_tail = on;
   return B2_OK;
+}
+// The cut of the last round for a given tile and cluster count (see b2_set_tf32_tail_split): returns 1 and the first
+// cut tile, the runs per tile and the chunks of the longest run, or 0.  For tests and tools.
+int b2_tf32_tail_plan(int tiles, int clusters, int K, int chunk_slabs, int *first, int *parts, int *longest) {
+  int f = 0, p = 0, l = 0;
+  const bool cut = K > 0 && b2::tf32_tail_plan(tiles, clusters, (K + 31) / 32, chunk_slabs, &f, &p, &l);
+  if (first) *first = f;
+  if (parts) *parts = p;
+  if (longest) *longest = l;
+  return cut ? 1 : 0;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.
 int b2_set_tf32_slab_k(int k) {

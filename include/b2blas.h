@@ -360,6 +360,10 @@ int b2_set_tf32_chunk(int slabs);
  * accepted, and the last round then runs tile by tile.  0: every tile on one cluster.  No counterpart in the
  * reference. */
 int b2_set_tf32_tail_split(int on);
+/* The cut that b2_set_tf32_tail_split(1) makes for `tiles` 256 x 256 tiles on `clusters` clusters and a K loop of K in
+ * chunks of `chunk_slabs` K-slabs: returns 1 and the first cut tile, the runs per tile and the chunks of the longest
+ * run (any of the three pointers may be NULL), or 0 when the last round is left whole.  For tests and tools. */
+int b2_tf32_tail_plan(int tiles, int clusters, int K, int chunk_slabs, int *first, int *parts, int *longest);
 /* The tensor cores add each MMA's products to the accumulator with truncation, which costs an accumulator a
  * fraction of its value per K-slab of 32 (about 4e-7 on B200, the built-in figure; the same for uniform and normal
  * operands of any scale).  The CUDA-core checksums keep, beside each checksum, its sum over the K-slabs, and the

@@ -111,6 +111,41 @@ def test_partition_helpers_need_no_device(L):
     assert L.b2_mg_k_panel(5, 0, 4, C.byref(k0), C.byref(kw)) == 5 and (k0.value, kw.value) == (4, 1)   # panel < 1 means 1
 
 
+def test_tail_plan_of_the_3xtf32_path(L):
+    """b2_tf32_tail_plan: when the tiles of the last round leave at least half of the clusters idle, each of them is cut
+    into `parts` non-empty runs of whole chunks that cover the K loop once, on parts * R distinct clusters."""
+    first, parts, longest = C.c_int(), C.c_int(), C.c_int()
+    ref = lambda: (first.value, parts.value, longest.value)
+    cases = 0
+    for clusters in (74, 66, 8):
+        for tiles in list(range(1, 3 * clusters + 2)) + [576, 1024]:
+            for K in (1100, 2304, 4096, 8192, 16384):
+                for chunk in (16, 8, 3):
+                    cut = L.b2_tf32_tail_plan(tiles, clusters, K, chunk, C.byref(first), C.byref(parts), C.byref(longest))
+                    nkb = (K + 31) // 32
+                    nch = (nkb + chunk - 1) // chunk
+                    rem = tiles % clusters
+                    if not cut:
+                        assert ref() == (tiles, 0, 0)
+                        want = min(clusters // rem, nch) if rem else 0
+                        assert want < 2 or (nch - (nch + want - 1) // want) * chunk < 32
+                        continue
+                    cases += 1
+                    f, p, lg = ref()
+                    assert f == tiles - rem and f % clusters == 0 and 2 <= p <= nch and p * rem <= clusters
+                    runs = [(r * nch // p, (r + 1) * nch // p) for r in range(p)]
+                    assert runs[0][0] == 0 and runs[-1][1] == nch
+                    assert all(b > a for a, b in runs) and all(runs[i][1] == runs[i + 1][0] for i in range(p - 1))
+                    assert max(b - a for a, b in runs) == lg and (nch - lg) * chunk >= 32
+    assert cases > 1000
+    # the shapes quoted in the design notes, on the 74 clusters of a B200
+    assert L.b2_tf32_tail_plan(81, 74, 2304, 16, C.byref(first), C.byref(parts), C.byref(longest)) == 1 and ref() == (74, 5, 1)
+    assert L.b2_tf32_tail_plan(256, 74, 4096, 16, C.byref(first), C.byref(parts), C.byref(longest)) == 1 and ref() == (222, 2, 4)
+    assert L.b2_tf32_tail_plan(576, 74, 6144, 16, C.byref(first), C.byref(parts), C.byref(longest)) == 0      # 58 of 74 busy
+    assert L.b2_tf32_tail_plan(4, 74, 16384, 16, None, C.byref(parts), None) == 1 and parts.value == 18
+    assert L.b2_tf32_tail_plan(0, 74, 4096, 16, None, None, None) == 0 and L.b2_tf32_tail_plan(5, 74, 0, 16, None, None, None) == 0
+
+
 def test_new_entry_points_validate_before_touching_a_device(L):
     null = C.c_void_p(None)
     plan = C.c_void_p()
