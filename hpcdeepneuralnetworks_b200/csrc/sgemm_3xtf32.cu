@@ -21,11 +21,16 @@
 //                            stages half of the A rows and half of the B columns (64 KB per slab, 3
 //                            stages), the leader issues MMAs of M = 256 over both CTAs' tiles.  The
 //                            form chosen for large problems; same warp roles, same epilogue.
-//   sgemm_3xtf32_pair_persistent_kernel  the default for large problems: as many clusters as the device
-//                            holds, each walking several 256 x 256 tiles with the accumulator double-buffered
-//                            in tensor memory; plain and ABFT (CUDA-core checksums) forms.
-// The one-tile kernels have ABFT forms with the checksums on the tensor cores or on the CUDA cores
-// (template FT); verification and repair sit in the shared epilogue.
+//   sgemm_3xtf32_pair_persistent_kernel  as many clusters as the device holds, each walking several 256 x 256
+//                            tiles with the accumulator double-buffered in tensor memory; plain (K <= 1024)
+//                            and ABFT (CUDA-core checksums) forms.
+//   sgemm_3xtf32_pair_chunked_kernel, sgemm_3xtf32_chunked_kernel  the default for plain calls with K > 1024:
+//                            the K loop in chunks of 16 slabs whose sums the epilogue warps add up in FP32
+//                            registers (bounds the tensor cores' truncation loss whatever K), C in and out by
+//                            TMA; the pair form is persistent and cuts a partial last round of tiles along K
+//                            (tf32_tail_fixup_kernel adds the runs).
+// The one-tile kernels and the persistent kernel have ABFT forms with the checksums on the CUDA cores (template
+// FT); verification and repair sit in the shared epilogue.
 // Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
 #include <math.h>
 #include <stdlib.h>
