@@ -152,6 +152,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32
   return false;
 }
 
+// After a wait has run out somewhere in the CTA: the thread that issued the ring's TMA loads waits, with a short
+// bound, for the (at most `stages`) loads that may still be in flight to land, so that nothing is being written
+// into the CTA's shared memory when it leaves.  `issued` counts the stages that thread has filled so far.
+__device__ __forceinline__ void ring_settle(uint64_t *full, int stages, uint32_t issued) {
+  const uint32_t first = issued > (uint32_t)stages ? issued - (uint32_t)stages : 0u;
+  for (uint32_t j = first; j < issued; ++j) (void)mbar_wait(&full[j % stages], (j / stages) & 1u, 1u << 18, 100000000ull);
+}
+
 // A bounded wait ran out in the launch numbered `seq`: record it (status[0] sticky for b2_check_status, status[1]
 // the number of the launch, which lets the launch's remaining CTAs leave at once).
 __device__ __forceinline__ void record_timeout(int *status, unsigned int seq) {

@@ -459,6 +459,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  uint32_t issued = 0;   // the producer thread: stages it has filled so far
 
   if (warp == 0) {
     // ---- TMA producer -----------------------------------------------------------------
@@ -471,6 +472,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
         }
         unsigned char *st = smem + s * kTStage;
         mbar_expect_tx(&full[s], kTStage);
+        issued = (uint32_t)kb + 1u;
         tma_load_2d(st, &tmAh, &full[s], kb * TBK, m0);
         tma_load_2d(st + kTA, &tmAl, &full[s], kb * TBK, m0);
         {
@@ -552,6 +554,10 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag) {   // the same answer in every thread: read after the barrier
+    if (tid == 0) ring_settle(full, TSTAGES, issued);
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -567,6 +573,15 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
 // the leader's "full" barrier; the leader's commits free the stage in both CTAs.
 // FT: both CTAs stage the tile's S rows; their checksum warps cover their own 128 accumulator rows.
 constexpr int kPairBand = 8;   // tile rows per band of the pair kernel's tile order
+// End of a pair kernel, after the cluster barrier that follows the roles: if a wait ran out anywhere in the pair
+// (the leader's flag is set from both CTAs, and both read it here, so they take the same branch), the leader's
+// producer thread lets the loads that signal its "full" barriers land before either CTA leaves.
+__device__ __forceinline__ void pair_settle(volatile int *abort_flag, uint64_t *full, int stages, uint32_t issued, uint32_t rank,
+                                            int tid) {
+  if (ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(abort_flag)), 0)) == 0) return;
+  if (rank == 0 && tid == 0) ring_settle(full, stages, issued);
+  cluster_sync_all();
+}
 template <int FT>
 struct PairCfg {
   static constexpr int kTA = TBM * 32 * 4;           // bytes per A plane tile (128 rows)
@@ -634,6 +649,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   // an earlier CTA of this launch timed out: both CTAs of the pair skip the work (tensor memory is still freed below)
   const bool aborted = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(gate)), 0)) != 0;
 
+  uint32_t issued = 0;   // the producer thread: stages it has filled so far
   if (aborted) {
   } else if (warp == 0) {
     // ---- TMA producer (one per CTA) ------------------------------------------------------
@@ -647,6 +663,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
         unsigned char *st = smem + s * kStage;
         const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
         if (rank == 0) mbar_expect_tx(&full[s], 2 * kStage);   // the bytes of both CTAs
+        issued = (uint32_t)kb + 1u;
         tma_load_2d_pair(st, &tmAh, leader_full, kb * 32, m0);
         tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
         tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
@@ -729,6 +746,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
   // neither CTA leaves (or frees tensor memory) while the other may still be read by an MMA
   tc_fence_before();
   cluster_sync_all();
+  pair_settle(abort_flag, full, S, issued, rank, tid);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, PC::kTmemCols);
@@ -825,6 +843,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
   // an earlier CTA of this launch timed out: both CTAs of the pair skip the work (tensor memory is still freed below)
   const bool aborted = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(gate)), 0)) != 0;
 
+  uint32_t issued = 0;   // the producer thread: stages it has filled so far
   if (aborted) {
   } else if (warp == 0) {
     // ---- TMA producer (one per CTA): one slab counter across all of this cluster's tiles ------
@@ -844,6 +863,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
           unsigned char *st = smem + s * kStage;
           const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
           if (rank == 0) mbar_expect_tx(&full[s], 2 * kStage);
+          issued = it + 1u;
           tma_load_2d_pair(st, &tmAh, leader_full, kb * 32, m0);
           tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
           tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
@@ -970,6 +990,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
 
   tc_fence_before();
   cluster_sync_all();
+  pair_settle(abort_flag, full, S, issued, rank, tid);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, 512);
@@ -1255,6 +1276,7 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
   const uint32_t tmem_base = *tmem_slot;
   const bool aborted = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<const int *>(gate)), 0)) != 0;
 
+  uint32_t issued = 0;   // the producer thread: stages it has filled so far
   if (aborted) {
   } else if (warp == 0) {
     // ---- TMA producer (one per CTA): one slab counter across all of this cluster's tiles ------
@@ -1277,6 +1299,7 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
           unsigned char *st = smem + s * kStage;
           const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
           if (rank == 0) mbar_expect_tx(&full[s], 2 * kStage);
+          issued = it + 1u;
           tma_load_2d_pair(st, &tmAh, leader_full, kb * 32, m0);
           tma_load_2d_pair(st + kTA, &tmAl, leader_full, kb * 32, m0);
           tma_load_2d_pair(st + 2 * kTA, &tmBh, leader_full, kb * 32, n0 + (int)rank * 128);
@@ -1388,6 +1411,7 @@ sgemm_3xtf32_pair_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const
 
   tc_fence_before();
   cluster_sync_all();
+  pair_settle(abort_flag, full, S, issued, rank, tid);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, 512);
@@ -1454,6 +1478,7 @@ sgemm_3xtf32_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __gr
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  uint32_t issued = 0;   // the producer thread: stages it has filled so far
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1465,6 +1490,7 @@ sgemm_3xtf32_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __gr
         }
         unsigned char *st = smem + s * kStage;
         mbar_expect_tx(&full[s], kStage);
+        issued = (uint32_t)kb + 1u;
         tma_load_2d(st, &tmAh, &full[s], kb * 32, m0);
         tma_load_2d(st + kTA, &tmAl, &full[s], kb * 32, m0);
         tma_load_2d(st + 2 * kTA, &tmBh, &full[s], kb * 32, n0);
@@ -1547,6 +1573,10 @@ sgemm_3xtf32_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __gr
 
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag) {   // the same answer in every thread: read after the barrier
+    if (tid == 0) ring_settle(full, S, issued);
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);

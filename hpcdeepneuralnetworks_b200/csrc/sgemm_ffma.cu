@@ -317,8 +317,10 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
   __syncthreads();
+  uint32_t issued = 0;   // thread 0: stages it has filled so far
   if (tid == 0) {
     for (int s = 0; s < FSTAGES && s < nkb; ++s) {
+      issued = (uint32_t)s + 1u;
       mbar_expect_tx(&full[s], kStageBytes);
       if (TRANS_A) tma_load_2d(sA + s * kStageA, &tmA, &full[s], m0, (kb0 + s) * FBK);
       else tma_load_2d(sA + s * kStageA, &tmA, &full[s], (kb0 + s) * FBK, m0);
@@ -442,6 +444,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           break;
         }
         mbar_expect_tx(&full[sp], kStageBytes);
+        issued = (uint32_t)knext + 1u;
         if (TRANS_A) tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], m0, (kb0 + knext) * FBK);
         else tma_load_2d(sA + sp * kStageA, &tmA, &full[sp], (kb0 + knext) * FBK, m0);
         tma_load_2d(sB + sp * kStageB, &tmB, &full[sp], n0, (kb0 + knext) * FBK);
@@ -454,6 +457,7 @@ sgemm_ffma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   if (!ok) {
     record_timeout(p.status, p.seq);
+    if (tid == 0) ring_settle(full, FSTAGES, issued);   // no copy in flight into this CTA's shared memory when it leaves
     return;
   }
 
