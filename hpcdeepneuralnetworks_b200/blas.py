@@ -408,6 +408,12 @@ def set_tf32_chunk(slabs: int):
     check(_lib.load().b2_set_tf32_chunk(slabs))
 
 
+def set_tf32_fused_split(mode: int):
+    """The 3xTF32 hi/lo split inside the GEMM kernel: 0 never, 1 for very small plain products (default), 2 whenever
+    the operands' alignment allows."""
+    check(_lib.load().b2_set_tf32_fused_split(mode))
+
+
 def set_tf32_tail_split(on: int):
     """1 (default): the last, partial round of tiles of a chunked CTA-pair 3xTF32 call is shared out in chunks over all
     clusters; 0: every tile on one cluster."""

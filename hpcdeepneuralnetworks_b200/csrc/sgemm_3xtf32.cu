@@ -1584,6 +1584,191 @@ sgemm_3xtf32_chunked_kernel(const __grid_constant__ CUtensorMap tmAh, const __gr
   if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
 }
 
+// ---- single-CTA form with the hi/lo split inside the kernel (plain SGEMM, very small problems) ----------
+// Three launches (two split kernels, then the GEMM) cost a small product more than its arithmetic.  Here the TMA
+// producer brings the RAW tiles of A (128 rows x 32 k, 128-byte swizzle) and B (32 k x 128 columns, as they lie in
+// the row-major B) into a two-stage ring, and the four warps that will later be the epilogue convert them, between
+// the loads and the MMAs, into the four K-major plane tiles the MMAs read: A_hi/A_lo element by element in place of
+// the same swizzled layout, B_hi/B_lo transposed on the way (thread = column of B = row of the plane tile).  Same
+// split arithmetic, same MMA order as the kernels behind the pre-pass: identical results.  Measured: a K-slab takes
+// 1.4 us here against 0.6 us behind the pre-pass - the conversion puts 2.5 times the operand bytes through the
+// SM's one shared-memory pipe (768 wavefronts of conversion + 512 of MMA operands + 256 of TMA writes per slab
+// against the MMAs' 768 cycles of tensor time) - so the launch it saves pays only up to K = 512 on one wave of tiles
+// (256^3: 23.6 us against 29.7 us); beyond that the dispatcher keeps the pre-pass, and a third raw stage or integer
+// rounding in place of cvt.rna changed nothing.
+constexpr int kFusedRaw = 2, kFusedPl = 2;
+constexpr int kFusedTile = 128 * 32 * 4;                        // bytes of one 128 x 32 (or 32 x 128) FP32 tile
+constexpr int kFusedSmem = 1024 + kFusedPl * 4 * kFusedTile + kFusedRaw * 2 * kFusedTile + 256;
+__global__ void __launch_bounds__(192, 1)
+sgemm_3xtf32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Tf32Args p) {
+  constexpr int R = kFusedRaw, P = kFusedPl, kT = kFusedTile;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char *planes = smem;                     // stage ps: A_hi, A_lo, B_hi, B_lo
+  unsigned char *raw = smem + P * 4 * kT;           // stage r: raw A, raw B
+  uint64_t *raw_full = reinterpret_cast<uint64_t *>(raw + R * 2 * kT);
+  uint64_t *raw_empty = raw_full + R;
+  uint64_t *pl_full = raw_empty + R;
+  uint64_t *pl_empty = pl_full + P;
+  uint64_t *acc_ready = pl_empty + P;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_n = (p.N + 127) / 128;
+  const int m0 = (blockIdx.x / tiles_n) * TBM, n0 = (blockIdx.x % tiles_n) * 128;
+  const int nkb = (p.K + 31) / 32;
+
+  {
+    __shared__ int launch_aborted;
+    if (threadIdx.x == 0) launch_aborted = b2::launch_aborted(p.status, p.seq) ? 1 : 0;
+    __syncthreads();
+    if (launch_aborted != 0) return;
+  }
+  if (tid == 0) {
+    for (int r = 0; r < R; ++r) {
+      mbar_init(&raw_full[r], 1);
+      mbar_init(&raw_empty[r], 4);   // the four converter warps
+    }
+    for (int s = 0; s < P; ++s) {
+      mbar_init(&pl_full[s], 4);
+      mbar_init(&pl_empty[s], 1);    // the MMA commit
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  uint32_t issued = 0;   // the producer thread: raw stages it has filled so far
+
+  if (warp == 0) {
+    // ---- TMA producer: raw tiles --------------------------------------------------------------
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int r = kb % R;
+        if (!mbar_wait(&raw_empty[r], ((uint32_t)(kb / R) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(&raw_full[r], 2 * kT);
+        issued = (uint32_t)kb + 1u;
+        tma_load_2d(raw + r * 2 * kT, &tmA, &raw_full[r], kb * 32, m0);
+        tma_load_2d(raw + r * 2 * kT + kT, &tmB, &raw_full[r], n0, kb * 32);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(TBM, 128, 0, 0);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int ps = kb % P;
+        if (!mbar_wait(&pl_full[ps], (uint32_t)(kb / P) & 1u)) {
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t st = smem_u32(planes + ps * 4 * kT);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint64_t a_hi = umma_smem_desc(st + k4 * 32, 16, 1024, 2);
+          const uint64_t a_lo = umma_smem_desc(st + kT + k4 * 32, 16, 1024, 2);
+          const uint64_t b_hi = umma_smem_desc(st + 2 * kT + k4 * 32, 16, 1024, 2);
+          const uint64_t b_lo = umma_smem_desc(st + 3 * kT + k4 * 32, 16, 1024, 2);
+          umma_tf32(tmem_base, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          umma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
+          umma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
+        }
+        umma_commit(&pl_empty[ps]);
+      }
+      if (ok) umma_commit(acc_ready);
+    }
+  } else {
+    // ---- warps 2..5: converters during the K loop, epilogue after it -------------------------------
+    const int t = (warp - 2) * 32 + lane;   // row of the A tile, column of the B tile
+    const int q = warp & 3;
+    bool ok = true;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int r = kb % R, ps = kb % P;
+      if (!mbar_wait(&raw_full[r], (uint32_t)(kb / R) & 1u) || !mbar_wait(&pl_empty[ps], ((uint32_t)(kb / P) & 1u) ^ 1u)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        *abort_flag = 1;
+        break;
+      }
+      const unsigned char *ra = raw + r * 2 * kT, *rb = ra + kT;
+      unsigned char *pa = planes + ps * 4 * kT;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t off = (uint32_t)t * 128u + (uint32_t)((j ^ (t & 7)) << 4);
+        // A: chunk j of row t, in place of the same swizzled position
+        const float4 x = *reinterpret_cast<const float4 *>(ra + off);
+        float4 h, l;
+        h.x = tf32_rna(x.x); l.x = tf32_rna(x.x - h.x);
+        h.y = tf32_rna(x.y); l.y = tf32_rna(x.y - h.y);
+        h.z = tf32_rna(x.z); l.z = tf32_rna(x.z - h.z);
+        h.w = tf32_rna(x.w); l.w = tf32_rna(x.w - h.w);
+        *reinterpret_cast<float4 *>(pa + off) = h;
+        *reinterpret_cast<float4 *>(pa + kT + off) = l;
+        // B: k = 4j .. 4j+3 of column t become chunk j of row t of the transposed plane tiles
+        float4 y;
+        y.x = *reinterpret_cast<const float *>(rb + (4 * j + 0) * 512 + t * 4);
+        y.y = *reinterpret_cast<const float *>(rb + (4 * j + 1) * 512 + t * 4);
+        y.z = *reinterpret_cast<const float *>(rb + (4 * j + 2) * 512 + t * 4);
+        y.w = *reinterpret_cast<const float *>(rb + (4 * j + 3) * 512 + t * 4);
+        h.x = tf32_rna(y.x); l.x = tf32_rna(y.x - h.x);
+        h.y = tf32_rna(y.y); l.y = tf32_rna(y.y - h.y);
+        h.z = tf32_rna(y.z); l.z = tf32_rna(y.z - h.z);
+        h.w = tf32_rna(y.w); l.w = tf32_rna(y.w - h.w);
+        *reinterpret_cast<float4 *>(pa + 2 * kT + off) = h;
+        *reinterpret_cast<float4 *>(pa + 3 * kT + off) = l;
+      }
+      fence_proxy_async();   // the MMAs read these tiles through the async proxy
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&pl_full[ps]);
+        mbar_arrive(&raw_empty[r]);
+      }
+    }
+    if (ok && nkb > 0) {
+      bool done = false;
+      const uint64_t t0 = global_timer_ns();
+      for (int it = 0; it < (1 << 14) && !done; ++it) {
+        done = mbar_wait(acc_ready, 0, 1u << 10);
+        if (!done && (*abort_flag || global_timer_ns() - t0 > 2000000000ull)) break;
+      }
+      ok = done;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) *abort_flag = 1;
+    tc_fence_after();
+    FtInj inj;
+    tf32_epilogue<128, 0>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, nullptr);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {   // the same answer in every thread: read after the barrier
+    if (tid == 0) ring_settle(raw_full, R, issued);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 128);
+  }
+  if (tid == 0 && *abort_flag) record_timeout(p.status, p.seq);
+}
+
 static std::atomic<int> g_tf32_tile_n{0};  // 0: automatic; 128 or 256 pins the tile width
 static std::atomic<int> g_tf32_slab_k{32}; // K-slab depth: 32 (128-byte swizzle) or 16 (64-byte swizzle, twice the stages)
 static std::atomic<int> g_tf32_persistent{1};  // 1: the CTA-pair SGEMM runs as a persistent kernel with a double-buffered accumulator
@@ -1591,6 +1776,7 @@ static std::atomic<float> g_tf32_ft_bias{-1.f};  // < 0: default
 static std::atomic<int> g_tf32_tail{1};    // 1: the last round of the chunked CTA-pair kernel is shared out in chunks over all clusters
 constexpr int kDefaultChunk = 16;
 static std::atomic<int> g_tf32_chunk{kDefaultChunk};  // plain SGEMM: K-slabs per accumulation chunk (0: one accumulation over all of K)
+static std::atomic<int> g_tf32_fused{1};   // 1: small plain products split their operands inside the GEMM kernel; 0: always the pre-pass; 2: whenever the layout allows
 static std::atomic<int> g_tf32_pair{1};    // CTA pairs (256 x 256 tiles, cta_group::2): 0 never, 1 when the wave model favours them, 2 always
 
 // hi/lo planes of A (M x kp) and of B transposed (N x kp), plus the ABFT checksum planes
@@ -1690,6 +1876,31 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
   if (M == 0 || N == 0) return B2_OK;
   // nothing for the tensor cores to do: the FFMA path's scaling pass covers it
   if (K == 0 || alpha == 0.f) return sgemm_ffma_dispatch_ft(ctx, 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, ft, s);
+  // Very small plain products (one wave of 128 x 128 tiles, K <= 512): the split inside the GEMM kernel, no workspace.
+  {
+    const int fused = g_tf32_fused.load();
+    const long long tiles128 = (long long)((M + 127) / 128) * ((N + 127) / 128);
+    const bool aligned = ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0 && (lda % 4) == 0 && (ldb % 4) == 0;
+    if (ft == nullptr && fused != 0 && aligned && g_tf32_tile_n == 0 && g_tf32_slab_k == 32 &&
+        (fused == 2 || (g_tf32_pair == 1 && K <= 512 && tiles128 <= ctx->sm_count))) {   // an explicit choice of kernel form keeps the pre-pass
+      CUtensorMap ta, tb;
+      int st0 = make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (st0 != B2_OK) return st0;
+      st0 = make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (st0 != B2_OK) return st0;
+      Tf32Args fa;
+      memset(&fa, 0, sizeof(fa));
+      fa.C = C; fa.M = M; fa.N = N; fa.K = K; fa.ldc = ldc; fa.alpha = alpha; fa.beta = beta;
+      fa.vec_c = ((((uintptr_t)C) & 15) == 0 && (ldc % 4) == 0) ? 1 : 0;
+      fa.status = (int *)((char *)ctx->fixed + kFixedStatus);
+      fa.seq = next_launch_seq(ctx);
+      st0 = ensure_func_attributes((const void *)sgemm_3xtf32_fused_kernel, ctx->device, kFusedSmem);
+      if (st0 != B2_OK) return st0;
+      sgemm_3xtf32_fused_kernel<<<(int)tiles128, 192, kFusedSmem, s>>>(ta, tb, fa);
+      B2_CUDA(cudaGetLastError());
+      return B2_OK;
+    }
+  }
   // the planes are needed; the slots of the tail tiles only let the last round be shared out
   bool tail_slots = ft == nullptr && K > 1024;
   if (tail_slots && ctx->ws && !ctx->ws_owned && ctx->ws_bytes < tf32_workspace_bytes(M, N, K)) tail_slots = false;
@@ -1961,6 +2172,13 @@ int b2_tf32_tail_plan(int tiles, int clusters, int K, int chunk_slabs, int *firs
   if (parts) *parts = p;
   if (longest) *longest = l;
   return cut ? 1 : 0;
+}
+// The hi/lo split inside the GEMM kernel: 0 never (always the two split kernels in front), 1 for very small plain
+// products (one wave of 128 x 128 tiles, K <= 512; the default), 2 whenever A and B are 16-byte aligned.
+int b2_set_tf32_fused_split(int mode) {
+  B2_REQUIRE(mode >= 0 && mode <= 2, B2_ERR_INVALID_ARG, "b2_set_tf32_fused_split: %d is not 0, 1 or 2", mode);
+  b2::g_tf32_fused = mode;
+  return B2_OK;
 }
 // K-slab depth of the 3xTF32 kernel: 16 or 32.  For benchmarking.
 int b2_set_tf32_slab_k(int k) {

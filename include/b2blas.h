@@ -352,6 +352,12 @@ int b2_set_tf32_persistent(int on);
  * default) and no pinned tile width; 0: one accumulation over all of K; negative: the default.  No counterpart in
  * the reference. */
 int b2_set_tf32_chunk(int slabs);
+/* The hi/lo split of the 3xTF32 path inside the GEMM kernel (raw tiles of A and B by TMA, converted in shared memory
+ * between the loads and the MMAs; no workspace, one launch instead of three; identical results): 0 never, 1 for very
+ * small plain products where the saved launches outweigh the slower K-slabs (one wave of 128 x 128 tiles, K <= 512;
+ * the default, and only while the kernel form is left to the library), 2 whenever A and B are 16-byte aligned with
+ * lda, ldb multiples of 4 (accumulates over all of K in one go).  No counterpart in the reference. */
+int b2_set_tf32_fused_split(int mode);
 /* 1 (default): when the tiles of a chunked CTA-pair call leave at least half of the clusters idle in the last round,
  * each tile of that round is cut along K into runs of whole chunks on different clusters; the runs' sums go through
  * the workspace and a second kernel adds them in K order and applies alpha and beta (deterministic for a given shape

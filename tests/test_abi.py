@@ -164,4 +164,5 @@ def test_new_entry_points_validate_before_touching_a_device(L):
     assert L.b2_ft_sgemm_workspace_bytes(1, 1024, 1024, 1024) == L.b2_sgemm_workspace_bytes(1, 1024, 1024, 1024)
     assert L.b2_set_tf32_abft_bias(0.5) == -1
     assert L.b2_set_tf32_tail_split(2) == -1 and L.b2_set_tf32_tail_split(1) == 0
+    assert L.b2_set_tf32_fused_split(3) == -1 and L.b2_set_tf32_fused_split(1) == 0
     assert L.b2_set_tf32_chunk(5000) == -1 and L.b2_set_tf32_chunk(8) == 0 and L.b2_set_tf32_chunk(-1) == 0   # -1: default

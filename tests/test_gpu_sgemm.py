@@ -308,6 +308,58 @@ def test_3xtf32_leading_dimensions(cuda):
     assert np.array_equal(got[mask], Cb[mask])          # nothing outside the view was touched
 
 
+# ---- the hi/lo split inside the GEMM kernel (very small products) -----------------------------------------
+@pytest.mark.parametrize("shape", [(128, 128, 32), (256, 256, 256), (384, 256, 320), (130, 300, 70), (17, 13, 5), (1, 1, 1),
+                                   (200, 520, 36), (257, 255, 33), (512, 768, 1000), (640, 640, 4096)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.5), (-1.5, 0.0)])
+def test_3xtf32_split_inside_the_kernel_is_identical_to_the_pre_pass(cuda, shape, alpha, beta):
+    """The kernel that converts the raw tiles of A and B in shared memory (one launch, no workspace) does the same
+    split arithmetic and issues the same MMAs in the same order as the 128 x 128 single-CTA kernel behind the two
+    split kernels: bit-identical results on whole and partial tiles, K not a multiple of the slab, padded rows."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = shape
+    lda, ldb, ldc = (K + 3) // 4 * 4 + 4, (N + 3) // 4 * 4, (N + 3) // 4 * 4 + 8
+    A = oracle.fill_uniform(M * lda, 1).reshape(M, lda)
+    B = oracle.fill_uniform(K * ldb, 2).reshape(K, ldb)
+    Cb = oracle.fill_uniform(M * ldc, 3).reshape(M, ldc)
+    out = {}
+    try:
+        for mode, tile_n in ((0, 128), (2, 0)):
+            b2.set_tf32_fused_split(mode)
+            b2.set_tf32_tile_n(tile_n)
+            dC = dev(Cb)
+            b2.sgemm(M, N, K, alpha, dev(A), dev(B), beta, dC, path=1, lda=lda, ldb=ldb, ldc=ldc)
+            b2.check_status()
+            out[mode] = dC.cpu().numpy()
+    finally:
+        b2.set_tf32_fused_split(1)
+        b2.set_tf32_tile_n(0)
+    assert np.array_equal(out[2], out[0])
+    assert np.array_equal(out[2][:, N:], Cb[:, N:])
+    c64, den = oracle.sgemm_f64(alpha, A[:, :K], B[:, :N], beta, Cb[:, :N])
+    assert oracle.gemm_error(np.ascontiguousarray(out[2][:, :N]), c64, den) <= TOL_3XTF32
+
+
+def test_3xtf32_split_inside_the_kernel_needs_aligned_operands_and_falls_back(cuda):
+    """Operands that TMA cannot address (not 16-byte aligned, or a leading dimension that is not a multiple of 4) go
+    through the pre-pass as before, whatever the knob says."""
+    import hpcdeepneuralnetworks_b200 as b2
+    M, N, K = 96, 160, 200
+    a, b, c = mats(M, N, K)
+    big_a = np.zeros((M, K + 1), np.float32)
+    big_a[:, 1:] = a
+    dA = dev(big_a)
+    try:
+        b2.set_tf32_fused_split(2)
+        dC = dev(c)
+        b2.sgemm(M, N, K, 1.0, dA[:, 1:], dev(b), 0.5, dC, path=1, lda=K + 1)     # A starts 4 bytes into its allocation, odd pitch
+        b2.check_status()
+    finally:
+        b2.set_tf32_fused_split(1)
+    c64, den = oracle.sgemm_f64(1.0, a, b, 0.5, c)
+    assert oracle.gemm_error(dC.cpu().numpy(), c64, den) <= TOL_3XTF32
+
+
 # ---- chunked accumulation of the 3xTF32 path (K beyond two chunks of 16 K-slabs) --------------------------
 @pytest.mark.parametrize("shape", [(300, 1000, 2100), (256, 256, 1056), (1, 5, 1100), (513, 260, 4096), (130, 36, 1500),
                                    (2048, 2048, 2048), (3200, 2200, 1100)])     # the last: 117 pair tiles on 74 clusters
