@@ -29,6 +29,8 @@
 //                            registers (bounds the tensor cores' truncation loss whatever K), C in and out by
 //                            TMA; the pair form is persistent and cuts a partial last round of tiles along K
 //                            (tf32_tail_fixup_kernel adds the runs).
+//   sgemm_3xtf32_fused_kernel  very small products: the split inside the GEMM kernel (raw tiles by TMA, converted in
+//                            shared memory by the warps that later run the epilogue); one launch, no workspace.
 // The one-tile kernels and the persistent kernel have ABFT forms with the checksums on the CUDA cores (template
 // FT); verification and repair sit in the shared epilogue.
 // Every wait is bounded; a wait that runs out sets the status word, TMEM is still freed.
