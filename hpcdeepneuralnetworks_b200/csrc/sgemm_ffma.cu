@@ -797,8 +797,7 @@ static int auto_split_ways(const Context *ctx, const FfmaTile &tl, double ctas, 
   return ways < 1 ? 1 : ways;
 }
 
-static int pick_tile(const Context *ctx, int M, int N) {
-  if (g_ffma_tile >= 0 && g_ffma_tile < kNumTiles) return g_ffma_tile;
+static int pick_tile_for(int sm_count, int M, int N) {
   // Time model: the CTAs of a launch are dealt out over the SMs, and the CTAs resident on one SM share its FMA
   // pipes, so the launch lasts as long as the SM with the most CTAs needs for them: ceil(CTAs / SMs) tiles of
   // bm x bn outputs at the tile's measured efficiency.  (Counting whole waves of resident CTAs instead overrates
@@ -810,9 +809,9 @@ static int pick_tile(const Context *ctx, int M, int N) {
     const FfmaTile &tl = g_tiles[t];
     const double ctas = (double)((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
     // the 8-row thread tiles run 8 warps per SM: below two waves of resident CTAs they lose to the 16-warp tiles
-    const double slots = (double)ctx->sm_count * ((tl.mr == 4 ? 512 : 256) / tl.threads);
+    const double slots = (double)sm_count * ((tl.mr == 4 ? 512 : 256) / tl.threads);
     if (ctas / slots < (double)tl.min_waves) continue;
-    const double per_sm = ceil(ctas / (double)ctx->sm_count);
+    const double per_sm = ceil(ctas / (double)sm_count);
     double time = per_sm * (double)(tl.bm * tl.bn) / tl.efficiency;
     // an SM needs two warps per scheduler to keep its FMA pipes busy: a launch that leaves fewer resident runs
     // slower than the efficiency measured on full SMs says (1024^3: 128 CTAs of 4 warps, 32.8 TFLOP/s against 36.4)
@@ -825,6 +824,10 @@ static int pick_tile(const Context *ctx, int M, int N) {
     }
   }
   return best;
+}
+static int pick_tile(const Context *ctx, int M, int N) {
+  if (g_ffma_tile >= 0 && g_ffma_tile < kNumTiles) return g_ffma_tile;
+  return pick_tile_for(ctx->sm_count, M, N);
 }
 
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
@@ -1052,6 +1055,11 @@ int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name) 
   if (threads) *threads = b2::g_tiles[i].threads;
   if (name) *name = b2::g_tiles[i].name;
   return B2_OK;
+}
+// The tile the picker takes for an M x N output on a device of `sm_count` SMs (no pin, no device needed).
+int b2_ffma_pick_tile(int M, int N, int sm_count) {
+  B2_REQUIRE(M > 0 && N > 0 && sm_count > 0, B2_ERR_INVALID_ARG, "b2_ffma_pick_tile: M = %d, N = %d, sm_count = %d must be positive", M, N, sm_count);
+  return b2::pick_tile_for(sm_count, M, N);
 }
 int b2_set_ffma_tile(int i) {
   B2_REQUIRE(i >= -1 && i < b2::kNumTiles, B2_ERR_INVALID_ARG, "b2_set_ffma_tile: tile %d not in -1..%d", i, b2::kNumTiles - 1);

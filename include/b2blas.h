@@ -330,6 +330,9 @@ int b2_set_ffma_split_k(int ways);
 int b2_ffma_tile_count(void);
 int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name);
 int b2_set_ffma_tile(int i);
+/* The index of the tile the picker takes for an M x N output on a device of `sm_count` SMs (148 on B200) when nothing is
+ * pinned: a host-side time model, no device needed.  Negative status on invalid arguments. */
+int b2_ffma_pick_tile(int M, int N, int sm_count);
 /* Pins the tile width of the 3xTF32 kernel (128 or 256 output columns per CTA; 0 = automatic). */
 int b2_set_tf32_tile_n(int n);
 /* K-slab depth of the 3xTF32 kernel: 16 (64-byte swizzle, 4-6 stages) or 32 (128-byte swizzle, 2-3 stages). */

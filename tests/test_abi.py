@@ -111,6 +111,28 @@ def test_partition_helpers_need_no_device(L):
     assert L.b2_mg_k_panel(5, 0, 4, C.byref(k0), C.byref(kw)) == 5 and (k0.value, kw.value) == (4, 1)   # panel < 1 means 1
 
 
+def test_ffma_picker_ranks_tiles_as_measured(L):
+    """b2_ffma_pick_tile: the time model (CTAs of the busiest SM at the tile's measured efficiency, occupancy penalty,
+    the 8 x 16 tile from two waves on) takes, on 148 SMs, the tile that `b2_driver tiles <n>` measured fastest or within
+    1.5 % of it at these sizes."""
+    name = C.c_char_p()
+    def pick(m, n):
+        i = L.b2_ffma_pick_tile(m, n, 148)
+        assert i >= 0 and L.b2_ffma_tile_info(i, None, None, None, C.byref(name)) == 0
+        return name.value.decode()
+    assert pick(1024, 1024) in ("large", "tall")          # 36.2 / 36.4 TFLOP/s; 128 x 128 tiles fill 64 SMs only: 20.7
+    assert pick(1280, 1280) == "large"                      # 41.8 against 33 for every other tile
+    assert pick(1536, 1536) == "huge"                       # 144 tiles, one per SM: 48.5
+    assert pick(1792, 1792) in ("b200_64x128", "tall", "large")   # 45.6 / 45.3 / 45.0; huge: 35.6
+    assert pick(2048, 2048) == "large"                      # 50.7; huge 48.5
+    assert pick(2816, 2816) == "b200_64x128"                # 52.2; huge 48.0
+    assert pick(3072, 3072) == "huge"                       # 57.2; the 8 x 16 tile below two waves: 55.9
+    for n in (3328, 4096, 5120, 6144, 8192):
+        assert pick(n, n) == "b200_8x16"
+    assert pick(768, 6144) == "huge" and pick(3072, 768) in ("huge", "b200_64x128")    # panels of the host-buffer pipeline
+    assert L.b2_ffma_pick_tile(0, 5, 148) < 0 and L.b2_ffma_pick_tile(5, 5, 0) < 0
+
+
 def test_tail_plan_of_the_3xtf32_path(L):
     """b2_tf32_tail_plan: when the tiles of the last round leave at least half of the clusters idle, each of them is cut
     into `parts` non-empty runs of whole chunks that cover the K loop once, on parts * R distinct clusters."""
