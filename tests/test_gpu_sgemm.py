@@ -470,6 +470,37 @@ def test_3xtf32_chunks_bound_the_loss_for_operands_of_one_sign(cuda, pair):
     assert err["signed", -1] <= 1e-6 and err["signed", -1] < 0.2 * err["signed", 0], err
 
 
+def test_random_shapes_through_the_dispatchers(cuda):
+    """Forty seeded random shapes (M, N up to 700, K up to 2600, leading dimensions with slack, alpha and beta drawn
+    from {0, 1, -1.5, 0.5, 2}) through both dispatchers as a caller would use them - whatever tile, kernel form, split,
+    chunking or cut of the last round they choose: FFMA bit-exact against the fused oracle, 3xTF32 within its tolerance,
+    nothing outside the M x N view touched."""
+    import hpcdeepneuralnetworks_b200 as b2
+    rng = np.random.default_rng(20240607)
+    for case in range(40):
+        M, N = int(rng.integers(1, 700)), int(rng.integers(1, 700))
+        K = int(rng.integers(1, 2600)) if case % 3 else int(rng.integers(1, 200))
+        pad = lambda x: (x + 3) // 4 * 4 + 4 * int(rng.integers(0, 3))
+        lda, ldb, ldc = pad(K), pad(N), pad(N)
+        alpha, beta = float(rng.choice([1.0, -1.5, 0.5, 2.0])), float(rng.choice([0.0, 1.0, -1.5, 0.5]))
+        A = oracle.fill_uniform(M * lda, 100 + case).reshape(M, lda)
+        B = oracle.fill_uniform(K * ldb, 200 + case).reshape(K, ldb)
+        Cb = oracle.fill_uniform(M * ldc, 300 + case).reshape(M, ldc)
+        a, b, c = np.ascontiguousarray(A[:, :K]), np.ascontiguousarray(B[:, :N]), np.ascontiguousarray(Cb[:, :N])
+        c64, den = oracle.sgemm_f64(alpha, a, b, beta, c)
+        want = oracle.sgemm_fma(alpha, a, b, beta, c)
+        for path, tol in ((0, TOL_FFMA), (1, TOL_3XTF32)):
+            dC = dev(Cb)
+            b2.sgemm(M, N, K, alpha, dev(A), dev(B), beta, dC, path=path, lda=lda, ldb=ldb, ldc=ldc)
+            b2.check_status()
+            got = dC.cpu().numpy()
+            tag = (case, path, M, N, K, lda, ldb, ldc, alpha, beta)
+            assert np.array_equal(got[:, N:], Cb[:, N:]), tag
+            if path == 0:
+                assert np.array_equal(got[:, :N], want), tag
+            assert oracle.gemm_error(np.ascontiguousarray(got[:, :N]), c64, den) <= tol, tag
+
+
 def test_sweep_sizes_both_paths(cuda):
     """Benchmark configuration 2 (alpha=1, beta=0.5) at a few sweep sizes, inputs generated on the device; checked on
     sampled rows against the double reference."""
