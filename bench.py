@@ -216,12 +216,23 @@ def abft_fault_report(b2, torch, n, path):
     B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
     plain = torch.zeros((n, n), device="cuda")
     if path == 1:
-        b2.set_tf32_chunk(0)      # the ABFT kernel accumulates over all of K in one go: compare with the plain kernel that does too
+        # the ABFT kernel accumulates a tile over all of K in one go: compare with the plain kernel that does too, and
+        # keep both from cutting the tiles of a partial last round along K (which changes the last bits of those tiles)
+        b2.set_tf32_chunk(0)
+        b2.set_tf32_tail_split(0)
     try:
         b2.sgemm(n, n, n, 1.0, A, B, 0.0, plain, path=path)
     finally:
         if path == 1:
             b2.set_tf32_chunk(-1)
+    try:
+        return _abft_fault_report_body(b2, torch, n, path, tol, A, B, plain)
+    finally:
+        if path == 1:
+            b2.set_tf32_tail_split(1)
+
+
+def _abft_fault_report_body(b2, torch, n, path, tol, A, B, plain):
     out = torch.zeros((n, n), device="cuda")
     rep = b2.new_report()
     b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, path=path, report=rep)

@@ -173,21 +173,33 @@ struct Tf32Args {
   float tau_elem;   // an output further than this from its recomputed value is replaced
   float ft_bias;    // FT = 2: expected loss of an accumulator per K-slab, as a fraction of its value (see tf32_epilogue)
 };
+// Where an accumulator tile goes and which k it covers: C itself with the call's alpha and beta for a whole tile, or,
+// for a run of a tile cut along K, its workspace slot, unscaled, with the run's k range (the ABFT repair recomputes
+// over that range only).
+struct EpiOut {
+  float *C;
+  int ldc;
+  float alpha, beta;
+  int vec_c;
+  int k_begin, k_end;
+  __device__ __forceinline__ static EpiOut whole(const Tf32Args &p) { return EpiOut{p.C, p.ldc, p.alpha, p.beta, p.vec_c, 0, p.K}; }
+};
 
 // FP32 dot product of row `row` of A with column col0 + lane of B, from global memory (two
 // interleaved chains over K).  Called by whole warps.
-__device__ __forceinline__ float ft_recompute32(const Tf32Args &p, int row, int col0, int lane) {
+__device__ __forceinline__ float ft_recompute32(const Tf32Args &p, int k_begin, int k_end, int row, int col0, int lane) {
   const int col = col0 + lane;
   float acc0 = 0.f, acc1 = 0.f;
   if (row < p.M && col < p.N) {
     const float *a = p.ft.A + (size_t)row * p.ft.lda;
     const float *b = p.ft.B + col;
-    int k = 0;
-    for (; k + 1 < p.K; k += 2) {
+    int k = k_begin;
+    const int kend = k_end;
+    for (; k + 1 < kend; k += 2) {
       acc0 = __fmaf_rn(a[k], b[(size_t)k * p.ft.ldb], acc0);
       acc1 = __fmaf_rn(a[k + 1], b[(size_t)(k + 1) * p.ft.ldb], acc1);
     }
-    if (k < p.K) acc0 = __fmaf_rn(a[k], b[(size_t)k * p.ft.ldb], acc0);
+    if (k < kend) acc0 = __fmaf_rn(a[k], b[(size_t)k * p.ft.ldb], acc0);
   }
   return acc0 + acc1;
 }
@@ -288,7 +300,7 @@ __device__ __forceinline__ void ft_cuda_finish(FtCudaAcc<RPL> &acc, float *table
 // `ok` (warp-uniform) says the accumulator is complete; called by whole warps.
 template <int TBN, int FT>
 __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_base, int q, int lane, int m0, int n0, bool ok,
-                                              int nkb, const FtInj &inj, const float *chk_row) {
+                                              int nkb, const FtInj &inj, const float *chk_row, const EpiOut o_, bool count_tile = true) {
   const int inj_col0 = inj.col0, inj_col1 = inj.col1;
   const uint32_t inj_mask0 = inj.mask0, inj_mask1 = inj.mask1;
   const float tscale = (FT && p.ft.tau_scale) ? __ldg(p.ft.tau_scale) : 1.f;
@@ -296,8 +308,8 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
   float worst = 0.f;          // largest in-tolerance |group sum - checksum| this thread saw
   int n_inj = 0, n_det = 0, n_cor = 0, n_false = 0;
   const int row = m0 + q * 32 + lane;
-  const bool read_c = (p.beta != 0.f);
-  float *crow = p.C + (size_t)row * p.ldc;
+  const bool read_c = (o_.beta != 0.f);
+  float *crow = o_.C + (size_t)row * o_.ldc;
 #pragma unroll 1
   for (int c = 0; c < TBN / 32; ++c) {
     uint32_t v[32];
@@ -342,7 +354,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
           const int L = __ffs(m) - 1;
           m &= m - 1;
           const int rowL = __shfl_sync(0xffffffffu, m0 + q * 32 + lane, L);
-          const float ref = ft_recompute32(p, rowL, n0 + c * 32, lane);
+          const float ref = ft_recompute32(p, o_.k_begin, o_.k_end, rowL, n0 + c * 32, lane);
           int replaced = 0;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -360,21 +372,21 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
     }
     if (!ok || row >= p.M) continue;
     const int col0 = n0 + c * 32;
-    if (p.vec_c && col0 + 31 < p.N) {
+    if (o_.vec_c && col0 + 31 < p.N) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         float4 o;
         if (read_c) {
           const float4 cc = *reinterpret_cast<const float4 *>(crow + col0 + j);
-          o.x = __fmaf_rn(p.alpha, __uint_as_float(v[j + 0]), __fmul_rn(p.beta, cc.x));
-          o.y = __fmaf_rn(p.alpha, __uint_as_float(v[j + 1]), __fmul_rn(p.beta, cc.y));
-          o.z = __fmaf_rn(p.alpha, __uint_as_float(v[j + 2]), __fmul_rn(p.beta, cc.z));
-          o.w = __fmaf_rn(p.alpha, __uint_as_float(v[j + 3]), __fmul_rn(p.beta, cc.w));
+          o.x = __fmaf_rn(o_.alpha, __uint_as_float(v[j + 0]), __fmul_rn(o_.beta, cc.x));
+          o.y = __fmaf_rn(o_.alpha, __uint_as_float(v[j + 1]), __fmul_rn(o_.beta, cc.y));
+          o.z = __fmaf_rn(o_.alpha, __uint_as_float(v[j + 2]), __fmul_rn(o_.beta, cc.z));
+          o.w = __fmaf_rn(o_.alpha, __uint_as_float(v[j + 3]), __fmul_rn(o_.beta, cc.w));
         } else {
-          o.x = __fmul_rn(p.alpha, __uint_as_float(v[j + 0]));
-          o.y = __fmul_rn(p.alpha, __uint_as_float(v[j + 1]));
-          o.z = __fmul_rn(p.alpha, __uint_as_float(v[j + 2]));
-          o.w = __fmul_rn(p.alpha, __uint_as_float(v[j + 3]));
+          o.x = __fmul_rn(o_.alpha, __uint_as_float(v[j + 0]));
+          o.y = __fmul_rn(o_.alpha, __uint_as_float(v[j + 1]));
+          o.z = __fmul_rn(o_.alpha, __uint_as_float(v[j + 2]));
+          o.w = __fmul_rn(o_.alpha, __uint_as_float(v[j + 3]));
         }
         *reinterpret_cast<float4 *>(crow + col0 + j) = o;
       }
@@ -383,7 +395,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
       for (int j = 0; j < 32; ++j) {
         if (col0 + j < p.N) {
           const float a = __uint_as_float(v[j]);
-          crow[col0 + j] = read_c ? __fmaf_rn(p.alpha, a, __fmul_rn(p.beta, crow[col0 + j])) : __fmul_rn(p.alpha, a);
+          crow[col0 + j] = read_c ? __fmaf_rn(o_.alpha, a, __fmul_rn(o_.beta, crow[col0 + j])) : __fmul_rn(o_.alpha, a);
         }
       }
     }
@@ -399,7 +411,7 @@ __device__ __forceinline__ void tf32_epilogue(const Tf32Args &p, uint32_t tmem_b
       worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
     }
     if (lane == 0) {
-      if (q == 0 && m0 < p.M) atomicAdd(&p.ft.report[0], 1);   // a pair's second CTA may lie wholly below the matrix
+      if (count_tile && q == 0 && m0 < p.M) atomicAdd(&p.ft.report[0], 1);   // a pair's second CTA may lie wholly below the matrix
       if (n_inj) atomicAdd(&p.ft.report[1], n_inj);
       if (n_det) atomicAdd(&p.ft.report[2], n_det);
       if (n_cor) atomicAdd(&p.ft.report[3], n_cor);
@@ -551,7 +563,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_const
     ok = __all_sync(0xffffffffu, ok);   // the checksum pass below uses warp collectives
     if (!ok) *abort_flag = 1;
     tc_fence_after();
-    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16);
+    tf32_epilogue<TBN, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16, EpiOut::whole(p));
   }
 
   tc_fence_before();
@@ -742,7 +754,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) pair_abort(abort_flag);
     tc_fence_after();
-    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16);
+    tf32_epilogue<256, FT>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, table + (q * 32 + lane) * 16, EpiOut::whole(p));
   }
 
   // neither CTA leaves (or frees tensor memory) while the other may still be read by an MMA
@@ -774,6 +786,37 @@ __device__ __forceinline__ void pair_tile_origin(const Tf32Args &p, int t, uint3
   n0 = (within / band_rows) * 256;
 }
 
+constexpr size_t kTailSlotBytes = 256 * 256 * sizeof(float);
+constexpr size_t kTailSlotsMax = 80;   // one per cluster
+struct ChunkWork {
+  int tile, ch0, ch1;   // chunks [ch0, ch1) of this tile
+  int slot;             // < 0: the whole tile, result to C; else the workspace slot of the run
+};
+struct ChunkWorkIter {
+  int t, n_clusters, first_sk, nch, cluster, parts, tail_tiles;
+  bool tail_done;
+  __device__ __forceinline__ ChunkWorkIter(int cluster_, int n_clusters_, int first_sk_, int parts_, int tail_tiles_, int nch_)
+      : t(cluster_), n_clusters(n_clusters_), first_sk(first_sk_), nch(nch_), cluster(cluster_), parts(parts_),
+        tail_tiles(tail_tiles_), tail_done(false) {}
+  __device__ __forceinline__ bool next(ChunkWork &w) {
+    if (t < first_sk) {
+      w.tile = t; w.ch0 = 0; w.ch1 = nch; w.slot = -1;
+      t += n_clusters;
+      return true;
+    }
+    if (!tail_done && parts > 0 && cluster < parts * tail_tiles) {
+      tail_done = true;
+      const int run = cluster / tail_tiles;
+      w.tile = first_sk + cluster % tail_tiles;
+      w.ch0 = (int)((long long)run * nch / parts);
+      w.ch1 = (int)((long long)(run + 1) * nch / parts);
+      w.slot = cluster;
+      return w.ch1 > w.ch0;
+    }
+    return false;
+  }
+};
+
 // FT = kFtCuda adds the ABFT form: eight more warps (6..13, 16 tile rows each) form the checksums of the tile being accumulated on the
 // CUDA cores, beside the MMAs, exactly as in the one-tile kernel, and leave them in one of two shared tables
 // (tab_full / tab_empty barriers, local to each CTA); the epilogue warps verify and repair the tile they drain
@@ -790,7 +833,8 @@ template <int FT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PersistCfg<FT>::kThreads, 1)
 sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
-                                    const __grid_constant__ CUtensorMap tmS, const Tf32Args p, int n_tiles) {
+                                    const __grid_constant__ CUtensorMap tmS, const Tf32Args p, int first_sk, int tail_parts,
+                                    int tail_tiles, float *tail_ws) {
   static_assert(FT == 0 || FT == kFtCuda, "the persistent form has plain and CUDA-core-checksum variants");
   using PC = PairCfg<FT>;
   constexpr int S = PC::kStages, kTA = PC::kTA, kTB = PC::kTB, kStage = PC::kStage;
@@ -852,10 +896,12 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = cluster; t < n_tiles && ok; t += n_clusters) {
+      ChunkWorkIter work(cluster, n_clusters, first_sk, tail_parts, tail_tiles, nkb);   // units of one K-slab
+      ChunkWork w;
+      while (ok && work.next(w)) {
         int m0, n0;
-        pair_tile_origin(p, t, rank, m0, n0);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        pair_tile_origin(p, w.tile, rank, m0, n0);
+        for (int kb = w.ch0; kb < w.ch1; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(&empty[s], ((it / S) & 1u) ^ 1u)) {
             pair_abort(abort_flag);
@@ -880,7 +926,9 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
       constexpr uint32_t idesc = umma_idesc_tf32(256, 256, 0, 0);
       uint32_t it = 0, n_done = 0;
       bool ok = true;
-      for (int t = cluster; t < n_tiles && ok; t += n_clusters, ++n_done) {
+      ChunkWorkIter work(cluster, n_clusters, first_sk, tail_parts, tail_tiles, nkb);
+      ChunkWork w;
+      for (; ok && work.next(w); ++n_done) {
         const uint32_t buf = n_done & 1u;
         // the epilogue warps of both CTAs have drained this buffer (two tiles ago)
         if (!mbar_wait(&acc_empty[buf], ((n_done >> 1) & 1u) ^ 1u)) {
@@ -889,7 +937,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
         }
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * 256u;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = w.ch0; kb < w.ch1; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(&full[s], (it / S) & 1u)) {
             pair_abort(abort_flag);
@@ -907,7 +955,7 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
             const uint64_t a_lo = umma_smem_desc(st + kTA + k4 * 32, 16, 1024, 2);
             const uint64_t b_hi = umma_smem_desc(st + 2 * kTA + k4 * 32, 16, 1024, 2);
             const uint64_t b_lo = umma_smem_desc(st + 2 * kTA + kTB + k4 * 32, 16, 1024, 2);
-            umma_tf32_pair(acc, a_lo, b_hi, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+            umma_tf32_pair(acc, a_lo, b_hi, idesc, (kb > w.ch0 || k4 > 0) ? 1u : 0u);
             umma_tf32_pair(acc, a_hi, b_lo, idesc, 1u);
             umma_tf32_pair(acc, a_hi, b_hi, idesc, 1u);
           }
@@ -921,12 +969,14 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
     const int q = warp & 3;
     uint32_t n_done = 0;
     const uint32_t leader_empty0 = mapa_u32(smem_u32(&acc_empty[0]), 0), leader_empty1 = mapa_u32(smem_u32(&acc_empty[1]), 0);
-    for (int t = cluster; t < n_tiles; t += n_clusters, ++n_done) {
+    ChunkWorkIter work(cluster, n_clusters, first_sk, tail_parts, tail_tiles, nkb);
+    ChunkWork w;
+    for (; work.next(w); ++n_done) {
       const uint32_t buf = n_done & 1u;
       int m0, n0;
-      pair_tile_origin(p, t, rank, m0, n0);
+      pair_tile_origin(p, w.tile, rank, m0, n0);
       FtInj inj;
-      if (FT) inj = ft_scan_plan<256>(p, m0 + q * 32 + lane, n0);
+      if (FT && w.ch0 == 0) inj = ft_scan_plan<256>(p, m0 + q * 32 + lane, n0);   // a planned fault strikes a tile's first run
       // one lane polls (the barrier words share the shared-memory pipe with the MMAs' operand reads); the others
       // then look once for themselves
       bool done = false;
@@ -946,8 +996,22 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
         break;
       }
       tc_fence_after();
-      tf32_epilogue<256, FT>(p, tmem_base + buf * 256u, q, lane, m0, n0, true, nkb, inj,
-                             tables + buf * (PersistCfg<FT>::kTable / 4) + (q * 32 + lane) * 16);
+      // a whole tile goes to C; a run of a tile cut along K is verified and repaired against the checksums of its own k
+      // range and stored unscaled in its workspace slot (row r of the tile at row r of the slot) for the fix-up kernel
+      EpiOut eo = EpiOut::whole(p);
+      if (w.slot >= 0) {
+        int mt, nt;
+        pair_tile_origin(p, w.tile, 0, mt, nt);
+        eo.C = tail_ws + (size_t)w.slot * 256 * 256 - (ptrdiff_t)mt * 256 - nt;
+        eo.ldc = 256;
+        eo.alpha = 1.f;
+        eo.beta = 0.f;
+        eo.vec_c = 1;
+        eo.k_begin = w.ch0 * 32;
+        eo.k_end = min(w.ch1 * 32, p.K);
+      }
+      tf32_epilogue<256, FT>(p, tmem_base + buf * 256u, q, lane, m0, n0, true, w.ch1 - w.ch0, inj,
+                             tables + buf * (PersistCfg<FT>::kTable / 4) + (q * 32 + lane) * 16, eo, w.ch0 == 0);
       // this warp's reads of the buffer are complete (every chunk waited for its tcgen05.ld): hand it back
       tc_fence_before();
       __syncwarp();
@@ -963,10 +1027,20 @@ sgemm_3xtf32_pair_persistent_kernel(const __grid_constant__ CUtensorMap tmAh, co
     uint64_t *data_bar = (rank == 0) ? full : landed;
     uint32_t it = 0, n_done = 0;
     bool ok = true;
-    for (int t = cluster; t < n_tiles && ok; t += n_clusters, ++n_done) {
+    // the same sequence of work as ChunkWorkIter gives the other roles, with little state live across the slab loop:
+    // this cluster's whole tiles, then at most one run of a tile of the last round
+    const int n_whole = first_sk > cluster ? (first_sk - cluster + n_clusters - 1) / n_clusters : 0;
+    const int n_works = n_whole + ((tail_parts > 0 && cluster < tail_parts * tail_tiles) ? 1 : 0);
+    for (int i = 0; ok && i < n_works; ++i, ++n_done) {
       FtCudaAcc<4> acc;
       acc.zero();
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      int kb = 0, kb_end = nkb;
+      if (i >= n_whole) {
+        const int run = cluster / tail_tiles;
+        kb = (int)((long long)run * nkb / tail_parts);
+        kb_end = (int)((long long)(run + 1) * nkb / tail_parts);
+      }
+      for (; kb < kb_end; ++kb, ++it) {
         const int s = it % S;
         if (!mbar_wait(&data_bar[s], (it / S) & 1u)) {
           ok = false;
@@ -1131,37 +1205,6 @@ __device__ __forceinline__ bool chunk_store(const Tf32Args &p, const CUtensorMap
 // in a whole round).  A run's FP32 sums go, unscaled, to slot c of the workspace (256 x 256 floats), from which
 // tf32_tail_fixup_kernel adds a tile's runs in K order and applies alpha and beta.  Deterministic: the cut depends
 // on the shape and the cluster count only.
-constexpr size_t kTailSlotBytes = 256 * 256 * sizeof(float);
-constexpr size_t kTailSlotsMax = 80;   // one per cluster
-struct ChunkWork {
-  int tile, ch0, ch1;   // chunks [ch0, ch1) of this tile
-  int slot;             // < 0: the whole tile, result to C; else the workspace slot of the run
-};
-struct ChunkWorkIter {
-  int t, n_clusters, first_sk, nch, cluster, parts, tail_tiles;
-  bool tail_done;
-  __device__ __forceinline__ ChunkWorkIter(int cluster_, int n_clusters_, int first_sk_, int parts_, int tail_tiles_, int nch_)
-      : t(cluster_), n_clusters(n_clusters_), first_sk(first_sk_), nch(nch_), cluster(cluster_), parts(parts_),
-        tail_tiles(tail_tiles_), tail_done(false) {}
-  __device__ __forceinline__ bool next(ChunkWork &w) {
-    if (t < first_sk) {
-      w.tile = t; w.ch0 = 0; w.ch1 = nch; w.slot = -1;
-      t += n_clusters;
-      return true;
-    }
-    if (!tail_done && parts > 0 && cluster < parts * tail_tiles) {
-      tail_done = true;
-      const int run = cluster / tail_tiles;
-      w.tile = first_sk + cluster % tail_tiles;
-      w.ch0 = (int)((long long)run * nch / parts);
-      w.ch1 = (int)((long long)(run + 1) * nch / parts);
-      w.slot = cluster;
-      return w.ch1 > w.ch0;
-    }
-    return false;
-  }
-};
-
 // The warp's 32 x 128 sums, unscaled, to the workspace tile at (x0, y0) of the tensor map tmW, through its staging area.
 __device__ __forceinline__ void chunk_store_raw(const CUtensorMap *tmW, unsigned char *stg, const float (&acc)[128], int x0,
                                                 int y0, int lane) {
@@ -1755,7 +1798,7 @@ sgemm_3xtf32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (!ok) *abort_flag = 1;
     tc_fence_after();
     FtInj inj;
-    tf32_epilogue<128, 0>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, nullptr);
+    tf32_epilogue<128, 0>(p, tmem_base, q, lane, m0, n0, ok, nkb, inj, nullptr, EpiOut::whole(p));
   }
 
   tc_fence_before();
@@ -1904,7 +1947,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     }
   }
   // the planes are needed; the slots of the tail tiles only let the last round be shared out
-  bool tail_slots = ft == nullptr && K > 1024;
+  bool tail_slots = K > 1024;
   if (tail_slots && ctx->ws && !ctx->ws_owned && ctx->ws_bytes < tf32_workspace_bytes(M, N, K)) tail_slots = false;
   int st = ensure_workspace(ctx, tail_slots ? tf32_workspace_bytes(M, N, K) : tf32_planes_bytes(M, N, K), s);
   if (st != B2_OK) return st;
@@ -2054,11 +2097,25 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
       st = ensure_func_attributes(fn, ctx->device, ftm ? PersistCfg<kFtCuda>::kSmem : PersistCfg<0>::kSmem);
       if (st != B2_OK) return st;
       const int clusters = pairs < slots ? pairs : (slots > 0 ? slots : pairs);
-      if (ftm == kFtCuda)
-        sgemm_3xtf32_pair_persistent_kernel<kFtCuda><<<2 * clusters, PersistCfg<kFtCuda>::kThreads, PersistCfg<kFtCuda>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa, pairs);
-      else
-        sgemm_3xtf32_pair_persistent_kernel<0><<<2 * clusters, PersistCfg<0>::kThreads, PersistCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa, pairs);
-      B2_CUDA(cudaGetLastError());
+      if (ftm == kFtCuda) {
+        // the fault-tolerant form cuts a partial last round along K too, in units of one K-slab: every run is verified
+        // and repaired against the checksums of its own k range before its sums go to the workspace
+        int t_first = pairs, t_parts = 0, t_longest = 0;
+        float *tail_ws = (float *)(w + 2 * align1k(a_elems * 4) + 2 * align1k(b_elems * 4) + align1k((size_t)srows * kp * 4));
+        const bool cut = tail_slots && g_tf32_tail.load() != 0 && (size_t)slots <= kTailSlotsMax &&
+                         tf32_tail_plan(pairs, slots, (K + 31) / 32, 1, &t_first, &t_parts, &t_longest);
+        const int cl = cut ? slots : clusters;
+        sgemm_3xtf32_pair_persistent_kernel<kFtCuda><<<2 * cl, PersistCfg<kFtCuda>::kThreads, PersistCfg<kFtCuda>::kSmem, s>>>(
+            maps[0], maps[1], maps[2], maps[3], maps[4], pa, cut ? t_first : pairs, cut ? t_parts : 0, pairs - t_first, tail_ws);
+        B2_CUDA(cudaGetLastError());
+        if (cut) {
+          tf32_tail_fixup_kernel<<<dim3(64, pairs - t_first), 256, 0, s>>>(pa, tail_ws, t_first, t_parts, pairs - t_first, (K + 31) / 32);
+          B2_CUDA(cudaGetLastError());
+        }
+      } else {
+        sgemm_3xtf32_pair_persistent_kernel<0><<<2 * clusters, PersistCfg<0>::kThreads, PersistCfg<0>::kSmem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], pa, pairs, 0, 0, nullptr);
+        B2_CUDA(cudaGetLastError());
+      }
       return B2_OK;
     }
     st = ftm == kFtCuda ? ensure_func_attributes((const void *)sgemm_3xtf32_pair_kernel<kFtCuda>, ctx->device, PairCfg<kFtCuda>::kSmem)

@@ -361,7 +361,9 @@ int b2_set_tf32_chunk(int slabs);
  * the default, and only while the kernel form is left to the library), 2 whenever A and B are 16-byte aligned with
  * lda, ldb multiples of 4 (accumulates over all of K in one go).  No counterpart in the reference. */
 int b2_set_tf32_fused_split(int mode);
-/* 1 (default): when the tiles of a chunked CTA-pair call leave at least half of the clusters idle in the last round,
+/* 1 (default): when the tiles of a chunked CTA-pair call (or of the fault-tolerant CTA-pair kernel, which cuts in units
+ * of one K-slab and verifies every run against the checksums of its own k range) leave at least half of the clusters
+ * idle in the last round,
  * each tile of that round is cut along K into runs of whole chunks on different clusters; the runs' sums go through
  * the workspace and a second kernel adds them in K order and applies alpha and beta (deterministic for a given shape
  * and device; identical to the uncut result when every run is one chunk, else different in the last bits).  A

@@ -24,16 +24,19 @@ ELEM = 0.75              # an output further than this fraction of tau from its 
 def _kernel_form(request, cuda):
     """Every test runs on the persistent CTA-pair kernel (the default for large problems: 256 x 256 tiles), on the
     one-tile-per-cluster CTA-pair kernel and on the single-CTA kernel (128 x 256 tiles).  The ABFT kernels accumulate
-    over all of K in one go, so the plain products they are compared with here are made the same way (no chunks)."""
+    over all of K in one go, so the plain products they are compared with here are made the same way (no chunks, no
+    cut of the last round)."""
     import hpcdeepneuralnetworks_b200 as b2
     pair, persistent = request.param
     b2.set_tf32_pair(pair)
     b2.set_tf32_persistent(persistent)
     b2.set_tf32_chunk(0)
+    b2.set_tf32_tail_split(0)      # one accumulation per tile, as in the plain products compared with (the cut has its own test)
     yield
     b2.set_tf32_pair(1)
     b2.set_tf32_persistent(1)
     b2.set_tf32_chunk(-1)
+    b2.set_tf32_tail_split(1)
 
 
 def dev(a):
@@ -290,6 +293,46 @@ def test_config3_large_sizes(cuda, n):
     assert int((diff > 0).sum().item()) <= len(plan)
     # repaired outputs carry the FP32 recomputation (within tau/2 of the tensor-core value); flips that stay are below 2 tau
     assert float(diff.max().item()) <= (2 * tau if gray else elem_tol(n))
+
+
+@pytest.mark.parametrize("n", [2304, 4096])
+def test_abft_with_the_last_round_cut_along_k(cuda, n):
+    """The persistent ABFT kernel cuts a partial last round of tiles along K like the plain kernel (2304: 81 tiles, the last
+    7 in five runs each; 4096: 256 tiles, the last 34 in two): every run is verified and repaired against the checksums
+    of its own k range, then the runs are added.  Clean: every tile counted once, no alarm, the result as close to the uncut
+    one as the path's own error at this K.  Seeded flips (one per 64 tiles, bits 20..30, striking a tile's first run): all
+    injected, no false alarm, and the repaired result meets the path's accuracy contract everywhere."""
+    import hpcdeepneuralnetworks_b200 as b2
+    A = b2.fill_uniform(torch.empty((n, n), device="cuda"), 1)
+    B = b2.fill_uniform(torch.empty((n, n), device="cuda"), 2)
+    uncut = torch.zeros((n, n), device="cuda")
+    b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, uncut, path=b2.PATH_3XTF32)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        den = A.abs() @ B.abs()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    try:
+        b2.set_tf32_tail_split(1)
+        rep = b2.new_report()
+        out = torch.zeros((n, n), device="cuda")
+        b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, out, path=b2.PATH_3XTF32, report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert counts(r) == {"tiles": ((n + 127) // 128) * ((n + 255) // 256), "injected": 0, "detected": 0, "corrected": 0,
+                             "uncorrectable": 0, "false_alarms": 0}
+        assert bool(((out - uncut).abs() <= 3e-6 * den).all().item())      # runs lose less to the tensor cores' truncation than one long accumulation
+        plan = oracle.make_fault_plan(n, n, n, seed=6)
+        rep = b2.new_report()
+        hit = torch.zeros((n, n), device="cuda")
+        b2.ft_sgemm(n, n, n, 1.0, A, B, 0.0, hit, path=b2.PATH_3XTF32, plan=b2.make_plan(plan), report=rep)
+        b2.check_status()
+        r = b2.read_report(rep)
+        assert r["injected"] == len(plan) and r["false_alarms"] == 0 and r["uncorrectable"] == 0, r
+        assert bool(((hit - uncut).abs() <= TOL * den).all().item())
+    finally:
+        b2.set_tf32_tail_split(0)
 
 
 def _smallest_flip_beyond(v, tol):
