@@ -1831,16 +1831,16 @@ static size_t tf32_planes_bytes(int M, int N, int K) {
   const size_t srows = (((size_t)N + 255) / 256) * 8;
   return (2 * (size_t)M * kp + 2 * (size_t)N * kp + srows * kp) * sizeof(float) + 8 * 1024;
 }
-// ... plus, for the K that chunked accumulation applies to by default, the slots that the tail tiles' runs go
+// ... plus, from K = 1024 on, the slots that the tail tiles' runs go
 // through (one 256 x 256 tile per cluster, 80 clusters at most); a caller-supplied workspace without them is
 // accepted and the last round then runs tile by tile.
 size_t tf32_workspace_bytes(int M, int N, int K) {
-  return tf32_planes_bytes(M, N, K) + (K > 1024 ? kTailSlotsMax * kTailSlotBytes + 1024 : 0);
+  return tf32_planes_bytes(M, N, K) + (K >= 1024 ? kTailSlotsMax * kTailSlotBytes + 1024 : 0);
 }
 
 // How the chunked CTA-pair kernel treats `tiles` tiles on `clusters` clusters with `nkb` K-slabs in chunks of `chunk`:
 // whole rounds for the tiles below *first; when the remaining R tiles would leave at least half of the clusters
-// idle and the cut saves 32 K-slabs or more of time, each of them in *parts runs of whole chunks (run r = chunks
+// idle and the cut saves 16 K-slabs or more of time, each of them in *parts runs of whole chunks (run r = chunks
 // [r*nch/parts, (r+1)*nch/parts), none empty; the longest has *longest chunks) on clusters r*R + j.  False: no cut.
 bool tf32_tail_plan(int tiles, int clusters, int nkb, int chunk, int *first, int *parts, int *longest) {
   *first = tiles;
@@ -1852,7 +1852,7 @@ bool tf32_tail_plan(int tiles, int clusters, int nkb, int chunk, int *first, int
   const int p = clusters / rem < nch ? clusters / rem : nch;
   if (p < 2) return false;
   const int lg = (nch + p - 1) / p;
-  if ((nch - lg) * chunk < 32) return false;
+  if ((nch - lg) * chunk < 16) return false;
   *first = tiles - rem;
   *parts = p;
   *longest = lg;
@@ -1947,7 +1947,7 @@ int sgemm_3xtf32_dispatch(Context *ctx, int M, int N, int K, float alpha, const 
     }
   }
   // the planes are needed; the slots of the tail tiles only let the last round be shared out
-  bool tail_slots = K > 1024;
+  bool tail_slots = K >= 1024;
   if (tail_slots && ctx->ws && !ctx->ws_owned && ctx->ws_bytes < tf32_workspace_bytes(M, N, K)) tail_slots = false;
   int st = ensure_workspace(ctx, tail_slots ? tf32_workspace_bytes(M, N, K) : tf32_planes_bytes(M, N, K), s);
   if (st != B2_OK) return st;

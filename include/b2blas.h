@@ -57,7 +57,7 @@ int b2_create(b2_handle *out);
 int b2_destroy(b2_handle h);
 int b2_set_workspace(b2_handle h, void *dev_ptr, size_t bytes);
 /* Bytes of workspace an MxNxK problem uses.  path = B2_PATH_3XTF32: the hi/lo planes of A and B are required; for
- * K > 1024 the figure includes 20 MB of slots that let a partial last round of tiles be cut along K (see
+ * K >= 1024 the figure includes 20 MB of slots that let a partial last round of tiles be cut along K (see
  * b2_set_tf32_tail_split), and a caller-supplied workspace without them is accepted.
  * path = B2_PATH_FFMA: optional; when that much scratch is there (or the handle may grow its own) a
  * row-major A is transposed into it first, which makes large products about 3 % faster; 0 when the

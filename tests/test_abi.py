@@ -150,7 +150,7 @@ def test_tail_plan_of_the_3xtf32_path(L):
                     if not cut:
                         assert ref() == (tiles, 0, 0)
                         want = min(clusters // rem, nch) if rem else 0
-                        assert want < 2 or (nch - (nch + want - 1) // want) * chunk < 32
+                        assert want < 2 or (nch - (nch + want - 1) // want) * chunk < 16
                         continue
                     cases += 1
                     f, p, lg = ref()
@@ -158,7 +158,7 @@ def test_tail_plan_of_the_3xtf32_path(L):
                     runs = [(r * nch // p, (r + 1) * nch // p) for r in range(p)]
                     assert runs[0][0] == 0 and runs[-1][1] == nch
                     assert all(b > a for a, b in runs) and all(runs[i][1] == runs[i + 1][0] for i in range(p - 1))
-                    assert max(b - a for a, b in runs) == lg and (nch - lg) * chunk >= 32
+                    assert max(b - a for a, b in runs) == lg and (nch - lg) * chunk >= 16
     assert cases > 1000
     # the shapes quoted in the design notes, on the 74 clusters of a B200
     assert L.b2_tf32_tail_plan(81, 74, 2304, 16, C.byref(first), C.byref(parts), C.byref(longest)) == 1 and ref() == (74, 5, 1)
