@@ -109,6 +109,8 @@ def load() -> C.CDLL:
     L.b2_set_tf32_persistent.argtypes = [i32]
     L.b2_set_tf32_chunk.argtypes = [i32]
     L.b2_ffma_pick_tile.argtypes = [i32, i32, i32]
+    L.b2_set_ffma_row_split.argtypes = [i32]
+    L.b2_ffma_row_split_plan.argtypes = [i32, i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]
     L.b2_set_tf32_fused_split.argtypes = [i32]
     L.b2_set_tf32_tail_split.argtypes = [i32]
     L.b2_tf32_tail_plan.argtypes = [i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]

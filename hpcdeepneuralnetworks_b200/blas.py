@@ -344,6 +344,12 @@ def device_info() -> dict:
     return {"sm_count": sm.value, "sm_clock_khz": khz.value, "global_mem_bytes": mem.value}
 
 
+def set_ffma_row_split(on: int):
+    """1 (default): the plain FFMA SGEMM may run as two launches on different tiles (rows split) when the time model
+    favours it; results are bit-identical.  0: one launch."""
+    check(_lib.load().b2_set_ffma_row_split(on))
+
+
 def set_ffma_variant(v: int):
     check(_lib.load().b2_set_ffma_variant(v))
 

@@ -667,6 +667,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
   }
 }
 
+static std::atomic<int> g_ffma_row_split{1};  // 1: a product may run as two launches on different tiles (rows split); 0: one launch
 static std::atomic<int> g_ffma_split_k{0};  // 0: never (every output is one FMA chain over all of K); n > 1: n ways; -1: automatic
 
 static int ffma_variant() {
@@ -797,30 +798,69 @@ static int auto_split_ways(const Context *ctx, const FfmaTile &tl, double ctas, 
   return ways < 1 ? 1 : ways;
 }
 
-static int pick_tile_for(int sm_count, int M, int N) {
-  // Time model: the CTAs of a launch are dealt out over the SMs, and the CTAs resident on one SM share its FMA
-  // pipes, so the launch lasts as long as the SM with the most CTAs needs for them: ceil(CTAs / SMs) tiles of
-  // bm x bn outputs at the tile's measured efficiency.  (Counting whole waves of resident CTAs instead overrates
-  // large tiles whenever the last wave is partly filled: 2816^3 runs 8.6 % faster on 64 x 128 tiles than on
-  // 128 x 128, 2048^3 4.4 % faster on 64 x 64; this model ranks the seven tiles as measured from 1024^3 to 8192^3.)
+// Time model of one launch: the CTAs are dealt out over the SMs, and the CTAs resident on one SM share its FMA
+// pipes, so the launch lasts as long as the SM with the most CTAs needs for them: ceil(CTAs / SMs) tiles of bm x bn
+// outputs at the tile's measured efficiency.  (Counting whole waves of resident CTAs instead overrates large tiles
+// whenever the last wave is partly filled: 2816^3 runs 8.6 % faster on 64 x 128 tiles than on 128 x 128, 2048^3 4.4 %
+// faster on 64 x 64; this model ranks the seven tiles as measured from 1024^3 to 8192^3.)  Unit: outputs of one
+// SM-round; a negative value: the tile is not considered for this shape.
+static double tile_time(int sm_count, const FfmaTile &tl, int M, int N) {
+  const double ctas = (double)((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
+  // the 8-row thread tiles run 8 warps per SM: below two waves of resident CTAs they lose to the 16-warp tiles
+  const double slots = (double)sm_count * ((tl.mr == 4 ? 512 : 256) / tl.threads);
+  if (ctas / slots < (double)tl.min_waves) return -1.0;
+  const double per_sm = ceil(ctas / (double)sm_count);
+  double time = per_sm * (double)(tl.bm * tl.bn) / tl.efficiency;
+  // an SM needs two warps per scheduler to keep its FMA pipes busy: a launch that leaves fewer resident runs
+  // slower than the efficiency measured on full SMs says (1024^3: 128 CTAs of 4 warps, 32.8 TFLOP/s against 36.4)
+  const double max_resident = (double)((tl.mr == 4 ? 512 : 256) / tl.threads);
+  const double warps = (per_sm < max_resident ? per_sm : max_resident) * (tl.threads / 32);
+  if (warps < 8.0) time *= sqrt(8.0 / warps);
+  return time;
+}
+static int pick_tile_for(int sm_count, int M, int N, double *time_out = nullptr) {
   int best = 0;
   double best_time = 1e300;
   for (int t = 0; t < kNumTiles; ++t) {
-    const FfmaTile &tl = g_tiles[t];
-    const double ctas = (double)((M + tl.bm - 1) / tl.bm) * ((N + tl.bn - 1) / tl.bn);
-    // the 8-row thread tiles run 8 warps per SM: below two waves of resident CTAs they lose to the 16-warp tiles
-    const double slots = (double)sm_count * ((tl.mr == 4 ? 512 : 256) / tl.threads);
-    if (ctas / slots < (double)tl.min_waves) continue;
-    const double per_sm = ceil(ctas / (double)sm_count);
-    double time = per_sm * (double)(tl.bm * tl.bn) / tl.efficiency;
-    // an SM needs two warps per scheduler to keep its FMA pipes busy: a launch that leaves fewer resident runs
-    // slower than the efficiency measured on full SMs says (1024^3: 128 CTAs of 4 warps, 32.8 TFLOP/s against 36.4)
-    const double max_resident = (double)((tl.mr == 4 ? 512 : 256) / tl.threads);
-    const double warps = (per_sm < max_resident ? per_sm : max_resident) * (tl.threads / 32);
-    if (warps < 8.0) time *= sqrt(8.0 / warps);
-    if (time < best_time) {
+    const double time = tile_time(sm_count, g_tiles[t], M, N);
+    if (time >= 0.0 && time < best_time) {
       best_time = time;
       best = t;
+    }
+  }
+  if (time_out) *time_out = best_time;
+  return best;
+}
+// Two launches instead of one: the first `rows1` rows on tile t1, as many whole SM-rounds of it as fit, the rest on
+// whatever tile suits the remainder best.  Every output is still one FMA chain over all of K whatever its tile, so
+// the result is bit-identical; the split is taken when the model gives it 3 % or more over the best single launch
+// (3840^3: 29 of 30 tile rows on 128 x 128 tiles and the last 128 rows on 32 x 64 tiles, measured +3.8 %).
+struct RowSplit {
+  int rows1 = 0, t1 = -1, t2 = -1;
+};
+static RowSplit plan_row_split(int sm_count, int M, int N) {
+  RowSplit best;
+  double single = 0.0;
+  (void)pick_tile_for(sm_count, M, N, &single);
+  double best_time = 0.97 * single;
+  for (int t1 = 0; t1 < kNumTiles; ++t1) {
+    const FfmaTile &tl = g_tiles[t1];
+    const long long per_row = (N + tl.bn - 1) / tl.bn, tile_rows = (M + tl.bm - 1) / tl.bm;
+    const long long rounds = tile_rows * per_row / sm_count;          // whole SM-rounds in the launch
+    if (rounds < 1) continue;
+    const long long rows_t = rounds * sm_count / per_row;              // tile rows that fit into them
+    if (rows_t < 1 || rows_t >= tile_rows) continue;
+    const int rows1 = (int)(rows_t * tl.bm);
+    const double time1 = tile_time(sm_count, tl, rows1, N);
+    if (time1 < 0.0) continue;
+    double time2 = 0.0;
+    const int t2 = pick_tile_for(sm_count, M - rows1, N, &time2);
+    const double launch = 0.01 * (double)(128 * 128);                  // a second launch: a hundredth of a 128 x 128 SM-round
+    if (time1 + time2 + launch < best_time) {
+      best_time = time1 + time2 + launch;
+      best.rows1 = rows1;
+      best.t1 = t1;
+      best.t2 = t2;
     }
   }
   return best;
@@ -875,7 +915,8 @@ int sgemm_ffma_dispatch(Context *ctx, int trans_a, int M, int N, int K, float al
 // ft == nullptr: plain SGEMM.  Otherwise the ABFT kernel (operands must be describable to TMA,
 // i.e. 16-byte aligned with leading dimensions that are multiples of 4).
 static int ffma_dispatch_impl(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda, const float *B,
-                              int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s, size_t ws_front);
+                              int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s, size_t ws_front,
+                              int force_tile = -1);
 
 int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda,
                            const float *B, int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s) {
@@ -884,7 +925,8 @@ int sgemm_ffma_dispatch_ft(Context *ctx, int trans_a, int M, int N, int K, float
 
 // ws_front: bytes at the front of the workspace that are in use (the transposed copy of A).
 static int ffma_dispatch_impl(Context *ctx, int trans_a, int M, int N, int K, float alpha, const float *A, int lda, const float *B,
-                              int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s, size_t ws_front) {
+                              int ldb, float beta, float *C, int ldc, const FtArgs *ft, cudaStream_t s, size_t ws_front,
+                              int force_tile) {
   if (M == 0 || N == 0) return B2_OK;
   if (K == 0 || alpha == 0.f) {
     if (beta == 1.f) return B2_OK;
@@ -929,7 +971,17 @@ static int ffma_dispatch_impl(Context *ctx, int trans_a, int M, int N, int K, fl
       set_error("");   // no scratch to be had: the row-major kernel needs none
     }
   }
-  const FfmaTile &tl = g_tiles[pick_tile(ctx, M, N)];
+  if (force_tile < 0 && ft == nullptr && g_ffma_tile < 0 && g_ffma_split_k == 0 && g_ffma_row_split != 0) {
+    const RowSplit rs = plan_row_split(ctx->sm_count, M, N);
+    if (rs.rows1 > 0) {
+      int st1 = ffma_dispatch_impl(ctx, trans_a, rs.rows1, N, K, alpha, A, lda, B, ldb, beta, C, ldc, nullptr, s, ws_front, rs.t1);
+      if (st1 != B2_OK) return st1;
+      const float *A2 = trans_a ? A + rs.rows1 : A + (size_t)rs.rows1 * lda;
+      return ffma_dispatch_impl(ctx, trans_a, M - rs.rows1, N, K, alpha, A2, lda, B, ldb, beta, C + (size_t)rs.rows1 * ldc, ldc, nullptr, s,
+                                ws_front, rs.t2);
+    }
+  }
+  const FfmaTile &tl = g_tiles[force_tile >= 0 ? force_tile : pick_tile(ctx, M, N)];
   CUtensorMap ta, tb, tsa, tsb;
   int st = trans_a ? make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, tl.bm, FBK, CU_TENSOR_MAP_SWIZZLE_NONE)
                    : make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, FBK, tl.bm, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1060,6 +1112,23 @@ int b2_ffma_tile_info(int i, int *bm, int *bn, int *threads, const char **name) 
 int b2_ffma_pick_tile(int M, int N, int sm_count) {
   B2_REQUIRE(M > 0 && N > 0 && sm_count > 0, B2_ERR_INVALID_ARG, "b2_ffma_pick_tile: M = %d, N = %d, sm_count = %d must be positive", M, N, sm_count);
   return b2::pick_tile_for(sm_count, M, N);
+}
+// 1 (default): the plain FFMA SGEMM may run as two launches, the first rows on one tile in whole SM-rounds and the rest
+// on another, when the time model gives that 3 % or more (bit-identical results); 0: always one launch.
+int b2_set_ffma_row_split(int on) {
+  B2_REQUIRE(on == 0 || on == 1, B2_ERR_INVALID_ARG, "b2_set_ffma_row_split: %d is not 0 or 1", on);
+  b2::g_ffma_row_split = on;
+  return B2_OK;
+}
+// The split b2_set_ffma_row_split(1) would make for an M x N output on `sm_count` SMs: returns 1 and the rows of the
+// first launch with the two tiles' indices, or 0 (one launch).  Host-side model, no device needed.
+int b2_ffma_row_split_plan(int M, int N, int sm_count, int *rows1, int *tile1, int *tile2) {
+  B2_REQUIRE(M > 0 && N > 0 && sm_count > 0, B2_ERR_INVALID_ARG, "b2_ffma_row_split_plan: M = %d, N = %d, sm_count = %d must be positive", M, N, sm_count);
+  const b2::RowSplit rs = b2::plan_row_split(sm_count, M, N);
+  if (rows1) *rows1 = rs.rows1;
+  if (tile1) *tile1 = rs.t1;
+  if (tile2) *tile2 = rs.t2;
+  return rs.rows1 > 0 ? 1 : 0;
 }
 int b2_set_ffma_tile(int i) {
   B2_REQUIRE(i >= -1 && i < b2::kNumTiles, B2_ERR_INVALID_ARG, "b2_set_ffma_tile: tile %d not in -1..%d", i, b2::kNumTiles - 1);

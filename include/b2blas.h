@@ -333,6 +333,12 @@ int b2_set_ffma_tile(int i);
 /* The index of the tile the picker takes for an M x N output on a device of `sm_count` SMs (148 on B200) when nothing is
  * pinned: a host-side time model, no device needed.  Negative status on invalid arguments. */
 int b2_ffma_pick_tile(int M, int N, int sm_count);
+/* 1 (default): the plain FFMA SGEMM may run as two launches, the first rows on one tile in whole SM-rounds and the remaining
+ * rows on the tile that suits them best, when the time model gives that 3 % or more over the best single launch.  Every
+ * output is one FMA chain over all of K on any tile, so results are bit-identical.  0: always one launch.
+ * b2_ffma_row_split_plan returns 1 and the rows of the first launch with the two tile indices, or 0. */
+int b2_set_ffma_row_split(int on);
+int b2_ffma_row_split_plan(int M, int N, int sm_count, int *rows1, int *tile1, int *tile2);
 /* Pins the tile width of the 3xTF32 kernel (128 or 256 output columns per CTA; 0 = automatic). */
 int b2_set_tf32_tile_n(int n);
 /* K-slab depth of the 3xTF32 kernel: 16 (64-byte swizzle, 4-6 stages) or 32 (128-byte swizzle, 2-3 stages). */

@@ -133,6 +133,29 @@ def test_ffma_picker_ranks_tiles_as_measured(L):
     assert L.b2_ffma_pick_tile(0, 5, 148) < 0 and L.b2_ffma_pick_tile(5, 5, 0) < 0
 
 
+def test_ffma_row_split_plan(L):
+    """b2_ffma_row_split_plan: on 148 SMs the model splits 3840^2 into 29 tile rows of the 8 x 16 tile (whole SM-rounds) and
+    a remainder of 128 rows on small tiles, and leaves 4096^2, 6144^2 and small outputs in one launch; the first part is
+    always whole tiles of its own tile shape and smaller than M."""
+    rows1, t1, t2 = C.c_int(), C.c_int(), C.c_int()
+    name = C.c_char_p()
+    def tile(i):
+        assert L.b2_ffma_tile_info(i, None, None, None, C.byref(name)) == 0
+        return name.value.decode()
+    assert L.b2_ffma_row_split_plan(3840, 3840, 148, C.byref(rows1), C.byref(t1), C.byref(t2)) == 1
+    assert (rows1.value, tile(t1.value)) == (3712, "b200_8x16") and tile(t2.value) in ("large", "medium", "b200_64x128")
+    for n in (256, 1024, 4096, 6144, 8192):
+        assert L.b2_ffma_row_split_plan(n, n, 148, C.byref(rows1), C.byref(t1), C.byref(t2)) == 0 and rows1.value == 0
+    bm = C.c_int()
+    for M in range(1500, 6200, 173):
+        for N in (1536, 2816, 4000, 6144):
+            if L.b2_ffma_row_split_plan(M, N, 148, C.byref(rows1), C.byref(t1), C.byref(t2)) == 1:
+                assert L.b2_ffma_tile_info(t1.value, C.byref(bm), None, None, None) == 0
+                assert 0 < rows1.value < M and rows1.value % bm.value == 0 and 0 <= t2.value < L.b2_ffma_tile_count()
+    assert L.b2_ffma_row_split_plan(0, 5, 148, None, None, None) < 0
+    assert L.b2_set_ffma_row_split(2) == -1 and L.b2_set_ffma_row_split(1) == 0
+
+
 def test_tail_plan_of_the_3xtf32_path(L):
     """b2_tf32_tail_plan: when the tiles of the last round leave at least half of the clusters idle, each of them is cut
     into `parts` non-empty runs of whole chunks that cover the K loop once, on parts * R distinct clusters."""

@@ -470,6 +470,28 @@ def test_3xtf32_chunks_bound_the_loss_for_operands_of_one_sign(cuda, pair):
     assert err["signed", -1] <= 1e-6 and err["signed", -1] < 0.2 * err["signed", 0], err
 
 
+@pytest.mark.parametrize("shape", [(2816, 2816, 96), (3840, 3840, 40), (3584, 1920, 70), (5000, 3000, 33)])
+def test_ffma_row_split_is_bit_identical(cuda, shape):
+    """A product that the time model runs as two launches on different tiles (b2_ffma_row_split_plan) gives the bits of
+    the single launch and of the fused oracle: every output is one FMA chain over all of K on any tile."""
+    import hpcdeepneuralnetworks_b200 as b2
+    from hpcdeepneuralnetworks_b200 import _lib
+    M, N, K = shape
+    a, b, c = mats(M, N, K)
+    out = {}
+    try:
+        for on in (1, 0):
+            b2.set_ffma_row_split(on)
+            out[on] = run_gpu(0, a, b, c, 1.0, 0.5)
+    finally:
+        b2.set_ffma_row_split(1)
+    assert np.array_equal(out[1], out[0])
+    assert np.array_equal(out[1], oracle.sgemm_fma(1.0, a, b, 0.5, c))
+    if shape[:2] in ((2816, 2816), (3840, 3840)):
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        assert sms != 148 or _lib.load().b2_ffma_row_split_plan(M, N, sms, None, None, None) == 1     # the split did happen
+
+
 def test_random_shapes_through_the_dispatchers(cuda):
     """Forty seeded random shapes (M, N up to 700, K up to 2600, leading dimensions with slack, alpha and beta drawn
     from {0, 1, -1.5, 0.5, 2}) through both dispatchers as a caller would use them - whatever tile, kernel form, split,
